@@ -1,0 +1,518 @@
+// Epilogues and host launcher of the tcgen05 GEMM (see gemm_sm100.cuh for the main loop).
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../include/fm_api.h"
+#include "gemm_sm100.cuh"
+
+namespace fm {
+
+// ----------------------------------------------------------------------------------------
+// helpers
+// ----------------------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_f(float x) {
+  return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
+}
+__device__ __forceinline__ float dgelu_f(float x) {
+  const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
+  return cdf + x * pdf;
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
+__device__ __forceinline__ float dsilu_f(float x) {
+  const float s = sigmoid_f(x);
+  return s * (1.0f + x * (1.0f - s));
+}
+__device__ __forceinline__ float act_f(int kind, float x) {
+  return kind == FM_ACT_GELU ? gelu_f(x) : (kind == FM_ACT_SILU ? silu_f(x) : x);
+}
+__device__ __forceinline__ float dact_f(int kind, float x) {
+  return kind == FM_ACT_GELU ? dgelu_f(x) : (kind == FM_ACT_SILU ? dsilu_f(x) : 1.0f);
+}
+
+__device__ __forceinline__ void load_acc(uint32_t taddr, float* v, bool zero) {
+  if (zero) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+    return;
+  }
+  uint32_t r[32];
+  tmem_ld_32x32(taddr, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Store 32 consecutive values of one row as bf16.  `ncols` = columns that exist (<= 32).
+__device__ __forceinline__ void store_row_bf16(__nv_bfloat16* dst, const float* v, int ncols) {
+  if (ncols >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 p;
+      p.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+      p.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+      p.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+      p.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+      reinterpret_cast<uint4*>(dst)[i] = p;
+    }
+  } else {
+    for (int i = 0; i < 32 && i < ncols; ++i) dst[i] = __float2bfloat16(v[i]);
+  }
+}
+__device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float* v, int ncols) {
+  if (ncols >= 32 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 p = reinterpret_cast<const uint4*>(src)[i];
+      const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+        v[8 * i + 2 * j] = __low2float(b);
+        v[8 * i + 2 * j + 1] = __high2float(b);
+      }
+    }
+  } else {
+    for (int i = 0; i < 32; ++i) v[i] = i < ncols ? __bfloat162float(src[i]) : 0.f;
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+// Epilogue 0: plain store (bf16 or fp32, optional accumulate; the fp32-accumulate form is the
+// weight-gradient epilogue that adds straight into a flat gradient buffer).
+// ----------------------------------------------------------------------------------------
+struct EpiStore {
+  void* C;
+  long long ldc;
+  long long group_stride;
+  int out_fp32;
+  int accumulate;
+  float alpha;
+
+  template <int BN>
+  __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
+                                      bool zero) const {
+    const long long row = a.mode == 0 ? (long long)t.row_base + t.m0 + r : (long long)t.m0 + r;
+    const long long goff = a.mode == 0 ? 0 : (long long)t.g * group_stride;
+    const bool row_ok = r < t.rows_valid;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = t.n_tile * BN + c * 32;
+      if (col >= a.N) break;
+      float v[32];
+      load_acc(taddr + c * 32, v, zero);
+      if (!row_ok) continue;
+      const int ncols = min(32, a.N - col);
+      if (alpha != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= alpha;
+      }
+      if (out_fp32) {
+        float* dst = reinterpret_cast<float*>(C) + goff + row * ldc + col;
+        if (ncols >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            if (accumulate) {
+              const float4 p = reinterpret_cast<const float4*>(dst)[i];
+              o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+            }
+            reinterpret_cast<float4*>(dst)[i] = o;
+          }
+        } else {
+          for (int i = 0; i < ncols; ++i) dst[i] = accumulate ? dst[i] + v[i] : v[i];
+        }
+      } else {
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + goff + row * ldc + col;
+        if (accumulate) {
+          float p[32];
+          load_row_bf16(dst, p, ncols);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] += p[i];
+        }
+        store_row_bf16(dst, v, ncols);
+      }
+    }
+  }
+  __device__ __forceinline__ void tile_done(const Tile&, const GemmArgs&, int) const {}
+};
+
+// ----------------------------------------------------------------------------------------
+// Epilogue 1: activation x routing probability (forward FC1).  Non-gated: out = act(x) * p.
+// Gated (SwiGLU): the tile holds 128 gate columns then 128 up columns; out = silu(g) * u * p.
+// Optionally keeps the pre-activation for the backward pass.
+// Reference semantics: fluid/moe/forward.py:231-238,299,317 (probability applied between the
+// activation and FC2).
+// ----------------------------------------------------------------------------------------
+struct EpiAct {
+  __nv_bfloat16* act_out;
+  long long ld_act;
+  __nv_bfloat16* pre_out;
+  long long ld_pre;
+  const float* probs;
+  int act_kind;
+
+  template <int BN>
+  __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
+                                      bool zero) const {
+    const long long row = (long long)t.row_base + t.m0 + r;
+    const bool row_ok = r < t.rows_valid;
+    const float p = (row_ok && probs) ? probs[row] : 1.0f;
+    if (a.gated) {
+#pragma unroll 1
+      for (int c = 0; c < BN / 64; ++c) {
+        const int col = t.n_tile * (BN / 2) + c * 32;
+        if (col >= a.N) break;
+        float g[32], u[32];
+        load_acc(taddr + c * 32, g, zero);
+        load_acc(taddr + BN / 2 + c * 32, u, zero);
+        if (!row_ok) continue;
+        const int ncols = min(32, a.N - col);
+        if (pre_out) {
+          store_row_bf16(pre_out + row * ld_pre + col, g, ncols);
+          store_row_bf16(pre_out + row * ld_pre + a.n_half + col, u, ncols);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) g[i] = silu_f(g[i]) * u[i] * p;
+        store_row_bf16(act_out + row * ld_act + col, g, ncols);
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col = t.n_tile * BN + c * 32;
+        if (col >= a.N) break;
+        float v[32];
+        load_acc(taddr + c * 32, v, zero);
+        if (!row_ok) continue;
+        const int ncols = min(32, a.N - col);
+        if (pre_out) store_row_bf16(pre_out + row * ld_pre + col, v, ncols);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = act_f(act_kind, v[i]) * p;
+        store_row_bf16(act_out + row * ld_act + col, v, ncols);
+      }
+    }
+  }
+  __device__ __forceinline__ void tile_done(const Tile&, const GemmArgs&, int) const {}
+};
+
+// ----------------------------------------------------------------------------------------
+// Epilogue 3: backward of (act x prob), fused after dActW = dY * W2^T.
+//   a = act(pre); dprob_partial[row, n_tile] = sum_cols(acc * a); dpre = acc * p * act'(pre)
+//   gated: a = silu(g) * u; dg = acc * p * u * silu'(g); du = acc * p * silu(g)
+// Partial sums per N tile keep the probability gradient deterministic (no atomics).
+// Reference math: fluid/moe/backward.py:341-356,1046-1061.
+// ----------------------------------------------------------------------------------------
+struct EpiDAct {
+  const __nv_bfloat16* pre_in;
+  long long ld_pre_in;
+  __nv_bfloat16* dpre;
+  long long ld_dpre;
+  const float* probs;
+  float* dprobs_partial;  // [rows, n_tiles]
+  int n_tiles;
+  int act_kind;
+  int gated;   // activation is SwiGLU: pre_in / dpre hold [gate | up] halves `n_half` apart
+  int n_half;
+
+  template <int BN>
+  __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
+                                      bool zero) const {
+    const long long row = (long long)t.row_base + t.m0 + r;
+    const bool row_ok = r < t.rows_valid;
+    const float p = (row_ok && probs) ? probs[row] : 1.0f;
+    float dp = 0.f;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = t.n_tile * BN + c * 32;
+      if (col >= a.N) break;
+      float v[32];
+      load_acc(taddr + c * 32, v, zero);
+      if (!row_ok) continue;
+      const int ncols = min(32, a.N - col);
+      if (gated) {
+        float g[32], u[32];
+        load_row_bf16(pre_in + row * ld_pre_in + col, g, ncols);
+        load_row_bf16(pre_in + row * ld_pre_in + n_half + col, u, ncols);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float s = silu_f(g[i]);
+          dp += v[i] * s * u[i];
+          const float da = v[i] * p;
+          g[i] = da * u[i] * dsilu_f(g[i]);
+          u[i] = da * s;
+        }
+        store_row_bf16(dpre + row * ld_dpre + col, g, ncols);
+        store_row_bf16(dpre + row * ld_dpre + n_half + col, u, ncols);
+      } else {
+        float x[32];
+        load_row_bf16(pre_in + row * ld_pre_in + col, x, ncols);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          dp += v[i] * act_f(act_kind, x[i]);
+          x[i] = v[i] * p * dact_f(act_kind, x[i]);
+        }
+        store_row_bf16(dpre + row * ld_dpre + col, x, ncols);
+      }
+    }
+    if (row_ok && dprobs_partial) dprobs_partial[row * n_tiles + t.n_tile] = dp;
+  }
+  __device__ __forceinline__ void tile_done(const Tile&, const GemmArgs&, int) const {}
+};
+
+// ----------------------------------------------------------------------------------------
+// Epilogue 2: scatter rows to their owners (FC2 + combine).  Row R of the result is written
+// as bf16 to dst_base[dst_rank[R]] + dst_row[R] * ld_dst, which may be another GPU's buffer
+// mapped over NVLink (plain 16-byte peer stores).  After a tile, each destination's arrival
+// counter grows by the number of rows the tile sent it; the owner waits until its counter
+// equals rows_expected * n_tiles.  Replaces the combine all-to-all rounds of
+// fluid/moe/forward.py:903-948.
+// ----------------------------------------------------------------------------------------
+struct EpiScatter {
+  __nv_bfloat16* const* dst_base;
+  const int* dst_rank;
+  const int* dst_row;
+  long long ld_dst;
+  int* const* dst_flags;  // per destination rank: pointer to the counter this rank bumps
+  int num_ranks;
+
+  template <int BN>
+  __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
+                                      bool zero) const {
+    const long long row = (long long)t.row_base + t.m0 + r;
+    const bool row_ok = r < t.rows_valid;
+    int rank = -1;
+    long long drow = 0;
+    if (row_ok) {
+      rank = dst_rank[row];
+      drow = dst_row[row];
+    }
+    __nv_bfloat16* base = rank >= 0 ? dst_base[rank] + drow * ld_dst : nullptr;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int col = t.n_tile * BN + c * 32;
+      if (col >= a.N) break;
+      float v[32];
+      load_acc(taddr + c * 32, v, zero);
+      if (rank < 0) continue;
+      store_row_bf16(base + col, v, min(32, a.N - col));
+    }
+    if (dst_flags != nullptr) __threadfence_system();
+  }
+  // Called by every epilogue thread after the tile's stores; `r` is the thread's row in the
+  // tile.  Each warp aggregates its 32 rows by destination, so no cross-warp barrier is needed.
+  __device__ __forceinline__ void tile_done(const Tile& t, const GemmArgs& a, int r) const {
+    if (dst_flags == nullptr) return;
+    const long long row = (long long)t.row_base + t.m0 + r;
+    const int rank = r < t.rows_valid ? dst_rank[row] : -1;
+    __syncwarp();
+    const unsigned peers = __match_any_sync(0xffffffffu, rank);
+    const int leader = __ffs(peers) - 1;
+    if ((int)(threadIdx.x & 31) == leader && rank >= 0)
+      flag_release_add(dst_flags[rank], __popc(peers));
+  }
+};
+
+// ----------------------------------------------------------------------------------------
+// host side
+// ----------------------------------------------------------------------------------------
+static char g_err[512] = {0};
+static void set_err(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+          cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(p);
+  return fn;
+}
+
+// 2-D bf16 tensor map, 128-byte swizzle, box = {64 inner, box_outer}.
+static bool make_tmap(CUtensorMap* m, const void* ptr, long long inner, long long outer,
+                      long long ld, int box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    set_err("cuTensorMapEncodeTiled unavailable");
+    return false;
+  }
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15)) {
+    set_err("TMA operand must be 16-byte aligned with a 16-byte-multiple row stride");
+    return false;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed: %d (inner=%lld outer=%lld ld=%lld)",
+             (int)r, inner, outer, ld);
+    return false;
+  }
+  return true;
+}
+
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+
+template <bool A_MN, bool B_MN, int BN, class Epi, class Gate>
+static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+                      const Epi& epi, const Gate& gate, int grid, cudaStream_t stream) {
+  auto kern = gemm_sm100_kernel<A_MN, B_MN, BN, Epi, Gate>;
+  constexpr int smem = gemm_smem_bytes<BN>();
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_err(cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, smem, stream>>>(ta, tb, args, epi, gate);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+template <class Epi, class Gate>
+static int dispatch_shape(const FmGemmDesc* d, const CUtensorMap& ta, const CUtensorMap& tb,
+                          const GemmArgs& args, const Epi& epi, const Gate& gate, int grid,
+                          cudaStream_t s) {
+  const bool amn = d->a_mn != 0, bmn = d->b_mn != 0;
+  if (d->bn == 256) {
+    if (!amn && !bmn) return launch_one<false, false, 256>(ta, tb, args, epi, gate, grid, s);
+    if (!amn && bmn) return launch_one<false, true, 256>(ta, tb, args, epi, gate, grid, s);
+    if (amn && bmn) return launch_one<true, true, 256>(ta, tb, args, epi, gate, grid, s);
+  } else if (d->bn == 128) {
+    if (!amn && !bmn) return launch_one<false, false, 128>(ta, tb, args, epi, gate, grid, s);
+    if (!amn && bmn) return launch_one<false, true, 128>(ta, tb, args, epi, gate, grid, s);
+    if (amn && bmn) return launch_one<true, true, 128>(ta, tb, args, epi, gate, grid, s);
+  }
+  set_err("unsupported operand-major / tile combination");
+  return -2;
+}
+
+template <class Epi>
+static int dispatch_gate(const FmGemmDesc* d, const CUtensorMap& ta, const CUtensorMap& tb,
+                         const GemmArgs& args, const Epi& epi, int grid, cudaStream_t s) {
+  if (d->gate_flags != nullptr) {
+    GateRowBlockFlags g{d->gate_flags, d->gate_group_base, d->gate_blocks_per_group,
+                        d->gate_expected};
+    return dispatch_shape(d, ta, tb, args, epi, g, grid, s);
+  }
+  return dispatch_shape(d, ta, tb, args, epi, GateNone{}, grid, s);
+}
+
+}  // namespace fm
+
+extern "C" const char* fm_last_error(void) { return fm::g_err; }
+
+extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
+  using namespace fm;
+  if (d->bn != 128 && d->bn != 256) {
+    set_err("bn must be 128 or 256");
+    return -1;
+  }
+  if (d->gated && d->bn != 256) {
+    set_err("gated tiles need bn == 256");
+    return -1;
+  }
+  if (d->mode == 1 && !(d->a_mn && d->b_mn)) {
+    set_err("grouped-K mode needs both operands stored [rows, M] / [rows, N]");
+    return -1;
+  }
+  if (d->mode == 0 && d->K % 8 != 0) {
+    set_err("K must be a multiple of 8");
+    return -1;
+  }
+  if (d->mode == 0 && d->num_groups > 1 && d->K % kBK != 0) {
+    set_err("grouped GEMM needs K to be a multiple of 64");
+    return -1;
+  }
+  CUtensorMap ta, tb;
+  // A: K-major -> box {64 k, 128 rows}; MN-major -> box {64 rows, 64 k}
+  if (!make_tmap(&ta, d->A, d->a_inner, d->a_outer, d->lda, d->a_mn ? 64 : 128)) return -3;
+  // B: K-major -> box {64 k, 128 n}; MN-major -> box {64 n, 64 k}
+  if (!make_tmap(&tb, d->B, d->b_inner, d->b_outer, d->ldb, d->b_mn ? 64 : 128)) return -3;
+
+  GemmArgs args;
+  memset(&args, 0, sizeof(args));
+  args.mode = d->mode;
+  args.num_groups = d->num_groups;
+  args.M = d->M;
+  args.N = d->N;
+  args.K = d->K;
+  args.uniform_rows = d->uniform_rows;
+  args.group_rows = d->group_rows;
+  args.group_offs = d->group_offs;
+  args.b_group_stride = d->b_group_stride;
+  args.gated = d->gated;
+  args.n_half = d->n_half;
+  args.swizzle_m = d->swizzle_m;
+  args.timeout_ns = d->timeout_ns ? d->timeout_ns : 4000000000ull;
+  args.status = d->status;
+
+  int grid = sm_count();
+  if (d->max_ctas > 0 && d->max_ctas < grid) grid = d->max_ctas;
+  // Do not launch more CTAs than tiles when the tile count is known on the host.
+  if (d->group_rows == nullptr) {
+    const int npt = d->gated ? d->bn / 2 : d->bn;
+    const long long nt = (d->N + npt - 1) / npt;
+    const long long mt = d->mode == 0 ? (d->uniform_rows + kBM - 1) / kBM : (d->M + kBM - 1) / kBM;
+    const long long tiles = nt * mt * d->num_groups;
+    if (tiles < grid) grid = (int)(tiles > 0 ? tiles : 1);
+  }
+
+  switch (d->epi) {
+    case FM_EPI_STORE: {
+      EpiStore e{d->C, d->ldc, d->c_group_stride, d->out_fp32, d->accumulate,
+                 d->alpha == 0.f ? 1.0f : d->alpha};
+      return dispatch_gate(d, ta, tb, args, e, grid, stream);
+    }
+    case FM_EPI_ACT: {
+      EpiAct e{reinterpret_cast<__nv_bfloat16*>(d->act_out), d->ld_act,
+               reinterpret_cast<__nv_bfloat16*>(d->pre_out), d->ld_pre, d->probs, d->act_kind};
+      return dispatch_gate(d, ta, tb, args, e, grid, stream);
+    }
+    case FM_EPI_DACT: {
+      const int nt = (d->N + d->bn - 1) / d->bn;
+      EpiDAct e{reinterpret_cast<const __nv_bfloat16*>(d->pre_in), d->ld_pre_in,
+                reinterpret_cast<__nv_bfloat16*>(d->C), d->ldc, d->probs, d->dprobs, nt,
+                d->act_kind, d->gated, d->n_half};
+      args.gated = 0;  // here `gated` describes the activation, not the layout of B
+      return dispatch_gate(d, ta, tb, args, e, grid, stream);
+    }
+    case FM_EPI_SCATTER: {
+      EpiScatter e{reinterpret_cast<__nv_bfloat16* const*>(d->dst_base), d->dst_rank, d->dst_row,
+                   d->ld_dst, d->dst_flags, d->num_ranks};
+      return dispatch_gate(d, ta, tb, args, e, grid, stream);
+    }
+    default:
+      set_err("unknown epilogue");
+      return -1;
+  }
+}

@@ -1,0 +1,369 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+// One CTA per SM walks a static list of 128 x BN output tiles.  Warp 0 feeds a 4-stage
+// shared-memory ring with TMA tiled loads (128-byte swizzle), warp 1 issues tcgen05.mma
+// with the accumulator in TMEM (two accumulators, so the epilogue of tile i overlaps the
+// main loop of tile i+1), warps 2-5 drain TMEM with tcgen05.ld and run a pluggable
+// epilogue.  A pluggable gate lets the producer wait (bounded) for a flag before it touches
+// the rows of a tile, which is how arriving peer data is consumed tile by tile.
+//
+// Two problem shapes share the kernel:
+//   mode 0 (grouped-M): C[rows_g, N] = A[rows_g, K] * B_g, groups partition the rows of A;
+//                       one group == an ordinary dense GEMM.
+//   mode 1 (grouped-K): C_g[M, N] (+)= A[rows_g, M]^T * B[rows_g, N]; the weight-gradient
+//                       shape, where the contraction runs over the rows of group g.
+// Operand majors are template parameters: A and B may each be K-major or MN-major; MN-major
+// tiles are loaded as 64-element-wide boxes and described to the MMA through LBO/SBO.
+//
+// This is the counterpart of the reference's grouped GEMM helpers, which call cuBLAS or an
+// external CUTLASS grouped GEMM (fluid/moe/forward.py:217-352, fluid/moe/backward.py:400-480).
+#pragma once
+#include "../include/sm100_ptx.cuh"
+
+namespace fm {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kKernelIdGemm = 1;
+
+struct GemmArgs {
+  int mode;          // 0 grouped-M, 1 grouped-K
+  int num_groups;
+  int M;             // mode 0: rows of A when group_rows == nullptr and num_groups == 1
+                     // mode 1: output rows (columns of A)
+  int N;             // output columns produced per tile row (gated: activation columns)
+  int K;             // mode 0: contraction length; mode 1: unused
+  int uniform_rows;  // rows per group when group_rows == nullptr
+  const int* group_rows;  // device, [num_groups], may be nullptr
+  const int* group_offs;  // device, [num_groups] row offset of each group in A (and C)
+  int b_group_stride;     // mode 0: rows of the flattened 2-D B between groups
+  int gated;              // B holds [gate | up] column halves, tile = 128 gate + 128 up
+  int n_half;             // column offset of the `up` half inside B
+  int swizzle_m;          // m-tiles per rasterisation super-row (L2 reuse)
+  unsigned long long timeout_ns;
+  int* status;
+};
+
+struct Tile {
+  int g;           // group
+  int m0;          // mode 0: row offset inside the group; mode 1: offset in output rows
+  int n_tile;      // tile index along N
+  int rows_valid;  // rows of this tile that exist (<= 128)
+  int row_base;    // first row of group g in A
+  int nk;          // number of 64-wide K blocks
+  int rows_g;      // rows in the group
+};
+
+template <int BN>
+struct TileWalker {
+  const GemmArgs& a;
+  int g = 0;
+  int base = 0;  // tiles before group g
+  int nt, mt_fixed;
+  __device__ TileWalker(const GemmArgs& args) : a(args) {
+    const int n_per_tile = a.gated ? BN / 2 : BN;
+    nt = (a.N + n_per_tile - 1) / n_per_tile;
+    mt_fixed = (a.M + kBM - 1) / kBM;
+  }
+  __device__ __forceinline__ int rows_of(int gi) const {
+    return a.group_rows ? a.group_rows[gi] : a.uniform_rows;
+  }
+  __device__ __forceinline__ int off_of(int gi) const {
+    return a.group_offs ? a.group_offs[gi] : gi * a.uniform_rows;
+  }
+  __device__ __forceinline__ int mtiles_of(int gi) const {
+    return a.mode == 0 ? (rows_of(gi) + kBM - 1) / kBM : mt_fixed;
+  }
+  // t must not decrease between calls.
+  __device__ bool get(int t, Tile& out) {
+    while (g < a.num_groups) {
+      const int mt = mtiles_of(g);
+      const int cnt = mt * nt;
+      if (t < base + cnt) {
+        const int l = t - base;
+        const int sw = a.swizzle_m > 0 ? a.swizzle_m : 8;
+        const int per_super = sw * nt;
+        const int super = l / per_super;
+        const int first_m = super * sw;
+        const int gsz = min(sw, mt - first_m);
+        const int in_super = l - super * per_super;
+        const int m_tile = first_m + in_super % gsz;
+        out.n_tile = in_super / gsz;
+        out.g = g;
+        out.m0 = m_tile * kBM;
+        out.rows_g = rows_of(g);
+        out.row_base = off_of(g);
+        if (a.mode == 0) {
+          out.rows_valid = min(kBM, out.rows_g - out.m0);
+          out.nk = (a.K + kBK - 1) / kBK;
+        } else {
+          out.rows_valid = min(kBM, a.M - out.m0);
+          out.nk = (out.rows_g + kBK - 1) / kBK;
+        }
+        return true;
+      }
+      base += cnt;
+      ++g;
+    }
+    return false;
+  }
+};
+
+// No gating: every tile is ready when the kernel starts.
+struct GateNone {
+  __device__ __forceinline__ bool wait(const Tile&, const GemmArgs&, volatile int*) const {
+    return true;
+  }
+};
+
+// Per-row-block flags: rows [128*i, 128*i+128) of group g are ready once
+// flags[flag_base(g) + i] >= expected.  Flags live in this GPU's memory and are bumped by the
+// producer (possibly on another GPU) with a system-scope release after its stores.
+struct GateRowBlockFlags {
+  const int* flags;
+  const int* group_flag_base;  // [num_groups] or nullptr (then g * blocks_per_group)
+  int blocks_per_group;
+  int expected;
+  __device__ __forceinline__ bool wait(const Tile& t, const GemmArgs& a,
+                                       volatile int* abort_flag) const {
+    const int idx = (group_flag_base ? group_flag_base[t.g] : t.g * blocks_per_group) +
+                    t.m0 / kBM;
+    int observed = 0;
+    if (flag_wait_ge(flags + idx, expected, a.timeout_ns, abort_flag, &observed)) return true;
+    report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, idx, expected, observed);
+    return false;
+  }
+};
+
+template <int BN>
+constexpr int gemm_smem_bytes() {
+  return kStages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 256 /*barriers*/;
+}
+
+template <bool A_MN, bool B_MN, int BN, class Epi, class Gate>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
+                  const __grid_constant__ CUtensorMap tma_b, const GemmArgs args, const Epi epi,
+                  const Gate gate) {
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int A_BYTES = kBM * kBK * 2;
+  constexpr int B_BYTES = BN * kBK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: powers of two
+  static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * STAGE_BYTES);
+  uint64_t* full = bars;                      // [kStages]
+  uint64_t* empty = bars + kStages;           // [kStages]
+  uint64_t* tfull = bars + 2 * kStages;       // [2]
+  uint64_t* tempty = bars + 2 * kStages + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint64_t timeout = args.timeout_ns;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer -------------------------------
+    if (lane == 0) {
+      TileWalker<BN> walker(args);
+      Tile t;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int ti = blockIdx.x; ok && walker.get(ti, t); ti += gridDim.x) {
+        if (!gate.wait(t, args, abort_flag)) break;
+        for (int kb = 0; kb < t.nk; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, timeout, abort_flag)) {
+            report_status(args.status, kStatusMbarTimeout, kKernelIdGemm, 100 + stage, 0, 0);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          const int k0 = kb * kBK;
+          // ---- A ----
+          if (args.mode == 0) {
+            if constexpr (!A_MN) {
+              tma_load_2d(sa, &tma_a, &full[stage], k0, t.row_base + t.m0);
+            } else {
+              // A stored [K, rows]: 64-row-wide boxes along the M index.
+#pragma unroll
+              for (int j = 0; j < kBM / 64; ++j)
+                tma_load_2d(sa + j * (64 * kBK * 2), &tma_a, &full[stage],
+                            t.row_base + t.m0 + 64 * j, k0);
+            }
+          } else {
+            // grouped-K: A is [rows_total, M], contraction over rows of the group.
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j)
+              tma_load_2d(sa + j * (64 * kBK * 2), &tma_a, &full[stage], t.m0 + 64 * j,
+                          t.row_base + k0);
+          }
+          // ---- B ----
+          if (args.mode == 0) {
+            const int brow = t.g * args.b_group_stride;
+            if constexpr (!B_MN) {
+              // B flattened [G * Nb, K]; 128-row boxes.
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j) {
+                int n;
+                if (args.gated)
+                  n = (j < BN / 256 ? 0 : args.n_half) + t.n_tile * (BN / 2) +
+                      128 * (j % (BN / 256 > 0 ? BN / 256 : 1));
+                else
+                  n = t.n_tile * BN + 128 * j;
+                tma_load_2d(sb + j * (128 * kBK * 2), &tma_b, &full[stage], k0, brow + n);
+              }
+            } else {
+              // B flattened [G * K, Nb]; 64-column boxes.
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) {
+                int n;
+                if (args.gated)
+                  n = (j < BN / 128 ? 0 : args.n_half) + t.n_tile * (BN / 2) +
+                      64 * (j % (BN / 128));
+                else
+                  n = t.n_tile * BN + 64 * j;
+                tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, &full[stage], n, brow + k0);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, &full[stage], t.n_tile * BN + 64 * j,
+                          t.row_base + k0);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer -------------------------------
+    if (lane == 0) {
+      constexpr bool A_IS_MN = A_MN;  // in mode 1 the launcher instantiates A_MN = true
+      constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN, A_IS_MN, B_MN);
+      TileWalker<BN> walker(args);
+      Tile t;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int ti = blockIdx.x; ok && walker.get(ti, t); ti += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, timeout, abort_flag)) {
+          report_status(args.status, kStatusMbarTimeout, kKernelIdGemm, 200 + acc, 0, 0);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.nk; ++kb) {
+          if (!mbar_wait(&full[stage], phase, timeout, abort_flag)) {
+            report_status(args.status, kStatusMbarTimeout, kKernelIdGemm, 300 + stage, 0, 0);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            uint64_t da, db;
+            if constexpr (!A_IS_MN)
+              da = umma_smem_desc(sa + k * 32, 0, 1024);
+            else
+              da = umma_smem_desc(sa + k * 2048, 64 * kBK * 2, 1024);
+            if constexpr (!B_MN)
+              db = umma_smem_desc(sb + k * 32, 0, 1024);
+            else
+              db = umma_smem_desc(sb + k * 2048, 64 * kBK * 2, 1024);
+            umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (4 warps) -------------------------------
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    TileWalker<BN> walker(args);
+    Tile t;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int ti = blockIdx.x; walker.get(ti, t); ti += gridDim.x) {
+      if (!mbar_wait(&tfull[acc], acc_phase, timeout, abort_flag)) {
+        if (lane == 0)
+          report_status(args.status, kStatusMbarTimeout, kKernelIdGemm, 400 + acc, 0, 0);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      epi.template run<BN>(t, args, taddr, q * 32 + lane, t.nk == 0);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      epi.tile_done(t, args, q * 32 + lane);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    // Give copies that are still in flight time to land before the CTA's shared memory is
+    // handed back (they complete within microseconds; this path is the error path only).
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace fm

@@ -1,0 +1,129 @@
+"""tcgen05 GEMM against a PyTorch fp32 reference of the same op."""
+import pytest
+import torch
+
+from fluidmoe_b200.ops import gemm
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(*shape, scale=1.0):
+    return (torch.randn(*shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _close(got, ref, tol=2e-2):
+    got, ref = got.float(), ref.float()
+    err = (got - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err / denom < tol, f"max err {err} vs scale {denom}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 128, 128), (256, 512, 256), (300, 520, 192), (1024, 1024, 1024), (77, 72, 72)])
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+def test_dense(M, N, K, layout):
+    torch.manual_seed(0)
+    a = _rand(M, K)
+    w = _rand(N, K) if layout == "nk" else _rand(K, N)
+    out = gemm.grouped_gemm(a, w, b_layout=layout)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ref = a.float() @ (w.float().t() if layout == "nk" else w.float())
+    _close(out, ref)
+
+
+def test_dense_fp32_accumulate():
+    a, w = _rand(256, 128), _rand(384, 128)
+    out = torch.ones(256, 384, device="cuda", dtype=torch.float32)
+    gemm.grouped_gemm(a, w, b_layout="nk", out=out, accumulate=True, alpha=0.5)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    _close(out, 1.0 + 0.5 * (a.float() @ w.float().t()))
+
+
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+def test_grouped_variable_rows(layout):
+    torch.manual_seed(1)
+    G, K, N = 4, 128, 320
+    rows = torch.tensor([130, 0, 64, 257], dtype=torch.int32)
+    offs = torch.tensor([0, 192, 192, 256], dtype=torch.int32)
+    total = 256 + 320
+    a = _rand(total, K)
+    w = _rand(G, N, K) if layout == "nk" else _rand(G, K, N)
+    out = gemm.grouped_gemm(a, w, b_layout=layout, group_rows=rows.cuda(), group_offs=offs.cuda())
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for g in range(G):
+        o, r = offs[g].item(), rows[g].item()
+        wg = w[g].float().t() if layout == "nk" else w[g].float()
+        _close(out[o:o + r], a[o:o + r].float() @ wg) if r else None
+
+
+@pytest.mark.parametrize("act", ["gelu", "silu", "swiglu"])
+def test_fc1_act_prob(act):
+    torch.manual_seed(2)
+    G, H, F, cap = 2, 256, 384, 192
+    a = _rand(G * cap, H)
+    w = _rand(G, H, 2 * F if act == "swiglu" else F, scale=0.05)
+    probs = torch.rand(G * cap, device="cuda")
+    out, pre = gemm.grouped_gemm_act(a, w, probs, activation=act, uniform_rows=cap)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for g in range(G):
+        x = a[g * cap:(g + 1) * cap].float() @ w[g].float()
+        _close(pre[g * cap:(g + 1) * cap], x)
+        ref = gemm.act_ref(x, act) * probs[g * cap:(g + 1) * cap, None]
+        _close(out[g * cap:(g + 1) * cap], ref)
+
+
+@pytest.mark.parametrize("act", ["gelu", "swiglu"])
+def test_fc2_dx_dact(act):
+    torch.manual_seed(3)
+    G, H, F, cap = 2, 256, 384, 160
+    dy = _rand(G * cap, H)
+    w2 = _rand(G, F, H, scale=0.05)
+    pre = _rand(G * cap, 2 * F if act == "swiglu" else F)
+    probs = torch.rand(G * cap, device="cuda")
+    dpre, dprobs = gemm.grouped_gemm_dact(dy, w2, pre, probs, activation=act, uniform_rows=cap)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    rdpre, rdprobs = gemm.grouped_gemm_dact(dy.cpu(), w2.cpu(), pre.cpu(), probs.cpu(), activation=act, uniform_rows=cap)
+    _close(dpre.cpu(), rdpre)
+    _close(dprobs.cpu(), rdprobs)
+
+
+def test_wgrad_grouped():
+    torch.manual_seed(4)
+    G, M, N = 3, 256, 320
+    rows = torch.tensor([128, 70, 200], dtype=torch.int32)
+    offs = torch.tensor([0, 128, 256], dtype=torch.int32)
+    total = 512
+    a, dy = _rand(total, M), _rand(total, N)
+    # rows outside the groups must be zero (64-row contraction blocks)
+    mask = torch.zeros(total, dtype=torch.bool)
+    for o, r in zip(offs.tolist(), rows.tolist()):
+        mask[o:o + r] = True
+    a[~mask.cuda()] = 0
+    out = torch.full((G, M, N), 2.0, device="cuda")
+    gemm.grouped_gemm_wgrad(a, dy, G, group_rows=rows.cuda(), group_offs=offs.cuda(), out=out, accumulate=True)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for g in range(G):
+        o, r = offs[g].item(), rows[g].item()
+        _close(out[g], 2.0 + a[o:o + r].float().t() @ dy[o:o + r].float())
+
+
+def test_large_perf_smoke():
+    a, w = _rand(4096, 4096), _rand(4096, 4096)
+    for _ in range(3):
+        out = gemm.grouped_gemm(a, w, b_layout="nk")
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(10):
+        out = gemm.grouped_gemm(a, w, b_layout="nk")
+    e.record()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ms = s.elapsed_time(e) / 10
+    print(f"\n4096^3 bf16: {ms:.3f} ms, {2 * 4096**3 / ms / 1e9:.1f} TFLOP/s")
+    _close(out, a.float() @ w.float().t())

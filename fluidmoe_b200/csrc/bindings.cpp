@@ -48,6 +48,7 @@ static void gemm_launch(const py::dict& d, uintptr_t stream) {
   g.uniform_rows = get<int>(d, "uniform_rows", 0);
   g.group_rows = ptr<const int*>(d, "group_rows");
   g.group_offs = ptr<const int*>(d, "group_offs");
+  g.group_b = ptr<const int*>(d, "group_b");
   g.b_group_stride = get<int>(d, "b_group_stride", 0);
   g.gated = get<int>(d, "gated", 0);
   g.n_half = get<int>(d, "n_half", 0);

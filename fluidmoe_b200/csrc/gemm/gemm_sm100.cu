@@ -317,8 +317,10 @@ struct EpiScatter {
 // ----------------------------------------------------------------------------------------
 // host side
 // ----------------------------------------------------------------------------------------
-static char g_err[512] = {0};
-static void set_err(const char* msg) { snprintf(g_err, sizeof(g_err), "%s", msg); }
+}  // namespace fm
+extern "C" void fm_set_error(const char* msg);
+namespace fm {
+static void set_err(const char* msg) { fm_set_error(msg); }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -358,8 +360,10 @@ static bool make_tmap(CUtensorMap* m, const void* ptr, long long inner, long lon
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    snprintf(g_err, sizeof(g_err), "cuTensorMapEncodeTiled failed: %d (inner=%lld outer=%lld ld=%lld)",
+    char buf[256];
+    snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed: %d (inner=%lld outer=%lld ld=%lld)",
              (int)r, inner, outer, ld);
+    set_err(buf);
     return false;
   }
   return true;
@@ -429,7 +433,6 @@ static int dispatch_gate(const FmGemmDesc* d, const CUtensorMap& ta, const CUten
 
 }  // namespace fm
 
-extern "C" const char* fm_last_error(void) { return fm::g_err; }
 
 extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   using namespace fm;
@@ -443,6 +446,10 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   }
   if (d->mode == 1 && !(d->a_mn && d->b_mn)) {
     set_err("grouped-K mode needs both operands stored [rows, M] / [rows, N]");
+    return -1;
+  }
+  if (d->gated && d->n_half % 8 != 0) {
+    set_err("gated layout needs the up half to start at a multiple of 8 columns");
     return -1;
   }
   if (d->mode == 0 && d->K % 8 != 0) {
@@ -469,6 +476,7 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   args.uniform_rows = d->uniform_rows;
   args.group_rows = d->group_rows;
   args.group_offs = d->group_offs;
+  args.group_b = d->group_b;
   args.b_group_stride = d->b_group_stride;
   args.gated = d->gated;
   args.n_half = d->n_half;

@@ -38,6 +38,7 @@ struct GemmArgs {
   int uniform_rows;  // rows per group when group_rows == nullptr
   const int* group_rows;  // device, [num_groups], may be nullptr
   const int* group_offs;  // device, [num_groups] row offset of each group in A (and C)
+  const int* group_b;     // device, [num_groups]: which B matrix a group uses (nullptr: g)
   int b_group_stride;     // mode 0: rows of the flattened 2-D B between groups
   int gated;              // B holds [gate | up] column halves, tile = 128 gate + 128 up
   int n_half;             // column offset of the `up` half inside B
@@ -231,7 +232,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
           }
           // ---- B ----
           if (args.mode == 0) {
-            const int brow = t.g * args.b_group_stride;
+            const int brow = (args.group_b ? args.group_b[t.g] : t.g) * args.b_group_stride;
             if constexpr (!B_MN) {
               // B flattened [G * Nb, K]; 128-row boxes.
 #pragma unroll

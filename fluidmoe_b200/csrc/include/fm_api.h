@@ -31,6 +31,7 @@ typedef struct FmGemmDesc {
   int uniform_rows;
   const int* group_rows;
   const int* group_offs;
+  const int* group_b;  // which B matrix each group multiplies with (null: group index)
   int b_group_stride;
   int gated;
   int n_half;

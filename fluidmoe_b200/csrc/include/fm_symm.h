@@ -1,10 +1,61 @@
-// C ABI of the symmetric-memory runtime (see csrc/symm/symm_heap.cpp).
+// C ABI of the symmetric-memory runtime: slabs of device memory that every rank of a group can
+// address directly over NVLink, plus the device-initiated primitives built on them (barrier,
+// all-to-all, all-reduce).  It takes the place of the reference's NVSHMEM host wrapper
+// (fluid/csrc/nvshmem_ops.cpp): same contract (collective alloc / free, non-owning views,
+// stream-ordered put + signal, bounded waits) but the transfers are issued by kernels, not by
+// the host.
 #pragma once
 #include <stdint.h>
 #include <cuda_runtime.h>
 #ifdef __cplusplus
 extern "C" {
 #endif
+
+#define FM_IPC_HANDLE_BYTES 64
+
+// ---- slab management (host) ----
+// Allocate `bytes` of device memory on the current device and export an IPC handle for it.
+int fm_symm_alloc(size_t bytes, void** ptr, unsigned char handle[FM_IPC_HANDLE_BYTES]);
+// Map a peer's slab into this process; enables peer access lazily.
+int fm_symm_open(const unsigned char handle[FM_IPC_HANDLE_BYTES], void** peer_ptr);
+int fm_symm_close(void* peer_ptr);
+int fm_symm_free(void* ptr);
+int fm_symm_can_access_peer(int dev, int peer_dev);
+
+// ---- device-initiated primitives ----
+// Barrier across `nranks` ranks.  flag_ptrs[p] = address of rank p's int32[nranks] barrier
+// words (in its slab); every rank passes the same epoch, which grows by one per barrier.
+int fm_symm_barrier(int* const* flag_ptrs_dev, int my_rank, int nranks, int epoch,
+                    unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
+// All-to-all push: slice p of `send` (send_offs[p] .. +send_bytes[p], 16-byte multiples) is
+// stored into rank p's receive buffer at recv_ptrs[p] + dst_offs[p]; afterwards rank p's
+// arrival word flag_ptrs[p][my_rank] is set to `epoch` with a system-scope release.
+// All index arrays are device arrays of length nranks.
+int fm_a2a_push(const void* send, const long long* send_offs, const long long* send_bytes,
+                void* const* recv_ptrs, const long long* dst_offs, int* const* flag_ptrs,
+                int* local_counters, int my_rank, int nranks, int epoch, int num_ctas,
+                cudaStream_t stream);
+// Wait (bounded) until every peer's arrival word in `my_flags` reached `epoch`.
+int fm_a2a_wait(const int* my_flags, int my_rank, int nranks, int epoch,
+                unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
+// Two-shot all-reduce (sum) over peer memory: every rank's `buf_ptrs[p]` points at its copy of
+// the same symmetric buffer of `count` elements (fp32 or bf16, in place).  Rank r reduces
+// chunk r by reading all peers, scales by `scale`, and writes the result to every peer.
+int fm_allreduce_p2p(void* const* buf_ptrs_dev, long long count, int dtype_fp32, float scale,
+                     int* const* flag_ptrs_dev, int my_rank, int nranks, int epoch, int num_ctas,
+                     unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
+// One-sided put + signal: copy `bytes` (16-byte multiple) from `src` to `dst` (a peer address),
+// then store `value` to `flag` (a peer address) with a system-scope release.
+int fm_put_signal(const void* src, long long bytes, void* dst, int* flag, int value, int num_ctas,
+                  int* local_counter, cudaStream_t stream);
+
+// Test hook for bounded waits: waits for *flag >= expected and reports a status on timeout.
+int fm_wait_flag(const int* flag, int expected, unsigned long long timeout_ns, int* status,
+                 cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,3 +1,79 @@
+// pybind11 bindings of the symmetric-memory runtime.
 #include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <stdexcept>
+#include <string>
+
+#include "include/fm_api.h"
+#include "include/fm_symm.h"
+
 namespace py = pybind11;
-void bind_symm(py::module_& m) {}
+
+static void chk(int rc, const char* what) {
+  if (rc != 0) throw std::runtime_error(std::string(what) + ": " + fm_last_error());
+}
+template <class P>
+static P as_ptr(uintptr_t v) {
+  return reinterpret_cast<P>(v);
+}
+
+void bind_symm(py::module_& m) {
+  m.def("symm_alloc", [](size_t bytes) {
+    void* p = nullptr;
+    unsigned char h[FM_IPC_HANDLE_BYTES];
+    chk(fm_symm_alloc(bytes, &p, h), "symm_alloc");
+    return py::make_tuple(reinterpret_cast<uintptr_t>(p),
+                          py::bytes(reinterpret_cast<const char*>(h), FM_IPC_HANDLE_BYTES));
+  });
+  m.def("symm_open", [](const std::string& handle) {
+    if (handle.size() != FM_IPC_HANDLE_BYTES) throw std::runtime_error("bad IPC handle size");
+    void* p = nullptr;
+    chk(fm_symm_open(reinterpret_cast<const unsigned char*>(handle.data()), &p), "symm_open");
+    return reinterpret_cast<uintptr_t>(p);
+  });
+  m.def("symm_close", [](uintptr_t p) { chk(fm_symm_close(as_ptr<void*>(p)), "symm_close"); });
+  m.def("symm_free", [](uintptr_t p) { chk(fm_symm_free(as_ptr<void*>(p)), "symm_free"); });
+  m.def("can_access_peer", &fm_symm_can_access_peer);
+  m.def("symm_barrier", [](uintptr_t flag_ptrs, int rank, int n, int epoch,
+                           unsigned long long timeout_ns, uintptr_t status, uintptr_t stream) {
+    chk(fm_symm_barrier(as_ptr<int* const*>(flag_ptrs), rank, n, epoch, timeout_ns,
+                        as_ptr<int*>(status), as_ptr<cudaStream_t>(stream)),
+        "symm_barrier");
+  });
+  m.def("a2a_push", [](uintptr_t send, uintptr_t send_offs, uintptr_t send_bytes,
+                       uintptr_t recv_ptrs, uintptr_t dst_offs, uintptr_t flag_ptrs,
+                       uintptr_t counters, int rank, int n, int epoch, int ctas, uintptr_t stream) {
+    chk(fm_a2a_push(as_ptr<const void*>(send), as_ptr<const long long*>(send_offs),
+                    as_ptr<const long long*>(send_bytes), as_ptr<void* const*>(recv_ptrs),
+                    as_ptr<const long long*>(dst_offs), as_ptr<int* const*>(flag_ptrs),
+                    as_ptr<int*>(counters), rank, n, epoch, ctas, as_ptr<cudaStream_t>(stream)),
+        "a2a_push");
+  });
+  m.def("a2a_wait", [](uintptr_t flags, int rank, int n, int epoch, unsigned long long timeout_ns,
+                       uintptr_t status, uintptr_t stream) {
+    chk(fm_a2a_wait(as_ptr<const int*>(flags), rank, n, epoch, timeout_ns, as_ptr<int*>(status),
+                    as_ptr<cudaStream_t>(stream)),
+        "a2a_wait");
+  });
+  m.def("put_signal", [](uintptr_t src, long long bytes, uintptr_t dst, uintptr_t flag, int value,
+                         int ctas, uintptr_t counter, uintptr_t stream) {
+    chk(fm_put_signal(as_ptr<const void*>(src), bytes, as_ptr<void*>(dst), as_ptr<int*>(flag), value,
+                      ctas, as_ptr<int*>(counter), as_ptr<cudaStream_t>(stream)),
+        "put_signal");
+  });
+  m.def("wait_flag", [](uintptr_t flag, int expected, unsigned long long timeout_ns,
+                        uintptr_t status, uintptr_t stream) {
+    chk(fm_wait_flag(as_ptr<const int*>(flag), expected, timeout_ns, as_ptr<int*>(status),
+                     as_ptr<cudaStream_t>(stream)),
+        "wait_flag");
+  });
+  m.def("allreduce_p2p", [](uintptr_t bufs, long long count, int fp32, float scale,
+                            uintptr_t flag_ptrs, int rank, int n, int epoch, int ctas,
+                            unsigned long long timeout_ns, uintptr_t status, uintptr_t stream) {
+    chk(fm_allreduce_p2p(as_ptr<void* const*>(bufs), count, fp32, scale,
+                         as_ptr<int* const*>(flag_ptrs), rank, n, epoch, ctas, timeout_ns,
+                         as_ptr<int*>(status), as_ptr<cudaStream_t>(stream)),
+        "allreduce_p2p");
+  });
+}

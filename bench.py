@@ -1,0 +1,424 @@
+#!/usr/bin/env python
+"""Flagship benchmark: training step of a 4-layer Mixtral-shaped MoE transformer.
+
+    python bench.py --gpus 1 --steps 10 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...        # the unmodified reference from baseline/_ref
+
+Model: hidden 4096, 32 query / 8 KV heads (d = 128), causal, RoPE, 8 experts top-2 with FFN
+14336, vocabulary 32000, 4096 positions per rank (weak scaling: SP = EP = N), batch 1,
+cross-entropy on shifted ids, backward scheduler on with 4 dX chunks, optimizer step included.
+The arm of this repository uses SwiGLU experts and RMSNorm; the reference has neither, so its arm
+runs GELU experts with FFN 21504 (the same FLOPs and weight bytes as SwiGLU 14336) and LayerNorm.
+
+Prints one JSON line on rank 0 (see the keys at the bottom of ``main``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+
+MODEL = dict(hidden=4096, heads=32, kv_heads=8, ffn=14336, experts=8, top_k=2, vocab=32000, layers=4,
+             seq_per_rank=4096, batch=1)
+BASELINE_TOKENS_PER_S = None  # the reference publishes no tokens/s figure for this configuration
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=MODEL["layers"])
+    ap.add_argument("--seq", type=int, default=MODEL["seq_per_rank"])
+    ap.add_argument("--chunks", type=int, default=4)
+    ap.add_argument("--mode", default="full", choices=["F", "FB", "full"])
+    ap.add_argument("--comm", default="auto", choices=["auto", "a2a", "p2p", "fused"])
+    ap.add_argument("--tiny", action="store_true", help="small shapes for a functional check")
+    ap.add_argument("--opt-state", default="bf16", choices=["bf16", "fp32"],
+                    help="dtype of the Adam moments (torch.optim.AdamW keeps bf16 moments for bf16 parameters)")
+    ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file")
+    return ap.parse_args()
+
+
+# ------------------------------------------------------------------------------------------------
+# helpers shared by both arms
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of this rank's GPU while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        busy = [c for c, p in zip(sm, power) if p > 300] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+
+
+def timed_region(torch, dist, world, fn_step, steps):
+    """Barrier + synchronize on both sides; device time by CUDA events; max over ranks."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    s.record()
+    for i in range(steps):
+        fn_step(i)
+    e.record()
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) * 1e3
+    if world > 1:
+        dist.barrier()
+    ms = s.elapsed_time(e)
+    t = torch.tensor([ms, wall], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t[0].item(), t[1].item()
+
+
+def make_batches(torch, n, seq, batch, vocab, seed):
+    """Pinned host batches of token ids, one extra position for the shifted labels."""
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (seq + 1, batch), generator=g).pin_memory() for _ in range(n)]
+
+
+def emit(rank, payload):
+    if rank == 0:
+        print(json.dumps(payload), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# this repository's arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from fluidmoe_b200.distributed import init_distributed, init_parallel
+    from fluidmoe_b200.models.gpt import MoEGPT
+    from fluidmoe_b200.ops import elementwise, gemm
+    from fluidmoe_b200.ops.optim import FusedAdam
+    from fluidmoe_b200.parallel.ddp import FluidDDP, FluidOptimizerWrapper
+    from fluidmoe_b200.parallel.scheduler import get_backward_scheduler
+
+    rank, local_rank, world = dist_env()
+    if args.gpus != world:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus} (launch with torch.distributed.run)")
+    device = init_distributed()
+    m = dict(MODEL)
+    if args.tiny:
+        m.update(hidden=512, heads=8, kv_heads=8, ffn=1024, vocab=2048)
+        args.seq = min(args.seq, 512)
+    heap = (6 << 30) if (world > 1 and args.comm in ("auto", "fused")) else 0
+    pc = init_parallel(ep_size=world, device=device, symmetric_heap_bytes=heap)
+    torch.manual_seed(1234)
+    model = MoEGPT(m["vocab"], args.layers, m["hidden"], m["heads"], m["kv_heads"], m["ffn"], m["experts"],
+                   m["top_k"], pc.cp_group, pc.ep_group, dtype=torch.bfloat16, device=device,
+                   router_dtype=torch.float32, activation_func="swiglu", norm_type="rmsnorm",
+                   moe_combine_chunks=args.chunks, moe_dispatch_chunks=args.chunks,
+                   attn_proj_chunks=args.chunks, attn_qkv_chunks=args.chunks, comm_mode=args.comm,
+                   parallel_ctx=pc)
+    sched = get_backward_scheduler()
+    if args.mode == "F":
+        sched.disable()
+    else:
+        sched.enable(device)
+    ddp = FluidDDP(None, model, sched, dp_cp_group=pc.dp_cp_group, expert_dp_group=pc.expert_dp_group,
+                   ar_enabled=args.mode == "full",
+                   gap_budgets={"moe_combine": 0.5, "moe_dispatch": 0.5, "attn_proj": 0.3, "attn_qkv": 0.3},
+                   shared_ar_bw=3.0e8, expert_ar_bw=3.0e8)
+    opt = FluidOptimizerWrapper(
+        FusedAdam(model.parameters(), lr=1e-4, weight_decay=0.0,
+                  state_dtype=torch.bfloat16 if args.opt_state == "bf16" else torch.float32), sched)
+    seq, batch = args.seq, m["batch"]
+    n_batches = 4
+    host = make_batches(torch, n_batches, seq, batch, m["vocab"], 100 + rank)
+    dev_batches = [b.to(device) for b in host]
+    last = {}
+
+    def train_step(ids_full):
+        ddp.zero_grad_buffer()
+        loss = ddp(ids_full[:-1], ids_full[1:])
+        loss.backward()
+        ddp.finish_grad_sync()
+        opt.step()
+        return loss
+
+    def step_device(i):
+        last["loss"] = train_step(dev_batches[i % n_batches])
+
+    def step_e2e(i):
+        ids = host[i % n_batches].to(device, non_blocking=True)
+        last["loss_val"] = train_step(ids).item()
+
+    for i in range(args.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    if args.profile and rank == 0:
+        _profile_one_step(torch, step_device, args.profile)
+    l0 = gemm.LAUNCHES + elementwise.LAUNCHES + _extra_launches()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, _ = timed_region(torch, dist, world, step_device, args.steps)
+    launches = gemm.LAUNCHES + elementwise.LAUNCHES + _extra_launches() - l0
+    _, wall_e2e = timed_region(torch, dist, world, step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    gemm.check_status()
+    tokens = world * seq * batch * args.steps
+    value = tokens / (ms / 1e3)
+    e2e = tokens / (wall_e2e / 1e3)
+    emit(rank, {
+        "metric": "MoE transformer training tokens/s (fwd+bwd+optimizer, 4-layer Mixtral-shaped block stack)",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)", "impl": "ours",
+        "config": {"model": "mixtral-8x7b-shaped, %d layers, hidden %d, %d/%d heads, 8 experts top-2 SwiGLU ffn %d, vocab %d"
+                            % (args.layers, m["hidden"], m["heads"], m["kv_heads"], m["ffn"], m["vocab"]),
+                   "global_batch": world * batch, "seq_len": seq * world, "seq_per_rank": seq,
+                   "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
+                   "comm": args.comm, "adam_moments": args.opt_state, "grad_accum": "fp32", "l2": "working set of a step is several GB (>> 126 MB L2); no explicit flush",
+                   "loss": float(last["loss_val"])},
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": wall_e2e / args.steps,
+                "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": int(launches),
+    })
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def _profile_one_step(torch, step_fn, path):
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        step_fn(0)
+        torch.cuda.synchronize()
+    os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+    with open(path, "w") as f:
+        f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=90))
+
+
+def _extra_launches() -> int:
+    total = 0
+    for name in ("fluidmoe_b200.ops.flash", "fluidmoe_b200.parallel.fused"):
+        mod = sys.modules.get(name)
+        total += getattr(mod, "LAUNCHES", 0) if mod is not None else 0
+    return total
+
+
+# ------------------------------------------------------------------------------------------------
+# reference arm: the unmodified reference package installed under baseline/_ref
+# ------------------------------------------------------------------------------------------------
+def run_reference(args):
+    ref_root = os.path.join(REPO, "baseline", "_ref")
+    rank, local_rank, world = dist_env()
+    if not os.path.isdir(os.path.join(ref_root, "fluid")):
+        emit(0, {"impl": "reference", "unavailable": "baseline/_ref is empty: the reference has no setup.py / "
+                 "pyproject.toml; install it from a copy with a packaging shim (see DESIGN.md)"})
+        return
+    sys.path.insert(0, ref_root)
+    for k in [k for k in sys.modules if k == "fluid" or k.startswith("fluid.")]:
+        del sys.modules[k]
+    os.environ.setdefault("FLUIDMOE_P2P_BACKEND", "nccl")
+    os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "1")
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    try:
+        import fluid  # noqa: F401 - the reference package
+        from fluid.core.scheduler import get_backward_scheduler
+        from fluid.layer.transformer import TransformerModel
+    except Exception as e:  # noqa: BLE001
+        emit(rank, {"impl": "reference", "unavailable": f"reference import failed: {type(e).__name__}: {e}"[:300]})
+        return
+    assert "baseline/_ref" in fluid.__file__.replace(os.sep, "/"), fluid.__file__
+    if args.gpus != world:
+        raise SystemExit(f"--gpus {args.gpus} needs WORLD_SIZE={args.gpus}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    m = dict(MODEL)
+    if args.tiny:
+        m.update(hidden=512, heads=8, kv_heads=8, ffn=1024, vocab=2048)
+        args.seq = min(args.seq, 512)
+    ffn_ref = m["ffn"] * 3 // 2          # GELU (2 matrices) FLOP- and byte-matched to SwiGLU (3 matrices)
+    all_group = dist.new_group(list(range(world)))
+    cp_group = ep_group = dist.new_group(list(range(world)))
+    torch.manual_seed(1234)
+    model = TransformerModel(
+        num_layers=args.layers, hidden_size=m["hidden"], num_heads=m["heads"], num_kv_heads=m["kv_heads"],
+        ffn_hidden_size=ffn_ref, num_experts=m["experts"], top_k=m["top_k"], cp_group=cp_group,
+        ep_group=ep_group, moe_combine_chunks=args.chunks, moe_dispatch_chunks=args.chunks,
+        attn_proj_chunks=args.chunks, attn_qkv_chunks=args.chunks, capacity_factor=1.0,
+        dtype=torch.bfloat16, device=device, router_dtype=torch.float32)
+    emb = torch.nn.Embedding(m["vocab"], m["hidden"], dtype=torch.bfloat16, device=device)
+    final_norm = torch.nn.LayerNorm(m["hidden"], dtype=torch.bfloat16, device=device)
+    head = torch.nn.Linear(m["hidden"], m["vocab"], bias=False, dtype=torch.bfloat16, device=device)
+    seq, batch = args.seq, m["batch"]
+    x_probe = torch.empty(seq, batch, m["hidden"], dtype=torch.bfloat16, device=device)
+    model.prepare_chunk_status(x_probe)
+    sched = get_backward_scheduler()
+    if args.mode == "F":
+        sched.enabled = False
+    else:
+        sched.enable()
+    sched.configure_allreduce(enabled=args.mode == "full", shared_dp_group=all_group, expert_dp_group=None,
+                              gap_budgets={"moe_combine": 0.5, "moe_dispatch": 0.5, "attn_proj": 0.3, "attn_qkv": 0.3},
+                              shared_ar_bw=3.0e8, expert_ar_bw=3.0e8)
+    if args.mode != "F":
+        model.setup_ar_buffer()
+    extra = list(emb.parameters()) + list(final_norm.parameters()) + list(head.parameters())
+    params = list(model.parameters()) + extra
+    opt = torch.optim.AdamW(params, lr=1e-4, weight_decay=0.0, fused=True)
+    # RoPE angles for the full sequence, Megatron layout [s, 1, 1, d]
+    d = m["hidden"] // m["heads"]
+    inv = 1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32, device=device) / d))
+    fr = torch.outer(torch.arange(seq * world, dtype=torch.float32, device=device), inv)
+    rotary = torch.cat([fr, fr], dim=-1).view(seq * world, 1, 1, d)
+    n_batches = 4
+    host = make_batches(torch, n_batches, seq, batch, m["vocab"], 100 + rank)
+    dev_batches = [b.to(device) for b in host]
+    last = {}
+
+    def train_step(ids_full):
+        for p in params:
+            p.grad = None
+            if hasattr(p, "_ar_buf_written"):
+                p._ar_buf_written = False
+        ids, labels = ids_full[:-1], ids_full[1:]
+        x = emb(ids)
+        for layer in model.layers:
+            x = layer(x, rotary)
+        logits = head(final_norm(x))
+        loss = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), labels.reshape(-1))
+        loss.backward()
+        sched.finish_batch()
+        if world > 1:
+            for p in extra:
+                if p.grad is not None:
+                    p.grad.div_(world)
+                    dist.all_reduce(p.grad, group=all_group)
+        for p in model.parameters():
+            mg = getattr(p, "main_grad", None)
+            if mg is not None and getattr(p, "_ar_buf_written", False):
+                p.grad = mg if mg.dtype == p.dtype else mg.to(p.dtype)
+        opt.step()
+        sched.clear_iteration()
+        return loss
+
+    def step_device(i):
+        last["loss"] = train_step(dev_batches[i % n_batches])
+
+    def step_e2e(i):
+        ids = host[i % n_batches].to(device, non_blocking=True)
+        last["loss_val"] = train_step(ids).item()
+
+    try:
+        for i in range(args.warmup):
+            step_device(i)
+        torch.cuda.synchronize()
+    except Exception as e:  # noqa: BLE001
+        emit(rank, {"impl": "reference", "unavailable": f"reference step failed: {type(e).__name__}: {e}"[:400]})
+        return
+    if args.profile and rank == 0:
+        _profile_one_step(torch, step_device, args.profile)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ms, _ = timed_region(torch, dist, world, step_device, args.steps)
+    _, wall_e2e = timed_region(torch, dist, world, step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    tokens = world * seq * batch * args.steps
+    value = tokens / (ms / 1e3)
+    emit(rank, {
+        "metric": "MoE transformer training tokens/s (fwd+bwd+optimizer, 4-layer Mixtral-shaped block stack)",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
+        "impl": "reference",
+        "config": {"model": "reference TransformerLayer x%d, hidden %d, %d/%d heads, 8 experts top-2 GELU ffn %d "
+                            "(FLOP-matched to SwiGLU %d), LayerNorm, vocab %d; embedding / head / loss / AdamW from torch"
+                            % (args.layers, m["hidden"], m["heads"], m["kv_heads"], ffn_ref, m["ffn"], m["vocab"]),
+                   "global_batch": world * batch, "seq_len": seq * world, "seq_per_rank": seq,
+                   "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
+                   "loss": float(last["loss_val"])},
+        "clocks": clocks,
+        "e2e": {"value": tokens / (wall_e2e / 1e3), "unit": "tokens/s", "ms_per_step": wall_e2e / args.steps,
+                "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": 0,
+    })
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

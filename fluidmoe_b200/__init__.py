@@ -1,0 +1,41 @@
+"""fluidmoe_b200: a Blackwell-native MoE / sequence-parallel overlap framework.
+
+One MoE transformer block (norm -> Ulysses attention -> residual -> norm -> top-k MoE -> residual)
+whose four per-layer all-to-alls are hidden behind compute in forward and backward, with a backward
+scheduler that defers weight-gradient GEMMs into communication windows and trickles the gradient
+all-reduce into the gaps.  The hot operators are hand-written sm_100a kernels (tcgen05 GEMMs with
+TMEM accumulators and fused epilogues, device-initiated dispatch / combine over symmetric memory,
+flash attention, normalisation, RoPE, router, permute, Adam).
+"""
+from __future__ import annotations
+
+__version__ = "0.1.0"
+
+from .parallel.comm import _all_to_all, _all_to_all_hp2sp_forward, _all_to_all_sp2hp_forward, all_to_all, hp2sp, sp2hp
+from .parallel.schedule import MultiCardOverlapContext, compute_round_robin_schedule
+from .parallel.scheduler import BackwardScheduler, DWTask, FlatGradBuffer, get_backward_scheduler
+from .parallel.streams import StreamManager, get_stream_manager
+from .parallel.p2p_backend import (CollectiveP2PBackend, NCCLBackend, NVSHMEMBackend, P2PBackend,
+                                   SymmetricP2PBackend, get_p2p_backend, reset_p2p_backend)
+from .parallel.ddp import FluidDDP, FluidOptimizerWrapper, setup_model_and_optimizer
+from .models.moe import (EPPlan, MoEBaseline, build_moe_chunk_config, combine_fc2_backward, decompose_chunks,
+                         dispatch_fc1_forward, dispatch_fc1_p2p_forward, fc1_dispatch_backward,
+                         fc2_combine_forward, fc2_combine_p2p_forward, moe_multicard_p2p_overlap_forward,
+                         pad_moe_dispatch, register_moe_dw_tasks, register_router_dw_task, router_backward,
+                         router_forward)
+from .models.attention import (CPPlan, hp2sp_qkv_backward, outproj_sp2hp_backward, output_projection_forward,
+                               output_projection_p2p_forward, output_projection_register_dw,
+                               qkv_projection_forward, qkv_projection_p2p_forward,
+                               scaled_dot_product_attention_forward)
+from .models.transformer import TransformerLayer, TransformerLayerFunction, TransformerModel
+from .models.gpt import MoEGPT
+from .models.megatron_spec import get_fluid_custom_layers, get_fluid_gpt_layer_spec
+from .distributed import ParallelContext, init_distributed, init_parallel
+from .ops.gemm import grouped_gemm, grouped_gemm_act, grouped_gemm_dact, grouped_gemm_wgrad
+from .ops.optim import FusedAdam
+
+# grouped-GEMM helpers under the names of the reference (fluid/moe/__init__.py:31-60)
+grouped_fc1_act = grouped_gemm_act
+grouped_fc2 = grouped_gemm
+grouped_fc2_dx = grouped_gemm_dact
+grouped_fc1_dx = grouped_gemm

@@ -93,12 +93,12 @@ struct EpiStore {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero) const {
+                                      bool zero, int chalf) const {
     const long long row = a.mode == 0 ? (long long)t.row_base + t.m0 + r : (long long)t.m0 + r;
     const long long goff = a.mode == 0 ? 0 : (long long)t.g * group_stride;
     const bool row_ok = r < t.rows_valid;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
       const int col = t.n_tile * BN + c * 32;
       if (col >= a.N) break;
       float v[32];
@@ -156,13 +156,13 @@ struct EpiAct {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero) const {
+                                      bool zero, int chalf) const {
     const long long row = (long long)t.row_base + t.m0 + r;
     const bool row_ok = r < t.rows_valid;
     const float p = (row_ok && probs) ? probs[row] : 1.0f;
     if (a.gated) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 64; ++c) {
+      for (int c = chalf * (BN / 128); c < (chalf + 1) * (BN / 128); ++c) {
         const int col = t.n_tile * (BN / 2) + c * 32;
         if (col >= a.N) break;
         float g[32], u[32];
@@ -180,7 +180,7 @@ struct EpiAct {
       }
     } else {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
+      for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
         const int col = t.n_tile * BN + c * 32;
         if (col >= a.N) break;
         float v[32];
@@ -201,7 +201,8 @@ struct EpiAct {
 // Epilogue 3: backward of (act x prob), fused after dActW = dY * W2^T.
 //   a = act(pre); dprob_partial[row, n_tile] = sum_cols(acc * a); dpre = acc * p * act'(pre)
 //   gated: a = silu(g) * u; dg = acc * p * u * silu'(g); du = acc * p * silu(g)
-// Partial sums per N tile keep the probability gradient deterministic (no atomics).
+// Partial sums per N tile and per column half (two epilogue warps share a row) keep the
+// probability gradient deterministic (no atomics): dprobs_partial is [rows, n_tiles, 2].
 // Reference math: fluid/moe/backward.py:341-356,1046-1061.
 // ----------------------------------------------------------------------------------------
 struct EpiDAct {
@@ -218,13 +219,13 @@ struct EpiDAct {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero) const {
+                                      bool zero, int chalf) const {
     const long long row = (long long)t.row_base + t.m0 + r;
     const bool row_ok = r < t.rows_valid;
     const float p = (row_ok && probs) ? probs[row] : 1.0f;
     float dp = 0.f;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
       const int col = t.n_tile * BN + c * 32;
       if (col >= a.N) break;
       float v[32];
@@ -256,7 +257,7 @@ struct EpiDAct {
         store_row_bf16(dpre + row * ld_dpre + col, x, ncols);
       }
     }
-    if (row_ok && dprobs_partial) dprobs_partial[row * n_tiles + t.n_tile] = dp;
+    if (row_ok && dprobs_partial) dprobs_partial[(row * n_tiles + t.n_tile) * 2 + chalf] = dp;
   }
   __device__ __forceinline__ void tile_done(const Tile&, const GemmArgs&, int) const {}
 };
@@ -266,7 +267,8 @@ struct EpiDAct {
 // as bf16 to dst_base[dst_rank[R]] + dst_row[R] * ld_dst, which may be another GPU's buffer
 // mapped over NVLink (plain 16-byte peer stores).  After a tile, each destination's arrival
 // counter grows by the number of rows the tile sent it; the owner waits until its counter
-// equals rows_expected * n_tiles.  Replaces the combine all-to-all rounds of
+// equals rows_expected * n_tiles * 2 (each of the two epilogue warps that share a row reports
+// its half).  Replaces the combine all-to-all rounds of
 // fluid/moe/forward.py:903-948.
 // ----------------------------------------------------------------------------------------
 struct EpiScatter {
@@ -279,7 +281,7 @@ struct EpiScatter {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero) const {
+                                      bool zero, int chalf) const {
     const long long row = (long long)t.row_base + t.m0 + r;
     const bool row_ok = r < t.rows_valid;
     int rank = -1;
@@ -290,7 +292,7 @@ struct EpiScatter {
     }
     __nv_bfloat16* base = rank >= 0 ? dst_base[rank] + drow * ld_dst : nullptr;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
       const int col = t.n_tile * BN + c * 32;
       if (col >= a.N) break;
       float v[32];
@@ -362,6 +364,32 @@ static bool make_tmap(CUtensorMap* m, const void* ptr, long long inner, long lon
   if (r != CUDA_SUCCESS) {
     char buf[256];
     snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed: %d (inner=%lld outer=%lld ld=%lld)",
+             (int)r, inner, outer, ld);
+    set_err(buf);
+    return false;
+  }
+  return true;
+}
+
+// 3-D view of an MN-major operand stored [outer, inner] (inner contiguous, a multiple of 64):
+// dims {64, outer, inner / 64}; one box {64, 64 k-rows, nblk} lands as nblk slabs of [64 k][64 mn].
+static bool make_tmap_mn3d(CUtensorMap* m, const void* ptr, long long inner, long long outer,
+                           long long ld, int nblk) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) {
+    set_err("cuTensorMapEncodeTiled unavailable");
+    return false;
+  }
+  cuuint64_t dims[3] = {64, (cuuint64_t)outer, (cuuint64_t)(inner / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  cuuint32_t box[3] = {64, 64, (cuuint32_t)nblk};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[256];
+    snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled (3-D) failed: %d (inner=%lld outer=%lld ld=%lld)",
              (int)r, inner, outer, ld);
     set_err(buf);
     return false;
@@ -461,10 +489,27 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
     return -1;
   }
   CUtensorMap ta, tb;
+  // One 3-D box per MN-major tile when every tile starts on a 64-element boundary of a
+  // 64-multiple inner extent; otherwise 64-wide 2-D boxes.
+  const bool a3 = d->a_mn && d->a_inner % 64 == 0 && (d->mode == 1 || d->group_offs == nullptr) &&
+                  (d->mode == 1 || d->uniform_rows % 64 == 0);
+  const bool b3 = d->b_mn && d->b_inner % 64 == 0 && (!d->gated || d->n_half % 64 == 0);
+  const bool mn3d = (!d->a_mn || a3) && (!d->b_mn || b3) && (d->a_mn || d->b_mn) &&
+                    ((uintptr_t)d->A % 16 == 0) && ((uintptr_t)d->B % 16 == 0) && d->lda % 8 == 0 &&
+                    d->ldb % 8 == 0;
   // A: K-major -> box {64 k, 128 rows}; MN-major -> box {64 rows, 64 k}
-  if (!make_tmap(&ta, d->A, d->a_inner, d->a_outer, d->lda, d->a_mn ? 64 : 128)) return -3;
+  if (d->a_mn && mn3d) {
+    if (!make_tmap_mn3d(&ta, d->A, d->a_inner, d->a_outer, d->lda, kBM / 64)) return -3;
+  } else if (!make_tmap(&ta, d->A, d->a_inner, d->a_outer, d->lda, d->a_mn ? 64 : 128)) {
+    return -3;
+  }
   // B: K-major -> box {64 k, 128 n}; MN-major -> box {64 n, 64 k}
-  if (!make_tmap(&tb, d->B, d->b_inner, d->b_outer, d->ldb, d->b_mn ? 64 : 128)) return -3;
+  if (d->b_mn && mn3d) {
+    if (!make_tmap_mn3d(&tb, d->B, d->b_inner, d->b_outer, d->ldb, d->gated ? d->bn / 128 : d->bn / 64))
+      return -3;
+  } else if (!make_tmap(&tb, d->B, d->b_inner, d->b_outer, d->ldb, d->b_mn ? 64 : 128)) {
+    return -3;
+  }
 
   GemmArgs args;
   memset(&args, 0, sizeof(args));
@@ -481,6 +526,7 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   args.gated = d->gated;
   args.n_half = d->n_half;
   args.swizzle_m = d->swizzle_m;
+  args.mn3d = mn3d ? 1 : 0;
   args.timeout_ns = d->timeout_ns ? d->timeout_ns : 4000000000ull;
   args.status = d->status;
 

@@ -25,7 +25,8 @@ namespace fm {
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kStages = 4;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;    // two warps per TMEM lane quarter, each takes half the columns
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kKernelIdGemm = 1;
 
 struct GemmArgs {
@@ -43,6 +44,7 @@ struct GemmArgs {
   int gated;              // B holds [gate | up] column halves, tile = 128 gate + 128 up
   int n_half;             // column offset of the `up` half inside B
   int swizzle_m;          // m-tiles per rasterisation super-row (L2 reuse)
+  int mn3d;               // MN-major operands are fetched with one 3-D box per tile
   unsigned long long timeout_ns;
   int* status;
 };
@@ -120,7 +122,7 @@ struct GateNone {
 };
 
 // Per-row-block flags: rows [128*i, 128*i+128) of group g are ready once
-// flags[flag_base(g) + i] >= expected.  Flags live in this GPU's memory and are bumped by the
+// flags[flag_base(g) + i] >= (rows in the block) * expected.  Flags live in this GPU's memory and are bumped by the
 // producer (possibly on another GPU) with a system-scope release after its stores.
 struct GateRowBlockFlags {
   const int* flags;
@@ -132,8 +134,10 @@ struct GateRowBlockFlags {
     const int idx = (group_flag_base ? group_flag_base[t.g] : t.g * blocks_per_group) +
                     t.m0 / kBM;
     int observed = 0;
-    if (flag_wait_ge(flags + idx, expected, a.timeout_ns, abort_flag, &observed)) return true;
-    report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, idx, expected, observed);
+    // One arrival per row: a block is ready when as many rows arrived as it holds.
+    const int want = t.rows_valid * expected;
+    if (flag_wait_ge(flags + idx, want, a.timeout_ns, abort_flag, &observed)) return true;
+    report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, idx, want, observed);
     return false;
   }
 };
@@ -175,7 +179,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 4);
+      mbar_init(&tempty[i], kEpiWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -218,17 +222,25 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
               tma_load_2d(sa, &tma_a, &full[stage], k0, t.row_base + t.m0);
             } else {
               // A stored [K, rows]: 64-row-wide boxes along the M index.
+              if (args.mn3d) {
+                tma_load_3d(sa, &tma_a, &full[stage], 0, k0, (t.row_base + t.m0) / 64);
+              } else {
 #pragma unroll
-              for (int j = 0; j < kBM / 64; ++j)
-                tma_load_2d(sa + j * (64 * kBK * 2), &tma_a, &full[stage],
-                            t.row_base + t.m0 + 64 * j, k0);
+                for (int j = 0; j < kBM / 64; ++j)
+                  tma_load_2d(sa + j * (64 * kBK * 2), &tma_a, &full[stage],
+                              t.row_base + t.m0 + 64 * j, k0);
+              }
             }
           } else {
             // grouped-K: A is [rows_total, M], contraction over rows of the group.
+            if (args.mn3d) {
+              tma_load_3d(sa, &tma_a, &full[stage], 0, t.row_base + k0, t.m0 / 64);
+            } else {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j)
-              tma_load_2d(sa + j * (64 * kBK * 2), &tma_a, &full[stage], t.m0 + 64 * j,
-                          t.row_base + k0);
+              for (int j = 0; j < kBM / 64; ++j)
+                tma_load_2d(sa + j * (64 * kBK * 2), &tma_a, &full[stage], t.m0 + 64 * j,
+                            t.row_base + k0);
+            }
           }
           // ---- B ----
           if (args.mode == 0) {
@@ -247,22 +259,37 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
               }
             } else {
               // B flattened [G * K, Nb]; 64-column boxes.
+              if (args.mn3d) {
+                if (args.gated) {
+                  const int n = t.n_tile * (BN / 2);
+                  tma_load_3d(sb, &tma_b, &full[stage], 0, brow + k0, n / 64);
+                  tma_load_3d(sb + (BN / 2) * kBK * 2, &tma_b, &full[stage], 0, brow + k0,
+                              (args.n_half + n) / 64);
+                } else {
+                  tma_load_3d(sb, &tma_b, &full[stage], 0, brow + k0, t.n_tile * BN / 64);
+                }
+              } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j) {
-                int n;
-                if (args.gated)
-                  n = (j < BN / 128 ? 0 : args.n_half) + t.n_tile * (BN / 2) +
-                      64 * (j % (BN / 128));
-                else
-                  n = t.n_tile * BN + 64 * j;
-                tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, &full[stage], n, brow + k0);
+                for (int j = 0; j < BN / 64; ++j) {
+                  int n;
+                  if (args.gated)
+                    n = (j < BN / 128 ? 0 : args.n_half) + t.n_tile * (BN / 2) +
+                        64 * (j % (BN / 128));
+                  else
+                    n = t.n_tile * BN + 64 * j;
+                  tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, &full[stage], n, brow + k0);
+                }
               }
             }
           } else {
+            if (args.mn3d) {
+              tma_load_3d(sb, &tma_b, &full[stage], 0, t.row_base + k0, t.n_tile * BN / 64);
+            } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, &full[stage], t.n_tile * BN + 64 * j,
-                          t.row_base + k0);
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_2d(sb + j * (64 * kBK * 2), &tma_b, &full[stage], t.n_tile * BN + 64 * j,
+                            t.row_base + k0);
+            }
           }
           if (++stage == kStages) {
             stage = 0;
@@ -327,8 +354,9 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
     }
   } else {
-    // ------------------------------- epilogue (4 warps) -------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    // ------------------------------- epilogue (8 warps) -------------------------------
+    const int q = warp & 3;             // TMEM lane quarter this warp may read
+    const int chalf = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     TileWalker<BN> walker(args);
     Tile t;
     int acc = 0;
@@ -341,7 +369,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      epi.template run<BN>(t, args, taddr, q * 32 + lane, t.nk == 0);
+      epi.template run<BN>(t, args, taddr, q * 32 + lane, t.nk == 0, chalf);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);

@@ -1,10 +1,44 @@
-// C ABI of the element-wise / reduction kernels (see csrc/ops/*.cu).
+// C ABI of the element-wise / reduction kernels (csrc/ops/elementwise.cu) and of the attention
+// kernels (csrc/ops/flash_attn.cu).  Pointers are device pointers; bf16 unless stated.
 #pragma once
 #include <stdint.h>
 #include <cuda_runtime.h>
 #ifdef __cplusplus
 extern "C" {
 #endif
+
+// kind: 0 LayerNorm, 1 RMSNorm.  mean may be null for RMSNorm, b may be null.
+int fm_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                int T, int H, float eps, int kind, cudaStream_t s);
+// Number of CTAs (= rows of the partial buffer [blocks, 2, H] fp32) the backward uses for T rows.
+int fm_norm_bwd_blocks(int T);
+int fm_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                const void* res_grad, void* dx, float* partial, float* dw, float* db, int T, int H,
+                int kind, cudaStream_t s);
+int fm_rope_packed(void* t, const float* freqs, long long rows, int heads_per_row, int rope_heads,
+                   int d, int rot, int rows_per_pos, int backward, cudaStream_t s);
+int fm_topk_softmax(const float* logits, long long* idx, float* probs, int T, int E, int k,
+                    cudaStream_t s);
+int fm_gather_rows(const void* x, const long long* idx, void* out, long long rows, int H,
+                   cudaStream_t s);
+int fm_unpermute_reduce(const void* rows, const int* slot, const void* residual, void* out, int T,
+                        int k, int H, cudaStream_t s);
+// Moments are fp32, or bf16 when state_bf16 != 0.
+int fm_adam(void* p, float* master, float* g, void* m, void* v, long long n, float lr, float beta1,
+            float beta2, float eps, float weight_decay, int step, float grad_scale, int zero_grad,
+            int state_bf16, cudaStream_t s);
+
+// Padded-capacity routing plan (see moe_plan_kernel).  Outputs: sorted_indices [E*cap] int64,
+// slot_probs [E*cap] fp32, slot_of_token [T,k] int32, routed_per_expert [E] int32.
+int fm_moe_plan(const long long* top_idx, const float* top_probs, int T, int k, int E, int cap,
+                long long* sorted_indices, float* slot_probs, int* slot_of_token,
+                int* routed_per_expert, cudaStream_t s);
+
+// Causal GQA flash attention forward on the packed projection buffer
+// qkv [s, b, G, (qpg + 2) * d] (d == 128): out [s, b, G*qpg, d] bf16, lse [b, G*qpg, s] fp32.
+int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg, int d,
+                      float scale, unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

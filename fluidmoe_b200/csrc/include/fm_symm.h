@@ -36,6 +36,12 @@ int fm_a2a_push(const void* send, const long long* send_offs, const long long* s
                 void* const* recv_ptrs, const long long* dst_offs, int* const* flag_ptrs,
                 int* local_counters, int my_rank, int nranks, int epoch, int num_ctas,
                 cudaStream_t stream);
+// Fused permute + dispatch (see permute_dispatch_kernel).  dst_* are device tables indexed by
+// destination rank; probs may be null (then no probabilities are sent).
+int fm_permute_dispatch(const void* x, const long long* sorted_idx, const float* probs,
+                        void* const* dst_tokens, float* const* dst_probs, int* const* dst_flags,
+                        long long total_slots, int H, int cap, int nle, int P, int me,
+                        int blocks_per_group, int num_ctas, cudaStream_t stream);
 // Wait (bounded) until every peer's arrival word in `my_flags` reached `epoch`.
 int fm_a2a_wait(const int* my_flags, int my_rank, int nranks, int epoch,
                 unsigned long long timeout_ns, int* status, cudaStream_t stream);

@@ -1,0 +1,720 @@
+// Memory-bound kernels of the layer: normalisation, rotary embedding, router top-k softmax,
+// token permute / un-permute, and the fused Adam step.  All activations are bf16 with fp32
+// arithmetic; every kernel moves 16 bytes per thread per access and touches each element once
+// where the math allows it.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../include/fm_ops.h"
+#include "../include/sm100_ptx.cuh"
+
+extern "C" void fm_set_error(const char* msg);
+
+namespace fm {
+
+__device__ __forceinline__ void unpack8(const uint4& p, float* v) {
+  const uint32_t w[4] = {p.x, p.y, p.z, p.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+    v[2 * j] = __low2float(b);
+    v[2 * j + 1] = __high2float(b);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float* v) {
+  uint4 p;
+  p.x = pack_bf16x2(v[0], v[1]);
+  p.y = pack_bf16x2(v[2], v[3]);
+  p.z = pack_bf16x2(v[4], v[5]);
+  p.w = pack_bf16x2(v[6], v[7]);
+  return p;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < THREADS / 32; ++i) t += red[i];
+  return t;
+}
+
+// --------------------------------------------------------------------------------------------
+// Normalisation forward.  One CTA per row; the row is cached in shared memory so global memory
+// is read once.  kind: 0 = LayerNorm (mean and rstd saved), 1 = RMSNorm (rstd saved).
+// --------------------------------------------------------------------------------------------
+constexpr int kNormThreads = 256;
+
+__global__ void __launch_bounds__(kNormThreads)
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                const __nv_bfloat16* __restrict__ b, __nv_bfloat16* __restrict__ y,
+                float* __restrict__ mean_out, float* __restrict__ rstd_out, int H, float eps,
+                int kind) {
+  extern __shared__ uint4 row_s[];
+  __shared__ float red[kNormThreads / 32];
+  const long long r = blockIdx.x;
+  const int nvec = H / 8;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + r * H);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += kNormThreads) {
+    const uint4 p = xr[i];
+    row_s[i] = p;
+    float v[8];
+    unpack8(p, v);
+    if (kind == 0) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[j] * v[j];
+    }
+  }
+  s = block_sum<kNormThreads>(s, red);
+  float mean = 0.f, rstd;
+  if (kind == 0) {
+    mean = s / H;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < nvec; i += kNormThreads) {
+      float v[8];
+      unpack8(row_s[i], v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) q += (v[j] - mean) * (v[j] - mean);
+    }
+    q = block_sum<kNormThreads>(q, red);
+    rstd = rsqrtf(q / H + eps);
+  } else {
+    rstd = rsqrtf(s / H + eps);
+  }
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[r] = mean;
+    rstd_out[r] = rstd;
+  }
+  uint4* yr = reinterpret_cast<uint4*>(y + r * H);
+  const uint4* wv = reinterpret_cast<const uint4*>(w);
+  const uint4* bv = reinterpret_cast<const uint4*>(b);
+  for (int i = threadIdx.x; i < nvec; i += kNormThreads) {
+    float v[8], g[8], o[8];
+    unpack8(row_s[i], v);
+    unpack8(wv[i], g);
+    if (b != nullptr) {
+      float bb[8];
+      unpack8(bv[i], bb);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * g[j] + bb[j];
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[j] - mean) * rstd * g[j];
+    }
+    yr[i] = pack8(o);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Normalisation backward.  Each CTA walks rows blockIdx.x, +gridDim.x, ...; a thread owns the
+// same columns in every row, so the weight / bias gradients accumulate in registers and are
+// written once per CTA to a partial buffer [gridDim.x, 2, H] that a second kernel reduces.
+// dx optionally adds the gradient that reaches the input through the residual branch.
+// --------------------------------------------------------------------------------------------
+constexpr int kNormBwdChunks = 4;  // columns per thread = 8 * chunks  ->  H <= 8192
+
+__global__ void __launch_bounds__(kNormThreads)
+norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+                const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean,
+                const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ res_grad,
+                __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int T, int H,
+                int kind) {
+  __shared__ float red[kNormThreads / 32];
+  const int nvec = H / 8;
+  float dg[kNormBwdChunks][8], db[kNormBwdChunks][8], g[kNormBwdChunks][8];
+#pragma unroll
+  for (int c = 0; c < kNormBwdChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < nvec) unpack8(reinterpret_cast<const uint4*>(w)[i], g[c]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dg[c][j] = db[c][j] = 0.f;
+  }
+  for (long long r = blockIdx.x; r < T; r += gridDim.x) {
+    const float mu = kind == 0 ? mean[r] : 0.f;
+    const float rs = rstd[r];
+    float xh[kNormBwdChunks][8], gy[kNormBwdChunks][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < kNormBwdChunks; ++c) {
+      const int i = threadIdx.x + c * kNormThreads;
+      if (i < nvec) {
+        float xv[8], dv[8];
+        unpack8(reinterpret_cast<const uint4*>(x + r * H)[i], xv);
+        unpack8(reinterpret_cast<const uint4*>(dy + r * H)[i], dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[c][j] = (xv[j] - mu) * rs;
+          gy[c][j] = dv[j] * g[c][j];
+          s1 += gy[c][j] * xh[c][j];
+          s2 += gy[c][j];
+          dg[c][j] += dv[j] * xh[c][j];
+          db[c][j] += dv[j];
+        }
+      }
+    }
+    const float c1 = block_sum<kNormThreads>(s1, red) / H;
+    const float c2 = kind == 0 ? block_sum<kNormThreads>(s2, red) / H : 0.f;
+#pragma unroll
+    for (int c = 0; c < kNormBwdChunks; ++c) {
+      const int i = threadIdx.x + c * kNormThreads;
+      if (i < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (gy[c][j] - c2 - xh[c][j] * c1) * rs;
+        if (res_grad != nullptr) {
+          float rg[8];
+          unpack8(reinterpret_cast<const uint4*>(res_grad + r * H)[i], rg);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += rg[j];
+        }
+        reinterpret_cast<uint4*>(dx + r * H)[i] = pack8(o);
+      }
+    }
+  }
+  float* pg = partial + (long long)blockIdx.x * 2 * H;
+#pragma unroll
+  for (int c = 0; c < kNormBwdChunks; ++c) {
+    const int i = threadIdx.x + c * kNormThreads;
+    if (i < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        pg[i * 8 + j] = dg[c][j];
+        pg[H + i * 8 + j] = db[c][j];
+      }
+    }
+  }
+}
+
+__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                                       float* __restrict__ db, int nblocks, int H) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= 2 * H) return;
+  float s = 0.f;
+  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * 2 * H + col];
+  if (col < H)
+    dw[col] = s;
+  else if (db != nullptr)
+    db[col - H] = s;
+}
+
+// --------------------------------------------------------------------------------------------
+// Rotary embedding in place on the packed QKV buffer [rows, heads_per_row, d]: heads
+// 0 .. rope_heads-1 of every row are rotated (the query heads and the key head of a KV group),
+// the rest (the value head) is left alone.  Position of a row = row / rows_per_pos.
+// sign = +1 forward, -1 backward (transposed rotation).
+// --------------------------------------------------------------------------------------------
+__global__ void rope_packed_kernel(__nv_bfloat16* __restrict__ t, const float* __restrict__ freqs,
+                                   long long rows, int heads_per_row, int rope_heads, int d,
+                                   int rot, int rows_per_pos, int backward) {
+  const int half = rot / 2;
+  const int vec_per_head = half / 8;
+  const long long total = rows * rope_heads * vec_per_head;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int vi = (int)(idx % vec_per_head);
+    const long long rh = idx / vec_per_head;
+    const int h = (int)(rh % rope_heads);
+    const long long row = rh / rope_heads;
+    const long long pos = row / rows_per_pos;
+    __nv_bfloat16* base = t + (row * heads_per_row + h) * d;
+    uint4* p1 = reinterpret_cast<uint4*>(base + vi * 8);
+    uint4* p2 = reinterpret_cast<uint4*>(base + half + vi * 8);
+    float a[8], b[8], o1[8], o2[8];
+    unpack8(*p1, a);
+    unpack8(*p2, b);
+    const float* f1 = freqs + pos * rot + vi * 8;
+    const float* f2 = f1 + half;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float s1, c1, s2, c2;
+      sincosf(f1[j], &s1, &c1);
+      sincosf(f2[j], &s2, &c2);
+      if (!backward) {
+        o1[j] = a[j] * c1 - b[j] * s1;
+        o2[j] = b[j] * c2 + a[j] * s2;
+      } else {
+        o1[j] = a[j] * c1 + b[j] * s2;
+        o2[j] = b[j] * c2 - a[j] * s1;
+      }
+    }
+    *p1 = pack8(o1);
+    *p2 = pack8(o2);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Router: top-k over experts then softmax over the k winners (fp32).  One thread per token.
+// Ties go to the lower expert index.
+// --------------------------------------------------------------------------------------------
+__global__ void topk_softmax_kernel(const float* __restrict__ logits, long long* __restrict__ idx_out,
+                                    float* __restrict__ prob_out, int T, int E, int k) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  const float* l = logits + (long long)t * E;
+  float vals[16];
+  int ids[16];
+  for (int j = 0; j < k; ++j) {
+    float best = -INFINITY;
+    int bi = -1;
+    for (int e = 0; e < E; ++e) {
+      const float v = l[e];
+      bool taken = false;
+      for (int q = 0; q < j; ++q) taken |= (ids[q] == e);
+      if (!taken && (v > best || bi < 0)) {
+        best = v;
+        bi = e;
+      }
+    }
+    vals[j] = best;
+    ids[j] = bi;
+  }
+  float m = vals[0], s = 0.f;
+  for (int j = 0; j < k; ++j) s += __expf(vals[j] - m);
+  for (int j = 0; j < k; ++j) {
+    idx_out[(long long)t * k + j] = ids[j];
+    prob_out[(long long)t * k + j] = __expf(vals[j] - m) / s;
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Permute: out[s] = x[idx[s]] (one warp per row, 16-byte accesses).
+// --------------------------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const long long* __restrict__ idx,
+                                   __nv_bfloat16* __restrict__ out, long long rows, int H) {
+  const int nvec = H / 8;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long s = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s < rows;
+       s += (long long)gridDim.x * warps_per_block) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + idx[s] * H);
+    uint4* dst = reinterpret_cast<uint4*>(out + s * H);
+    for (int i = lane; i < nvec; i += 32) dst[i] = src[i];
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Un-permute: out[t] = residual[t] + sum_j rows[slot[t, j]], fp32 accumulation, slots < 0
+// skipped.  Deterministic (a gather, not a scatter-add).
+// --------------------------------------------------------------------------------------------
+__global__ void unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ rows,
+                                        const int* __restrict__ slot,
+                                        const __nv_bfloat16* __restrict__ residual,
+                                        __nv_bfloat16* __restrict__ out, int T, int k, int H) {
+  const int nvec = H / 8;
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (long long t = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); t < T;
+       t += (long long)gridDim.x * warps_per_block) {
+    int sl[16];
+    for (int j = 0; j < k; ++j) sl[j] = slot[t * k + j];
+    for (int i = lane; i < nvec; i += 32) {
+      float acc[8];
+      if (residual != nullptr) {
+        unpack8(reinterpret_cast<const uint4*>(residual + t * H)[i], acc);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] = 0.f;
+      }
+      for (int j = 0; j < k; ++j) {
+        if (sl[j] < 0) continue;
+        float v[8];
+        unpack8(reinterpret_cast<const uint4*>(rows + (long long)sl[j] * H)[i], v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += v[q];
+      }
+      reinterpret_cast<uint4*>(out + t * H)[i] = pack8(acc);
+    }
+  }
+}
+
+// --------------------------------------------------------------------------------------------
+// Fused Adam(W) on a flat slice: fp32 gradient, fp32 moments, bf16 parameter updated in place
+// (optionally through an fp32 master copy).  The gradient may be zeroed in the same pass.
+// --------------------------------------------------------------------------------------------
+template <class ST>
+struct Vec4;
+template <>
+struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <>
+struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x);
+    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+    v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint2 x;
+    x.x = pack_bf16x2(v[0], v[1]);
+    x.y = pack_bf16x2(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = x;
+  }
+};
+
+// n must be a multiple of 4 and all pointers 16-byte aligned (the host falls back to the tail
+// kernel otherwise); every thread handles 4 consecutive elements per iteration with one vector
+// access per array.
+template <class ST>
+__global__ void __launch_bounds__(512)
+adam_kernel(__nv_bfloat16* __restrict__ p, float* __restrict__ master, float* __restrict__ g,
+            ST* __restrict__ m, ST* __restrict__ v, long long n4, float lr, float beta1, float beta2,
+            float eps, float weight_decay, float rbc1, float rbc2, float grad_scale, int zero_grad) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long q = i * 4;
+    float gr[4], w[4], mm[4], vv[4];
+    Vec4<float>::load(g + q, gr);
+    Vec4<ST>::load(m + q, mm);
+    Vec4<ST>::load(v + q, vv);
+    if (master)
+      Vec4<float>::load(master + q, w);
+    else
+      Vec4<__nv_bfloat16>::load(p + q, w);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = gr[j] * grad_scale;
+      mm[j] = beta1 * mm[j] + (1.f - beta1) * gj;
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
+      const float upd = (mm[j] * rbc1) / (sqrtf(vv[j] * rbc2) + eps) + weight_decay * w[j];
+      w[j] -= lr * upd;
+    }
+    Vec4<ST>::store(m + q, mm);
+    Vec4<ST>::store(v + q, vv);
+    if (master) Vec4<float>::store(master + q, w);
+    Vec4<__nv_bfloat16>::store(p + q, w);
+    if (zero_grad) *reinterpret_cast<float4*>(g + q) = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+}
+
+template <class ST>
+__global__ void adam_tail_kernel(__nv_bfloat16* p, float* master, float* g, ST* m, ST* v,
+                                 long long lo, long long n, float lr, float beta1, float beta2,
+                                 float eps, float weight_decay, float rbc1, float rbc2,
+                                 float grad_scale, int zero_grad) {
+  const long long q = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (q >= n) return;
+  const float gj = g[q] * grad_scale;
+  float w = master ? master[q] : __bfloat162float(p[q]);
+  const float mi = beta1 * (float)m[q] + (1.f - beta1) * gj;
+  const float vi = beta2 * (float)v[q] + (1.f - beta2) * gj * gj;
+  m[q] = (ST)mi;
+  v[q] = (ST)vi;
+  w -= lr * ((mi * rbc1) / (sqrtf(vi * rbc2) + eps) + weight_decay * w);
+  if (master) master[q] = w;
+  p[q] = __float2bfloat16(w);
+  if (zero_grad) g[q] = 0.f;
+}
+
+// --------------------------------------------------------------------------------------------
+// Routing plan for fixed (padded) capacity.  One CTA per expert:
+//   1. count the tokens routed to the expert;
+//   2. if there are more than `cap`, find the cap-th largest probability by radix select on the
+//      float bits (probabilities are positive, so the unsigned order is the numeric order) and
+//      keep ties in ascending token order;
+//   3. walk the tokens in order and assign slots: kept tokens, plus the first (cap - kept)
+//      tokens that are NOT routed to this expert as padding (probability 0), all in ascending
+//      token order.
+// Outputs have static shapes; nothing is read back by the host.
+// --------------------------------------------------------------------------------------------
+constexpr int kPlanThreads = 512;
+
+__device__ __forceinline__ int block_excl_scan(int v, int* total, int* smem /* [32] */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  __syncthreads();
+  if (lane == 31) smem[warp] = x;
+  __syncthreads();
+  if (warp == 0) {
+    int w = lane < kPlanThreads / 32 ? smem[lane] : 0;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += y;
+    }
+    smem[lane] = w;  // inclusive warp totals
+  }
+  __syncthreads();
+  const int base = warp == 0 ? 0 : smem[warp - 1];
+  *total = smem[kPlanThreads / 32 - 1];
+  return base + x - v;
+}
+
+__global__ void __launch_bounds__(kPlanThreads)
+moe_plan_kernel(const long long* __restrict__ top_idx, const float* __restrict__ top_probs, int T,
+                int k, int E, int cap, long long* __restrict__ sorted_indices,
+                float* __restrict__ slot_probs, int* __restrict__ slot_of_token,
+                int* __restrict__ routed_per_expert) {
+  __shared__ int hist[256];
+  __shared__ int scan_s[32];
+  __shared__ int sh_count, sh_prefix, sh_quota;
+  const int e = blockIdx.x;
+  const int tid = threadIdx.x;
+
+  auto lookup = [&](int t, int& j_out) -> float {
+    for (int j = 0; j < k; ++j)
+      if ((int)top_idx[(long long)t * k + j] == e) {
+        j_out = j;
+        return top_probs[(long long)t * k + j];
+      }
+    j_out = -1;
+    return 0.f;
+  };
+
+  // ---- 1. count ----
+  if (tid == 0) sh_count = 0;
+  __syncthreads();
+  int local = 0;
+  for (int t = tid; t < T; t += kPlanThreads) {
+    int j;
+    lookup(t, j);
+    local += j >= 0;
+  }
+  atomicAdd(&sh_count, local);
+  __syncthreads();
+  const int count = sh_count;
+  const int kept_total = min(count, cap);
+
+  // ---- 2. threshold by radix select (only when tokens must be dropped) ----
+  uint32_t thr_bits = 0;   // keep prob > thr, plus `quota` tokens with prob == thr
+  int quota = 0;
+  if (count > cap) {
+    uint32_t prefix = 0, mask = 0;
+    int want = cap;  // rank (1-based, from the top) of the threshold element
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int i = tid; i < 256; i += kPlanThreads) hist[i] = 0;
+      __syncthreads();
+      for (int t = tid; t < T; t += kPlanThreads) {
+        int j;
+        const float pr = lookup(t, j);
+        if (j < 0) continue;
+        const uint32_t b = __float_as_uint(pr);
+        if ((b & mask) == prefix) atomicAdd(&hist[(b >> shift) & 255], 1);
+      }
+      __syncthreads();
+      if (tid == 0) {
+        int acc = 0, bin = 255;
+        for (; bin >= 0; --bin) {
+          if (acc + hist[bin] >= want) break;
+          acc += hist[bin];
+        }
+        sh_prefix = bin;
+        sh_quota = want - acc;  // rank of the threshold inside the chosen bin
+      }
+      __syncthreads();
+      prefix |= (uint32_t)sh_prefix << shift;
+      mask |= 255u << shift;
+      want = sh_quota;
+      __syncthreads();
+    }
+    thr_bits = prefix;
+    quota = want;  // number of elements equal to the threshold that are kept
+  }
+
+  // ---- 3. ordered slot assignment ----
+  int ties_seen = 0, sel_seen = 0, nonrouted_seen = 0;
+  const int pad_budget = cap - kept_total;
+  for (int t0 = 0; t0 < T; t0 += kPlanThreads) {
+    const int t = t0 + tid;
+    int j = -1;
+    float pr = 0.f;
+    bool valid = t < T;
+    if (valid) pr = lookup(t, j);
+    const bool routed = valid && j >= 0;
+    const uint32_t b = __float_as_uint(pr);
+    const bool above = routed && (count <= cap || b > thr_bits);
+    const bool tie = routed && count > cap && b == thr_bits;
+    int tot;
+    const int tie_rank = block_excl_scan(tie ? 1 : 0, &tot, scan_s) + ties_seen;
+    ties_seen += tot;
+    const bool kept = above || (tie && tie_rank < quota);
+    const bool nonrouted = valid && !routed;
+    const int nr_rank = block_excl_scan(nonrouted ? 1 : 0, &tot, scan_s) + nonrouted_seen;
+    nonrouted_seen += tot;
+    const bool selected = kept || (nonrouted && nr_rank < pad_budget);
+    const int pos = block_excl_scan(selected ? 1 : 0, &tot, scan_s) + sel_seen;
+    sel_seen += tot;
+    if (selected && pos < cap) {
+      const long long slot = (long long)e * cap + pos;
+      sorted_indices[slot] = t;
+      slot_probs[slot] = kept ? pr : 0.f;
+      if (kept) slot_of_token[(long long)t * k + j] = (int)slot;
+    }
+    if (routed && !kept) slot_of_token[(long long)t * k + j] = -1;
+  }
+  if (tid == 0) routed_per_expert[e] = kept_total;
+}
+
+}  // namespace fm
+
+static int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    char buf[256];
+    snprintf(buf, sizeof(buf), "%s: %s", what, cudaGetErrorString(e));
+    fm_set_error(buf);
+    return (int)e;
+  }
+  return 0;
+}
+static int grid_for(long long work, int per_block, int cap = 148 * 16) {
+  long long g = (work + per_block - 1) / per_block;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  return (int)g;
+}
+
+extern "C" int fm_norm_fwd(const void* x, const void* w, const void* b, void* y, float* mean,
+                           float* rstd, int T, int H, float eps, int kind, cudaStream_t s) {
+  if (H % 8 != 0 || H > 24576) {
+    fm_set_error("norm_fwd: H must be a multiple of 8 and at most 24576");
+    return -1;
+  }
+  using bf = __nv_bfloat16;
+  fm::norm_fwd_kernel<<<T, fm::kNormThreads, (size_t)H * 2, s>>>(
+      (const bf*)x, (const bf*)w, (const bf*)b, (bf*)y, mean, rstd, H, eps, kind);
+  return check_launch("norm_fwd");
+}
+
+extern "C" int fm_norm_bwd_blocks(int T) { return T < 592 ? T : 592; }
+
+extern "C" int fm_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
+                           const float* rstd, const void* res_grad, void* dx, float* partial,
+                           float* dw, float* db, int T, int H, int kind, cudaStream_t s) {
+  if (H % 8 != 0 || H > 8 * fm::kNormBwdChunks * fm::kNormThreads) {
+    fm_set_error("norm_bwd: H must be a multiple of 8 and at most 8192");
+    return -1;
+  }
+  using bf = __nv_bfloat16;
+  const int nb = fm_norm_bwd_blocks(T);
+  fm::norm_bwd_kernel<<<nb, fm::kNormThreads, 0, s>>>((const bf*)dy, (const bf*)x, (const bf*)w,
+                                                     mean, rstd, (const bf*)res_grad, (bf*)dx,
+                                                     partial, T, H, kind);
+  int rc = check_launch("norm_bwd");
+  if (rc) return rc;
+  fm::norm_bwd_reduce_kernel<<<(2 * H + 255) / 256, 256, 0, s>>>(partial, dw, db, nb, H);
+  return check_launch("norm_bwd_reduce");
+}
+
+extern "C" int fm_rope_packed(void* t, const float* freqs, long long rows, int heads_per_row,
+                              int rope_heads, int d, int rot, int rows_per_pos, int backward,
+                              cudaStream_t s) {
+  if (rot % 16 != 0 || d % 8 != 0 || rot > d) {
+    fm_set_error("rope: rot_dim must be a multiple of 16 and at most head_dim");
+    return -1;
+  }
+  const long long total = rows * rope_heads * (rot / 16);
+  fm::rope_packed_kernel<<<grid_for(total, 256), 256, 0, s>>>(
+      (__nv_bfloat16*)t, freqs, rows, heads_per_row, rope_heads, d, rot, rows_per_pos, backward);
+  return check_launch("rope_packed");
+}
+
+extern "C" int fm_topk_softmax(const float* logits, long long* idx, float* probs, int T, int E,
+                               int k, cudaStream_t s) {
+  if (k > 16 || k > E) {
+    fm_set_error("topk_softmax: k must be at most 16 and at most the number of experts");
+    return -1;
+  }
+  fm::topk_softmax_kernel<<<(T + 127) / 128, 128, 0, s>>>(logits, idx, probs, T, E, k);
+  return check_launch("topk_softmax");
+}
+
+extern "C" int fm_gather_rows(const void* x, const long long* idx, void* out, long long rows, int H,
+                              cudaStream_t s) {
+  if (H % 8 != 0) {
+    fm_set_error("gather_rows: H must be a multiple of 8");
+    return -1;
+  }
+  fm::gather_rows_kernel<<<grid_for(rows, 8), 256, 0, s>>>((const __nv_bfloat16*)x, idx,
+                                                          (__nv_bfloat16*)out, rows, H);
+  return check_launch("gather_rows");
+}
+
+extern "C" int fm_unpermute_reduce(const void* rows, const int* slot, const void* residual,
+                                   void* out, int T, int k, int H, cudaStream_t s) {
+  if (H % 8 != 0 || k > 16) {
+    fm_set_error("unpermute_reduce: H must be a multiple of 8 and k at most 16");
+    return -1;
+  }
+  fm::unpermute_reduce_kernel<<<grid_for(T, 8), 256, 0, s>>>(
+      (const __nv_bfloat16*)rows, slot, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, T, k,
+      H);
+  return check_launch("unpermute_reduce");
+}
+
+extern "C" int fm_adam(void* p, float* master, float* g, void* m, void* v, long long n, float lr,
+                       float beta1, float beta2, float eps, float weight_decay, int step,
+                       float grad_scale, int zero_grad, int state_bf16, cudaStream_t s) {
+  const float rbc1 = 1.f / (1.f - powf(beta1, (float)step));
+  const float rbc2 = 1.f / (1.f - powf(beta2, (float)step));
+  using bf = __nv_bfloat16;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p) & 7) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(g) & 15) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(m) & 15) == 0) &&
+                       ((reinterpret_cast<uintptr_t>(v) & 15) == 0) &&
+                       (master == nullptr || (reinterpret_cast<uintptr_t>(master) & 15) == 0);
+  const long long n4 = aligned ? n / 4 : 0;
+  if (n4 > 0) {
+    const int grid = grid_for(n4, 512, 148 * 8);
+    if (state_bf16)
+      fm::adam_kernel<bf><<<grid, 512, 0, s>>>((bf*)p, master, g, (bf*)m, (bf*)v, n4, lr, beta1, beta2,
+                                              eps, weight_decay, rbc1, rbc2, grad_scale, zero_grad);
+    else
+      fm::adam_kernel<float><<<grid, 512, 0, s>>>((bf*)p, master, g, (float*)m, (float*)v, n4, lr,
+                                                 beta1, beta2, eps, weight_decay, rbc1, rbc2,
+                                                 grad_scale, zero_grad);
+    int rc = check_launch("adam");
+    if (rc) return rc;
+  }
+  const long long lo = n4 * 4;
+  if (lo < n) {
+    const int grid = (int)((n - lo + 255) / 256);
+    if (state_bf16)
+      fm::adam_tail_kernel<bf><<<grid, 256, 0, s>>>((bf*)p, master, g, (bf*)m, (bf*)v, lo, n, lr, beta1,
+                                                   beta2, eps, weight_decay, rbc1, rbc2, grad_scale,
+                                                   zero_grad);
+    else
+      fm::adam_tail_kernel<float><<<grid, 256, 0, s>>>((bf*)p, master, g, (float*)m, (float*)v, lo, n,
+                                                      lr, beta1, beta2, eps, weight_decay, rbc1, rbc2,
+                                                      grad_scale, zero_grad);
+    return check_launch("adam_tail");
+  }
+  return 0;
+}
+
+extern "C" int fm_moe_plan(const long long* top_idx, const float* top_probs, int T, int k, int E,
+                           int cap, long long* sorted_indices, float* slot_probs, int* slot_of_token,
+                           int* routed_per_expert, cudaStream_t s) {
+  if (k > 16 || cap > T) {
+    fm_set_error("moe_plan: k must be at most 16 and the capacity at most the number of tokens");
+    return -1;
+  }
+  fm::moe_plan_kernel<<<E, fm::kPlanThreads, 0, s>>>(top_idx, top_probs, T, k, E, cap, sorted_indices,
+                                                    slot_probs, slot_of_token, routed_per_expert);
+  return check_launch("moe_plan");
+}

@@ -1,0 +1,379 @@
+// Causal grouped-query flash attention (forward) on tcgen05 / TMEM, head dim 128.
+//
+// One CTA owns a 128-row query tile of one head.  Warp 0 streams K and V blocks of 128
+// positions through a two-stage shared-memory ring with TMA; warp 1 issues S = Q K^T and
+// O_j = P_j V_j with accumulators in TMEM; warps 2-5 (one thread per query row, which is the
+// natural TMEM layout: no cross-thread reductions) run the online softmax: they read S from
+// TMEM, keep the running max / sum, write P (bf16) into shared memory in the 128-byte-swizzled
+// K-major layout the MMA expects, and fold each finished O_j into a register accumulator with
+// the usual rescale.  Only the log-sum-exp is kept for the backward pass.
+//
+// Q, K and V are read in place from the packed projection buffer
+// [s, b, G, (q_per_group + 2) * d] (query heads, key head, value head of every KV group), so no
+// split / transpose copies are made.  The reference calls PyTorch SDPA or Transformer Engine
+// here (fluid/attention/forward.py:280-329).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+
+#include "../include/fm_ops.h"
+#include "../include/sm100_ptx.cuh"
+
+extern "C" void fm_set_error(const char* msg);
+
+namespace fm {
+
+constexpr int kFaD = 128;
+constexpr int kFaBM = 128;   // query rows per CTA
+constexpr int kFaBN = 128;   // key/value positions per block
+constexpr int kFaThreads = 192;
+constexpr int kKernelIdFlashFwd = 20;
+constexpr int kTileBytes = 128 * 128 * 2;  // one [128, 128] bf16 tile = two 64-wide K blocks
+
+struct FlashFwdArgs {
+  int s, b, G, qpg;
+  float scale_log2;      // softmax scale * log2(e)
+  __nv_bfloat16* out;    // [s, b, G*qpg, d]
+  float* lse;            // [b, G*qpg, s]
+  unsigned long long timeout_ns;
+  int* status;
+};
+
+__global__ void __launch_bounds__(kFaThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + kTileBytes;          // 2 stages
+  uint8_t* sV = smem + 3 * kTileBytes;      // 2 stages
+  uint8_t* sP = smem + 5 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  uint64_t* q_full = bars;            // [1]
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* v_full = bars + 3;        // [2]
+  uint64_t* k_empty = bars + 5;       // [2]
+  uint64_t* v_empty = bars + 7;       // [2]
+  uint64_t* s_full = bars + 9;        // [1]
+  uint64_t* p_full = bars + 10;       // [1]
+  uint64_t* o_full = bars + 11;       // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (a.s + kFaBM - 1) / kFaBM;
+  const int qt = nq - 1 - (int)blockIdx.x;  // longest rows first
+  const int h = blockIdx.y, bb = blockIdx.z;
+  const int g = h / a.qpg, hi = h % a.qpg;
+  const int heads_per_group = a.qpg + 2;
+  const int col_q = ((bb * a.G + g) * heads_per_group + hi) * kFaD;
+  const int col_k = ((bb * a.G + g) * heads_per_group + a.qpg) * kFaD;
+  const int col_v = col_k + kFaD;
+  const int q0 = qt * kFaBM;
+  const int nblocks = min(qt + 1, (a.s + kFaBN - 1) / kFaBN);  // causal: blocks 0 .. qt
+  const uint64_t timeout = a.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s = tmem_base;         // S: columns [0, 128)
+  const uint32_t tmem_o = tmem_base + 128;   // O_j: columns [128, 256)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, kTileBytes);
+      tma_load_2d(sQ, &tmap, q_full, col_q, q0);
+      tma_load_2d(sQ + kTileBytes / 2, &tmap, q_full, col_q + 64, q0);
+      for (int j = 0; j < nblocks; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd, 100 + st, 0, 0);
+          break;
+        }
+        mbar_expect_tx(&k_full[st], kTileBytes);
+        tma_load_2d(sK + st * kTileBytes, &tmap, &k_full[st], col_k, j * kFaBN);
+        tma_load_2d(sK + st * kTileBytes + kTileBytes / 2, &tmap, &k_full[st], col_k + 64, j * kFaBN);
+        if (!mbar_wait(&v_empty[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd, 110 + st, 0, 0);
+          break;
+        }
+        mbar_expect_tx(&v_full[st], kTileBytes);
+        tma_load_2d(sV + st * kTileBytes, &tmap, &v_full[st], col_v, j * kFaBN);
+        tma_load_2d(sV + st * kTileBytes + kTileBytes / 2, &tmap, &v_full[st], col_v + 64, j * kFaBN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
+      const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      bool ok = mbar_wait(q_full, 0, timeout, abort_flag);
+      if (!ok) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd, 200, 0, 0);
+      for (int j = 0; ok && j < nblocks; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        // S_j = Q K_j^T  (the S buffer is free: P_{j-1} was published after S_{j-1} was read)
+        if (!mbar_wait(&k_full[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd, 210 + st, 0, 0);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t k_addr = smem_u32(sK + st * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
+          umma_bf16(tmem_s, umma_smem_desc(q_addr + off, 0, 1024),
+                    umma_smem_desc(k_addr + off, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(s_full);
+        // O_j = P_j V_j once the softmax warps have published P_j
+        if (!mbar_wait(p_full, j & 1, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd, 220, 0, 0);
+          break;
+        }
+        if (!mbar_wait(&v_full[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd, 230 + st, 0, 0);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t v_addr = smem_u32(sV + st * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t poff = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
+          umma_bf16(tmem_o, umma_smem_desc(p_addr + poff, 0, 1024),
+                    umma_smem_desc(v_addr + kk * 2048, kTileBytes / 2, 1024), idesc_pv,
+                    kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&v_empty[st]);
+        umma_commit(o_full);
+      }
+    }
+  } else {
+    // ------------------------------- softmax warps -------------------------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;        // row inside the tile == TMEM lane
+    const int row = q0 + r;             // query position
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    float o_acc[kFaD];
+#pragma unroll
+    for (int i = 0; i < kFaD; ++i) o_acc[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblocks; ++j) {
+      if (!mbar_wait(s_full, j & 1, timeout, abort_flag)) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd, 300, 0, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      if (j > 0) {
+        // fold O_{j-1} (its MMAs were issued before S_j's, so they have completed)
+        if (!mbar_wait(o_full, (j - 1) & 1, timeout, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kFaD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(v[i]);
+        }
+      }
+      const bool diag = (j == qt);
+      const int kv0 = j * kFaBN;
+      // pass 1: row maximum of the scaled scores
+      float m_blk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < kFaBN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = kv0 + c * 32 + i;
+          const bool masked = (diag && col > row) || col >= a.s;
+          const float x = masked ? -INFINITY : __uint_as_float(v[i]) * a.scale_log2;
+          m_blk = fmaxf(m_blk, x);
+        }
+      }
+      const float m_new = fmaxf(m_run, m_blk);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_use);   // exp2(-inf) = 0 on the first block
+      // pass 2: probabilities -> shared memory (bf16, swizzled K-major), row sum
+      float l_blk = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < kFaBN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = kv0 + c * 32 + i;
+          const bool masked = (diag && col > row) || col >= a.s;
+          p[i] = masked ? 0.f : exp2f(__uint_as_float(v[i]) * a.scale_log2 - m_use);
+          l_blk += p[i];
+        }
+        // columns [c*32, c*32+32) of row r: K block kb = c / 2, 16-byte chunks (c & 1) * 4 + 0..3
+        uint8_t* rowp = sP + (c >> 1) * (kTileBytes / 2) + r * 128;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const int chunk = ((c & 1) * 4 + w) ^ (r & 7);
+          uint4 pk;
+          pk.x = pack_bf16x2(p[8 * w + 0], p[8 * w + 1]);
+          pk.y = pack_bf16x2(p[8 * w + 2], p[8 * w + 3]);
+          pk.z = pack_bf16x2(p[8 * w + 4], p[8 * w + 5]);
+          pk.w = pack_bf16x2(p[8 * w + 6], p[8 * w + 7]);
+          *reinterpret_cast<uint4*>(rowp + chunk * 16) = pk;
+        }
+      }
+      l_run = l_run * alpha + l_blk;
+      m_run = m_new;
+#pragma unroll
+      for (int i = 0; i < kFaD; ++i) o_acc[i] *= alpha;
+      // publish P_j: generic-proxy writes -> async proxy, TMEM reads done
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && nblocks > 0) {
+      if (mbar_wait(o_full, (nblocks - 1) & 1, timeout, abort_flag)) {
+        tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < kFaD / 32; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_o + lane_addr + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(v[i]);
+        }
+        if (row < a.s) {
+          const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+          const int hq = a.G * a.qpg;
+          __nv_bfloat16* dst = a.out + (((long long)row * a.b + bb) * hq + h) * kFaD;
+#pragma unroll
+          for (int w = 0; w < kFaD / 8; ++w) {
+            uint4 pk;
+            pk.x = pack_bf16x2(o_acc[8 * w + 0] * inv, o_acc[8 * w + 1] * inv);
+            pk.y = pack_bf16x2(o_acc[8 * w + 2] * inv, o_acc[8 * w + 3] * inv);
+            pk.z = pack_bf16x2(o_acc[8 * w + 4] * inv, o_acc[8 * w + 5] * inv);
+            pk.w = pack_bf16x2(o_acc[8 * w + 6] * inv, o_acc[8 * w + 7] * inv);
+            reinterpret_cast<uint4*>(dst)[w] = pk;
+          }
+          a.lse[((long long)bb * hq + h) * a.s + row] =
+              (m_run + log2f(l_run)) * 0.6931471805599453f;
+        }
+      }
+    }
+    tc_fence_before_sync();
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+}  // namespace fm
+
+typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg,
+                                 int d, float scale, unsigned long long timeout_ns, int* status,
+                                 cudaStream_t stream) {
+  if (d != fm::kFaD) {
+    fm_set_error("flash_attn_fwd: head_dim must be 128");
+    return -1;
+  }
+  static EncodeTiledFn2 enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      fm_set_error("cuTensorMapEncodeTiled unavailable");
+      return -2;
+    }
+    enc = reinterpret_cast<EncodeTiledFn2>(p);
+  }
+  const long long cols = (long long)b * G * (qpg + 2) * d;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15) != 0) {
+    fm_set_error("flash_attn_fwd: qkv must be 16-byte aligned");
+    return -1;
+  }
+  CUtensorMap tmap;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)s};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&tmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(qkv), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fm_set_error("flash_attn_fwd: cuTensorMapEncodeTiled failed");
+    return -3;
+  }
+  constexpr int smem = 6 * fm::kTileBytes + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(fm::flash_fwd_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      fm_set_error(cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = true;
+  }
+  fm::FlashFwdArgs a;
+  a.s = s; a.b = b; a.G = G; a.qpg = qpg;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.out = reinterpret_cast<__nv_bfloat16*>(out);
+  a.lse = lse;
+  a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
+  a.status = status;
+  dim3 grid((s + fm::kFaBM - 1) / fm::kFaBM, G * qpg, b);
+  fm::flash_fwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tmap, a);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    fm_set_error(cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}

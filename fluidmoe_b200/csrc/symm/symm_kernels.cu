@@ -74,6 +74,50 @@ __global__ void put_signal_kernel(const uint4* src, long long nvec, uint4* dst, 
   }
 }
 
+// Fused permute + dispatch: slot s of the sender's permuted order (global-expert-major,
+// `cap` slots per expert, `nle` experts per rank) is the row x[sorted_idx[s]].  It is stored
+// straight into the destination rank's expert-major buffer at row (j * P + me) * cap + i, its
+// routing probability into the matching fp32 slot, and the destination's arrival counter of the
+// 128-row block that contains the row is bumped with a system-scope release.  One warp moves one
+// row with 16-byte accesses.  Takes the place of the permute + dispatch all-to-all rounds of
+// fluid/moe/forward.py:446-461,623-733 (and, with probs == nullptr, of the combine-gradient
+// all-to-all of fluid/moe/backward.py:758-801).
+__global__ void permute_dispatch_kernel(const __nv_bfloat16* __restrict__ x,
+                                        const long long* __restrict__ sorted_idx,
+                                        const float* __restrict__ probs,
+                                        __nv_bfloat16* const* __restrict__ dst_tokens,
+                                        float* const* __restrict__ dst_probs,
+                                        int* const* __restrict__ dst_flags, long long total_slots,
+                                        int H, int cap, int nle, int P, int me,
+                                        int blocks_per_group) {
+  const int nvec = H / 8;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const long long S = (long long)nle * cap;
+  for (long long s = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s < total_slots;
+       s += (long long)gridDim.x * warps_per_block) {
+    // Visit destinations starting from my right-hand neighbour (the local copy comes last).
+    const long long dst_rank_seq = s / S;
+    const int p = (int)((me + 1 + dst_rank_seq) % P);
+    const long long within = s % S;
+    const int j = (int)(within / cap);
+    const int i = (int)(within % cap);
+    const long long src_slot = (long long)p * S + within;
+    const long long tok = sorted_idx[src_slot];
+    const long long row_in_group = (long long)me * cap + i;
+    const long long drow = (long long)j * P * cap + row_in_group;
+    const uint4* src = reinterpret_cast<const uint4*>(x + tok * H);
+    uint4* dst = reinterpret_cast<uint4*>(dst_tokens[p] + drow * H);
+    for (int v = lane; v < nvec; v += 32) dst[v] = src[v];
+    if (lane == 0 && probs != nullptr) dst_probs[p][drow] = probs[src_slot];
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_system();
+      flag_release_add(dst_flags[p] + j * blocks_per_group + (int)(row_in_group / 128), 1);
+    }
+  }
+}
+
 __global__ void a2a_wait_kernel(const int* my_flags, int my_rank, int nranks, int epoch,
                                 unsigned long long timeout_ns, int* status) {
   const int p = threadIdx.x;
@@ -252,6 +296,23 @@ extern "C" int fm_put_signal(const void* src, long long bytes, void* dst, int* f
                                                       bytes / 16, reinterpret_cast<uint4*>(dst),
                                                       flag, value, local_counter);
   return launch_check("put_signal");
+}
+
+extern "C" int fm_permute_dispatch(const void* x, const long long* sorted_idx, const float* probs,
+                                   void* const* dst_tokens, float* const* dst_probs,
+                                   int* const* dst_flags, long long total_slots, int H, int cap,
+                                   int nle, int P, int me, int blocks_per_group, int num_ctas,
+                                   cudaStream_t stream) {
+  if (H % 8 != 0) {
+    fm_set_error("permute_dispatch: H must be a multiple of 8");
+    return -1;
+  }
+  if (num_ctas <= 0) num_ctas = 148 * 2;
+  fm::permute_dispatch_kernel<<<num_ctas, 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), sorted_idx, probs,
+      reinterpret_cast<__nv_bfloat16* const*>(dst_tokens), dst_probs, dst_flags, total_slots, H, cap,
+      nle, P, me, blocks_per_group);
+  return launch_check("permute_dispatch");
 }
 
 extern "C" int fm_a2a_wait(const int* my_flags, int my_rank, int nranks, int epoch,

@@ -50,6 +50,15 @@ void bind_symm(py::module_& m) {
                     as_ptr<int*>(counters), rank, n, epoch, ctas, as_ptr<cudaStream_t>(stream)),
         "a2a_push");
   });
+  m.def("permute_dispatch", [](uintptr_t x, uintptr_t idx, uintptr_t probs, uintptr_t dst_tokens,
+                               uintptr_t dst_probs, uintptr_t dst_flags, long long total, int H, int cap,
+                               int nle, int P, int me, int bpg, int ctas, uintptr_t stream) {
+    chk(fm_permute_dispatch(as_ptr<const void*>(x), as_ptr<const long long*>(idx),
+                            as_ptr<const float*>(probs), as_ptr<void* const*>(dst_tokens),
+                            as_ptr<float* const*>(dst_probs), as_ptr<int* const*>(dst_flags), total, H,
+                            cap, nle, P, me, bpg, ctas, as_ptr<cudaStream_t>(stream)),
+        "permute_dispatch");
+  });
   m.def("a2a_wait", [](uintptr_t flags, int rank, int n, int epoch, unsigned long long timeout_ns,
                        uintptr_t status, uintptr_t stream) {
     chk(fm_a2a_wait(as_ptr<const int*>(flags), rank, n, epoch, timeout_ns, as_ptr<int*>(status),

@@ -48,6 +48,7 @@ class CPPlan:
         self.attn_per_rank = self.heads_per_rank * head_dim           # attention-output columns
         self.dtype, self.device = dtype, device
         self.overlap_ctx = overlap_ctx
+        self.layer_id = 0
         if overlap_ctx is not None and P > 1:
             self.partners = overlap_ctx.partners_in_order(self.cp_rank)
         else:
@@ -63,11 +64,11 @@ class CPPlan:
 
 
 def split_qkv(qkv_full: torch.Tensor, plan: CPPlan):
-    """``[s, b, G, gs] -> q [s,b,G*qpg,d], k [s,b,G,d], v [s,b,G,d]`` (views)."""
+    """``[s, b, G, gs] -> q [s,b,G*qpg,d] (a copy when G > 1), k [s,b,G,d], v [s,b,G,d]`` (views)."""
     s, b = qkv_full.shape[0], qkv_full.shape[1]
     G, qpg, d = plan.groups_per_rank, plan.q_per_group, plan.head_dim
     h = qkv_full.view(s, b, G, qpg + 2, d)
-    return h[:, :, :, :qpg].reshape(s, b, G * qpg, d) if False else h[:, :, :, :qpg], h[:, :, :, qpg], h[:, :, :, qpg + 1]
+    return h[:, :, :, :qpg].reshape(s, b, G * qpg, d), h[:, :, :, qpg], h[:, :, :, qpg + 1]
 
 
 # ============================================================================================
@@ -100,7 +101,8 @@ def qkv_projection_forward(x: torch.Tensor, qkv_weight: torch.Tensor, plan: CPPl
     backend = get_p2p_backend()
     cur = current_stream(dev)
     prof = get_overhead_profiler()
-    qkv_full = torch.empty(P * sl, b, ppr, dtype=dt, device=dev)
+    qkv_full = backend.alloc_recv_buffer(f"attn_qkv_L{plan.layer_id}", P * sl * b * ppr, dt, dev,
+                                         group=plan.group).view(P * sl, b, ppr)
     t0 = sched.begin_fwd_comm(comm_stream) if ctx is not None else None
     last_ev = None
     for rnd, q in enumerate(plan.partners):
@@ -177,7 +179,8 @@ def output_projection_forward(attn_out: torch.Tensor, proj_weight: torch.Tensor,
     for rnd, q in enumerate(plan.partners):
         tok = prof.enter("overhead.fwd_tournament_round")
         ev = ctx.get_round_event("attn_output", rnd) if ctx is not None else None
-        recv = torch.empty(sl, b, dpr, dtype=dt, device=dev)
+        recv = backend.alloc_recv_buffer(f"attn_out_L{plan.layer_id}_r{rnd}", sl * b * dpr, dt, dev,
+                                         group=plan.group).view(sl, b, dpr)
         backend.exchange(src[q].contiguous(), recv, plan.global_ranks[q], q, plan.group, comm_stream, ev)
         events.append(ev)
         staged.append((q, recv))
@@ -338,3 +341,17 @@ def output_projection_register_dw(layer_id: int, attn_input_full: torch.Tensor, 
                                   proj_param) -> None:
     """``dWproj = dOut^T @ attn_input_full`` (fluid/attention/backward.py:425-468)."""
     _register_dense_dw("attn.proj", layer_id, attn_input_full, d_out, proj_param)
+
+
+def scaled_dot_product_attention_forward(q, k, v, scale=None, is_causal=True, enable_gqa=False):
+    """``[b, h, s, d]`` inputs (the layout of the reference helper, fluid/attention/forward.py:280-329);
+    returns ``[b, hq, s, d]``."""
+    from ..ops import attention as attn_ops
+    out, _ = attn_ops.attention_fwd(q.permute(2, 0, 1, 3), k.permute(2, 0, 1, 3), v.permute(2, 0, 1, 3),
+                                    scale, is_causal)
+    return out.permute(1, 2, 0, 3)
+
+
+# names used by the reference for the same entry points
+qkv_projection_p2p_forward = qkv_projection_forward
+output_projection_p2p_forward = output_projection_forward

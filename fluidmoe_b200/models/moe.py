@@ -84,6 +84,7 @@ class EPPlan:
         self.expert_ids_gpu = torch.arange(num_experts, device=dev).repeat_interleave(cap)
         self.tokens_per_expert_gpu = torch.full((num_experts,), cap, dtype=torch.int32, device=dev)
         self.overlap_ctx = overlap_ctx
+        self.layer_id = 0
         if overlap_ctx is not None and P > 1:
             self.partners = overlap_ctx.partners_in_order(self.ep_rank)
         else:
@@ -214,8 +215,9 @@ def dispatch_fc1_forward(plan: EPPlan, permuted_tokens: torch.Tensor, permuted_p
     backend = get_p2p_backend()
     ctx = plan.overlap_ctx
     comm_stream = ctx.comm_stream if ctx is not None else None
-    tokens_em = torch.empty(R, H, dtype=dt, device=dev)
-    probs_em = torch.empty(R, dtype=torch.float32, device=dev)
+    tag = f"L{plan.layer_id}"
+    tokens_em = backend.alloc_recv_buffer(f"moe_tokens_{tag}", R * H, dt, dev, group=plan.group).view(R, H)
+    probs_em = backend.alloc_recv_buffer(f"moe_probs_{tag}", R, torch.float32, dev, group=plan.group)
     act = torch.empty(R, F, dtype=dt, device=dev)
     pre = torch.empty(R, Fw, dtype=dt, device=dev) if save_pre else None
     me = plan.ep_rank
@@ -295,7 +297,8 @@ def fc2_combine_forward(plan: EPPlan, state: MoEForwardState, w2: torch.Tensor, 
     me = plan.ep_rank
     out_em = torch.empty(plan.rows_local, H, dtype=dt, device=dev)
     o4 = out_em.view(nle, P, cap, H)
-    combined = torch.empty(P * plan.S, H, dtype=dt, device=dev)
+    combined = backend.alloc_recv_buffer(f"moe_combined_L{plan.layer_id}", P * plan.S * H, dt, dev,
+                                         group=plan.group).view(P * plan.S, H)
     c4 = combined.view(P, nle, cap, H)
     cur = current_stream(dev)
     prof = get_overhead_profiler()
@@ -723,3 +726,45 @@ def pad_moe_dispatch(tokens: torch.Tensor, tokens_per_expert: torch.Tensor, capa
     if probs is None:
         return out, valid.reshape(-1)
     return out, probs.index_select(0, src.reshape(-1)) * valid.reshape(-1).to(probs.dtype), valid.reshape(-1)
+
+
+# ============================================================================================
+# router backward (functional form of the code used inside the layer)
+# ============================================================================================
+def router_backward(grad_permuted_probs: torch.Tensor, plan_or_sorted_indices, top_indices: torch.Tensor,
+                    top_probs: torch.Tensor, router_logits: torch.Tensor, router_weight: torch.Tensor,
+                    num_experts: int, aux_loss_coeff: float = 0.0, z_loss_coeff: float = 0.0,
+                    cp_group=None, out_dtype: Optional[torch.dtype] = None):
+    """Gradient of the router: returns ``(d_hidden [T, H], d_logits [T, E] fp32)``.
+
+    ``grad_permuted_probs`` is the gradient of every slot's probability in permuted order;
+    ``plan_or_sorted_indices`` is the :class:`RoutingPlan` of the forward pass.  The load-balancing
+    loss uses the per-expert token counts summed over the sequence-parallel group
+    (fluid/moe/backward.py:1419-1532)."""
+    rplan = plan_or_sorted_indices
+    T = top_indices.shape[0]
+    tpe = None
+    world = comm.group_size(cp_group) if cp_group is not None else 1
+    if aux_loss_coeff > 0.0:
+        tpe = rplan.routed_per_expert.float()
+        if world > 1:
+            dist.all_reduce(tpe, group=cp_group)
+    dlogits = router_ops.router_backward_logits(grad_permuted_probs, rplan, top_indices, top_probs,
+                                                router_logits, num_experts, aux_loss_coeff, z_loss_coeff,
+                                                tpe, T * world)
+    w = router_weight.detach()
+    dx = dlogits.to(w.dtype) @ w.t()
+    return (dx.to(out_dtype) if out_dtype is not None else dx), dlogits
+
+
+def register_router_dw_task(layer_id: int, hidden_states: torch.Tensor, d_logits: torch.Tensor,
+                            router_weight_param, layer_name: str = "router") -> None:
+    """Queue ``dWr = hidden^T @ dLogits`` (fluid/moe/backward.py:1535-1578)."""
+    sched = get_backward_scheduler()
+    sched.register_dw_task(layer_name, layer_id,
+                           lambda: hidden_states.float().t() @ d_logits.float(), router_weight_param)
+
+
+# names used by the reference for the same entry points
+dispatch_fc1_p2p_forward = dispatch_fc1_forward
+fc2_combine_p2p_forward = fc2_combine_forward

@@ -66,6 +66,7 @@ class LayerRuntime:
                                       L.capacity_factor, x.dtype, x.device, L.moe_overlap_ctx)
         self.cp_plan = attn_mod.CPPlan(s_loc, b, H, L.num_heads, L.num_kv_heads, L.head_dim,
                                        L.cp_group, x.dtype, x.device, L.attn_overlap_ctx)
+        self.ep_plan.layer_id = self.cp_plan.layer_id = L.layer_id
         L._moe_chunk_config = moe_mod.build_moe_chunk_config(
             L.moe_combine_chunks, L.moe_dispatch_chunks, self.ep_plan.num_local_experts,
             self.ep_plan.expert_capacity)
@@ -89,7 +90,7 @@ class TransformerLayerFunction(torch.autograd.Function):
         x2 = x.reshape(T, H)
         needs_grad = any(ctx.needs_input_grad)
         act = L.activation
-        mode_attn = L.resolve_mode(cp.cp_size)
+        mode_attn = L.resolve_mode(cp.cp_size, attention=True)
         mode_moe = L.resolve_mode(ep.ep_size)
         fused = L.fused_ctx
 
@@ -100,14 +101,9 @@ class TransformerLayerFunction(torch.autograd.Function):
             qkv_full = attn_mod.qkv_projection_forward(ln1_out, qkv_w, cp, mode_attn, fused)
         if rotary is not None:
             rope.rope_packed_(qkv_full, rotary, cp.q_per_group, cp.head_dim)
-        s_full = qkv_full.shape[0]
         G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
-        heads = qkv_full.view(s_full, b, G, qpg + 2, d)
-        q = heads[:, :, :, :qpg].reshape(s_full, b, G * qpg, d)
-        k = heads[:, :, :, qpg]
-        v = heads[:, :, :, qpg + 1]
         with nvtx_range("attention"):
-            attn_out, lse = attn_ops.attention_fwd(q, k, v, 1.0 / math.sqrt(d), True)
+            attn_out, lse = attn_ops.attention_fwd_packed(qkv_full, qpg, d, 1.0 / math.sqrt(d))
         with nvtx_range("hp2sp_outproj"):
             h1, attn_in_full = attn_mod.output_projection_forward(attn_out, proj_w, cp, mode_attn, fused,
                                                                   residual=x2)
@@ -387,13 +383,16 @@ class TransformerLayer(nn.Module):
                 nn.init.normal_(self.shared_w2, mean=0.0, std=self.output_init_std)
 
     # ------------------------------------------------------------------ helpers
-    def resolve_mode(self, group_world: int) -> str:
+    def resolve_mode(self, group_world: int, attention: bool = False) -> str:
         if group_world == 1:
             return "a2a"
+        fused_ok = self.fused_ctx is not None and (not attention or self.fused_ctx.supports_attention)
         if self.comm_mode == "auto":
-            return "fused" if self.fused_ctx is not None else "p2p"
-        if self.comm_mode == "fused" and self.fused_ctx is None:
-            raise RuntimeError("comm_mode='fused' needs a parallel context with a symmetric heap")
+            return "fused" if fused_ok else "p2p"
+        if self.comm_mode == "fused":
+            if self.fused_ctx is None:
+                raise RuntimeError("comm_mode='fused' needs a parallel context with a symmetric heap")
+            return "fused" if fused_ok else "p2p"
         return self.comm_mode
 
     def attach_fused(self, fused_ctx) -> None:

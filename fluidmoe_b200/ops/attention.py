@@ -22,9 +22,6 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: floa
     with out ``[s, b, hq, d]`` and lse ``[b, hq, s]`` fp32."""
     s, b, hq, d = q.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
-    if _native.use_native(q, k, v) and hasattr(_native.lib(), "flash_attn_fwd"):
-        from . import flash
-        return flash.flash_attn_fwd(q, k, v, scale, causal)
     if q.is_cuda:
         return _sdpa_fwd(q, k, v, scale, causal)
     hkv = k.shape[2]
@@ -76,7 +73,21 @@ def attention_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch
     return to(dq, q), to(dk, k), to(dv, v)
 
 
-# ---- library attention, used on CUDA until this library's own kernel is present ----
+def attention_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float = None):
+    """Causal GQA attention on the packed projection buffer ``[s, b, G, (qpg + 2) * d]``.
+    Returns ``(out [s, b, G*qpg, d], lse or None)``."""
+    import os
+    from . import flash
+    s, b, G, gs = qkv.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    if flash.supported(qkv, head_dim) and os.environ.get("FLUIDMOE_ATTN", "native") == "native":
+        return flash.flash_attn_fwd_packed(qkv, q_per_group, head_dim, scale)
+    heads = qkv.view(s, b, G, q_per_group + 2, head_dim)
+    q = heads[:, :, :, :q_per_group].reshape(s, b, G * q_per_group, head_dim)
+    return attention_fwd(q, heads[:, :, :, q_per_group], heads[:, :, :, q_per_group + 1], scale, True)
+
+
+# ---- library attention, used on CUDA where this library's own kernel does not apply ----
 def _sdpa_fwd(q, k, v, scale, causal):
     import torch.nn.functional as F
     hq, hkv = q.shape[2], k.shape[2]

@@ -1,0 +1,125 @@
+"""Front-ends of the memory-bound CUDA kernels (bf16 activations).  Callers reach these through
+``ops.norm`` / ``ops.rope`` / ``ops.router`` / ``ops.permute`` / ``ops.optim``, which fall back to
+PyTorch for CPU tensors and for dtypes the kernels do not cover."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native
+
+LAUNCHES = 0
+
+
+def _s() -> int:
+    global LAUNCHES
+    LAUNCHES += 1
+    return _native.stream_ptr()
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _bf16(*ts) -> bool:
+    return all(t is None or t.dtype == torch.bfloat16 for t in ts)
+
+
+def norm_fwd(x, weight, bias, eps, kind):
+    if not _bf16(x, weight, bias) or x.shape[-1] % 8 or not x.is_contiguous():
+        return None
+    T, H = x.shape
+    y = torch.empty_like(x)
+    ln = kind == "layernorm"
+    mean = torch.empty(T, dtype=torch.float32, device=x.device) if ln else None
+    rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    _native.lib().norm_fwd(x.data_ptr(), weight.data_ptr(), _ptr(bias), y.data_ptr(), _ptr(mean),
+                           rstd.data_ptr(), T, H, float(eps), 0 if ln else 1, _s())
+    return y, mean, rstd
+
+
+def norm_bwd(dy, x, weight, mean, rstd, kind, has_bias, residual_grad):
+    if not _bf16(dy, x, weight, residual_grad) or x.shape[-1] % 8 or x.shape[-1] > 8192:
+        return None
+    T, H = x.shape
+    lib = _native.lib()
+    dy = dy.contiguous()
+    dx = torch.empty_like(x)
+    nb = lib.norm_bwd_blocks(T)
+    partial = torch.empty(nb, 2, H, dtype=torch.float32, device=x.device)
+    dw = torch.empty(H, dtype=torch.float32, device=x.device)
+    db = torch.empty(H, dtype=torch.float32, device=x.device) if has_bias else None
+    ln = kind == "layernorm"
+    lib.norm_bwd(dy.data_ptr(), x.data_ptr(), weight.data_ptr(), _ptr(mean) if ln else 0, rstd.data_ptr(),
+                 _ptr(residual_grad.contiguous() if residual_grad is not None else None), dx.data_ptr(),
+                 partial.data_ptr(), dw.data_ptr(), _ptr(db), T, H, 0 if ln else 1, _s())
+    return dx, dw, db
+
+
+def rope_packed_(qkv, freqs, q_per_group, head_dim, backward):
+    s, b, G, gs = qkv.shape
+    rot = freqs.shape[-1]
+    if qkv.dtype != torch.bfloat16 or rot % 16 or not qkv.is_contiguous():
+        return None
+    f = freqs.reshape(-1, rot).to(torch.float32).contiguous()
+    assert f.shape[0] >= s
+    _native.lib().rope_packed(qkv.data_ptr(), f.data_ptr(), s * b * G, q_per_group + 2, q_per_group + 1,
+                              head_dim, rot, b * G, int(backward), _s())
+    return qkv
+
+
+def topk_softmax(logits, top_k):
+    T, E = logits.shape
+    logits = logits.contiguous()
+    idx = torch.empty(T, top_k, dtype=torch.int64, device=logits.device)
+    probs = torch.empty(T, top_k, dtype=torch.float32, device=logits.device)
+    _native.lib().topk_softmax(logits.data_ptr(), idx.data_ptr(), probs.data_ptr(), T, E, top_k, _s())
+    return idx, probs
+
+
+def gather_rows(x, idx, out=None):
+    if x.dtype != torch.bfloat16 or x.shape[1] % 8 or not x.is_contiguous():
+        return None
+    idx = idx.to(torch.int64).contiguous()
+    if out is None:
+        out = torch.empty(idx.numel(), x.shape[1], dtype=x.dtype, device=x.device)
+    _native.lib().gather_rows(x.data_ptr(), idx.data_ptr(), out.data_ptr(), idx.numel(), x.shape[1], _s())
+    return out
+
+
+def unpermute_reduce(rows, slot_of_token, residual=None):
+    if rows.dtype != torch.bfloat16 or rows.shape[1] % 8 or not rows.is_contiguous() or slot_of_token.shape[1] > 16:
+        return None
+    T, k = slot_of_token.shape
+    H = rows.shape[1]
+    slot = slot_of_token.to(torch.int32).contiguous()
+    if residual is not None:
+        residual = residual.contiguous()
+        assert residual.dtype == torch.bfloat16
+    out = torch.empty(T, H, dtype=rows.dtype, device=rows.device)
+    _native.lib().unpermute_reduce(rows.data_ptr(), slot.data_ptr(), _ptr(residual), out.data_ptr(), T, k, H, _s())
+    return out
+
+
+def adam_step(p, master, g, m, v, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0, zero_grad=False):
+    assert p.dtype == torch.bfloat16 and g.dtype == torch.float32 and m.dtype == v.dtype
+    _native.lib().adam(p.data_ptr(), _ptr(master), g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(),
+                       float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step),
+                       float(grad_scale), int(zero_grad), int(m.dtype == torch.bfloat16), _s())
+
+
+def moe_plan(top_idx, top_probs, num_experts, capacity):
+    """Padded-capacity routing plan on the device (one CTA per expert, no sort, no host sync)."""
+    T, k = top_idx.shape
+    dev = top_idx.device
+    top_idx = top_idx.contiguous()
+    top_probs = top_probs.float().contiguous()
+    sorted_indices = torch.empty(num_experts * capacity, dtype=torch.int64, device=dev)
+    slot_probs = torch.empty(num_experts * capacity, dtype=torch.float32, device=dev)
+    slot_of_token = torch.empty(T, k, dtype=torch.int32, device=dev)
+    routed = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    _native.lib().moe_plan(top_idx.data_ptr(), top_probs.data_ptr(), T, k, num_experts, capacity,
+                           sorted_indices.data_ptr(), slot_probs.data_ptr(), slot_of_token.data_ptr(),
+                           routed.data_ptr(), _s())
+    return sorted_indices, slot_probs, slot_of_token, routed

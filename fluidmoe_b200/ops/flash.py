@@ -1,0 +1,28 @@
+"""Front-end of the tcgen05 flash-attention kernel (packed QKV layout, head dim 128)."""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from .gemm import status_buffer
+
+LAUNCHES = 0
+
+
+def supported(qkv: torch.Tensor, head_dim: int) -> bool:
+    return (qkv.is_cuda and qkv.dtype == torch.bfloat16 and head_dim == 128 and qkv.is_contiguous()
+            and _native.available() and hasattr(_native.lib(), "flash_attn_fwd"))
+
+
+def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float):
+    """qkv: [s, b, G, (qpg + 2) * d] -> (out [s, b, G*qpg, d], lse [b, G*qpg, s])."""
+    global LAUNCHES
+    s, b, G, gs = qkv.shape
+    hq = G * q_per_group
+    out = torch.empty(s, b, hq, head_dim, dtype=qkv.dtype, device=qkv.device)
+    lse = torch.empty(b, hq, s, dtype=torch.float32, device=qkv.device)
+    LAUNCHES += 1
+    _native.lib().flash_attn_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), s, b, G, q_per_group,
+                                 head_dim, float(scale), 0, status_buffer(qkv.device).data_ptr(),
+                                 _native.stream_ptr())
+    return out, lse

@@ -291,7 +291,7 @@ def grouped_gemm_dact(
     nt = (F + bn - 1) // bn
     alloc = torch.zeros if group_rows is not None else torch.empty
     dpre = dpre_out if dpre_out is not None else alloc(pre.shape, dtype=pre.dtype, device=pre.device)
-    partial = torch.zeros(rows, nt, dtype=torch.float32, device=dy.device)
+    partial = torch.zeros(rows, nt * 2, dtype=torch.float32, device=dy.device)
     wflat = w2.reshape(G * F, H)
     ap, ai, ao, lda = _operand(dy)
     bp, bi, bo, ldb = _operand(wflat)
@@ -310,7 +310,7 @@ def grouped_gemm_dact(
     if gate:
         desc.update(gate)
     _launch(desc)
-    dprobs = partial.sum(dim=1) if nt > 1 else partial.view(-1)
+    dprobs = partial.sum(dim=1)
     if dprobs_out is not None:
         # rows outside the groups touched by this call keep their previous value
         if group_rows is None and uniform_rows * G == rows:

@@ -18,7 +18,9 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]
     """x: [T, H].  Returns ``(y, mean or None, rstd)``; kind is ``layernorm`` or ``rmsnorm``."""
     if _native.use_native(x) and hasattr(_native.lib(), "norm_fwd"):
         from . import elementwise
-        return elementwise.norm_fwd(x, weight, bias, eps, kind)
+        res = elementwise.norm_fwd(x, weight, bias, eps, kind)
+        if res is not None:
+            return res
     xf = x.float()
     if kind == "layernorm":
         mean = xf.mean(-1)
@@ -39,7 +41,9 @@ def norm_bwd(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, mean: Opti
     """Returns ``(dx (+ residual_grad), dweight fp32, dbias fp32 or None)``."""
     if _native.use_native(dy, x) and hasattr(_native.lib(), "norm_bwd"):
         from . import elementwise
-        return elementwise.norm_bwd(dy, x, weight, mean, rstd, kind, has_bias, residual_grad)
+        res = elementwise.norm_bwd(dy, x, weight, mean, rstd, kind, has_bias, residual_grad)
+        if res is not None:
+            return res
     dyf, xf, w = dy.float(), x.float(), weight.float()
     r = rstd.unsqueeze(-1)
     if kind == "layernorm":

@@ -1,0 +1,86 @@
+"""Fused Adam(W) over flat gradient buffers.
+
+The scheduler accumulates gradients in flat fp32 buffers (``param.main_grad``), so the optimizer
+walks those buffers directly: one kernel per parameter, bf16 parameter updated in place, fp32
+moments (and an optional fp32 master copy).  CPU tensors take a PyTorch path with the same math.
+"""
+from __future__ import annotations
+
+from typing import Iterable, List, Optional
+
+import torch
+
+from .. import _native
+
+
+class FusedAdam:
+    def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999),
+                 eps: float = 1e-8, weight_decay: float = 0.0, master_weights: bool = False,
+                 state_dtype: torch.dtype = torch.float32):
+        self.params: List[torch.nn.Parameter] = [p for p in params if p.requires_grad]
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.step_count = 0
+        self.state = {}
+        self.master_weights = master_weights
+        self.state_dtype = state_dtype   # fp32, or bf16 moments as torch.optim.AdamW keeps for bf16 parameters
+        self.param_groups = [dict(params=self.params, lr=lr)]
+
+    def _state(self, p):
+        st = self.state.get(id(p))
+        if st is None:
+            st = dict(m=torch.zeros(p.shape, dtype=self.state_dtype, device=p.device),
+                      v=torch.zeros(p.shape, dtype=self.state_dtype, device=p.device),
+                      master=p.detach().float().clone() if self.master_weights else None)
+            self.state[id(p)] = st
+        return st
+
+    @staticmethod
+    def _grad_of(p) -> Optional[torch.Tensor]:
+        g = getattr(p, "main_grad", None)
+        if g is not None and getattr(p, "_ar_buf_written", True):
+            return g
+        return p.grad
+
+    @torch.no_grad()
+    def step(self, grad_scale: float = 1.0) -> None:
+        self.step_count += 1
+        b1, b2 = self.betas
+        for p in self.params:
+            g = self._grad_of(p)
+            if g is None:
+                continue
+            st = self._state(p)
+            if p.is_cuda and p.dtype == torch.bfloat16 and g.dtype == torch.float32 and _native.available() \
+                    and p.is_contiguous() and g.is_contiguous():
+                from . import elementwise
+                elementwise.adam_step(p.data, st["master"], g, st["m"], st["v"], self.lr, b1, b2, self.eps,
+                                      self.weight_decay, self.step_count, grad_scale)
+                continue
+            gf = g.float() * grad_scale
+            w = st["master"] if st["master"] is not None else p.data.float()
+            m32 = st["m"].float().mul_(b1).add_(gf, alpha=1 - b1)
+            v32 = st["v"].float().mul_(b2).addcmul_(gf, gf, value=1 - b2)
+            st["m"].copy_(m32)
+            st["v"].copy_(v32)
+            bc1, bc2 = 1 - b1 ** self.step_count, 1 - b2 ** self.step_count
+            upd = (m32 / bc1) / ((v32 / bc2).sqrt() + self.eps) + self.weight_decay * w
+            w = w - self.lr * upd
+            if st["master"] is not None:
+                st["master"].copy_(w)
+            p.data.copy_(w.to(p.dtype))
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for p in self.params:
+            p.grad = None
+            if hasattr(p, "_ar_buf_written"):
+                p._ar_buf_written = False
+
+    def state_dict(self):
+        return dict(step=self.step_count, state={i: {k: v for k, v in self.state.get(id(p), {}).items()}
+                                                 for i, p in enumerate(self.params)})
+
+    def load_state_dict(self, sd) -> None:
+        self.step_count = sd["step"]
+        for i, p in enumerate(self.params):
+            if i in sd["state"] and sd["state"][i]:
+                self.state[id(p)] = sd["state"][i]

@@ -18,7 +18,9 @@ def permute_rows(x: torch.Tensor, sorted_indices: torch.Tensor, out: Optional[to
     """``out[s] = x[sorted_indices[s]]``."""
     if _native.use_native(x) and hasattr(_native.lib(), "gather_rows"):
         from . import elementwise
-        return elementwise.gather_rows(x, sorted_indices, out)
+        res = elementwise.gather_rows(x, sorted_indices, out)
+        if res is not None:
+            return res
     res = x.index_select(0, sorted_indices.long())
     if out is not None:
         out.copy_(res)
@@ -31,7 +33,9 @@ def unpermute_reduce(rows: torch.Tensor, slot_of_token: torch.Tensor,
     """``out[t] = residual[t] + sum_j rows[slot_of_token[t, j]]`` (slots < 0 are skipped)."""
     if _native.use_native(rows) and hasattr(_native.lib(), "unpermute_reduce"):
         from . import elementwise
-        return elementwise.unpermute_reduce(rows, slot_of_token, residual)
+        res = elementwise.unpermute_reduce(rows, slot_of_token, residual)
+        if res is not None:
+            return res
     T, k = slot_of_token.shape
     idx = slot_of_token.long()
     gathered = rows[idx.clamp(min=0)].float()                      # [T, k, H]

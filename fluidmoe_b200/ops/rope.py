@@ -54,7 +54,9 @@ def rope_packed_(qkv: torch.Tensor, freqs: torch.Tensor, q_per_group: int, head_
     s, b, G, gs = qkv.shape
     if _native.use_native(qkv) and hasattr(_native.lib(), "rope_packed"):
         from . import elementwise
-        return elementwise.rope_packed_(qkv, freqs, q_per_group, head_dim, backward)
+        res = elementwise.rope_packed_(qkv, freqs, q_per_group, head_dim, backward)
+        if res is not None:
+            return res
     heads = qkv.view(s, b, G, q_per_group + 2, head_dim)
     part = heads[..., : q_per_group + 1, :].reshape(s, b, G * (q_per_group + 1), head_dim)
     fn = apply_rope_bwd if backward else apply_rope

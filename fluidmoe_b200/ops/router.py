@@ -25,7 +25,7 @@ class RoutingPlan:
     slot_of_token: torch.Tensor      # [T, k] int32: slot of the j-th choice of token t, -1 = dropped
     tokens_per_expert: torch.Tensor  # [E] int32 (== cap in padded mode)
     routed_per_expert: torch.Tensor  # [E] int32 routed (non-padding) tokens after dropping
-    routing_map: torch.Tensor        # [T, E] bool after capacity dropping
+    routing_map: Optional[torch.Tensor]  # [T, E] bool after capacity dropping (None on the CUDA path)
     capacity: int
 
 
@@ -64,6 +64,11 @@ def build_padded_plan(top_idx: torch.Tensor, top_probs: torch.Tensor, num_expert
     E = num_experts
     dev = top_idx.device
     assert capacity <= T, "capacity larger than the number of tokens is not supported"
+    if _native.use_native(top_idx, top_probs) and k <= 16:
+        from . import elementwise
+        si, sp, sot, routed = elementwise.moe_plan(top_idx, top_probs, E, capacity)
+        tpe = torch.full((E,), capacity, dtype=torch.int32, device=dev)
+        return RoutingPlan(si, sp, sot, tpe, routed, None, capacity)
     probs = torch.zeros(T, E, dtype=torch.float32, device=dev).scatter(1, top_idx, top_probs.float())
     rmap = torch.zeros(T, E, dtype=torch.bool, device=dev).scatter(1, top_idx, True)
     if capacity < T:

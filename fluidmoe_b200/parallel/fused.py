@@ -1,0 +1,197 @@
+"""Device-initiated expert-parallel exchange fused with the expert GEMMs.
+
+For one expert-parallel group this context owns a symmetric heap and, per layer, the buffers the
+peers write into:
+
+* ``tokens_em`` / ``probs_em``: expert-major receive buffers of the dispatch.  The sender's
+  permute kernel stores every routed row straight into the destination GPU's buffer and bumps the
+  arrival counter of the row's 128-row block; the receiver's grouped FC1 GEMM (tcgen05) waits on
+  that counter before its producer warp loads the block, so the first tiles start as soon as the
+  local rows are in place and peer rows are consumed as they land.
+* ``combined``: permuted-order buffer on the token owner.  The FC2 GEMM epilogue converts each
+  accumulator row to bf16 and stores it into the owner's buffer over NVLink; per-source counters
+  tell the owner when all rows of a source are in, then a gather-sum restores token order.
+* the same two mechanisms, with the roles swapped, carry the backward pass (combine gradient in,
+  dispatch gradient out).
+
+Every wait is bounded and reports through the status word; counters are reset by their consumer
+after use and a kernel-side barrier at the end of each iteration keeps iterations apart.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import _native
+from ..ops import gemm, permute
+from ..ops.gemm import status_buffer
+from .symm import SymmetricHeap, SymmTensor
+
+LAUNCHES = 0
+EPI_SPLIT = 2   # epilogue warps per accumulator row (each reports its half of the columns)
+
+
+def _count(n=1):
+    global LAUNCHES
+    LAUNCHES += n
+
+
+class _LayerBuffers:
+    def __init__(self, heap: SymmetricHeap, plan, dtype, ffn_cols: int):
+        R, H = plan.rows_local, plan.hidden_size
+        P, nle, cap = plan.ep_size, plan.num_local_experts, plan.expert_capacity
+        self.bpg = (P * cap + 127) // 128                      # 128-row blocks per local expert
+        nblk = nle * self.bpg
+        dev = heap.device
+        self.tokens_em = heap.alloc((R, H), dtype, zero=False)
+        self.probs_em = heap.alloc((R,), torch.float32)
+        self.flags_fwd = heap.alloc((nblk,), torch.int32)
+        self.dfc2_em = heap.alloc((R, H), dtype, zero=False)
+        self.flags_bwd = heap.alloc((nblk,), torch.int32)
+        self.combined = heap.alloc((P * plan.S, H), dtype, zero=False)
+        self.cnt_combine = heap.alloc((P,), torch.int32)
+        self.dperm = heap.alloc((P * plan.S, H), dtype, zero=False)
+        self.cnt_dperm = heap.alloc((P,), torch.int32)
+        me = heap.rank
+        # entry p = address of rank p's counter for rows coming from this rank
+        self.cnt_combine_tbl = torch.tensor([a + 4 * me for a in self.cnt_combine.peer_addrs],
+                                            dtype=torch.int64, device=dev)
+        self.cnt_dperm_tbl = torch.tensor([a + 4 * me for a in self.cnt_dperm.peer_addrs],
+                                          dtype=torch.int64, device=dev)
+
+
+class FusedCommContext:
+    supports_attention = False   # the Ulysses exchanges use the pairwise path for now
+
+    def __init__(self, group, heap_bytes: int, device, timeout_ms: float = 8000.0):
+        self.group = group
+        self.device = torch.device(device)
+        self.heap = SymmetricHeap(group, heap_bytes, self.device)
+        self.rank, self.world = self.heap.rank, self.heap.world
+        self.timeout_ns = int(timeout_ms * 1e6)
+        self._layers: Dict[int, _LayerBuffers] = {}
+        self._sig: Dict[int, tuple] = {}
+
+    # ------------------------------------------------------------------ set-up
+    def prepare(self, ep_plan, cp_plan, layer) -> None:
+        lid = layer.layer_id
+        sig = ep_plan.signature()
+        if self._sig.get(lid) == sig:
+            return
+        if lid in self._layers:
+            raise RuntimeError("input shape changed after symmetric buffers were allocated; "
+                               "create a new parallel context for a new shape")
+        self._sig[lid] = sig
+        self._layers[lid] = _LayerBuffers(self.heap, ep_plan, ep_plan.dtype, layer.ffn_hidden_size)
+        ep_plan._fused_layer = lid
+        # every rank must finish allocating (and zeroing counters) before anyone pushes
+        torch.cuda.synchronize(self.device)
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group=self.group)
+
+    def _buf(self, plan) -> _LayerBuffers:
+        return self._layers[plan._fused_layer]
+
+    def iteration_barrier(self) -> None:
+        """Kernel-side barrier over the group; call once per iteration after the backward pass."""
+        _count()
+        self.heap.barrier(self.timeout_ns / 1e6)
+
+    # ------------------------------------------------------------------ primitives
+    def _push(self, plan, x, sorted_indices, probs, dst_tokens: SymmTensor, dst_probs: Optional[SymmTensor],
+              flags: SymmTensor, bpg: int) -> None:
+        _count()
+        _native.lib().permute_dispatch(
+            x.data_ptr(), sorted_indices.data_ptr(), probs.data_ptr() if probs is not None else 0,
+            dst_tokens.ptr_table, dst_probs.ptr_table if dst_probs is not None else 0, flags.ptr_table,
+            plan.num_experts * plan.expert_capacity, plan.hidden_size, plan.expert_capacity,
+            plan.num_local_experts, plan.ep_size, plan.ep_rank, bpg, 0, _native.stream_ptr())
+
+    def _gate(self, flags: SymmTensor, bpg: int) -> dict:
+        return dict(gate_flags=flags.local.data_ptr(), gate_blocks_per_group=bpg, gate_expected=1,
+                    timeout_ns=self.timeout_ns)
+
+    def _scatter_gemm(self, plan, a, w, b_layout, dst: SymmTensor, cnt_tbl: torch.Tensor) -> None:
+        """Grouped GEMM over the expert-major rows whose epilogue stores each result row into the
+        owner's buffer (``plan.combine_dst_rank`` / ``combine_dst_row``)."""
+        _count()
+        G = w.shape[0]
+        K = a.shape[1]
+        N = w.shape[2] if b_layout == "kn" else w.shape[1]
+        b2 = w.reshape(-1, w.shape[2])
+        ap, ai, ao, lda = gemm._operand(a)
+        bp, bi, bo, ldb = gemm._operand(b2)
+        lib = _native.lib()
+        desc = dict(
+            A=ap, a_inner=ai, a_outer=ao, lda=lda, a_mn=0,
+            B=bp, b_inner=bi, b_outer=bo, ldb=ldb, b_mn=1 if b_layout == "kn" else 0,
+            mode=0, num_groups=G, M=a.shape[0], N=N, K=K, b_group_stride=w.shape[1],
+            uniform_rows=plan.ep_size * plan.expert_capacity, bn=256 if N > 128 else 128,
+            epi=lib.EPI_SCATTER, dst_base=dst.ptr_table, dst_rank=plan.combine_dst_rank.data_ptr(),
+            dst_row=plan.combine_dst_row.data_ptr(), ld_dst=plan.hidden_size,
+            dst_flags=cnt_tbl.data_ptr(), num_ranks=plan.ep_size,
+            timeout_ns=self.timeout_ns, status=status_buffer(a.device).data_ptr())
+        gemm.LAUNCHES += 0
+        lib.gemm_launch(desc, _native.stream_ptr())
+
+    def _wait_counters(self, cnt: SymmTensor, expected: int) -> None:
+        _count()
+        _native.lib().a2a_wait(cnt.local.data_ptr(), self.rank, self.world, expected, self.timeout_ns,
+                               status_buffer(self.device).data_ptr(), _native.stream_ptr())
+
+    @staticmethod
+    def _n_tiles(n: int) -> int:
+        bn = 256 if n > 128 else 128
+        return (n + bn - 1) // bn
+
+    # ------------------------------------------------------------------ forward
+    def dispatch_fc1(self, plan, hidden_states, sorted_indices, probs32, w1, activation, save_pre):
+        from ..models.moe import MoEForwardState
+        b = self._buf(plan)
+        self._push(plan, hidden_states, sorted_indices, probs32, b.tokens_em, b.probs_em, b.flags_fwd, b.bpg)
+        act, pre = gemm.grouped_gemm_act(b.tokens_em.local, w1, b.probs_em.local, activation=activation,
+                                         uniform_rows=plan.ep_size * plan.expert_capacity,
+                                         save_pre=save_pre, gate=self._gate(b.flags_fwd, b.bpg))
+        b.flags_fwd.local.zero_()
+        return MoEForwardState(b.tokens_em.local, b.probs_em.local, pre, act)
+
+    def fc2_combine(self, plan, state, w2):
+        b = self._buf(plan)
+        self._scatter_gemm(plan, state.act_em, w2, "kn", b.combined, b.cnt_combine_tbl)
+        return b.combined.local
+
+    def unpermute(self, plan, rows, slot_of_token, residual):
+        """Wait until every source's rows are in ``rows`` (the combine or dispatch-gradient buffer
+        of this layer), then gather-sum them into token order."""
+        b = self._buf(plan)
+        cnt = b.cnt_combine if rows.data_ptr() == b.combined.local.data_ptr() else b.cnt_dperm
+        self._wait_counters(cnt, plan.S * self._n_tiles(plan.hidden_size) * EPI_SPLIT)
+        out = permute.unpermute_reduce(rows, slot_of_token, residual)
+        cnt.local.zero_()
+        return out
+
+    # ------------------------------------------------------------------ backward
+    def combine_fc2_backward(self, plan, dy2, rplan, state, w2, activation):
+        from .scheduler import get_backward_scheduler
+        b = self._buf(plan)
+        sched = get_backward_scheduler()
+        self._push(plan, dy2, rplan.sorted_indices, None, b.dfc2_em, None, b.flags_bwd, b.bpg)
+        if sched.is_enabled():
+            sched.execute_dw_tasks(max_defer_tasks=2)
+        dpre, dprobs = gemm.grouped_gemm_dact(b.dfc2_em.local, w2, state.pre_em, state.probs_em,
+                                              activation=activation,
+                                              uniform_rows=plan.ep_size * plan.expert_capacity,
+                                              gate=self._gate(b.flags_bwd, b.bpg))
+        b.flags_bwd.local.zero_()
+        return b.dfc2_em.local, dpre, dprobs
+
+    def fc1_dispatch_backward(self, plan, dpre_em, w1):
+        from .scheduler import get_backward_scheduler
+        b = self._buf(plan)
+        self._scatter_gemm(plan, dpre_em, w1, "nk", b.dperm, b.cnt_dperm_tbl)
+        sched = get_backward_scheduler()
+        if sched.is_enabled():
+            sched.execute_dw_tasks(max_defer_tasks=2)
+        return b.dperm.local

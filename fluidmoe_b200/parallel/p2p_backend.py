@@ -79,7 +79,7 @@ class CollectiveP2PBackend(P2PBackend):
         if event is not None:
             event.record(comm_stream) if comm_stream is not None else event.record()
 
-    def alloc_recv_buffer(self, tag, numel, dtype, device):
+    def alloc_recv_buffer(self, tag, numel, dtype, device, group=None):
         device = torch.device(device)
         key = (tag, dtype, device.type, device.index)
         buf = self._bufs.get(key)
@@ -137,17 +137,25 @@ class SymmetricP2PBackend(P2PBackend):
         if cur is None or cur.local.numel() < numel:
             cur = st["heap"].alloc((max(numel, 8),), dtype, zero=False)
             self._bufs[key] = cur
-        t = cur.local[:numel]
-        t._fm_symm = cur  # the exchange needs the peers' addresses of this buffer
-        return t
+        return cur.local[:numel]
+
+    def _locate(self, t: torch.Tensor):
+        """Find the symmetric allocation that contains ``t`` and ``t``'s byte offset inside it."""
+        addr = t.data_ptr()
+        for cur in self._bufs.values():
+            lo = cur.local.data_ptr()
+            if lo <= addr < lo + cur.local.numel() * cur.local.element_size():
+                return cur, addr - lo
+        return None, 0
 
     def exchange(self, send_buf, recv_buf, partner_global_rank, partner_local_rank, group,
                  comm_stream, event):
         if send_buf is None or recv_buf is None:
             raise ValueError("SymmetricP2PBackend.exchange needs both a send and a receive buffer")
-        symm = getattr(recv_buf, "_fm_symm", None) or getattr(recv_buf._base, "_fm_symm", None)
+        symm, offset = self._locate(recv_buf)
         if symm is None:
             raise ValueError("receive buffer was not allocated by alloc_recv_buffer()")
+        assert recv_buf.is_contiguous() and send_buf.is_contiguous()
         st = self._state(group, recv_buf.device)
         heap = st["heap"]
         P, me, q = heap.world, heap.rank, partner_local_rank
@@ -159,19 +167,19 @@ class SymmetricP2PBackend(P2PBackend):
         with on_stream(comm_stream):
             s = torch.cuda.current_stream().cuda_stream
             send_buf.record_stream(torch.cuda.current_stream())
-            self._push_one(lib, st, send_buf, None, symm, q, epoch, s)
+            self._push_one(lib, st, send_buf, offset, symm, q, epoch, s)
             lib.wait_flag(st["flags"].local.data_ptr() + 4 * q, epoch, int(4e9),
                           _status(recv_buf.device), s)
             if event is not None:
                 event.record(torch.cuda.current_stream())
 
-    def _push_one(self, lib, st, send_buf, send_bytes_dev, symm, q, epoch, stream):
+    def _push_one(self, lib, st, send_buf, offset, symm, q, epoch, stream):
         heap = st["heap"]
         P = heap.world
         # Per-partner flag pointer table: entry p points at rank p's word for *me*; the kernel
         # indexes it as flag_ptrs[p] + my_rank.
         lib.put_signal(send_buf.data_ptr(), send_buf.numel() * send_buf.element_size(),
-                       symm.peer_addrs[q], st["flags"].peer_addrs[q] + 4 * heap.rank, epoch, 16,
+                       symm.peer_addrs[q] + offset, st["flags"].peer_addrs[q] + 4 * heap.rank, epoch, 16,
                        st["counters"].data_ptr() + 4 * q, stream)
 
     def needs_final_wait(self) -> bool:
@@ -220,14 +228,10 @@ def get_p2p_backend() -> P2PBackend:
         elif choice == "nccl" or choice == "gloo":
             _BACKEND = CollectiveP2PBackend()
         else:
-            if _has_peer_access() and _native.available():
-                try:
-                    _BACKEND = SymmetricP2PBackend()
-                except Exception as e:  # noqa: BLE001
-                    warnings.warn(f"symmetric-memory back-end unavailable ({e}); using collectives")
-                    _BACKEND = CollectiveP2PBackend()
-            else:
-                _BACKEND = CollectiveP2PBackend()
+            # auto: the round-ordered pairwise path runs on library point-to-point (NCCL / gloo).
+            # Device-initiated transfers are the business of the fused paths
+            # (parallel/fused.py); the symmetric pairwise back-end is opt-in.
+            _BACKEND = CollectiveP2PBackend()
         return _BACKEND
 
 

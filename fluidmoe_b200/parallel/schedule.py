@@ -63,7 +63,7 @@ class MultiCardOverlapContext:
         self.schedule = compute_round_robin_schedule(ep_size)
         self.num_rounds = len(self.schedule)
         self._partners = partner_table(ep_size)
-        self._sm = get_stream_manager()
+        self._sm = get_stream_manager(self.device)
         self._sm.initialize(self.device)
         self._cache: Dict[Tuple[int, int], int] = {}
 

@@ -264,7 +264,7 @@ class BackwardScheduler:
         if device is None:
             device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() \
                 else torch.device("cpu")
-        sm = get_stream_manager()
+        sm = get_stream_manager(device)
         if not sm.initialized:
             sm.initialize(device)
         self._device = sm.device
@@ -275,12 +275,12 @@ class BackwardScheduler:
     @property
     def comm_stream(self):
         self._ensure_device()
-        return get_stream_manager().comm_stream
+        return get_stream_manager(self._device).comm_stream
 
     @property
     def dw_stream(self):
         self._ensure_device()
-        return get_stream_manager().dw_stream
+        return get_stream_manager(self._device).dw_stream
 
     # ------------------------------------------------------------------ configuration
     def enable(self, device=None) -> None:
@@ -497,7 +497,7 @@ class BackwardScheduler:
         tok = get_overhead_profiler().enter("overhead.bwd_submit_a2a")
         tid = self._next_task_id
         self._next_task_id += 1
-        sm = get_stream_manager()
+        sm = get_stream_manager(self._device)
         start = sm.get_sync_event(("a2a", 2 * (tid % 4096)), enable_timing=False)
         comm = self.comm_stream
         start.record(current_stream(self._device))

@@ -151,8 +151,18 @@ class StreamManager:
             self.data_ready_event = None
 
 
-_MANAGER = StreamManager()
+# One manager per device type: a process drives one GPU, but CPU-resident models (tests, the
+# gloo path) may live beside it and must not share its streams.
+_MANAGERS = {"cpu": StreamManager(), "cuda": StreamManager()}
 
 
-def get_stream_manager() -> StreamManager:
-    return _MANAGER
+def get_stream_manager(device=None) -> StreamManager:
+    """Manager for ``device`` (by type).  Without a device: the CUDA manager once it is bound,
+    else the CPU manager once it is bound, else the one matching the machine."""
+    if device is not None:
+        return _MANAGERS[torch.device(device).type if torch.device(device).type == "cuda" else "cpu"]
+    if _MANAGERS["cuda"].initialized:
+        return _MANAGERS["cuda"]
+    if _MANAGERS["cpu"].initialized:
+        return _MANAGERS["cpu"]
+    return _MANAGERS["cuda" if torch.cuda.is_available() else "cpu"]

@@ -74,6 +74,7 @@ class SymmetricHeap:
                         self._peer_bases[r] = lib.symm_open(h)
         self._slab = tensor_from_ptr(self._base, self.nbytes, self.device, owner=self)
         self._cursor = 0
+        self._high_water = 0     # the slab is zero-filled at creation; bytes above this mark are still zero
         self._closed = False
         self._barrier_flags = self.alloc((max(self.world, 1),), torch.int32)
         self._barrier_epoch = 0
@@ -92,8 +93,11 @@ class SymmetricHeap:
                 f"symmetric heap exhausted: need {end - start} more bytes, {self.nbytes - start} left")
         self._cursor = end
         local = self._slab[start:start + nbytes].view(dtype).view(*shape)
-        if zero:
+        if zero and start < self._high_water:
+            # Re-used region: clear it.  Peers may only write here after the next collective
+            # synchronisation of the group (callers that hand the buffer to peers do that).
             local.zero_()
+        self._high_water = max(self._high_water, end)
         addrs = [b + start for b in self._peer_bases]
         table = torch.tensor(addrs, dtype=torch.int64, device=self.device)
         return SymmTensor(local, start, addrs, table)
@@ -118,6 +122,13 @@ class SymmetricHeap:
         _native.lib().symm_barrier(
             self._barrier_flags.ptr_table, self.rank, self.world, self._barrier_epoch,
             int(timeout_ms * 1e6), status_buffer(self.device).data_ptr(), _native.stream_ptr())
+
+    def sync_group(self) -> None:
+        """Host-side rendezvous: every rank has finished its allocations (and clears) before any
+        rank lets a kernel write into a peer."""
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
 
     def close(self) -> None:
         if self._closed:
@@ -156,6 +167,7 @@ class SymmAllToAll:
         dev = heap.device
         self._dst_offs = torch.full((P,), heap.rank * self.cap, dtype=torch.int64, device=dev)
         self._cache: Dict[int, tuple] = {}
+        heap.sync_group()
 
     def __call__(self, x: torch.Tensor, timeout_ms: float = 4000.0) -> torch.Tensor:
         P, heap = self.P, self.heap
@@ -194,6 +206,7 @@ class SymmAllReduce:
         self.flags = heap.alloc((heap.world + 2,), torch.int32)
         self.epoch = 0
         self.num_ctas = num_ctas  # fixed for the life of the object (grid-wide hand-off counts CTAs)
+        heap.sync_group()
 
     def __call__(self, numel: Optional[int] = None, scale: float = 1.0, timeout_ms: float = 4000.0) -> torch.Tensor:
         heap = self.heap

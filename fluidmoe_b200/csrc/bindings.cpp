@@ -54,6 +54,7 @@ static void gemm_launch(const py::dict& d, uintptr_t stream) {
   g.n_half = get<int>(d, "n_half", 0);
   g.bn = get<int>(d, "bn", 256);
   g.swizzle_m = get<int>(d, "swizzle_m", 0);
+  g.cta_pair = get<int>(d, "cta_pair", 0);
   g.epi = get<int>(d, "epi", 0);
   g.C = ptr<void*>(d, "C");
   g.ldc = get<long long>(d, "ldc", 0);

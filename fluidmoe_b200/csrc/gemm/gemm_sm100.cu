@@ -430,11 +430,64 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmAr
   return 0;
 }
 
+template <bool A_MN, bool B_MN, class Epi, class Gate>
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+                       const Epi& epi, const Gate& gate, int grid, cudaStream_t stream) {
+  auto kern = gemm2_sm100_kernel<A_MN, B_MN, Epi, Gate>;
+  constexpr int smem = gemm2_smem_bytes();
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      set_err(cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = true;
+  }
+  // The kernel is persistent: never launch more pairs than can be resident at once (pairs must
+  // sit on two SMs of one GPC, so this can be fewer than SMs / 2).
+  static int max_pairs = 0;
+  if (max_pairs == 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sm_count() & ~1);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      (void)cudaGetLastError();
+      n = sm_count() / 2 - 2;
+    }
+    max_pairs = n;
+  }
+  grid &= ~1;   // whole CTA pairs
+  if (grid > 2 * max_pairs) grid = 2 * max_pairs;
+  if (grid < 2) grid = 2;
+  kern<<<grid, kGemmThreads, smem, stream>>>(ta, tb, args, epi, gate);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_err(cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
 template <class Epi, class Gate>
 static int dispatch_shape(const FmGemmDesc* d, const CUtensorMap& ta, const CUtensorMap& tb,
                           const GemmArgs& args, const Epi& epi, const Gate& gate, int grid,
                           cudaStream_t s) {
   const bool amn = d->a_mn != 0, bmn = d->b_mn != 0;
+  if (d->cta_pair && d->bn == 256) {
+    if (!amn && !bmn) return launch_pair<false, false>(ta, tb, args, epi, gate, grid, s);
+    if (!amn && bmn) return launch_pair<false, true>(ta, tb, args, epi, gate, grid, s);
+    if (amn && bmn) return launch_pair<true, true>(ta, tb, args, epi, gate, grid, s);
+  }
   if (d->bn == 256) {
     if (!amn && !bmn) return launch_one<false, false, 256>(ta, tb, args, epi, gate, grid, s);
     if (!amn && bmn) return launch_one<false, true, 256>(ta, tb, args, epi, gate, grid, s);
@@ -497,6 +550,11 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   const bool mn3d = (!d->a_mn || a3) && (!d->b_mn || b3) && (d->a_mn || d->b_mn) &&
                     ((uintptr_t)d->A % 16 == 0) && ((uintptr_t)d->B % 16 == 0) && d->lda % 8 == 0 &&
                     d->ldb % 8 == 0;
+  // The CTA-pair kernel fetches MN-major operands only through 3-D boxes.
+  FmGemmDesc dd = *d;
+  if (dd.cta_pair && (dd.bn != 256 || ((dd.a_mn || dd.b_mn) && !mn3d) || (dd.mode == 0 && dd.a_mn)))
+    dd.cta_pair = 0;
+  d = &dd;
   // A: K-major -> box {64 k, 128 rows}; MN-major -> box {64 rows, 64 k}
   if (d->a_mn && mn3d) {
     if (!make_tmap_mn3d(&ta, d->A, d->a_inner, d->a_outer, d->lda, kBM / 64)) return -3;
@@ -505,7 +563,8 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   }
   // B: K-major -> box {64 k, 128 n}; MN-major -> box {64 n, 64 k}
   if (d->b_mn && mn3d) {
-    if (!make_tmap_mn3d(&tb, d->B, d->b_inner, d->b_outer, d->ldb, d->gated ? d->bn / 128 : d->bn / 64))
+    if (!make_tmap_mn3d(&tb, d->B, d->b_inner, d->b_outer, d->ldb,
+                        (d->gated || d->cta_pair) ? d->bn / 128 : d->bn / 64))
       return -3;
   } else if (!make_tmap(&tb, d->B, d->b_inner, d->b_outer, d->ldb, d->b_mn ? 64 : 128)) {
     return -3;
@@ -536,8 +595,9 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   if (d->group_rows == nullptr) {
     const int npt = d->gated ? d->bn / 2 : d->bn;
     const long long nt = (d->N + npt - 1) / npt;
-    const long long mt = d->mode == 0 ? (d->uniform_rows + kBM - 1) / kBM : (d->M + kBM - 1) / kBM;
-    const long long tiles = nt * mt * d->num_groups;
+    const int tm = d->cta_pair ? 2 * kBM : kBM;
+    const long long mt = d->mode == 0 ? (d->uniform_rows + tm - 1) / tm : (d->M + tm - 1) / tm;
+    const long long tiles = nt * mt * d->num_groups * (d->cta_pair ? 2 : 1);
     if (tiles < grid) grid = (int)(tiles > 0 ? tiles : 1);
   }
 

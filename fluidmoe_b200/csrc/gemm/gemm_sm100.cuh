@@ -59,7 +59,7 @@ struct Tile {
   int rows_g;      // rows in the group
 };
 
-template <int BN>
+template <int BN, int TM = kBM>
 struct TileWalker {
   const GemmArgs& a;
   int g = 0;
@@ -68,7 +68,7 @@ struct TileWalker {
   __device__ TileWalker(const GemmArgs& args) : a(args) {
     const int n_per_tile = a.gated ? BN / 2 : BN;
     nt = (a.N + n_per_tile - 1) / n_per_tile;
-    mt_fixed = (a.M + kBM - 1) / kBM;
+    mt_fixed = (a.M + TM - 1) / TM;
   }
   __device__ __forceinline__ int rows_of(int gi) const {
     return a.group_rows ? a.group_rows[gi] : a.uniform_rows;
@@ -77,7 +77,7 @@ struct TileWalker {
     return a.group_offs ? a.group_offs[gi] : gi * a.uniform_rows;
   }
   __device__ __forceinline__ int mtiles_of(int gi) const {
-    return a.mode == 0 ? (rows_of(gi) + kBM - 1) / kBM : mt_fixed;
+    return a.mode == 0 ? (rows_of(gi) + TM - 1) / TM : mt_fixed;
   }
   // t must not decrease between calls.
   __device__ bool get(int t, Tile& out) {
@@ -95,14 +95,14 @@ struct TileWalker {
         const int m_tile = first_m + in_super % gsz;
         out.n_tile = in_super / gsz;
         out.g = g;
-        out.m0 = m_tile * kBM;
+        out.m0 = m_tile * TM;
         out.rows_g = rows_of(g);
         out.row_base = off_of(g);
         if (a.mode == 0) {
-          out.rows_valid = min(kBM, out.rows_g - out.m0);
+          out.rows_valid = min(TM, out.rows_g - out.m0);
           out.nk = (a.K + kBK - 1) / kBK;
         } else {
-          out.rows_valid = min(kBM, a.M - out.m0);
+          out.rows_valid = min(TM, a.M - out.m0);
           out.nk = (out.rows_g + kBK - 1) / kBK;
         }
         return true;
@@ -392,6 +392,230 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// =========================================================================================
+// CTA-pair variant: two CTAs of a cluster compute one 256 x 256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own 128 columns of
+// B (no multicast), so every MMA reads half the shared-memory bytes per CTA that the
+// single-CTA kernel reads, and six pipeline stages fit.  CTA 0 of the pair issues the MMAs;
+// completion is broadcast to both CTAs' barriers with tcgen05.commit (multicast of the
+// *arrival*, not of a load).  Each CTA drains its own 128 accumulator rows from its own TMEM.
+// =========================================================================================
+constexpr int kStages2 = 6;
+constexpr int kKernelIdGemm2 = 2;
+
+constexpr int gemm2_smem_bytes() {
+  return kStages2 * (kBM * kBK * 2 + 128 * kBK * 2) + 1024 + 256;
+}
+
+template <bool A_MN, bool B_MN, class Epi, class Gate>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
+                   const __grid_constant__ CUtensorMap tma_b, const GemmArgs args, const Epi epi,
+                   const Gate gate) {
+  constexpr int BN = 256;
+  extern __shared__ uint8_t smem_raw[];
+  constexpr int A_BYTES = kBM * kBK * 2;          // 128 rows of A
+  constexpr int B_BYTES = 128 * kBK * 2;          // this CTA's 128 columns of B
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // per CTA
+  constexpr uint32_t TMEM_COLS = 2 * BN;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * STAGE_BYTES);
+  uint64_t* full = bars;                        // [kStages2]  used in the leader CTA
+  uint64_t* empty = bars + kStages2;            // [kStages2]  one per CTA
+  uint64_t* tfull = bars + 2 * kStages2;        // [2]         one per CTA
+  uint64_t* tempty = bars + 2 * kStages2 + 2;   // [2]         used in the leader CTA
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages2 + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages2; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 2 * kEpiWarps);   // epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+  }
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
+  if (warp == 1) {
+    tmem_alloc2(tmem_slot, TMEM_COLS);
+    tmem_relinquish2();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint64_t timeout = args.timeout_ns;
+  const int pair_id = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer (both CTAs) -------------------------------
+    if (lane == 0) {
+      TileWalker<BN, 2 * kBM> walker(args);
+      Tile t;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int ti = pair_id; ok && walker.get(ti, t); ti += num_pairs) {
+        Tile mine = t;                       // this CTA's 128 rows of the pair tile
+        mine.m0 = t.m0 + (int)cta_rank * kBM;
+        mine.rows_valid = max(0, min(kBM, t.rows_valid - (int)cta_rank * kBM));
+        if (mine.rows_valid > 0 && !gate.wait(mine, args, abort_flag)) break;
+        for (int kb = 0; kb < t.nk; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, timeout, abort_flag)) {
+            report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 100 + stage, 0, 0);
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * STAGE_BYTES;
+          uint8_t* sb = sa + A_BYTES;
+          if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
+          const int k0 = kb * kBK;
+          // ---- A: this CTA's 128 rows ----
+          if (args.mode == 0) {
+            tma2_load_2d(sa, &tma_a, &full[stage], k0, t.row_base + mine.m0);
+          } else {
+            tma2_load_3d(sa, &tma_a, &full[stage], 0, t.row_base + k0, mine.m0 / 64);
+          }
+          // ---- B: this CTA's 128 columns ----
+          int n;
+          if (args.gated)
+            n = (cta_rank == 0 ? 0 : args.n_half) + t.n_tile * 128;
+          else
+            n = t.n_tile * BN + (int)cta_rank * 128;
+          if (args.mode == 0) {
+            const int brow = (args.group_b ? args.group_b[t.g] : t.g) * args.b_group_stride;
+            if constexpr (!B_MN)
+              tma2_load_2d(sb, &tma_b, &full[stage], k0, brow + n);
+            else
+              tma2_load_3d(sb, &tma_b, &full[stage], 0, brow + k0, n / 64);
+          } else {
+            tma2_load_3d(sb, &tma_b, &full[stage], 0, t.row_base + k0, n / 64);
+          }
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer (leader CTA only) -------------------------------
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = umma_idesc_bf16(2 * kBM, BN, A_MN, B_MN);
+      TileWalker<BN, 2 * kBM> walker(args);
+      Tile t;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int ti = pair_id; ok && walker.get(ti, t); ti += num_pairs) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, timeout, abort_flag)) {
+          report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 200 + acc, 0, 0);
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.nk; ++kb) {
+          if (!mbar_wait(&full[stage], phase, timeout, abort_flag)) {
+            report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 300 + stage, 0, 0);
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            uint64_t da, db;
+            if constexpr (!A_MN)
+              da = umma_smem_desc(sa + k * 32, 0, 1024);
+            else
+              da = umma_smem_desc(sa + k * 2048, 64 * kBK * 2, 1024);
+            if constexpr (!B_MN)
+              db = umma_smem_desc(sb + k * 32, 0, 1024);
+            else
+              db = umma_smem_desc(sb + k * 2048, 64 * kBK * 2, 1024);
+            umma2_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma2_commit_mc(&empty[stage], 3);   // frees the stage in both CTAs
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma2_commit_mc(&tfull[acc], 3);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------- epilogue (8 warps per CTA) -------------------------------
+    const int q = warp & 3;
+    const int chalf = (warp - 2) >> 2;
+    TileWalker<BN, 2 * kBM> walker(args);
+    Tile t;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int ti = pair_id; walker.get(ti, t); ti += num_pairs) {
+      Tile mine = t;
+      mine.m0 = t.m0 + (int)cta_rank * kBM;
+      mine.rows_valid = max(0, min(kBM, t.rows_valid - (int)cta_rank * kBM));
+      if (!mbar_wait(&tfull[acc], acc_phase, timeout, abort_flag)) {
+        if (lane == 0)
+          report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 400 + acc, 0, 0);
+        break;
+      }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      epi.template run<BN>(mine, args, taddr, q * 32 + lane, t.nk == 0, chalf);
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (leader)
+          mbar_arrive(&tempty[acc]);
+        else
+          mbar_arrive_remote(map_to_cta(smem_u32(&tempty[acc]), 0));
+      }
+      epi.tile_done(mine, args, q * 32 + lane);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();   // the peer may still signal this CTA's barriers until here
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc2(tmem_base, TMEM_COLS);
   }
 }
 

@@ -37,6 +37,7 @@ typedef struct FmGemmDesc {
   int n_half;
   int bn;  // 128 or 256
   int swizzle_m;
+  int cta_pair;  // 1: two CTAs share a 256 x 256 tile (tcgen05 cta_group::2) when the shape allows
   // ---- epilogue ----
   int epi;
   void* C;

@@ -42,9 +42,13 @@ def check_status(device=None) -> None:
             )
 
 
+CTA_PAIR = int(__import__("os").environ.get("FLUIDMOE_GEMM_CTA_PAIR", "0"))
+
+
 def _launch(desc: dict) -> None:
     global LAUNCHES
     LAUNCHES += 1
+    desc.setdefault("cta_pair", CTA_PAIR)
     _native.lib().gemm_launch(desc, _native.stream_ptr())
 
 

@@ -1,0 +1,51 @@
+"""Exposed-communication report: total vs visible all-to-all and all-reduce time per region,
+MAX over ranks (counterpart of the reference's tests/overlap_ratio_analyzer.py:43-182)."""
+from __future__ import annotations
+
+import argparse
+
+import torch
+import torch.distributed as dist
+
+from ..parallel.scheduler import get_backward_scheduler
+from . import common
+from .experiment_configs import get_block_benchmark_defaults
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="mixtral_8x7b")
+    ap.add_argument("--comm", default="p2p")
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args(argv)
+    bench = get_block_benchmark_defaults()
+    device, cfg, pc = common.setup(args.model, None, args.comm)
+    model = common.build_model(cfg, bench, pc, device, args.comm)
+    x = common.make_input(cfg, pc, device)
+    sched = get_backward_scheduler()
+    sched.enable(device)
+    sched.configure_allreduce(True, pc.dp_cp_group, pc.expert_dp_group, bench.get("gap_budgets"),
+                              bench.get("shared_ar_bw"), bench.get("expert_ar_bw"))
+    model.setup_ar_buffer()
+    common.run_iters(model, x, 3, pc)
+    sched.set_comm_metrics_enabled(True)
+    sched.reset_comm_metrics()
+    common.run_iters(model, x, args.iters, pc)
+    m = sched.get_comm_metrics()
+    sched.set_comm_metrics_enabled(False)
+    vals = torch.tensor([m["a2a_total_ms"], m["a2a_visible_ms"], m["ar_total_ms"], m["ar_visible_ms"]],
+                        dtype=torch.float64, device=device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+    a2a_t, a2a_v, ar_t, ar_v = (v / args.iters for v in vals.tolist())
+    common.p0(f"a2a_total_ms={a2a_t:.3f} a2a_visible_ms={a2a_v:.3f} a2a_overlap={1 - a2a_v / a2a_t if a2a_t > 0 else 0:.3f}")
+    common.p0(f"ar_total_ms={ar_t:.3f} ar_visible_ms={ar_v:.3f} ar_overlap={1 - ar_v / ar_t if ar_t > 0 else 0:.3f}")
+    for region, b in sorted(m["per_region"].items()):
+        common.p0(f"  {region:14s} a2a {b['a2a_total_ms'] / args.iters:8.3f} ms visible {b['a2a_visible_ms'] / args.iters:8.3f} ms")
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

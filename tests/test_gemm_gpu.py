@@ -127,3 +127,62 @@ def test_large_perf_smoke():
     ms = s.elapsed_time(e) / 10
     print(f"\n4096^3 bf16: {ms:.3f} ms, {2 * 4096**3 / ms / 1e9:.1f} TFLOP/s")
     _close(out, a.float() @ w.float().t())
+
+
+@pytest.fixture
+def cta_pair():
+    old = gemm.CTA_PAIR
+    gemm.CTA_PAIR = 1
+    yield
+    gemm.CTA_PAIR = old
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 512, 256), (300, 520, 192), (1024, 1024, 1024)])
+@pytest.mark.parametrize("layout", ["nk", "kn"])
+def test_cta_pair_dense(cta_pair, M, N, K, layout):
+    torch.manual_seed(0)
+    a = _rand(M, K)
+    w = _rand(N, K) if layout == "nk" else _rand(K, N)
+    out = gemm.grouped_gemm(a, w, b_layout=layout)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    _close(out, a.float() @ (w.float().t() if layout == "nk" else w.float()))
+
+
+def test_cta_pair_grouped_fused_epilogues(cta_pair):
+    torch.manual_seed(2)
+    G, H, F, cap = 2, 256, 384, 320
+    a = _rand(G * cap, H)
+    w = _rand(G, H, 2 * F, scale=0.05)
+    probs = torch.rand(G * cap, device="cuda")
+    out, pre = gemm.grouped_gemm_act(a, w, probs, activation="swiglu", uniform_rows=cap)
+    dy = _rand(G * cap, H)
+    w2 = _rand(G, F, H, scale=0.05)
+    dpre, dprobs = gemm.grouped_gemm_dact(dy, w2, pre, probs, activation="swiglu", uniform_rows=cap)
+    g1 = gemm.grouped_gemm_wgrad(a, dpre, G, uniform_rows=cap)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for g in range(G):
+        x = a[g * cap:(g + 1) * cap].float() @ w[g].float()
+        _close(pre[g * cap:(g + 1) * cap], x)
+        _close(out[g * cap:(g + 1) * cap], gemm.act_ref(x, "swiglu") * probs[g * cap:(g + 1) * cap, None])
+        _close(g1[g], a[g * cap:(g + 1) * cap].float().t() @ dpre[g * cap:(g + 1) * cap].float())
+    rdpre, rdprobs = gemm.grouped_gemm_dact(dy.cpu(), w2.cpu(), pre.cpu(), probs.cpu(), activation="swiglu", uniform_rows=cap)
+    _close(dpre.cpu(), rdpre)
+    _close(dprobs.cpu(), rdprobs)
+
+
+def test_cta_pair_speed(cta_pair):
+    a, w = _rand(8192, 8192), _rand(8192, 8192)
+    for _ in range(3):
+        out = gemm.grouped_gemm(a, w, b_layout="nk")
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(10):
+        out = gemm.grouped_gemm(a, w, b_layout="nk")
+    e.record()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ms = s.elapsed_time(e) / 10
+    print(f"\n8192^3 bf16 (CTA pair): {ms:.3f} ms, {2 * 8192**3 / ms / 1e9:.1f} TFLOP/s")

@@ -253,6 +253,10 @@ def _profile_one_step(torch, step_fn, path):
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
     with open(path, "w") as f:
         f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=90))
+        f.write("\n\nper-launch device time of the GEMM kernels (us), in launch order:\n")
+        for ev in prof.events():
+            if "gemm" in ev.name and "sm100_kernel" in ev.name and ev.device_time_total > 0:
+                f.write(f"{ev.device_time_total:10.1f}  {ev.name[:110]}\n")
 
 
 def _extra_launches() -> int:

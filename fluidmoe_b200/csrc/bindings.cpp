@@ -81,6 +81,11 @@ static void gemm_launch(const py::dict& d, uintptr_t stream) {
   g.gate_group_base = ptr<const int*>(d, "gate_group_base");
   g.gate_blocks_per_group = get<int>(d, "gate_blocks_per_group", 0);
   g.gate_expected = get<int>(d, "gate_expected", 0);
+  g.gate_k_blocks_per_src = get<int>(d, "gate_k_blocks_per_src", 0);
+  g.n_rotate = get<int>(d, "n_rotate", 0);
+  g.k_rotate = get<int>(d, "k_rotate", 0);
+  g.cols_per_rank = get<int>(d, "cols_per_rank", 0);
+  g.dst_row_offset = get<long long>(d, "dst_row_offset", 0);
   g.max_ctas = get<int>(d, "max_ctas", 0);
   g.timeout_ns = get<unsigned long long>(d, "timeout_ns", 0ull);
   g.status = ptr<int*>(d, "status");
@@ -98,6 +103,7 @@ PYBIND11_MODULE(_C, m) {
   m.attr("EPI_ACT") = (int)FM_EPI_ACT;
   m.attr("EPI_SCATTER") = (int)FM_EPI_SCATTER;
   m.attr("EPI_DACT") = (int)FM_EPI_DACT;
+  m.attr("EPI_COLSCATTER") = (int)FM_EPI_COLSCATTER;
   m.attr("ACT_GELU") = (int)FM_ACT_GELU;
   m.attr("ACT_SILU") = (int)FM_ACT_SILU;
   m.attr("ACT_NONE") = (int)FM_ACT_NONE;

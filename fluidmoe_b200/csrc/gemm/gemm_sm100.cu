@@ -80,6 +80,120 @@ __device__ __forceinline__ void load_row_bf16(const __nv_bfloat16* src, float* v
 }
 
 // ----------------------------------------------------------------------------------------
+// Coalesced epilogue stores.  After tcgen05.ld every lane holds 32 consecutive columns of ONE
+// row, so a direct store makes each warp instruction touch 32 different rows.  Instead the
+// warp writes its 32 x 32 block to a padded shared-memory stage and reads it back so that a
+// group of lanes covers one row segment contiguously: every global store instruction then
+// writes whole 32-byte sectors (fp32: 8 lanes x 16 B per row, 4 rows per instruction; bf16:
+// 4 lanes x 16 B per row, 8 rows per instruction).
+// ----------------------------------------------------------------------------------------
+constexpr int kStgLd = 36;  // floats per staged row (16-byte aligned, conflict-free)
+
+__device__ __forceinline__ void stage_put(float* stg, int lane, const float* v) {
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    *reinterpret_cast<float4*>(stg + lane * kStgLd + 4 * i) =
+        make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  __syncwarp();
+}
+// The inverse: rows were filled cooperatively, every lane takes its own row back.
+__device__ __forceinline__ void stage_get(const float* stg, int lane, float* v) {
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float4 x = *reinterpret_cast<const float4*>(stg + lane * kStgLd + 4 * i);
+    v[4 * i] = x.x; v[4 * i + 1] = x.y; v[4 * i + 2] = x.z; v[4 * i + 3] = x.w;
+  }
+  __syncwarp();
+}
+
+// bf16 rows at base + rr * ld (rr = 0..rows_ok-1), 32 columns each; base 16-byte aligned, ld % 8 == 0.
+__device__ __forceinline__ void staged_store_bf16(float* stg, int lane, const float* v, int rows_ok,
+                                                  __nv_bfloat16* base, long long ld) {
+  stage_put(stg, lane, v);
+  const int sub = lane >> 2, c8 = (lane & 3) * 8;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int rr = pass * 8 + sub;
+    if (rr < rows_ok) {
+      const float4 a = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+      const float4 b = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+      uint4 p;
+      p.x = pack_bf16x2(a.x, a.y); p.y = pack_bf16x2(a.z, a.w);
+      p.z = pack_bf16x2(b.x, b.y); p.w = pack_bf16x2(b.z, b.w);
+      *reinterpret_cast<uint4*>(base + rr * ld + c8) = p;
+    }
+  }
+}
+// Same with an arbitrary destination per row: `my_row_ptr` is the destination of THIS lane's
+// row (null = skip); the other lanes fetch it with a shuffle.
+__device__ __forceinline__ void staged_store_bf16_scatter(float* stg, int lane, const float* v,
+                                                          __nv_bfloat16* my_row_ptr) {
+  stage_put(stg, lane, v);
+  const int sub = lane >> 2, c8 = (lane & 3) * 8;
+  const unsigned long long mine = reinterpret_cast<unsigned long long>(my_row_ptr);
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int rr = pass * 8 + sub;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(__shfl_sync(0xffffffffu, mine, rr));
+    if (dst != nullptr) {
+      const float4 a = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+      const float4 b = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+      uint4 p;
+      p.x = pack_bf16x2(a.x, a.y); p.y = pack_bf16x2(a.z, a.w);
+      p.z = pack_bf16x2(b.x, b.y); p.w = pack_bf16x2(b.z, b.w);
+      *reinterpret_cast<uint4*>(dst + c8) = p;
+    }
+  }
+}
+// fp32 rows, optional accumulate; base 16-byte aligned, ld % 4 == 0.
+__device__ __forceinline__ void staged_store_f32(float* stg, int lane, const float* v, int rows_ok,
+                                                 float* base, long long ld, bool accumulate) {
+  stage_put(stg, lane, v);
+  const int sub = lane >> 3, c4 = (lane & 7) * 4;
+#pragma unroll
+  for (int pass = 0; pass < 8; ++pass) {
+    const int rr = pass * 4 + sub;
+    if (rr < rows_ok) {
+      float4 x = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c4);
+      float4* dst = reinterpret_cast<float4*>(base + rr * ld + c4);
+      if (accumulate) {
+        const float4 o = *dst;
+        x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+      }
+      *dst = x;
+    }
+  }
+}
+// Coalesced load of 32 bf16 rows x 32 columns into the stage; every lane then reads its row.
+__device__ __forceinline__ void staged_load_bf16(float* stg, int lane, float* v, int rows_ok,
+                                                 const __nv_bfloat16* base, long long ld) {
+  __syncwarp();
+  const int sub = lane >> 2, c8 = (lane & 3) * 8;
+#pragma unroll
+  for (int pass = 0; pass < 4; ++pass) {
+    const int rr = pass * 8 + sub;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+    if (rr < rows_ok) {
+      const uint4 p = *reinterpret_cast<const uint4*>(base + rr * ld + c8);
+      const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&p.x);
+      const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&p.y);
+      const __nv_bfloat162 p2 = *reinterpret_cast<const __nv_bfloat162*>(&p.z);
+      const __nv_bfloat162 p3 = *reinterpret_cast<const __nv_bfloat162*>(&p.w);
+      a = make_float4(__low2float(p0), __high2float(p0), __low2float(p1), __high2float(p1));
+      b = make_float4(__low2float(p2), __high2float(p2), __low2float(p3), __high2float(p3));
+    }
+    *reinterpret_cast<float4*>(stg + rr * kStgLd + c8) = a;
+    *reinterpret_cast<float4*>(stg + rr * kStgLd + c8 + 4) = b;
+  }
+  stage_get(stg, lane, v);
+}
+__device__ __forceinline__ bool aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
+// ----------------------------------------------------------------------------------------
 // Epilogue 0: plain store (bf16 or fp32, optional accumulate; the fp32-accumulate form is the
 // weight-gradient epilogue that adds straight into a flat gradient buffer).
 // ----------------------------------------------------------------------------------------
@@ -93,51 +207,79 @@ struct EpiStore {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero, int chalf) const {
+                                      bool zero, int chalf, float* stg) const {
+    const int lane = r & 31;
     const long long row = a.mode == 0 ? (long long)t.row_base + t.m0 + r : (long long)t.m0 + r;
+    const long long row0 = row - lane;   // first row of this warp
     const long long goff = a.mode == 0 ? 0 : (long long)t.g * group_stride;
     const bool row_ok = r < t.rows_valid;
+    const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
 #pragma unroll 1
     for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
       const int col = t.n_tile * BN + c * 32;
       if (col >= a.N) break;
       float v[32];
       load_acc(taddr + c * 32, v, zero);
-      if (!row_ok) continue;
+      if (rows_ok == 0) continue;
       const int ncols = min(32, a.N - col);
       if (alpha != 1.0f) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= alpha;
       }
       if (out_fp32) {
-        float* dst = reinterpret_cast<float*>(C) + goff + row * ldc + col;
-        if (ncols >= 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            if (accumulate) {
-              const float4 p = reinterpret_cast<const float4*>(dst)[i];
-              o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-            }
-            reinterpret_cast<float4*>(dst)[i] = o;
-          }
-        } else {
+        float* base = reinterpret_cast<float*>(C) + goff + row0 * ldc + col;
+        if (ncols == 32 && (ldc & 3) == 0 && aligned16(base)) {
+          staged_store_f32(stg, lane, v, rows_ok, base, ldc, accumulate != 0);
+        } else if (row_ok) {
+          float* dst = base + (long long)lane * ldc;
           for (int i = 0; i < ncols; ++i) dst[i] = accumulate ? dst[i] + v[i] : v[i];
         }
       } else {
-        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(C) + goff + row * ldc + col;
-        if (accumulate) {
-          float p[32];
-          load_row_bf16(dst, p, ncols);
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(C) + goff + row0 * ldc + col;
+        if (ncols == 32 && (ldc & 7) == 0 && aligned16(base)) {
+          if (accumulate) {
+            float p[32];
+            staged_load_bf16(stg, lane, p, rows_ok, base, ldc);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] += p[i];
+            for (int i = 0; i < 32; ++i) v[i] += p[i];
+          }
+          staged_store_bf16(stg, lane, v, rows_ok, base, ldc);
+        } else if (row_ok) {
+          __nv_bfloat16* dst = base + (long long)lane * ldc;
+          if (accumulate) {
+            float p[32];
+            load_row_bf16(dst, p, ncols);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += p[i];
+          }
+          store_row_bf16(dst, v, ncols);
         }
-        store_row_bf16(dst, v, ncols);
       }
     }
   }
   __device__ __forceinline__ void tile_done(const Tile&, const GemmArgs&, int) const {}
 };
+
+// Store one 32 x 32 block of bf16 rows (consecutive rows, leading dimension ld), coalesced when
+// the block is full-width and aligned, per-row otherwise.
+__device__ __forceinline__ void put_block_bf16(float* stg, int lane, const float* v, int rows_ok,
+                                               bool row_ok, __nv_bfloat16* base, long long ld, int ncols) {
+  if (ncols == 32 && (ld & 7) == 0 && aligned16(base))
+    staged_store_bf16(stg, lane, v, rows_ok, base, ld);
+  else if (row_ok)
+    store_row_bf16(base + (long long)lane * ld, v, ncols);
+}
+__device__ __forceinline__ void get_block_bf16(float* stg, int lane, float* v, int rows_ok, bool row_ok,
+                                               const __nv_bfloat16* base, long long ld, int ncols) {
+  if (ncols == 32 && (ld & 7) == 0 && aligned16(base)) {
+    staged_load_bf16(stg, lane, v, rows_ok, base, ld);
+  } else if (row_ok) {
+    load_row_bf16(base + (long long)lane * ld, v, ncols);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = 0.f;
+  }
+}
 
 // ----------------------------------------------------------------------------------------
 // Epilogue 1: activation x routing probability (forward FC1).  Non-gated: out = act(x) * p.
@@ -156,9 +298,12 @@ struct EpiAct {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero, int chalf) const {
+                                      bool zero, int chalf, float* stg) const {
+    const int lane = r & 31;
     const long long row = (long long)t.row_base + t.m0 + r;
+    const long long row0 = row - lane;
     const bool row_ok = r < t.rows_valid;
+    const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
     const float p = (row_ok && probs) ? probs[row] : 1.0f;
     if (a.gated) {
 #pragma unroll 1
@@ -168,15 +313,15 @@ struct EpiAct {
         float g[32], u[32];
         load_acc(taddr + c * 32, g, zero);
         load_acc(taddr + BN / 2 + c * 32, u, zero);
-        if (!row_ok) continue;
+        if (rows_ok == 0) continue;
         const int ncols = min(32, a.N - col);
         if (pre_out) {
-          store_row_bf16(pre_out + row * ld_pre + col, g, ncols);
-          store_row_bf16(pre_out + row * ld_pre + a.n_half + col, u, ncols);
+          put_block_bf16(stg, lane, g, rows_ok, row_ok, pre_out + row0 * ld_pre + col, ld_pre, ncols);
+          put_block_bf16(stg, lane, u, rows_ok, row_ok, pre_out + row0 * ld_pre + a.n_half + col, ld_pre, ncols);
         }
 #pragma unroll
         for (int i = 0; i < 32; ++i) g[i] = silu_f(g[i]) * u[i] * p;
-        store_row_bf16(act_out + row * ld_act + col, g, ncols);
+        put_block_bf16(stg, lane, g, rows_ok, row_ok, act_out + row0 * ld_act + col, ld_act, ncols);
       }
     } else {
 #pragma unroll 1
@@ -185,12 +330,12 @@ struct EpiAct {
         if (col >= a.N) break;
         float v[32];
         load_acc(taddr + c * 32, v, zero);
-        if (!row_ok) continue;
+        if (rows_ok == 0) continue;
         const int ncols = min(32, a.N - col);
-        if (pre_out) store_row_bf16(pre_out + row * ld_pre + col, v, ncols);
+        if (pre_out) put_block_bf16(stg, lane, v, rows_ok, row_ok, pre_out + row0 * ld_pre + col, ld_pre, ncols);
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = act_f(act_kind, v[i]) * p;
-        store_row_bf16(act_out + row * ld_act + col, v, ncols);
+        put_block_bf16(stg, lane, v, rows_ok, row_ok, act_out + row0 * ld_act + col, ld_act, ncols);
       }
     }
   }
@@ -199,7 +344,7 @@ struct EpiAct {
 
 // ----------------------------------------------------------------------------------------
 // Epilogue 3: backward of (act x prob), fused after dActW = dY * W2^T.
-//   a = act(pre); dprob_partial[row, n_tile] = sum_cols(acc * a); dpre = acc * p * act'(pre)
+//   a = act(pre); dprob_partial[row, n_tile, half] = sum_cols(acc * a); dpre = acc * p * act'(pre)
 //   gated: a = silu(g) * u; dg = acc * p * u * silu'(g); du = acc * p * silu(g)
 // Partial sums per N tile and per column half (two epilogue warps share a row) keep the
 // probability gradient deterministic (no atomics): dprobs_partial is [rows, n_tiles, 2].
@@ -211,7 +356,7 @@ struct EpiDAct {
   __nv_bfloat16* dpre;
   long long ld_dpre;
   const float* probs;
-  float* dprobs_partial;  // [rows, n_tiles]
+  float* dprobs_partial;  // [rows, n_tiles, 2]
   int n_tiles;
   int act_kind;
   int gated;   // activation is SwiGLU: pre_in / dpre hold [gate | up] halves `n_half` apart
@@ -219,9 +364,12 @@ struct EpiDAct {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero, int chalf) const {
+                                      bool zero, int chalf, float* stg) const {
+    const int lane = r & 31;
     const long long row = (long long)t.row_base + t.m0 + r;
+    const long long row0 = row - lane;
     const bool row_ok = r < t.rows_valid;
+    const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
     const float p = (row_ok && probs) ? probs[row] : 1.0f;
     float dp = 0.f;
 #pragma unroll 1
@@ -230,12 +378,12 @@ struct EpiDAct {
       if (col >= a.N) break;
       float v[32];
       load_acc(taddr + c * 32, v, zero);
-      if (!row_ok) continue;
+      if (rows_ok == 0) continue;
       const int ncols = min(32, a.N - col);
       if (gated) {
         float g[32], u[32];
-        load_row_bf16(pre_in + row * ld_pre_in + col, g, ncols);
-        load_row_bf16(pre_in + row * ld_pre_in + n_half + col, u, ncols);
+        get_block_bf16(stg, lane, g, rows_ok, row_ok, pre_in + row0 * ld_pre_in + col, ld_pre_in, ncols);
+        get_block_bf16(stg, lane, u, rows_ok, row_ok, pre_in + row0 * ld_pre_in + n_half + col, ld_pre_in, ncols);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const float s = silu_f(g[i]);
@@ -244,17 +392,17 @@ struct EpiDAct {
           g[i] = da * u[i] * dsilu_f(g[i]);
           u[i] = da * s;
         }
-        store_row_bf16(dpre + row * ld_dpre + col, g, ncols);
-        store_row_bf16(dpre + row * ld_dpre + n_half + col, u, ncols);
+        put_block_bf16(stg, lane, g, rows_ok, row_ok, dpre + row0 * ld_dpre + col, ld_dpre, ncols);
+        put_block_bf16(stg, lane, u, rows_ok, row_ok, dpre + row0 * ld_dpre + n_half + col, ld_dpre, ncols);
       } else {
         float x[32];
-        load_row_bf16(pre_in + row * ld_pre_in + col, x, ncols);
+        get_block_bf16(stg, lane, x, rows_ok, row_ok, pre_in + row0 * ld_pre_in + col, ld_pre_in, ncols);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           dp += v[i] * act_f(act_kind, x[i]);
           x[i] = v[i] * p * dact_f(act_kind, x[i]);
         }
-        store_row_bf16(dpre + row * ld_dpre + col, x, ncols);
+        put_block_bf16(stg, lane, x, rows_ok, row_ok, dpre + row0 * ld_dpre + col, ld_dpre, ncols);
       }
     }
     if (row_ok && dprobs_partial) dprobs_partial[(row * n_tiles + t.n_tile) * 2 + chalf] = dp;
@@ -265,11 +413,11 @@ struct EpiDAct {
 // ----------------------------------------------------------------------------------------
 // Epilogue 2: scatter rows to their owners (FC2 + combine).  Row R of the result is written
 // as bf16 to dst_base[dst_rank[R]] + dst_row[R] * ld_dst, which may be another GPU's buffer
-// mapped over NVLink (plain 16-byte peer stores).  After a tile, each destination's arrival
-// counter grows by the number of rows the tile sent it; the owner waits until its counter
-// equals rows_expected * n_tiles * 2 (each of the two epilogue warps that share a row reports
-// its half).  Replaces the combine all-to-all rounds of
-// fluid/moe/forward.py:903-948.
+// mapped over NVLink (plain 16-byte peer stores, 64 contiguous bytes per row per instruction
+// group).  After a tile, each destination's arrival counter grows by the number of rows the
+// tile sent it; the owner waits until its counter equals rows_expected * n_tiles * 2 (each of
+// the two epilogue warps that share a row reports its half).  Replaces the combine all-to-all
+// rounds of fluid/moe/forward.py:903-948.
 // ----------------------------------------------------------------------------------------
 struct EpiScatter {
   __nv_bfloat16* const* dst_base;
@@ -281,7 +429,8 @@ struct EpiScatter {
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
-                                      bool zero, int chalf) const {
+                                      bool zero, int chalf, float* stg) const {
+    const int lane = r & 31;
     const long long row = (long long)t.row_base + t.m0 + r;
     const bool row_ok = r < t.rows_valid;
     int rank = -1;
@@ -291,14 +440,20 @@ struct EpiScatter {
       drow = dst_row[row];
     }
     __nv_bfloat16* base = rank >= 0 ? dst_base[rank] + drow * ld_dst : nullptr;
+    const bool fast = (ld_dst & 7) == 0 &&
+                      __all_sync(0xffffffffu, base == nullptr || aligned16(base));
 #pragma unroll 1
     for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
       const int col = t.n_tile * BN + c * 32;
       if (col >= a.N) break;
       float v[32];
       load_acc(taddr + c * 32, v, zero);
-      if (rank < 0) continue;
-      store_row_bf16(base + col, v, min(32, a.N - col));
+      const int ncols = min(32, a.N - col);
+      if (fast && ncols == 32 && (col & 7) == 0) {
+        staged_store_bf16_scatter(stg, lane, v, base ? base + col : nullptr);
+      } else if (base != nullptr) {
+        store_row_bf16(base + col, v, ncols);
+      }
     }
     if (dst_flags != nullptr) __threadfence_system();
   }
@@ -314,6 +469,61 @@ struct EpiScatter {
     if ((int)(threadIdx.x & 31) == leader && rank >= 0)
       flag_release_add(dst_flags[rank], __popc(peers));
   }
+};
+
+// ----------------------------------------------------------------------------------------
+// Epilogue 4: scatter COLUMN blocks to their owners (QKV projection + SP->HP exchange, and
+// out-projection input gradient + SP->HP).  Columns [p*cpr, (p+1)*cpr) of every result row
+// belong to rank p; they are stored as bf16 into rank p's buffer at row (dst_row_offset + row),
+// column (col - p*cpr), leading dimension dst_ld -- the position the all-to-all would have put
+// them (fluid/core/comm.py:162-209).  Each warp adds the rows it delivered, once per 32-column
+// chunk, to the destination's counter for this source; the owner waits for
+// rows * (cpr / 32) per source.
+// ----------------------------------------------------------------------------------------
+struct EpiColScatter {
+  __nv_bfloat16* const* dst_base;
+  int cols_per_rank;
+  long long dst_ld;
+  long long dst_row_offset;
+  int* const* dst_flags;
+
+  template <int BN>
+  __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
+                                      bool zero, int chalf, float* stg) const {
+    const int lane = r & 31;
+    const long long row0 = (long long)t.row_base + t.m0 + (r - lane);
+    const bool row_ok = r < t.rows_valid;
+    const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
+    int pend_rank = -1, pend_cnt = 0;
+#pragma unroll 1
+    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+      const int col = t.n_tile * BN + c * 32;
+      if (col >= a.N) break;
+      float v[32];
+      load_acc(taddr + c * 32, v, zero);
+      if (rows_ok == 0) continue;
+      const int rank = col / cols_per_rank;
+      const int cin = col - rank * cols_per_rank;
+      __nv_bfloat16* base = dst_base[rank] + (dst_row_offset + row0) * dst_ld + cin;
+      put_block_bf16(stg, lane, v, rows_ok, row_ok, base, dst_ld, min(32, a.N - col));
+      if (rank != pend_rank) {
+        if (pend_cnt > 0 && dst_flags != nullptr) {
+          __threadfence_system();
+          __syncwarp();
+          if (lane == 0) flag_release_add(dst_flags[pend_rank], pend_cnt);
+        }
+        pend_rank = rank;
+        pend_cnt = 0;
+      }
+      pend_cnt += rows_ok;
+    }
+    if (pend_cnt > 0 && dst_flags != nullptr) {
+      __threadfence_system();
+      __syncwarp();
+      if (lane == 0) flag_release_add(dst_flags[pend_rank], pend_cnt);
+    }
+  }
+  __device__ __forceinline__ void tile_done(const Tile&, const GemmArgs&, int) const {}
 };
 
 // ----------------------------------------------------------------------------------------
@@ -504,6 +714,10 @@ static int dispatch_shape(const FmGemmDesc* d, const CUtensorMap& ta, const CUte
 template <class Epi>
 static int dispatch_gate(const FmGemmDesc* d, const CUtensorMap& ta, const CUtensorMap& tb,
                          const GemmArgs& args, const Epi& epi, int grid, cudaStream_t s) {
+  if (d->gate_flags != nullptr && d->gate_k_blocks_per_src > 0) {
+    GateKSource g{d->gate_flags, d->gate_k_blocks_per_src, d->gate_blocks_per_group};
+    return dispatch_shape(d, ta, tb, args, epi, g, grid, s);
+  }
   if (d->gate_flags != nullptr) {
     GateRowBlockFlags g{d->gate_flags, d->gate_group_base, d->gate_blocks_per_group,
                         d->gate_expected};
@@ -586,6 +800,8 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   args.n_half = d->n_half;
   args.swizzle_m = d->swizzle_m;
   args.mn3d = mn3d ? 1 : 0;
+  args.n_rotate = d->n_rotate;
+  args.k_rotate = d->k_rotate;
   args.timeout_ns = d->timeout_ns ? d->timeout_ns : 4000000000ull;
   args.status = d->status;
 
@@ -623,6 +839,15 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
     case FM_EPI_SCATTER: {
       EpiScatter e{reinterpret_cast<__nv_bfloat16* const*>(d->dst_base), d->dst_rank, d->dst_row,
                    d->ld_dst, d->dst_flags, d->num_ranks};
+      return dispatch_gate(d, ta, tb, args, e, grid, stream);
+    }
+    case FM_EPI_COLSCATTER: {
+      if (d->cols_per_rank <= 0 || d->cols_per_rank % 32 != 0) {
+        set_err("column scatter needs cols_per_rank to be a positive multiple of 32");
+        return -1;
+      }
+      EpiColScatter e{reinterpret_cast<__nv_bfloat16* const*>(d->dst_base), d->cols_per_rank, d->ld_dst,
+                      d->dst_row_offset, d->dst_flags};
       return dispatch_gate(d, ta, tb, args, e, grid, stream);
     }
     default:

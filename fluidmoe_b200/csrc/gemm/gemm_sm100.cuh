@@ -24,7 +24,8 @@ namespace fm {
 
 constexpr int kBM = 128;
 constexpr int kBK = 64;
-constexpr int kStages = 4;
+constexpr int kStages = 4;                 // BN = 128; the 256-wide single-CTA tile uses 3
+constexpr int kEpiStageFloats = 32 * 36;   // per epilogue warp: 32 rows x 32 columns, padded rows
 constexpr int kEpiWarps = 8;    // two warps per TMEM lane quarter, each takes half the columns
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kKernelIdGemm = 1;
@@ -45,6 +46,8 @@ struct GemmArgs {
   int n_half;             // column offset of the `up` half inside B
   int swizzle_m;          // m-tiles per rasterisation super-row (L2 reuse)
   int mn3d;               // MN-major operands are fetched with one 3-D box per tile
+  int n_rotate;           // tiles visit N starting at this tile index (destination round-robin)
+  int k_rotate;           // the K loop starts at this 64-wide block (local source first)
   unsigned long long timeout_ns;
   int* status;
 };
@@ -93,7 +96,7 @@ struct TileWalker {
         const int gsz = min(sw, mt - first_m);
         const int in_super = l - super * per_super;
         const int m_tile = first_m + in_super % gsz;
-        out.n_tile = in_super / gsz;
+        out.n_tile = (in_super / gsz + a.n_rotate) % nt;
         out.g = g;
         out.m0 = m_tile * TM;
         out.rows_g = rows_of(g);
@@ -119,6 +122,9 @@ struct GateNone {
   __device__ __forceinline__ bool wait(const Tile&, const GemmArgs&, volatile int*) const {
     return true;
   }
+  __device__ __forceinline__ bool wait_k(const Tile&, int, bool, const GemmArgs&, volatile int*) const {
+    return true;
+  }
 };
 
 // Per-row-block flags: rows [128*i, 128*i+128) of group g are ready once
@@ -140,11 +146,43 @@ struct GateRowBlockFlags {
     report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, idx, want, observed);
     return false;
   }
+  __device__ __forceinline__ bool wait_k(const Tile&, int, bool, const GemmArgs&, volatile int*) const {
+    return true;
+  }
+};
+
+// Gating along K: the contraction dimension is a concatenation of column blocks that arrive from
+// different source ranks (`kblocks_per_src` 64-wide blocks each).  Before the producer loads the
+// first K block of a source for a row block it waits until that source has delivered all rows of
+// the block: flags[src * row_blocks + row_block] >= rows in the block.  Used by the output
+// projection after the HP->SP exchange and by the QKV input gradient.
+struct GateKSource {
+  const int* flags;
+  int kblocks_per_src;
+  int row_blocks;      // 128-row blocks per source
+  __device__ __forceinline__ bool wait(const Tile&, const GemmArgs&, volatile int*) const {
+    return true;
+  }
+  __device__ __forceinline__ bool wait_k(const Tile& t, int kb, bool first, const GemmArgs& a,
+                                         volatile int* abort_flag) const {
+    if (!first && kb % kblocks_per_src != 0) return true;
+    const int src = kb / kblocks_per_src;
+    const int idx = src * row_blocks + (t.row_base + t.m0) / kBM;
+    int observed = 0;
+    if (flag_wait_ge(flags + idx, t.rows_valid, a.timeout_ns, abort_flag, &observed)) return true;
+    report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, 10000 + idx, t.rows_valid, observed);
+    return false;
+  }
 };
 
 template <int BN>
+constexpr int gemm_stages() {
+  return BN == 256 ? 3 : 4;
+}
+template <int BN>
 constexpr int gemm_smem_bytes() {
-  return kStages * (kBM * kBK * 2 + BN * kBK * 2) + 1024 /*align*/ + 256 /*barriers*/;
+  return gemm_stages<BN>() * (kBM * kBK * 2 + BN * kBK * 2) + kEpiWarps * kEpiStageFloats * 4 +
+         1024 /*align*/ + 256 /*barriers*/;
 }
 
 template <bool A_MN, bool B_MN, int BN, class Epi, class Gate>
@@ -156,24 +194,26 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
   constexpr int A_BYTES = kBM * kBK * 2;
   constexpr int B_BYTES = BN * kBK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int NSTAGE = gemm_stages<BN>();
   constexpr uint32_t TMEM_COLS = 2 * BN;  // 256 or 512: powers of two
   static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
 
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * STAGE_BYTES);
-  uint64_t* full = bars;                      // [kStages]
-  uint64_t* empty = bars + kStages;           // [kStages]
-  uint64_t* tfull = bars + 2 * kStages;       // [2]
-  uint64_t* tempty = bars + 2 * kStages + 2;  // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  float* epi_stage = reinterpret_cast<float*>(smem + NSTAGE * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + NSTAGE * STAGE_BYTES + kEpiWarps * kEpiStageFloats * 4);
+  uint64_t* full = bars;                      // [NSTAGE]
+  uint64_t* empty = bars + NSTAGE;           // [NSTAGE]
+  uint64_t* tfull = bars + 2 * NSTAGE;       // [2]
+  uint64_t* tempty = bars + 2 * NSTAGE + 2;  // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTAGE + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < NSTAGE; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
@@ -207,6 +247,11 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
       for (int ti = blockIdx.x; ok && walker.get(ti, t); ti += gridDim.x) {
         if (!gate.wait(t, args, abort_flag)) break;
         for (int kb = 0; kb < t.nk; ++kb) {
+          const int kbe = args.k_rotate ? (kb + args.k_rotate) % t.nk : kb;
+          if (!gate.wait_k(t, kbe, kb == 0, args, abort_flag)) {
+            ok = false;
+            break;
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1, timeout, abort_flag)) {
             report_status(args.status, kStatusMbarTimeout, kKernelIdGemm, 100 + stage, 0, 0);
             ok = false;
@@ -215,7 +260,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           mbar_expect_tx(&full[stage], STAGE_BYTES);
-          const int k0 = kb * kBK;
+          const int k0 = kbe * kBK;
           // ---- A ----
           if (args.mode == 0) {
             if constexpr (!A_MN) {
@@ -291,7 +336,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
                             t.row_base + k0);
             }
           }
-          if (++stage == kStages) {
+          if (++stage == NSTAGE) {
             stage = 0;
             phase ^= 1;
           }
@@ -340,7 +385,7 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
             umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);  // frees the stage once these MMAs have read it
-          if (++stage == kStages) {
+          if (++stage == NSTAGE) {
             stage = 0;
             phase ^= 1;
           }
@@ -369,7 +414,8 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      epi.template run<BN>(t, args, taddr, q * 32 + lane, t.nk == 0, chalf);
+      epi.template run<BN>(t, args, taddr, q * 32 + lane, t.nk == 0, chalf,
+                           epi_stage + (warp - 2) * kEpiStageFloats);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -399,15 +445,15 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
 // CTA-pair variant: two CTAs of a cluster compute one 256 x 256 tile with
 // tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and its own 128 columns of
 // B (no multicast), so every MMA reads half the shared-memory bytes per CTA that the
-// single-CTA kernel reads, and six pipeline stages fit.  CTA 0 of the pair issues the MMAs;
+// single-CTA kernel reads, and five pipeline stages fit beside the epilogue staging area.  CTA 0 of the pair issues the MMAs;
 // completion is broadcast to both CTAs' barriers with tcgen05.commit (multicast of the
 // *arrival*, not of a load).  Each CTA drains its own 128 accumulator rows from its own TMEM.
 // =========================================================================================
-constexpr int kStages2 = 6;
+constexpr int kStages2 = 5;
 constexpr int kKernelIdGemm2 = 2;
 
 constexpr int gemm2_smem_bytes() {
-  return kStages2 * (kBM * kBK * 2 + 128 * kBK * 2) + 1024 + 256;
+  return kStages2 * (kBM * kBK * 2 + 128 * kBK * 2) + kEpiWarps * kEpiStageFloats * 4 + 1024 + 256;
 }
 
 template <bool A_MN, bool B_MN, class Epi, class Gate>
@@ -424,7 +470,8 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * STAGE_BYTES);
+  float* epi_stage = reinterpret_cast<float*>(smem + kStages2 * STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages2 * STAGE_BYTES + kEpiWarps * kEpiStageFloats * 4);
   uint64_t* full = bars;                        // [kStages2]  used in the leader CTA
   uint64_t* empty = bars + kStages2;            // [kStages2]  one per CTA
   uint64_t* tfull = bars + 2 * kStages2;        // [2]         one per CTA
@@ -479,6 +526,11 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
         mine.rows_valid = max(0, min(kBM, t.rows_valid - (int)cta_rank * kBM));
         if (mine.rows_valid > 0 && !gate.wait(mine, args, abort_flag)) break;
         for (int kb = 0; kb < t.nk; ++kb) {
+          const int kbe = args.k_rotate ? (kb + args.k_rotate) % t.nk : kb;
+          if (mine.rows_valid > 0 && !gate.wait_k(mine, kbe, kb == 0, args, abort_flag)) {
+            ok = false;
+            break;
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1, timeout, abort_flag)) {
             report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 100 + stage, 0, 0);
             ok = false;
@@ -487,7 +539,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
           uint8_t* sa = smem + stage * STAGE_BYTES;
           uint8_t* sb = sa + A_BYTES;
           if (leader) mbar_expect_tx(&full[stage], 2 * STAGE_BYTES);
-          const int k0 = kb * kBK;
+          const int k0 = kbe * kBK;
           // ---- A: this CTA's 128 rows ----
           if (args.mode == 0) {
             tma2_load_2d(sa, &tma_a, &full[stage], k0, t.row_base + mine.m0);
@@ -589,7 +641,8 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      epi.template run<BN>(mine, args, taddr, q * 32 + lane, t.nk == 0, chalf);
+      epi.template run<BN>(mine, args, taddr, q * 32 + lane, t.nk == 0, chalf,
+                           epi_stage + (warp - 2) * kEpiStageFloats);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {

@@ -13,6 +13,7 @@ enum FmEpilogue {
   FM_EPI_ACT = 1,      // act(acc) * prob[row] -> bf16 (GELU / SiLU / SwiGLU), optional pre-act copy
   FM_EPI_SCATTER = 2,  // row r of the result goes to dst_base[dst_rank[r]] + dst_row[r] * ld
   FM_EPI_DACT = 3,     // backward of act * prob fused after the FC2 input-gradient GEMM
+  FM_EPI_COLSCATTER = 4,  // column block p of the result goes to rank p's buffer
 };
 enum FmAct { FM_ACT_GELU = 0, FM_ACT_SILU = 1, FM_ACT_NONE = 2 };
 
@@ -64,11 +65,17 @@ typedef struct FmGemmDesc {
   long long ld_dst;
   int* const* dst_flags;   // device array [num_ranks]: counter this rank bumps on each peer (may be null)
   int num_ranks;
+  // FM_EPI_COLSCATTER (also uses dst_base, ld_dst, dst_flags)
+  int cols_per_rank;
+  long long dst_row_offset;
   // ---- gate (producer waits until flags[...] >= expected before loading a row block) ----
   const int* gate_flags;
   const int* gate_group_base;
   int gate_blocks_per_group;
   int gate_expected;
+  int gate_k_blocks_per_src;  // > 0: gate along K by source rank (gate_blocks_per_group = row blocks per source)
+  int n_rotate;               // first N tile to visit
+  int k_rotate;               // first K block to visit
   // ---- launch ----
   int max_ctas;  // 0 = one per SM
   unsigned long long timeout_ns;

@@ -28,6 +28,11 @@ int fm_adam(void* p, float* master, float* g, void* m, void* v, long long n, flo
             float beta2, float eps, float weight_decay, int step, float grad_scale, int zero_grad,
             int state_bf16, cudaStream_t s);
 
+// Cross-entropy forward + backward in place: loss_out[row] = lse - logit[label]; logits are
+// overwritten with (softmax - onehot) * grad_scale (rows with a negative label get zeros).
+int fm_cross_entropy(void* logits, const long long* labels, float* loss_out, int T, int V,
+                     float grad_scale, cudaStream_t s);
+
 // Padded-capacity routing plan (see moe_plan_kernel).  Outputs: sorted_indices [E*cap] int64,
 // slot_probs [E*cap] fp32, slot_of_token [T,k] int32, routed_per_expert [E] int32.
 int fm_moe_plan(const long long* top_idx, const float* top_probs, int T, int k, int E, int cap,

@@ -42,6 +42,9 @@ int fm_permute_dispatch(const void* x, const long long* sorted_idx, const float*
                         void* const* dst_tokens, float* const* dst_probs, int* const* dst_flags,
                         long long total_slots, int H, int cap, int nle, int P, int me,
                         int blocks_per_group, int num_ctas, cudaStream_t stream);
+// HP->SP push (see rows_push_kernel).
+int fm_rows_push(const void* src, void* const* dst_base, int* const* dst_flags, long long rows_blk,
+                 int W, int P, int me, int row_blocks, int num_ctas, cudaStream_t stream);
 // Wait (bounded) until every peer's arrival word in `my_flags` reached `epoch`.
 int fm_a2a_wait(const int* my_flags, int my_rank, int nranks, int epoch,
                 unsigned long long timeout_ns, int* status, cudaStream_t stream);

@@ -570,6 +570,80 @@ moe_plan_kernel(const long long* __restrict__ top_idx, const float* __restrict__
   if (tid == 0) routed_per_expert[e] = kept_total;
 }
 
+// --------------------------------------------------------------------------------------------
+// Cross-entropy over bf16 logits, forward and backward in one kernel: one CTA per row makes one
+// pass for the running max / sum (log-sum-exp) and one pass that overwrites the logits with
+// dlogits = (softmax - onehot) * grad_scale.  Rows whose label is negative are ignored (loss 0,
+// zero gradient).  loss_out[row] = lse - logit[label].
+// --------------------------------------------------------------------------------------------
+constexpr int kCeThreads = 512;
+
+__global__ void __launch_bounds__(kCeThreads)
+cross_entropy_kernel(__nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels,
+                     float* __restrict__ loss_out, int V, float grad_scale) {
+  __shared__ float red[kCeThreads / 32];
+  __shared__ float bcast[2];
+  const long long r = blockIdx.x;
+  __nv_bfloat16* row = logits + r * V;
+  const long long label = labels[r];
+  const int nvec = V / 8;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+    float v[8];
+    unpack8(reinterpret_cast<const uint4*>(row)[i], v);
+    float mx = v[0];
+#pragma unroll
+    for (int j = 1; j < 8; ++j) mx = fmaxf(mx, v[j]);
+    if (mx > m) {
+      s *= __expf(m - mx);
+      m = mx;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += __expf(v[j] - m);
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += kCeThreads) {
+    const float x = __bfloat162float(row[i]);
+    if (x > m) {
+      s *= __expf(m - x);
+      m = x;
+    }
+    s += __expf(x - m);
+  }
+  // block reduce of (m, s)
+  float gm = m;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = gm;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = red[0];
+    for (int i = 1; i < kCeThreads / 32; ++i) t = fmaxf(t, red[i]);
+    bcast[0] = t;
+  }
+  __syncthreads();
+  gm = bcast[0];
+  const float total = block_sum<kCeThreads>(m == -INFINITY ? 0.f : s * __expf(m - gm), red);
+  const float lse = gm + __logf(total);
+  if (threadIdx.x == 0)
+    loss_out[r] = label >= 0 ? lse - __bfloat162float(row[label]) : 0.f;
+  __syncthreads();
+  const float scale = label >= 0 ? grad_scale : 0.f;
+  for (int i = threadIdx.x; i < nvec; i += kCeThreads) {
+    float v[8];
+    unpack8(reinterpret_cast<const uint4*>(row)[i], v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float pr = __expf(v[j] - lse);
+      v[j] = (pr - ((long long)(i * 8 + j) == label ? 1.f : 0.f)) * scale;
+    }
+    reinterpret_cast<uint4*>(row)[i] = pack8(v);
+  }
+  for (int i = nvec * 8 + threadIdx.x; i < V; i += kCeThreads) {
+    const float pr = __expf(__bfloat162float(row[i]) - lse);
+    row[i] = __float2bfloat16((pr - ((long long)i == label ? 1.f : 0.f)) * scale);
+  }
+}
+
 }  // namespace fm
 
 static int check_launch(const char* what) {
@@ -717,4 +791,15 @@ extern "C" int fm_moe_plan(const long long* top_idx, const float* top_probs, int
   fm::moe_plan_kernel<<<E, fm::kPlanThreads, 0, s>>>(top_idx, top_probs, T, k, E, cap, sorted_indices,
                                                     slot_probs, slot_of_token, routed_per_expert);
   return check_launch("moe_plan");
+}
+
+extern "C" int fm_cross_entropy(void* logits, const long long* labels, float* loss_out, int T, int V,
+                                float grad_scale, cudaStream_t s) {
+  if ((reinterpret_cast<uintptr_t>(logits) & 15) != 0 || (V % 8) != 0) {
+    fm_set_error("cross_entropy: logits must be 16-byte aligned with V a multiple of 8");
+    return -1;
+  }
+  fm::cross_entropy_kernel<<<T, fm::kCeThreads, 0, s>>>((__nv_bfloat16*)logits, labels, loss_out, V,
+                                                      grad_scale);
+  return check_launch("cross_entropy");
 }

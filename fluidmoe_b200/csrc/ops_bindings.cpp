@@ -57,6 +57,10 @@ void bind_ops(py::module_& m) {
     chk(fm_flash_attn_fwd(p<const void*>(qkv), p<void*>(out), p<float*>(lse), s_, b, G, qpg, d, scale,
                           timeout_ns, p<int*>(status), st(s)), "flash_attn_fwd");
   });
+  m.def("cross_entropy", [](u logits, u labels, u loss, int T, int V, float scale, u s) {
+    chk(fm_cross_entropy(p<void*>(logits), p<const long long*>(labels), p<float*>(loss), T, V, scale, st(s)),
+        "cross_entropy");
+  });
   m.def("adam", [](u prm, u master, u g, u mm, u v, long long n, float lr, float b1, float b2,
                    float eps, float wd, int step, float grad_scale, int zero_grad, int state_bf16, u s) {
     chk(fm_adam(p<void*>(prm), p<float*>(master), p<float*>(g), p<void*>(mm), p<void*>(v), n, lr,

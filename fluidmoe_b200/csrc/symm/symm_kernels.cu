@@ -118,6 +118,34 @@ __global__ void permute_dispatch_kernel(const __nv_bfloat16* __restrict__ x,
   }
 }
 
+// HP->SP push: `src` is [P * rows_blk, W] (rows of block p belong to rank p).  Row i of block p
+// is stored into rank p's buffer at row i, columns [me * W, (me + 1) * W) (leading dimension
+// P * W), and rank p's counter flags[p][me * row_blocks + i / 128] grows by one.  One warp per row.
+// Replaces the HP->SP pairwise rounds of fluid/attention/forward.py:435-452 (and the HP->SP
+// all-to-all of fluid/attention/backward.py:294-349).
+__global__ void rows_push_kernel(const __nv_bfloat16* __restrict__ src,
+                                 __nv_bfloat16* const* __restrict__ dst_base,
+                                 int* const* __restrict__ dst_flags, long long rows_blk, int W, int P,
+                                 int me, int row_blocks) {
+  const int nvec = W / 8;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const long long total = rows_blk * P;
+  for (long long s = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s < total;
+       s += (long long)gridDim.x * warps_per_block) {
+    const int p = (int)((me + 1 + s / rows_blk) % P);   // right-hand neighbour first, self last
+    const long long i = s % rows_blk;
+    const uint4* from = reinterpret_cast<const uint4*>(src + ((long long)p * rows_blk + i) * W);
+    uint4* to = reinterpret_cast<uint4*>(dst_base[p] + i * (long long)P * W + (long long)me * W);
+    for (int v = lane; v < nvec; v += 32) to[v] = from[v];
+    __syncwarp();
+    if (lane == 0) {
+      __threadfence_system();
+      flag_release_add(dst_flags[p] + me * row_blocks + (int)(i / 128), 1);
+    }
+  }
+}
+
 __global__ void a2a_wait_kernel(const int* my_flags, int my_rank, int nranks, int epoch,
                                 unsigned long long timeout_ns, int* status) {
   const int p = threadIdx.x;
@@ -313,6 +341,20 @@ extern "C" int fm_permute_dispatch(const void* x, const long long* sorted_idx, c
       reinterpret_cast<__nv_bfloat16* const*>(dst_tokens), dst_probs, dst_flags, total_slots, H, cap,
       nle, P, me, blocks_per_group);
   return launch_check("permute_dispatch");
+}
+
+extern "C" int fm_rows_push(const void* src, void* const* dst_base, int* const* dst_flags,
+                            long long rows_blk, int W, int P, int me, int row_blocks, int num_ctas,
+                            cudaStream_t stream) {
+  if (W % 8 != 0) {
+    fm_set_error("rows_push: row width must be a multiple of 8");
+    return -1;
+  }
+  if (num_ctas <= 0) num_ctas = 148 * 2;
+  fm::rows_push_kernel<<<num_ctas, 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(src), reinterpret_cast<__nv_bfloat16* const*>(dst_base),
+      dst_flags, rows_blk, W, P, me, row_blocks);
+  return launch_check("rows_push");
 }
 
 extern "C" int fm_a2a_wait(const int* my_flags, int my_rank, int nranks, int epoch,

@@ -59,6 +59,12 @@ void bind_symm(py::module_& m) {
                             cap, nle, P, me, bpg, ctas, as_ptr<cudaStream_t>(stream)),
         "permute_dispatch");
   });
+  m.def("rows_push", [](uintptr_t src, uintptr_t dst_base, uintptr_t dst_flags, long long rows_blk, int W,
+                        int P, int me, int row_blocks, int ctas, uintptr_t stream) {
+    chk(fm_rows_push(as_ptr<const void*>(src), as_ptr<void* const*>(dst_base), as_ptr<int* const*>(dst_flags),
+                     rows_blk, W, P, me, row_blocks, ctas, as_ptr<cudaStream_t>(stream)),
+        "rows_push");
+  });
   m.def("a2a_wait", [](uintptr_t flags, int rank, int n, int epoch, unsigned long long timeout_ns,
                        uintptr_t status, uintptr_t stream) {
     chk(fm_a2a_wait(as_ptr<const int*>(flags), rank, n, epoch, timeout_ns, as_ptr<int*>(status),

@@ -15,6 +15,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
+from .. import _native
 from ..ops import gemm, norm
 from ..ops.rope import make_rope_freqs
 from ..parallel import comm
@@ -50,6 +51,17 @@ class _HeadLoss(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, w, labels):
         logits = gemm.gemm_nt(h, w)                          # [T, V]
+        if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.shape[1] % 8 == 0 \
+                and _native.available():
+            # fused path: the kernel leaves d(loss)/d(logits) for a mean loss in `logits`
+            from ..ops import elementwise
+            n = (labels >= 0).sum().clamp(min=1)
+            rows = elementwise.cross_entropy_(logits, labels, 1.0)
+            loss = rows.sum() / n
+            ctx.save_for_backward(h, logits, n)
+            ctx.w, ctx.fused = w, True
+            return loss
+        ctx.fused = False
         lf = logits.float()
         lse = torch.logsumexp(lf, dim=-1)
         valid = labels >= 0
@@ -62,8 +74,14 @@ class _HeadLoss(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dloss):
-        h, logits, lse, labels, n = ctx.saved_tensors
         w = ctx.w
+        if ctx.fused:
+            h, dlogits, n = ctx.saved_tensors
+            dlogits.mul_((dloss / n).to(dlogits.dtype))
+            dh = gemm.gemm_nn(dlogits, w)
+            _register_dense_dw("lm_head", -1, h, dlogits, w)
+            return dh, None, None
+        h, logits, lse, labels, n = ctx.saved_tensors
         p = torch.exp(logits.float() - lse.unsqueeze(1))
         valid = (labels >= 0).unsqueeze(1)
         p.scatter_add_(1, labels.clamp(min=0).unsqueeze(1), -torch.ones_like(lse).unsqueeze(1))

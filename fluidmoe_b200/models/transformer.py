@@ -90,7 +90,7 @@ class TransformerLayerFunction(torch.autograd.Function):
         x2 = x.reshape(T, H)
         needs_grad = any(ctx.needs_input_grad)
         act = L.activation
-        mode_attn = L.resolve_mode(cp.cp_size, attention=True)
+        mode_attn = L.resolve_mode(cp.cp_size, attention=True, cp_plan=cp)
         mode_moe = L.resolve_mode(ep.ep_size)
         fused = L.fused_ctx
 
@@ -383,10 +383,11 @@ class TransformerLayer(nn.Module):
                 nn.init.normal_(self.shared_w2, mean=0.0, std=self.output_init_std)
 
     # ------------------------------------------------------------------ helpers
-    def resolve_mode(self, group_world: int, attention: bool = False) -> str:
+    def resolve_mode(self, group_world: int, attention: bool = False, cp_plan=None) -> str:
         if group_world == 1:
             return "a2a"
-        fused_ok = self.fused_ctx is not None and (not attention or self.fused_ctx.supports_attention)
+        fused_ok = self.fused_ctx is not None and (
+            not attention or (self.fused_ctx.supports_attention and self.fused_ctx.attention_supported(cp_plan)))
         if self.comm_mode == "auto":
             return "fused" if fused_ok else "p2p"
         if self.comm_mode == "fused":

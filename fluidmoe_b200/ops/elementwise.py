@@ -123,3 +123,13 @@ def moe_plan(top_idx, top_probs, num_experts, capacity):
                            sorted_indices.data_ptr(), slot_probs.data_ptr(), slot_of_token.data_ptr(),
                            routed.data_ptr(), _s())
     return sorted_indices, slot_probs, slot_of_token, routed
+
+
+def cross_entropy_(logits, labels, grad_scale):
+    """In place: returns per-row losses (fp32) and leaves ``(softmax - onehot) * grad_scale`` in
+    ``logits`` (bf16 [T, V], V a multiple of 8)."""
+    T, V = logits.shape
+    loss = torch.empty(T, dtype=torch.float32, device=logits.device)
+    _native.lib().cross_entropy(logits.data_ptr(), labels.contiguous().data_ptr(), loss.data_ptr(), T, V,
+                                float(grad_scale), _s())
+    return loss

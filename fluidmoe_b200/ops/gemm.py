@@ -42,7 +42,7 @@ def check_status(device=None) -> None:
             )
 
 
-CTA_PAIR = int(__import__("os").environ.get("FLUIDMOE_GEMM_CTA_PAIR", "0"))
+CTA_PAIR = int(__import__("os").environ.get("FLUIDMOE_GEMM_CTA_PAIR", "1"))
 
 
 def _launch(desc: dict) -> None:

@@ -62,8 +62,29 @@ class _LayerBuffers:
                                           dtype=torch.int64, device=dev)
 
 
+class _AttnBuffers:
+    """Symmetric buffers of the Ulysses exchanges of one layer."""
+
+    def __init__(self, heap: SymmetricHeap, cp, dtype):
+        P, sl, b = cp.cp_size, cp.seq_local, cp.batch
+        T = sl * b
+        self.row_blocks = (T + 127) // 128
+        dev = heap.device
+        me = heap.rank
+        self.qkv_full = heap.alloc((P * T, cp.proj_per_rank), dtype, zero=False)       # [s_full*b, ppr]
+        self.cnt_qkv = heap.alloc((P,), torch.int32)
+        self.attn_in = heap.alloc((T, P * cp.attn_per_rank), dtype, zero=False)        # [T, n_h*d]
+        self.flags_proj = heap.alloc((P * self.row_blocks,), torch.int32)
+        self.d_attn = heap.alloc((P * T, cp.attn_per_rank), dtype, zero=False)         # [s_full*b, dpr]
+        self.cnt_dattn = heap.alloc((P,), torch.int32)
+        self.dqkv_sp = heap.alloc((T, P * cp.proj_per_rank), dtype, zero=False)        # [T, P*ppr]
+        self.flags_dqkv = heap.alloc((P * self.row_blocks,), torch.int32)
+        self.cnt_qkv_tbl = torch.tensor([a + 4 * me for a in self.cnt_qkv.peer_addrs], dtype=torch.int64, device=dev)
+        self.cnt_dattn_tbl = torch.tensor([a + 4 * me for a in self.cnt_dattn.peer_addrs], dtype=torch.int64, device=dev)
+
+
 class FusedCommContext:
-    supports_attention = False   # the Ulysses exchanges use the pairwise path for now
+    supports_attention = True
 
     def __init__(self, group, heap_bytes: int, device, timeout_ms: float = 8000.0):
         self.group = group
@@ -72,7 +93,13 @@ class FusedCommContext:
         self.rank, self.world = self.heap.rank, self.heap.world
         self.timeout_ns = int(timeout_ms * 1e6)
         self._layers: Dict[int, _LayerBuffers] = {}
+        self._attn: Dict[int, _AttnBuffers] = {}
         self._sig: Dict[int, tuple] = {}
+
+    @staticmethod
+    def attention_supported(cp_plan) -> bool:
+        """The fused Ulysses paths move whole 64-column blocks per source."""
+        return cp_plan is None or (cp_plan.proj_per_rank % 64 == 0 and cp_plan.attn_per_rank % 64 == 0)
 
     # ------------------------------------------------------------------ set-up
     def prepare(self, ep_plan, cp_plan, layer) -> None:
@@ -86,6 +113,9 @@ class FusedCommContext:
         self._sig[lid] = sig
         self._layers[lid] = _LayerBuffers(self.heap, ep_plan, ep_plan.dtype, layer.ffn_hidden_size)
         ep_plan._fused_layer = lid
+        if cp_plan is not None and cp_plan.cp_size > 1 and self.attention_supported(cp_plan):
+            self._attn[lid] = _AttnBuffers(self.heap, cp_plan, cp_plan.dtype)
+            cp_plan._fused_layer = lid
         # every rank must finish allocating (and zeroing counters) before anyone pushes
         torch.cuda.synchronize(self.device)
         if dist.is_initialized() and self.world > 1:
@@ -195,3 +225,93 @@ class FusedCommContext:
         if sched.is_enabled():
             sched.execute_dw_tasks(max_defer_tasks=2)
         return b.dperm.local
+
+
+    # ------------------------------------------------------------------ Ulysses exchanges
+    def _colscatter_gemm(self, a, w, b_layout, P, cols_per_rank, dst: SymmTensor, cnt_tbl, row_offset):
+        """``a @ W`` whose column block p is stored into rank p's buffer at row ``row_offset + row``.
+        N tiles are visited starting right after this rank's own block, so remote data leaves first
+        and the local block is written last."""
+        _count()
+        K = a.shape[1]
+        N = w.shape[1] if b_layout == "kn" else w.shape[0]
+        ap, ai, ao, lda = gemm._operand(a)
+        bp, bi, bo, ldb = gemm._operand(w)
+        lib = _native.lib()
+        bn = 256 if N > 128 else 128
+        nt = (N + bn - 1) // bn
+        me = self.rank
+        rot = (((me + 1) % P) * cols_per_rank // bn) % nt if cols_per_rank % bn == 0 else 0
+        desc = dict(
+            A=ap, a_inner=ai, a_outer=ao, lda=lda, a_mn=0,
+            B=bp, b_inner=bi, b_outer=bo, ldb=ldb, b_mn=1 if b_layout == "kn" else 0,
+            mode=0, num_groups=1, M=a.shape[0], N=N, K=K, b_group_stride=0, uniform_rows=a.shape[0],
+            bn=bn, epi=lib.EPI_COLSCATTER, dst_base=dst.ptr_table, ld_dst=cols_per_rank,
+            cols_per_rank=cols_per_rank, dst_row_offset=row_offset, dst_flags=cnt_tbl.data_ptr(),
+            num_ranks=P, n_rotate=rot, timeout_ns=self.timeout_ns,
+            status=status_buffer(a.device).data_ptr(), cta_pair=gemm.CTA_PAIR)
+        lib.gemm_launch(desc, _native.stream_ptr())
+
+    def _rows_push(self, src2d, P, dst: SymmTensor, flags: SymmTensor, row_blocks):
+        _count()
+        rows_blk = src2d.shape[0] // P
+        _native.lib().rows_push(src2d.data_ptr(), dst.ptr_table, flags.ptr_table, rows_blk, src2d.shape[1],
+                                P, self.rank, row_blocks, 0, _native.stream_ptr())
+
+    def _ksource_gate(self, flags: SymmTensor, cols_per_src: int, row_blocks: int) -> dict:
+        return dict(gate_flags=flags.local.data_ptr(), gate_k_blocks_per_src=cols_per_src // 64,
+                    gate_blocks_per_group=row_blocks, k_rotate=self.rank * (cols_per_src // 64),
+                    timeout_ns=self.timeout_ns)
+
+    def qkv_sp2hp(self, x, qkv_weight, plan):
+        """QKV projection whose epilogue performs the SP->HP exchange (fluid/attention/forward.py:130-277)."""
+        b = self._attn[plan._fused_layer]
+        P, sl, bt, ppr = plan.cp_size, plan.seq_local, plan.batch, plan.proj_per_rank
+        T = sl * bt
+        self._colscatter_gemm(x, qkv_weight, "nk", P, ppr, b.qkv_full, b.cnt_qkv_tbl, self.rank * T)
+        self._wait_counters(b.cnt_qkv, T * (ppr // 32))
+        b.cnt_qkv.local.zero_()
+        return b.qkv_full.local.view(P * sl, bt, plan.groups_per_rank, plan.group_size)
+
+    def hp2sp_outproj(self, attn_out, proj_weight, plan, residual):
+        """HP->SP push followed by the output projection whose K loop consumes each source's
+        column block as it arrives, local block first (fluid/attention/forward.py:332-484)."""
+        b = self._attn[plan._fused_layer]
+        P, sl, bt, dpr = plan.cp_size, plan.seq_local, plan.batch, plan.attn_per_rank
+        T = sl * bt
+        self._rows_push(attn_out.reshape(P * T, dpr), P, b.attn_in, b.flags_proj, b.row_blocks)
+        out = residual.clone() if residual is not None else None
+        out = gemm.grouped_gemm(b.attn_in.local, proj_weight, b_layout="nk", out=out,
+                                accumulate=residual is not None,
+                                gate=self._ksource_gate(b.flags_proj, dpr, b.row_blocks))
+        b.flags_proj.local.zero_()
+        return out, b.attn_in.local
+
+    def outproj_dx_sp2hp(self, d_out, proj_weight, plan):
+        """Region attn_proj: ``dAttn = dOut @ Wproj`` with the SP->HP exchange in the epilogue."""
+        from .scheduler import get_backward_scheduler
+        b = self._attn[plan._fused_layer]
+        P, sl, bt, dpr = plan.cp_size, plan.seq_local, plan.batch, plan.attn_per_rank
+        T = sl * bt
+        self._colscatter_gemm(d_out, proj_weight, "kn", P, dpr, b.d_attn, b.cnt_dattn_tbl, self.rank * T)
+        sched = get_backward_scheduler()
+        if sched.is_enabled():
+            sched.execute_dw_tasks(max_defer_tasks=2)
+        self._wait_counters(b.cnt_dattn, T * (dpr // 32))
+        b.cnt_dattn.local.zero_()
+        return b.d_attn.local.view(P * sl, bt, plan.heads_per_rank, plan.head_dim)
+
+    def hp2sp_qkv_dx(self, dqkv_hp, qkv_weight, plan):
+        """Region attn_qkv: HP->SP push of dQKV, then ``dX = dQKV @ Wqkv`` gated along K by source."""
+        from .scheduler import get_backward_scheduler
+        b = self._attn[plan._fused_layer]
+        P, sl, bt, ppr = plan.cp_size, plan.seq_local, plan.batch, plan.proj_per_rank
+        T = sl * bt
+        self._rows_push(dqkv_hp.reshape(P * T, ppr), P, b.dqkv_sp, b.flags_dqkv, b.row_blocks)
+        sched = get_backward_scheduler()
+        if sched.is_enabled():
+            sched.execute_dw_tasks(max_defer_tasks=2)
+        dx = gemm.grouped_gemm(b.dqkv_sp.local, qkv_weight, b_layout="kn",
+                               gate=self._ksource_gate(b.flags_dqkv, ppr, b.row_blocks))
+        b.flags_dqkv.local.zero_()
+        return dx, b.dqkv_sp.local

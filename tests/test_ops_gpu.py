@@ -102,3 +102,18 @@ def test_moe_plan_kernel_matches_prefix_sum_plan(T, E, k):
     assert torch.equal(got.slot_of_token.cpu(), ref.slot_of_token)
     assert torch.equal(got.routed_per_expert.cpu(), ref.routed_per_expert)
     _close(got.permuted_probs, ref.permuted_probs, 1e-6)
+
+
+def test_fused_cross_entropy():
+    torch.manual_seed(6)
+    T, V = 300, 32000
+    logits = (torch.randn(T, V, device="cuda") * 3).bfloat16()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[5] = -1
+    ref_in = logits.float().clone().requires_grad_(True)
+    ref = torch.nn.functional.cross_entropy(ref_in, labels, ignore_index=-1, reduction="none")
+    ref.sum().backward()
+    work = logits.clone()
+    loss = ew.cross_entropy_(work, labels, 1.0)
+    _close(loss, ref, 1e-2)
+    assert (work.float() - ref_in.grad).abs().max().item() < 1e-2

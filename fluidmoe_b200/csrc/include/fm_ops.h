@@ -41,8 +41,10 @@ int fm_moe_plan(const long long* top_idx, const float* top_probs, int T, int k, 
 
 // Causal GQA flash attention forward on the packed projection buffer
 // qkv [s, b, G, (qpg + 2) * d] (d == 128): out [s, b, G*qpg, d] bf16, lse [b, G*qpg, s] fp32.
+// version 1: one query tile per CTA, P staged in shared memory; 2: two tiles ping-pong, P in TMEM.
 int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg, int d,
-                      float scale, unsigned long long timeout_ns, int* status, cudaStream_t stream);
+                      float scale, unsigned long long timeout_ns, int* status, int version,
+                      cudaStream_t stream);
 
 #ifdef __cplusplus
 }

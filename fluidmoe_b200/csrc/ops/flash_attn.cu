@@ -308,6 +308,304 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a)
   }
 }
 
+// =========================================================================================
+// Second-generation forward: one CTA owns TWO consecutive 128-row query tiles of a head and
+// ping-pongs between them.  While the softmax warps of one tile work on their score block, the
+// tensor core runs P.V of the other tile and the next Q.K^T, so MMA and softmax overlap.
+// The probability block is written back to TMEM over the score block (bf16, two values per
+// 32-bit column) and P.V takes its A operand from TMEM, which frees the shared memory that
+// staged P before and lets K/V blocks (shared by both tiles) be double buffered.  The output
+// accumulates in TMEM across key blocks; it is rescaled only when the running row maximum grows
+// by more than 2^8 (otherwise the stale maximum stays in use, which is exact after the final
+// division by the row sum).
+// =========================================================================================
+constexpr int kFa2Threads = 320;   // TMA warp, MMA warp, 4 + 4 softmax warps
+constexpr int kKernelIdFlashFwd2 = 21;
+
+__global__ void __launch_bounds__(kFa2Threads, 1)
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                      // 2 tiles
+  uint8_t* sK = smem + 2 * kTileBytes;     // 2 stages
+  uint8_t* sV = smem + 4 * kTileBytes;     // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  uint64_t* q_full = bars;           // [2]
+  uint64_t* k_full = bars + 2;       // [2]
+  uint64_t* v_full = bars + 4;       // [2]
+  uint64_t* k_empty = bars + 6;      // [2]
+  uint64_t* v_empty = bars + 8;      // [2]
+  uint64_t* s_full = bars + 10;      // [2] per tile
+  uint64_t* p_full = bars + 12;      // [2]
+  uint64_t* o_full = bars + 14;      // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (a.s + kFaBM - 1) / kFaBM;
+  const int npairs = (nq + 1) / 2;
+  const int pair = npairs - 1 - (int)blockIdx.x;   // longest rows first
+  const int h = blockIdx.y, bb = blockIdx.z;
+  const int g = h / a.qpg, hi = h % a.qpg;
+  const int heads_per_group = a.qpg + 2;
+  const int col_q = ((bb * a.G + g) * heads_per_group + hi) * kFaD;
+  const int col_k = ((bb * a.G + g) * heads_per_group + a.qpg) * kFaD;
+  const int col_v = col_k + kFaD;
+  const int nkv = (a.s + kFaBN - 1) / kFaBN;
+  int nblk[2];
+  nblk[0] = min(2 * pair + 1, nkv);
+  nblk[1] = (2 * pair + 1 < nq) ? min(2 * pair + 2, nkv) : 0;
+  const int nmax = max(nblk[0], nblk[1]);
+  const uint64_t timeout = a.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&o_full[i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int w = 0; w < 2; ++w) {
+        if (nblk[w] == 0) continue;
+        const int q0 = (2 * pair + w) * kFaBM;
+        mbar_expect_tx(&q_full[w], kTileBytes);
+        tma_load_2d(sQ + w * kTileBytes, &tmap, &q_full[w], col_q, q0);
+        tma_load_2d(sQ + w * kTileBytes + kTileBytes / 2, &tmap, &q_full[w], col_q + 64, q0);
+      }
+      for (int j = 0; j < nmax; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = ((j >> 1) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd2, 100 + st, 0, 0);
+          break;
+        }
+        mbar_expect_tx(&k_full[st], kTileBytes);
+        tma_load_2d(sK + st * kTileBytes, &tmap, &k_full[st], col_k, j * kFaBN);
+        tma_load_2d(sK + st * kTileBytes + kTileBytes / 2, &tmap, &k_full[st], col_k + 64, j * kFaBN);
+        if (!mbar_wait(&v_empty[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd2, 110 + st, 0, 0);
+          break;
+        }
+        mbar_expect_tx(&v_full[st], kTileBytes);
+        tma_load_2d(sV + st * kTileBytes, &tmap, &v_full[st], col_v, j * kFaBN);
+        tma_load_2d(sV + st * kTileBytes + kTileBytes / 2, &tmap, &v_full[st], col_v + 64, j * kFaBN);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
+      bool ok = true;
+      auto issue_qk = [&](int w, int j) {
+        const uint32_t q_addr = smem_u32(sQ + w * kTileBytes);
+        const uint32_t k_addr = smem_u32(sK + (j & 1) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
+          umma_bf16(tmem_base + w * 128, umma_smem_desc(q_addr + off, 0, 1024),
+                    umma_smem_desc(k_addr + off, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[w]);
+      };
+      auto issue_pv = [&](int w, int j) {
+        const uint32_t v_addr = smem_u32(sV + (j & 1) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ts(tmem_base + 256 + w * 128, tmem_base + w * 128 + kk * 8,
+                       umma_smem_desc(v_addr + kk * 2048, kTileBytes / 2, 1024), idesc_pv,
+                       (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&o_full[w]);
+      };
+      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
+        if (mbar_wait(bar, parity, timeout, abort_flag)) return true;
+        report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd2, what, 0, 0);
+        return false;
+      };
+      // prologue: S_w(0) for both tiles
+      for (int w = 0; ok && w < 2; ++w)
+        if (nblk[w] > 0) ok = wait_or_fail(&q_full[w], 0, 200 + w);
+      if (ok && nmax > 0) ok = wait_or_fail(&k_full[0], 0, 210);
+      if (ok) {
+        tc_fence_after_sync();
+        for (int w = 0; w < 2; ++w)
+          if (nblk[w] > 0) issue_qk(w, 0);
+        umma_commit(&k_empty[0]);
+      }
+      for (int j = 0; ok && j < nmax; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        ok = wait_or_fail(&v_full[st], ph, 230 + st);
+        bool k_next_ready = false;
+        for (int w = 0; ok && w < 2; ++w) {
+          if (j >= nblk[w]) continue;
+          ok = wait_or_fail(&p_full[w], j & 1, 220 + w);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_pv(w, j);
+          if (j + 1 < nblk[w]) {
+            if (!k_next_ready) {
+              ok = wait_or_fail(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 240);
+              if (!ok) break;
+              tc_fence_after_sync();
+              k_next_ready = true;
+            }
+            issue_qk(w, j + 1);
+          }
+        }
+        if (!ok) break;
+        umma_commit(&v_empty[st]);
+        if (j + 1 < nmax) umma_commit(&k_empty[(j + 1) & 1]);
+      }
+    }
+  } else {
+    // ------------------------------- softmax warps (two groups of 4) -------------------------------
+    const int w = (warp - 2) >> 2;       // which query tile this warp group owns
+    const int q = warp & 3;              // TMEM lane quarter
+    const int r = q * 32 + lane;
+    const int qt = 2 * pair + w;
+    const int row = qt * kFaBM + r;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t t_s = tmem_base + w * 128 + lane_addr;          // S (fp32) / P (packed bf16)
+    const uint32_t t_o = tmem_base + 256 + w * 128 + lane_addr;    // O accumulator
+    const int nb = nblk[w];
+    float m_used = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb; ++j) {
+      if (!mbar_wait(&s_full[w], j & 1, timeout, abort_flag)) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd2, 300 + w, 0, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const bool diag = (j == qt);
+      const int kv0 = j * kFaBN;
+      float m_blk = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = kv0 + c * 32 + i;
+          const bool masked = (diag && col > row) || col >= a.s;
+          m_blk = fmaxf(m_blk, masked ? -INFINITY : __uint_as_float(v[i]) * a.scale_log2);
+        }
+      }
+      // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 above it.
+      const float m_new = fmaxf(m_used, m_blk);
+      const bool first = (j == 0);
+      const bool grow = !first && (m_new > m_used + 8.0f);
+      if (first) m_used = (m_new == -INFINITY) ? 0.f : m_new;
+      if (__any_sync(0xffffffffu, grow)) {
+        // O holds the sum of blocks 0..j-1; P.V of block j-1 must have finished before it is touched.
+        if (!mbar_wait(&o_full[w], (j - 1) & 1, timeout, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const float f = grow ? exp2f(m_used - m_new) : 1.0f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_st_32x32(t_o + c * 32, v);
+        }
+        tmem_st_wait();
+        if (grow) {
+          l_run *= f;
+          m_used = m_new;
+        }
+      }
+      float l_blk = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + c * 32, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int col = kv0 + c * 32 + 2 * i;
+          const bool mk0 = (diag && col > row) || col >= a.s;
+          const bool mk1 = (diag && col + 1 > row) || col + 1 >= a.s;
+          const float p0 = mk0 ? 0.f : exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_used);
+          const float p1 = mk1 ? 0.f : exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_used);
+          l_blk += p0 + p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        // P columns [16c, 16c+16) alias score columns that were read in an earlier chunk
+        tmem_st_32x16(t_s + c * 16, pk);
+      }
+      tmem_st_wait();
+      l_run += l_blk;
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[w]);
+    }
+    if (ok && nb > 0 && mbar_wait(&o_full[w], (nb - 1) & 1, timeout, abort_flag)) {
+      tc_fence_after_sync();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int hq = a.G * a.qpg;
+      __nv_bfloat16* dst = a.out + (((long long)row * a.b + bb) * hq + h) * kFaD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_o + c * 32, v);
+        tmem_ld_wait();
+        if (row < a.s) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
+            reinterpret_cast<uint4*>(dst)[c * 4 + u] = o;
+          }
+        }
+      }
+      if (row < a.s)
+        a.lse[((long long)bb * hq + h) * a.s + row] = (m_used + log2f(l_run)) * 0.6931471805599453f;
+    }
+    tc_fence_before_sync();
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 }  // namespace fm
 
 typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -317,7 +615,7 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg,
                                  int d, float scale, unsigned long long timeout_ns, int* status,
-                                 cudaStream_t stream) {
+                                 int version, cudaStream_t stream) {
   if (d != fm::kFaD) {
     fm_set_error("flash_attn_fwd: head_dim must be 128");
     return -1;
@@ -368,8 +666,24 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
   a.lse = lse;
   a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
   a.status = status;
-  dim3 grid((s + fm::kFaBM - 1) / fm::kFaBM, G * qpg, b);
-  fm::flash_fwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tmap, a);
+  if (version == 2) {
+    static bool configured2 = false;
+    if (!configured2) {
+      cudaError_t e2 = cudaFuncSetAttribute(fm::flash_fwd2_kernel,
+                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e2 != cudaSuccess) {
+        fm_set_error(cudaGetErrorString(e2));
+        return (int)e2;
+      }
+      configured2 = true;
+    }
+    const int nq = (s + fm::kFaBM - 1) / fm::kFaBM;
+    dim3 grid2((nq + 1) / 2, G * qpg, b);
+    fm::flash_fwd2_kernel<<<grid2, fm::kFa2Threads, smem, stream>>>(tmap, a);
+  } else {
+    dim3 grid((s + fm::kFaBM - 1) / fm::kFaBM, G * qpg, b);
+    fm::flash_fwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tmap, a);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fm_set_error(cudaGetErrorString(e));

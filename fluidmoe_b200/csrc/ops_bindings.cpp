@@ -53,9 +53,9 @@ void bind_ops(py::module_& m) {
                     p<float*>(sp), p<int*>(sot), p<int*>(rpe), st(s)), "moe_plan");
   });
   m.def("flash_attn_fwd", [](u qkv, u out, u lse, int s_, int b, int G, int qpg, int d, float scale,
-                             unsigned long long timeout_ns, u status, u s) {
+                             unsigned long long timeout_ns, u status, int version, u s) {
     chk(fm_flash_attn_fwd(p<const void*>(qkv), p<void*>(out), p<float*>(lse), s_, b, G, qpg, d, scale,
-                          timeout_ns, p<int*>(status), st(s)), "flash_attn_fwd");
+                          timeout_ns, p<int*>(status), version, st(s)), "flash_attn_fwd");
   });
   m.def("cross_entropy", [](u logits, u labels, u loss, int T, int V, float scale, u s) {
     chk(fm_cross_entropy(p<void*>(logits), p<const long long*>(labels), p<float*>(loss), T, V, scale, st(s)),

@@ -6,7 +6,10 @@ import torch
 from .. import _native
 from .gemm import status_buffer
 
+import os
+
 LAUNCHES = 0
+VERSION = int(os.environ.get("FLUIDMOE_FLASH_VERSION", "1"))
 
 
 def supported(qkv: torch.Tensor, head_dim: int) -> bool:
@@ -14,7 +17,7 @@ def supported(qkv: torch.Tensor, head_dim: int) -> bool:
             and _native.available() and hasattr(_native.lib(), "flash_attn_fwd"))
 
 
-def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float):
+def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float, version: int = 0):
     """qkv: [s, b, G, (qpg + 2) * d] -> (out [s, b, G*qpg, d], lse [b, G*qpg, s])."""
     global LAUNCHES
     s, b, G, gs = qkv.shape
@@ -24,5 +27,5 @@ def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sc
     LAUNCHES += 1
     _native.lib().flash_attn_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), s, b, G, q_per_group,
                                  head_dim, float(scale), 0, status_buffer(qkv.device).data_ptr(),
-                                 _native.stream_ptr())
+                                 version or VERSION, _native.stream_ptr())
     return out, lse

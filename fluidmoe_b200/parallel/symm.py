@@ -92,7 +92,11 @@ class SymmetricHeap:
             raise MemoryError(
                 f"symmetric heap exhausted: need {end - start} more bytes, {self.nbytes - start} left")
         self._cursor = end
-        local = self._slab[start:start + nbytes].view(dtype).view(*shape)
+        # A tensor of its own over the slice (not a view of the slab): every allocation gets its
+        # own autograd version counter, so an in-place update of one buffer (a counter reset, an
+        # in-place RoPE) does not invalidate tensors saved for backward that live in another.
+        local = tensor_from_ptr(self._base + start, max(nbytes, 1), self.device, owner=self)[:nbytes] \
+            .view(dtype).view(*shape)
         if zero and start < self._high_water:
             # Re-used region: clear it.  Peers may only write here after the next collective
             # synchronisation of the group (callers that hand the buffer to peers do that).

@@ -9,13 +9,14 @@ from fluidmoe_b200.ops import attention, flash, gemm
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("s,b,G,qpg", [(128, 1, 1, 1), (256, 2, 2, 4), (1000, 1, 1, 4), (2048, 1, 2, 2)])
-def test_flash_fwd_matches_reference(s, b, G, qpg):
+@pytest.mark.parametrize("version", [1, 2])
+@pytest.mark.parametrize("s,b,G,qpg", [(128, 1, 1, 1), (256, 2, 2, 4), (1000, 1, 1, 4), (2048, 1, 2, 2), (640, 1, 1, 2)])
+def test_flash_fwd_matches_reference(s, b, G, qpg, version):
     d = 128
     torch.manual_seed(0)
     qkv = torch.randn(s, b, G, (qpg + 2) * d, device="cuda").bfloat16()
     assert flash.supported(qkv, d)
-    out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, 1.0 / math.sqrt(d))
+    out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, 1.0 / math.sqrt(d), version)
     torch.cuda.synchronize()
     gemm.check_status()
     heads = qkv.float().cpu().view(s, b, G, qpg + 2, d)
@@ -26,19 +27,20 @@ def test_flash_fwd_matches_reference(s, b, G, qpg):
     assert (lse.cpu() - rl).abs().max().item() < 2e-2
 
 
-def test_flash_fwd_speed():
+@pytest.mark.parametrize("version", [1, 2])
+def test_flash_fwd_speed(version):
     s, b, G, qpg, d = 8192, 1, 2, 4, 128
     qkv = torch.randn(s, b, G, (qpg + 2) * d, device="cuda").bfloat16()
     for _ in range(3):
-        flash.flash_attn_fwd_packed(qkv, qpg, d, 0.088)
+        flash.flash_attn_fwd_packed(qkv, qpg, d, 0.088, version)
     torch.cuda.synchronize()
     st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     st.record()
     for _ in range(10):
-        flash.flash_attn_fwd_packed(qkv, qpg, d, 0.088)
+        flash.flash_attn_fwd_packed(qkv, qpg, d, 0.088, version)
     en.record()
     torch.cuda.synchronize()
     gemm.check_status()
     ms = st.elapsed_time(en) / 10
     flops = 4 * s * s * G * qpg * d / 2
-    print(f"\nflash fwd s={s} heads={G*qpg}: {ms:.3f} ms, {flops / ms / 1e9:.1f} TFLOP/s")
+    print(f"\nflash fwd v{version} s={s} heads={G*qpg}: {ms:.3f} ms, {flops / ms / 1e9:.1f} TFLOP/s")

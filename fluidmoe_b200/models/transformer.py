@@ -29,6 +29,7 @@ from ..parallel.schedule import MultiCardOverlapContext
 from ..utils.nvtx import nvtx_range
 from . import attention as attn_mod
 from . import moe as moe_mod
+from . import moe_dropless
 
 
 def _activation_name(fn: Union[str, Callable, None]) -> str:
@@ -63,7 +64,8 @@ class LayerRuntime:
         self.sig = sig
         s_loc, b, H = x.shape
         self.ep_plan = moe_mod.EPPlan(s_loc * b, H, L.num_experts, L.top_k, L.ep_group,
-                                      L.capacity_factor, x.dtype, x.device, L.moe_overlap_ctx)
+                                      L.capacity_factor if not L.dropless else 1.0, x.dtype, x.device,
+                                      L.moe_overlap_ctx)
         self.cp_plan = attn_mod.CPPlan(s_loc, b, H, L.num_heads, L.num_kv_heads, L.head_dim,
                                        L.cp_group, x.dtype, x.device, L.attn_overlap_ctx)
         self.ep_plan.layer_id = self.cp_plan.layer_id = L.layer_id
@@ -111,15 +113,24 @@ class TransformerLayerFunction(torch.autograd.Function):
         # ---- MoE half ----
         with nvtx_range("ln2"):
             ln2_out, mean2, rstd2 = norm.norm_fwd(h1, ln2_w, ln2_b, L.norm_eps, L.norm_type)
-        gather = not (mode_moe == "fused" and ep.ep_size > 1)
-        (permuted, probs, sorted_idx, _tpe, top_idx, top_probs, logits, _rmap, rplan) = \
-            moe_mod.router_forward(ln2_out, router_w, L.num_experts, L.top_k, L.ep_group,
-                                   L.capacity_factor, ep, L.router_dtype, gather_tokens=gather)
-        with nvtx_range("dispatch_fc1"):
-            st = moe_mod.dispatch_fc1_forward(ep, permuted, probs, w1, act, mode_moe, save_pre=needs_grad,
-                                              fused_ctx=fused, hidden_states=ln2_out, sorted_indices=sorted_idx)
-        with nvtx_range("fc2_combine"):
-            combined = moe_mod.fc2_combine_forward(ep, st, w2, mode_moe, fused)
+        if L.dropless:
+            mode_moe = "dropless"
+            logits = router_ops.router_logits(ln2_out, router_w, L.router_dtype)
+            top_idx, top_probs = router_ops.topk_softmax(logits, L.top_k)
+            rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
+            with nvtx_range("dropless_moe"):
+                combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, needs_grad)
+        else:
+            gather = not (mode_moe == "fused" and ep.ep_size > 1)
+            (permuted, probs, sorted_idx, _tpe, top_idx, top_probs, logits, _rmap, rplan) = \
+                moe_mod.router_forward(ln2_out, router_w, L.num_experts, L.top_k, L.ep_group,
+                                       L.capacity_factor, ep, L.router_dtype, gather_tokens=gather)
+            with nvtx_range("dispatch_fc1"):
+                st = moe_mod.dispatch_fc1_forward(ep, permuted, probs, w1, act, mode_moe, save_pre=needs_grad,
+                                                  fused_ctx=fused, hidden_states=ln2_out,
+                                                  sorted_indices=sorted_idx)
+            with nvtx_range("fc2_combine"):
+                combined = moe_mod.fc2_combine_forward(ep, st, w2, mode_moe, fused)
         residual = h1
         sh_pre = sh_act = None
         if shared_w1 is not None:
@@ -172,24 +183,13 @@ class TransformerLayerFunction(torch.autograd.Function):
         nle, cap = ep.num_local_experts, ep.expert_capacity
         cfg = L._moe_chunk_config
 
-        # ---- R1: combine gradient -> FC2 dX + activation backward ----
-        with nvtx_range("bwd_moe_combine"):
-            if mode_moe == "fused" and P > 1:
-                grad_combined = None
-            else:
+        if mode_moe == "dropless":
+            # variable-split path: all-to-all-v in, grouped GEMMs over device-sized groups, all-to-all-v out
+            with nvtx_range("bwd_dropless_moe"):
                 grad_combined = permute.permute_rows(dy2, rplan.sorted_indices)
-            dfc2_em, dpre_em, dprobs_em = moe_mod.combine_fc2_backward(
-                ep, grad_combined, st, w2, act, cfg["moe_combine"].num_chunks, mode_moe,
-                fused_ctx=_FusedBwd(fused, dy2, rplan) if (mode_moe == "fused" and P > 1) else None)
-        moe_mod.register_moe_dw_tasks(ep, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe")
-
-        # ---- routing-probability gradient back to the token owners, router backward ----
-        with nvtx_range("bwd_router"):
-            if P > 1:
-                send = moe_mod.expert_to_rank_major(dprobs_em, P, nle, cap).contiguous()
-                dprobs_perm = comm.all_to_all(send, ep.group)
-            else:
-                dprobs_perm = dprobs_em
+                dfc2_em, dpre_em, dprobs_perm, dperm = moe_dropless.backward(rplan, grad_combined, st, w1, w2,
+                                                                             act, L.ep_group)
+            moe_dropless.register_dw_tasks(rplan, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe")
             tpe_global = None
             if L.aux_loss_coeff > 0.0:
                 tpe_global = rplan.routed_per_expert.float()
@@ -200,19 +200,51 @@ class TransformerLayerFunction(torch.autograd.Function):
                 L.z_loss_coeff, tpe_global, T * cp.cp_size)
             d_ln2_router = (dlogits.to(router_w.dtype) @ router_w.detach().t()).to(dy2.dtype)
             ln2_for_dw = ln2_out
+            sched.register_dw_task(f"layer{lid}.router", lid,
+                                   lambda: (ln2_for_dw.float().t() @ dlogits).to(torch.float32), router_w)
+            d_ln2 = permute.unpermute_reduce(dperm, rplan.slot_of_token, d_ln2_router)
+        else:
+            # ---- R1: combine gradient -> FC2 dX + activation backward ----
+            with nvtx_range("bwd_moe_combine"):
+                if mode_moe == "fused" and P > 1:
+                    grad_combined = None
+                else:
+                    grad_combined = permute.permute_rows(dy2, rplan.sorted_indices)
+                dfc2_em, dpre_em, dprobs_em = moe_mod.combine_fc2_backward(
+                    ep, grad_combined, st, w2, act, cfg["moe_combine"].num_chunks, mode_moe,
+                    fused_ctx=_FusedBwd(fused, dy2, rplan) if (mode_moe == "fused" and P > 1) else None)
+            moe_mod.register_moe_dw_tasks(ep, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe")
 
-            def router_dw():
-                return (ln2_for_dw.float().t() @ dlogits).to(torch.float32)
-            sched.register_dw_task(f"layer{lid}.router", lid, router_dw, router_w)
+            # ---- routing-probability gradient back to the token owners, router backward ----
+            with nvtx_range("bwd_router"):
+                if P > 1:
+                    send = moe_mod.expert_to_rank_major(dprobs_em, P, nle, cap).contiguous()
+                    dprobs_perm = comm.all_to_all(send, ep.group)
+                else:
+                    dprobs_perm = dprobs_em
+                tpe_global = None
+                if L.aux_loss_coeff > 0.0:
+                    tpe_global = rplan.routed_per_expert.float()
+                    if cp.cp_size > 1:
+                        dist.all_reduce(tpe_global, group=cp.group)
+                dlogits = router_ops.router_backward_logits(
+                    dprobs_perm, rplan, top_idx, top_probs, logits, L.num_experts, L.aux_loss_coeff,
+                    L.z_loss_coeff, tpe_global, T * cp.cp_size)
+                d_ln2_router = (dlogits.to(router_w.dtype) @ router_w.detach().t()).to(dy2.dtype)
+                ln2_for_dw = ln2_out
 
-        # ---- R2: FC1 dX -> dispatch gradient -> token order ----
-        with nvtx_range("bwd_moe_dispatch"):
-            dperm = moe_mod.fc1_dispatch_backward(ep, dpre_em, w1, cfg["moe_dispatch"].num_chunks, mode_moe,
-                                                  fused_ctx=fused)
-            if mode_moe == "fused" and P > 1:
-                d_ln2 = fused.unpermute(ep, dperm, rplan.slot_of_token, d_ln2_router)
-            else:
-                d_ln2 = permute.unpermute_reduce(dperm, rplan.slot_of_token, d_ln2_router)
+                def router_dw():
+                    return (ln2_for_dw.float().t() @ dlogits).to(torch.float32)
+                sched.register_dw_task(f"layer{lid}.router", lid, router_dw, router_w)
+
+            # ---- R2: FC1 dX -> dispatch gradient -> token order ----
+            with nvtx_range("bwd_moe_dispatch"):
+                dperm = moe_mod.fc1_dispatch_backward(ep, dpre_em, w1, cfg["moe_dispatch"].num_chunks, mode_moe,
+                                                      fused_ctx=fused)
+                if mode_moe == "fused" and P > 1:
+                    d_ln2 = fused.unpermute(ep, dperm, rplan.slot_of_token, d_ln2_router)
+                else:
+                    d_ln2 = permute.unpermute_reduce(dperm, rplan.slot_of_token, d_ln2_router)
 
         # ---- shared experts (dense, local) ----
         if ctx.has_shared:
@@ -315,6 +347,7 @@ class TransformerLayer(nn.Module):
         self.activation = _activation_name(activation_func)
         self.shared_activation = self.activation
         self.capacity_factor = capacity_factor
+        self.dropless = capacity_factor is None or capacity_factor <= 0   # keep every routed pair
         self.router_dtype = router_dtype
         self.aux_loss_coeff, self.z_loss_coeff = aux_loss_coeff, z_loss_coeff
         self.init_std = init_std

@@ -50,7 +50,7 @@ def attention_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch
         from . import flash
         return flash.flash_attn_bwd(dout, q, k, v, out, lse, scale, causal)
     if q.is_cuda:
-        return _sdpa_bwd(dout, q, k, v, scale, causal)
+        return _sdpa_bwd(dout, q, k, v, scale, causal, out, lse if (lse is not None and lse.dtype == torch.float32) else None)
     qf = q.float().permute(1, 2, 0, 3)
     kf = k.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
     vf = v.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
@@ -88,16 +88,51 @@ def attention_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sca
 
 
 # ---- library attention, used on CUDA where this library's own kernel does not apply ----
+_CUDNN_DIRECT = {"ok": None}   # None = untested, True / False after the first attempt
+
+
 def _sdpa_fwd(q, k, v, scale, causal):
+    """Library forward.  When the fused cuDNN op is reachable directly it also yields the
+    log-sum-exp, so the backward can run without recomputing the forward."""
     import torch.nn.functional as F
     hq, hkv = q.shape[2], k.shape[2]
+    if _CUDNN_DIRECT["ok"] is not False and q.dtype in (torch.bfloat16, torch.float16):
+        try:
+            res = torch.ops.aten._scaled_dot_product_cudnn_attention(
+                q.permute(1, 2, 0, 3), k.permute(1, 2, 0, 3), v.permute(1, 2, 0, 3), None, True, 0.0,
+                causal, False, scale=scale)
+            _CUDNN_DIRECT["ok"] = True
+            lse = res[1]
+            return res[0].permute(2, 0, 1, 3).contiguous(), lse.reshape(lse.shape[0], lse.shape[1], -1)
+        except Exception:  # noqa: BLE001 - op unavailable for this shape / build
+            if _CUDNN_DIRECT["ok"] is None:
+                _CUDNN_DIRECT["ok"] = False
     out = F.scaled_dot_product_attention(q.permute(1, 2, 0, 3), k.permute(1, 2, 0, 3),
                                          v.permute(1, 2, 0, 3), is_causal=causal, scale=scale,
                                          enable_gqa=hq != hkv)
     return out.permute(2, 0, 1, 3).contiguous(), None
 
 
-def _sdpa_bwd(dout, q, k, v, scale, causal):
+def _cudnn_bwd_direct(dout, q, k, v, out, lse, scale, causal):
+    """Library backward from saved output and log-sum-exp ([b, h, s] fp32, natural log)."""
+    s, b, hq, d = q.shape
+    empty = torch.empty(0, device=q.device, dtype=torch.int32)
+    seed = torch.zeros((), dtype=torch.int64, device=q.device)
+    dq, dk, dv = torch.ops.aten._scaled_dot_product_cudnn_attention_backward(
+        dout.permute(1, 2, 0, 3), q.permute(1, 2, 0, 3), k.permute(1, 2, 0, 3), v.permute(1, 2, 0, 3),
+        out.permute(1, 2, 0, 3), lse.reshape(b, hq, s, 1).contiguous(), seed, seed, None, empty, empty,
+        s, s, 0.0, causal, scale=scale)
+    return dq.permute(2, 0, 1, 3), dk.permute(2, 0, 1, 3), dv.permute(2, 0, 1, 3)
+
+
+def _sdpa_bwd(dout, q, k, v, scale, causal, out=None, lse=None):
+    if out is not None and lse is not None and lse.dim() == 3 and _CUDNN_DIRECT["ok"] is not False:
+        try:
+            res = _cudnn_bwd_direct(dout, q, k, v, out, lse, scale, causal)
+            _CUDNN_DIRECT["ok"] = True
+            return res
+        except Exception:  # noqa: BLE001
+            _CUDNN_DIRECT["ok"] = False
     import torch.nn.functional as F
     hq, hkv = q.shape[2], k.shape[2]
     with torch.enable_grad():

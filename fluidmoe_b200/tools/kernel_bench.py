@@ -171,8 +171,54 @@ def case_rope(a):
            bytes_=s * G * (qpg + 1) * d * 4.0)
 
 
+def case_fused(a):
+    """The device-initiated dispatch / combine kernels on one GPU: the only "peer" is this GPU
+    itself, so the same kernels (peer-pointer tables, arrival counters, gated producer, scatter
+    epilogue) run as on several GPUs, minus the NVLink hop."""
+    from ..models.moe import EPPlan, MoEForwardState
+    from ..parallel.fused import FusedCommContext
+
+    T, H, F, E, k = a.rows // 2, a.hidden, a.ffn, a.experts if a.experts > 1 else 8, 2
+    dev = torch.device("cuda", torch.cuda.current_device())
+    ctx = FusedCommContext(None, 2 << 30, dev)
+    plan = EPPlan(T, H, E, k, None, 1.0, torch.bfloat16, dev)
+
+    class _L:
+        layer_id, ffn_hidden_size = 0, F
+    ctx.prepare(plan, None, _L)
+    x = _r(T, H)
+    ti, tp = router.topk_softmax(torch.randn(T, E, device="cuda"), k)
+    rp = router.build_padded_plan(ti, tp, E, plan.expert_capacity)
+    w1, w2 = _r(E, H, 2 * F, scale=0.02), _r(E, F, H, scale=0.02)
+    b = ctx._buf(plan)
+    rows = E * plan.expert_capacity
+
+    def push():
+        ctx._push(plan, x, rp.sorted_indices, rp.permuted_probs, b.tokens_em, b.probs_em, b.flags_fwd, b.bpg)
+
+    def push_and_reset():
+        push()
+        b.flags_fwd.local.zero_()
+    report(f"permute+dispatch (peer stores) {rows}x{H}", timed(push_and_reset), bytes_=rows * H * 4.0)
+
+    def fc1():
+        push()
+        st = gemm.grouped_gemm_act(b.tokens_em.local, w1, b.probs_em.local, activation="swiglu",
+                                   uniform_rows=plan.expert_capacity, gate=ctx._gate(b.flags_fwd, b.bpg))
+        b.flags_fwd.local.zero_()
+        return st
+    report(f"dispatch + gated FC1 G={E} {rows}x{H}x{2 * F}", timed(fc1), 2.0 * rows * H * 2 * F)
+    act, pre = fc1()
+    state = MoEForwardState(b.tokens_em.local, b.probs_em.local, pre, act)
+
+    def fc2():
+        ctx._scatter_gemm(plan, state.act_em, w2, "kn", b.combined, b.cnt_combine_tbl)
+        return ctx.unpermute(plan, b.combined.local, rp.slot_of_token, x)
+    report(f"FC2 + combine (scatter epilogue) + unpermute {rows}x{F}x{H}", timed(fc2), 2.0 * rows * F * H)
+
+
 CASES = dict(gemm=case_gemm, fc1=case_fc1, dact=case_dact, wgrad=case_wgrad, flash=case_flash, norm=case_norm,
-             permute=case_permute, adam=case_adam, ce=case_ce, rope=case_rope)
+             permute=case_permute, adam=case_adam, ce=case_ce, rope=case_rope, fused=case_fused)
 
 
 def main(argv=None):

@@ -10,7 +10,7 @@ import torch
 from tests.dist_utils import run_distributed
 
 
-def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act):
+def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act, capacity_factor=1.0):
     import torch.distributed as dist
     from fluidmoe_b200.distributed import init_parallel
     from fluidmoe_b200.models.transformer import TransformerLayer
@@ -22,7 +22,7 @@ def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act):
     s_loc, b = 32, 2
     pc = init_parallel()
     kw = dict(dtype=torch.float32, device="cpu", router_dtype=torch.float32, activation_func=act,
-              norm_type=norm_type, init_std=0.05)
+              norm_type=norm_type, init_std=0.05, capacity_factor=capacity_factor)
     # every rank builds the same full single-process layer, then its sharded twin
     torch.manual_seed(1)
     solo = [dist.new_group([r]) for r in range(world)][rank]   # a group of this rank alone
@@ -148,3 +148,18 @@ def test_moe_overlap_matches_moebaseline_world2():
     for res in run_distributed(_moe_vs_moebaseline, 2):
         for name, (err, scale) in res.items():
             assert err / (scale + 1e-9) < 1e-4, (name, err, scale)
+
+
+def test_dropless_matches_padded_without_drops_world2():
+    """With capacity = all tokens nothing is dropped in padded mode, so the variable-split
+    (dropless) path must give the same outputs and gradients."""
+    base = run_distributed(_layer_vs_single, 2, "a2a", "F", 1, "rmsnorm", "swiglu", 2.0)   # E/k = 2 -> cap = T
+    got = run_distributed(_layer_vs_single, 2, "a2a", "FB", 1, "rmsnorm", "swiglu", 0.0)
+    for r in range(2):
+        yb, gxb, gb = base[r]
+        y, gx, g = got[r]
+        assert torch.allclose(y, yb, atol=2e-5), (y - yb).abs().max()
+        assert torch.allclose(gx, gxb, atol=2e-4), (gx - gxb).abs().max()
+        for n in gb:
+            scale = gb[n].abs().max().item() + 1e-6
+            assert (g[n] - gb[n]).abs().max().item() / scale < 1e-4, n

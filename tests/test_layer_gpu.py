@@ -56,3 +56,41 @@ def test_layer_forward_backward_matches_cpu(norm_type, act, nsh, E, k):
     assert fro(xg.grad, xc.grad) < 8e-2, fro(xg.grad, xc.grad)
     for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
         assert fro(pg.grad, pc.grad) < 8e-2, (n, fro(pg.grad, pc.grad))
+
+
+def test_dropless_fine_grained_layer_runs_and_matches_cpu():
+    """Fine-grained MoE: many small experts, top-6, shared experts, skewed routing, no dropping."""
+    from fluidmoe_b200.models.transformer import TransformerLayer
+    from fluidmoe_b200.ops import gemm
+    from fluidmoe_b200.parallel.scheduler import get_backward_scheduler
+
+    get_backward_scheduler().disable()
+    torch.manual_seed(0)
+    H, nh, nkv, F, E, k = 512, 4, 4, 256, 16, 16       # k == E keeps the comparison continuous
+    s, b = 128, 2
+    kw = dict(router_dtype=torch.float32, activation_func="swiglu", norm_type="rmsnorm",
+              num_shared_experts=2, init_std=0.05, capacity_factor=0.0)
+    cpu = TransformerLayer(H, nh, nkv, F, E, k, None, None, dtype=torch.float32, device="cpu", **kw)
+    with torch.no_grad():
+        for p in cpu.parameters():
+            p.copy_(p.bfloat16().float())
+    gpu = TransformerLayer(H, nh, nkv, F, E, k, None, None, dtype=torch.bfloat16, device="cuda", **kw)
+    gpu.load_state_dict({n: v.bfloat16() for n, v in cpu.state_dict().items()})
+    x = torch.randn(s, b, H).bfloat16().float()
+    g = torch.randn(s, b, H).bfloat16().float()
+    xc = x.clone().requires_grad_(True)
+    yc = cpu(xc)
+    yc.backward(g)
+    xg = x.cuda().bfloat16().requires_grad_(True)
+    yg = gpu(xg)
+    yg.backward(g.cuda().bfloat16())
+    torch.cuda.synchronize()
+    gemm.check_status()
+
+    def fro(a, b_):
+        a, b_ = a.float().cpu(), b_.float()
+        return ((a - b_).norm() / (b_.norm() + 1e-9)).item()
+    assert fro(yg, yc) < 5e-2
+    assert fro(xg.grad, xc.grad) < 8e-2
+    for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
+        assert fro(pg.grad, pc.grad) < 8e-2, n

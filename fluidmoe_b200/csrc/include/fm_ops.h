@@ -28,6 +28,13 @@ int fm_adam(void* p, float* master, float* g, void* m, void* v, long long n, flo
             float beta2, float eps, float weight_decay, int step, float grad_scale, int zero_grad,
             int state_bf16, cudaStream_t s);
 
+// Attention backward on the packed layout.  out / dout: [s, b, G*qpg, d] bf16; lse: [b, G*qpg, s];
+// delta: fp32 scratch [b, G*qpg, s]; dq_accum: fp32 scratch [s, b, G*qpg, d], zeroed by the caller;
+// dqkv: packed gradient [s, b, G, (qpg + 2) * d] bf16 (every element is written).
+int fm_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                      float* dq_accum, void* dqkv, int s, int b, int G, int qpg, int d, float scale,
+                      unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
 // Cross-entropy forward + backward in place: loss_out[row] = lse - logit[label]; logits are
 // overwritten with (softmax - onehot) * grad_scale (rows with a negative label get zeros).
 int fm_cross_entropy(void* logits, const long long* labels, float* loss_out, int T, int V,

@@ -319,6 +319,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a)
 // by more than 2^8 (otherwise the stale maximum stays in use, which is exact after the final
 // division by the row sum).
 // =========================================================================================
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 constexpr int kFa2Threads = 320;   // TMA warp, MMA warp, 4 + 4 softmax warps
 constexpr int kKernelIdFlashFwd2 = 21;
 
@@ -499,19 +505,27 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       tc_fence_after_sync();
       const bool diag = (j == qt);
       const int kv0 = j * kFaBN;
-      float m_blk = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_ld_wait();
+      // The whole score row (128 values) is kept in registers: one TMEM read per block.
+      uint32_t sv[4][32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = kv0 + c * 32 + i;
-          const bool masked = (diag && col > row) || col >= a.s;
-          m_blk = fmaxf(m_blk, masked ? -INFINITY : __uint_as_float(v[i]) * a.scale_log2);
-        }
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
+      tmem_ld_wait();
+      if (diag || kv0 + kFaBN > a.s) {
+        // only the diagonal block and a ragged last block need masking
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = kv0 + c * 32 + i;
+            if ((diag && col > row) || col >= a.s) sv[c][i] = 0xff800000u;   // -inf
+          }
       }
+      float m_raw = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 32; ++i) m_raw = fmaxf(m_raw, __uint_as_float(sv[c][i]));
+      const float m_blk = m_raw * a.scale_log2;   // scale > 0
       // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 above it.
       const float m_new = fmaxf(m_used, m_blk);
       const bool first = (j == 0);
@@ -541,23 +555,18 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         }
       }
       float l_blk = 0.f;
-#pragma unroll 1
+      const float neg_m = -m_used;
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_s + c * 32, v);
-        tmem_ld_wait();
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const int col = kv0 + c * 32 + 2 * i;
-          const bool mk0 = (diag && col > row) || col >= a.s;
-          const bool mk1 = (diag && col + 1 > row) || col + 1 >= a.s;
-          const float p0 = mk0 ? 0.f : exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_used);
-          const float p1 = mk1 ? 0.f : exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_used);
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i]), a.scale_log2, neg_m));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i + 1]), a.scale_log2, neg_m));
           l_blk += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        // P columns [16c, 16c+16) alias score columns that were read in an earlier chunk
+        // P columns [16c, 16c+16) alias score columns; the scores are already in registers
         tmem_st_32x16(t_s + c * 16, pk);
       }
       tmem_st_wait();
@@ -590,6 +599,320 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       }
       if (row < a.s)
         a.lse[((long long)bb * hq + h) * a.s + row] = (m_used + log2f(l_run)) * 0.6931471805599453f;
+    }
+    tc_fence_before_sync();
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// =========================================================================================
+// Backward.  One CTA owns a 128-position key/value block of one KV head and walks every query
+// tile (and every query head of the group) that attends to it.  Per step, on tcgen05:
+//   S  = Q K^T,  dP = dO V^T                      (accumulators in TMEM)
+//   P  = exp2(S * c - lse),  dS = P * (dP - delta) * scale     (one thread per query row)
+//   dV += P^T dO,  dK += dS^T Q                   (accumulate in TMEM across all steps)
+//   dQ  = dS K                                    (added to an fp32 buffer with vector atomics)
+// P and dS are staged once in shared memory in the 128-byte-swizzled layout, which serves both as
+// K-major A operand (dS K) and as MN-major A operand (P^T dO, dS^T Q).  dK / dV are written
+// straight into the packed [q.. | k | v] gradient buffer, so no concatenation pass is needed
+// (the reference concatenates dQ, dK, dV per KV group, fluid/attention/backward.py:284-287).
+// =========================================================================================
+constexpr int kKernelIdFlashBwd = 22;
+
+struct FlashBwdArgs {
+  int s, b, G, qpg;
+  float scale, scale_log2;
+  const float* lse;      // [b, hq, s]
+  const float* delta;    // [b, hq, s]  rowsum(dO * O)
+  float* dq_accum;       // [s, b, hq, d] fp32, zero-initialised
+  __nv_bfloat16* dqkv;   // packed gradient buffer [s, b, G, (qpg + 2) * d]
+  unsigned long long timeout_ns;
+  int* status;
+};
+
+__global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
+                                  float* __restrict__ delta, int s, int b, int hq) {
+  // one warp per (row, batch, head): delta[b, h, row] = sum_d dO * O   (d == 128)
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long total = (long long)s * b * hq;
+  if (w >= total) return;
+  const int lane = threadIdx.x & 31;
+  const uint2 o = reinterpret_cast<const uint2*>(out + w * kFaD)[lane];
+  const uint2 g = reinterpret_cast<const uint2*>(dout + w * kFaD)[lane];
+  const __nv_bfloat162 o0 = *reinterpret_cast<const __nv_bfloat162*>(&o.x);
+  const __nv_bfloat162 o1 = *reinterpret_cast<const __nv_bfloat162*>(&o.y);
+  const __nv_bfloat162 g0 = *reinterpret_cast<const __nv_bfloat162*>(&g.x);
+  const __nv_bfloat162 g1 = *reinterpret_cast<const __nv_bfloat162*>(&g.y);
+  float acc = __low2float(o0) * __low2float(g0) + __high2float(o0) * __high2float(g0) +
+              __low2float(o1) * __low2float(g1) + __high2float(o1) * __high2float(g1);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    const long long h = w % hq, bb = (w / hq) % b, row = w / ((long long)hq * b);
+    delta[(bb * hq + h) * s + row] = acc;
+  }
+}
+
+// dq_accum (fp32 [s, b, hq, d]) -> bf16 into the query-head columns of the packed buffer
+__global__ void attn_dq_store_kernel(const float* __restrict__ dq, __nv_bfloat16* __restrict__ dqkv,
+                                     long long rows /* s*b */, int G, int qpg) {
+  const int hq = G * qpg;
+  const long long total = rows * hq * (kFaD / 8);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v8 = (int)(i % (kFaD / 8));
+    const long long rh = i / (kFaD / 8);
+    const int h = (int)(rh % hq);
+    const long long row = rh / hq;
+    const float4 a = reinterpret_cast<const float4*>(dq + rh * kFaD)[v8 * 2];
+    const float4 c = reinterpret_cast<const float4*>(dq + rh * kFaD)[v8 * 2 + 1];
+    uint4 p;
+    p.x = pack_bf16x2(a.x, a.y); p.y = pack_bf16x2(a.z, a.w);
+    p.z = pack_bf16x2(c.x, c.y); p.w = pack_bf16x2(c.z, c.w);
+    const int g = h / qpg, hi = h % qpg;
+    __nv_bfloat16* dst = dqkv + ((row * G + g) * (qpg + 2) + hi) * kFaD;
+    reinterpret_cast<uint4*>(dst)[v8] = p;
+  }
+}
+
+__global__ void __launch_bounds__(kFaThreads, 1)
+flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                 const FlashBwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTileBytes;
+  uint8_t* sQ = smem + 2 * kTileBytes;
+  uint8_t* sdO = smem + 3 * kTileBytes;
+  uint8_t* sP = smem + 4 * kTileBytes;
+  uint8_t* sdS = smem + 5 * kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
+  uint64_t* kv_full = bars;        // K and V of this block
+  uint64_t* qdo_full = bars + 1;   // Q_i and dO_i of the current step
+  uint64_t* qdo_empty = bars + 2;  // the step's MMAs have finished reading Q_i / dO_i
+  uint64_t* sdp_full = bars + 3;   // S and dP are in TMEM
+  uint64_t* pds_full = bars + 4;   // P and dS are in shared memory (4 warps)
+  uint64_t* dq_full = bars + 5;    // dQ is in TMEM (and dV, dK updated)
+  uint64_t* dq_read = bars + 6;    // dQ has been drained (4 warps)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x, g = blockIdx.y, bb = blockIdx.z;
+  const int nq = (a.s + kFaBM - 1) / kFaBM;
+  const int hq = a.G * a.qpg;
+  const int hpg = a.qpg + 2;
+  const int col_k = ((bb * a.G + g) * hpg + a.qpg) * kFaD;
+  const int col_v = col_k + kFaD;
+  const int tiles = nq - j;                 // query tiles i = j .. nq-1
+  const int nsteps = tiles * a.qpg;
+  const uint64_t timeout = a.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 4);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_read, 4);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_qkv);
+    tma_prefetch_desc(&tmap_do);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * kTileBytes);
+      tma_load_2d(sK, &tmap_qkv, kv_full, col_k, j * kFaBN);
+      tma_load_2d(sK + kTileBytes / 2, &tmap_qkv, kv_full, col_k + 64, j * kFaBN);
+      tma_load_2d(sV, &tmap_qkv, kv_full, col_v, j * kFaBN);
+      tma_load_2d(sV + kTileBytes / 2, &tmap_qkv, kv_full, col_v + 64, j * kFaBN);
+      for (int n = 0; n < nsteps; ++n) {
+        const int hi = n / tiles, i = j + n % tiles;
+        if (!mbar_wait(qdo_empty, (n & 1) ^ 1, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd, 100, 0, 0);
+          break;
+        }
+        const int col_q = ((bb * a.G + g) * hpg + hi) * kFaD;
+        const int col_do = (bb * hq + g * a.qpg + hi) * kFaD;
+        mbar_expect_tx(qdo_full, 2 * kTileBytes);
+        tma_load_2d(sQ, &tmap_qkv, qdo_full, col_q, i * kFaBM);
+        tma_load_2d(sQ + kTileBytes / 2, &tmap_qkv, qdo_full, col_q + 64, i * kFaBM);
+        tma_load_2d(sdO, &tmap_do, qdo_full, col_do, i * kFaBM);
+        tma_load_2d(sdO + kTileBytes / 2, &tmap_do, qdo_full, col_do + 64, i * kFaBM);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, false, false);   // A K-major, B K-major
+      constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, true, true);     // A MN-major, B MN-major
+      constexpr uint32_t id_km = umma_idesc_bf16(128, 128, false, true);    // A K-major, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aO = smem_u32(sdO);
+      const uint32_t aP = smem_u32(sP), aS = smem_u32(sdS);
+      constexpr uint32_t HALF = kTileBytes / 2;
+      auto kdesc = [&](uint32_t base, int kk) {   // K-major operand, k-step kk of 8
+        return umma_smem_desc(base + (kk >> 2) * HALF + (kk & 3) * 32, 0, 1024);
+      };
+      auto mdesc = [&](uint32_t base, int kk) {   // MN-major operand ([128 k rows][64] slabs)
+        return umma_smem_desc(base + kk * 2048, HALF, 1024);
+      };
+      bool ok = mbar_wait(kv_full, 0, timeout, abort_flag);
+      if (!ok) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd, 200, 0, 0);
+      for (int n = 0; ok && n < nsteps; ++n) {
+        const uint32_t par = n & 1;
+        if (!mbar_wait(qdo_full, par, timeout, abort_flag) ||
+            !mbar_wait(dq_read, par ^ 1, timeout, abort_flag)) {   // S columns (= dQ) are free again
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd, 210, 0, 0);
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_s, kdesc(aQ, kk), kdesc(aK, kk), id_kk, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dp, kdesc(aO, kk), kdesc(aV, kk), id_kk, kk > 0);
+        umma_commit(sdp_full);
+        if (!mbar_wait(pds_full, par, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd, 220, 0, 0);
+          break;
+        }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dv, mdesc(aP, kk), mdesc(aO, kk), id_mm, (n > 0 || kk > 0));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dk, mdesc(aS, kk), mdesc(aQ, kk), id_mm, (n > 0 || kk > 0));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_s, kdesc(aS, kk), mdesc(aK, kk), id_km, kk > 0);
+        umma_commit(qdo_empty);
+        umma_commit(dq_full);
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    bool ok = true;
+    for (int n = 0; n < nsteps; ++n) {
+      const uint32_t par = n & 1;
+      const int hi = n / tiles, i = j + n % tiles;
+      const int h = g * a.qpg + hi;
+      const int row = i * kFaBM + r;
+      const bool row_ok = row < a.s;
+      const float lse2 = row_ok ? a.lse[((long long)bb * hq + h) * a.s + row] * 1.4426950408889634f : 0.f;
+      const float dl = row_ok ? a.delta[((long long)bb * hq + h) * a.s + row] : 0.f;
+      if (!mbar_wait(sdp_full, par, timeout, abort_flag)) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd, 300, 0, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      const bool diag = (i == j);
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, sv);
+        tmem_ld_32x32(t_dp + lane_addr + c * 32, dv);
+        tmem_ld_wait();
+        uint8_t* prow = sP + (c >> 1) * (kTileBytes / 2) + r * 128;
+        uint8_t* drow = sdS + (c >> 1) * (kTileBytes / 2) + r * 128;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          float p[8], ds[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int col = j * kFaBN + c * 32 + w * 8 + e;
+            const bool masked = !row_ok || (diag && col > row) || col >= a.s;
+            p[e] = masked ? 0.f : exp2f(__uint_as_float(sv[w * 8 + e]) * a.scale_log2 - lse2);
+            ds[e] = p[e] * (__uint_as_float(dv[w * 8 + e]) - dl) * a.scale;
+          }
+          const int chunk = ((c & 1) * 4 + w) ^ (r & 7);
+          uint4 pp, dd;
+          pp.x = pack_bf16x2(p[0], p[1]); pp.y = pack_bf16x2(p[2], p[3]);
+          pp.z = pack_bf16x2(p[4], p[5]); pp.w = pack_bf16x2(p[6], p[7]);
+          dd.x = pack_bf16x2(ds[0], ds[1]); dd.y = pack_bf16x2(ds[2], ds[3]);
+          dd.z = pack_bf16x2(ds[4], ds[5]); dd.w = pack_bf16x2(ds[6], ds[7]);
+          *reinterpret_cast<uint4*>(prow + chunk * 16) = pp;
+          *reinterpret_cast<uint4*>(drow + chunk * 16) = dd;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_full);
+      // drain dQ of this step
+      if (!mbar_wait(dq_full, par, timeout, abort_flag)) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd, 310, 0, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      float* dq_row = a.dq_accum + (((long long)row * a.b + bb) * hq + h) * kFaD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_s + lane_addr + c * 32, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            atomicAdd(reinterpret_cast<float4*>(dq_row + c * 32) + u,
+                      make_float4(__uint_as_float(v[4 * u]), __uint_as_float(v[4 * u + 1]),
+                                  __uint_as_float(v[4 * u + 2]), __uint_as_float(v[4 * u + 3])));
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(dq_read);
+    }
+    if (ok && nsteps > 0) {
+      // dK / dV of this block are complete once the last step's MMAs have finished (dq_full).
+      const int kvrow = j * kFaBN + r;
+      __nv_bfloat16* dk_dst = a.dqkv + (((long long)kvrow * a.b + bb) * a.G + g) * hpg * kFaD + a.qpg * kFaD;
+      __nv_bfloat16* dv_dst = dk_dst + kFaD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t vk[32], vv[32];
+        tmem_ld_32x32(t_dk + lane_addr + c * 32, vk);
+        tmem_ld_32x32(t_dv + lane_addr + c * 32, vv);
+        tmem_ld_wait();
+        if (kvrow < a.s) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 k4, v4;
+            k4.x = pack_bf16x2(__uint_as_float(vk[8 * u]), __uint_as_float(vk[8 * u + 1]));
+            k4.y = pack_bf16x2(__uint_as_float(vk[8 * u + 2]), __uint_as_float(vk[8 * u + 3]));
+            k4.z = pack_bf16x2(__uint_as_float(vk[8 * u + 4]), __uint_as_float(vk[8 * u + 5]));
+            k4.w = pack_bf16x2(__uint_as_float(vk[8 * u + 6]), __uint_as_float(vk[8 * u + 7]));
+            v4.x = pack_bf16x2(__uint_as_float(vv[8 * u]), __uint_as_float(vv[8 * u + 1]));
+            v4.y = pack_bf16x2(__uint_as_float(vv[8 * u + 2]), __uint_as_float(vv[8 * u + 3]));
+            v4.z = pack_bf16x2(__uint_as_float(vv[8 * u + 4]), __uint_as_float(vv[8 * u + 5]));
+            v4.w = pack_bf16x2(__uint_as_float(vv[8 * u + 6]), __uint_as_float(vv[8 * u + 7]));
+            reinterpret_cast<uint4*>(dk_dst)[c * 4 + u] = k4;
+            reinterpret_cast<uint4*>(dv_dst)[c * 4 + u] = v4;
+          }
+        }
+      }
     }
     tc_fence_before_sync();
   }
@@ -684,6 +1007,79 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
     dim3 grid((s + fm::kFaBM - 1) / fm::kFaBM, G * qpg, b);
     fm::flash_fwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tmap, a);
   }
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    fm_set_error(cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+static bool make_rows_tmap(CUtensorMap* m, const void* ptr, long long cols, long long rows) {
+  static EncodeTiledFn2 enc = nullptr;
+  if (!enc) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return false;
+    enc = reinterpret_cast<EncodeTiledFn2>(p);
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {64, 128};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
+                                 float* delta, float* dq_accum, void* dqkv, int s, int b, int G, int qpg,
+                                 int d, float scale, unsigned long long timeout_ns, int* status,
+                                 cudaStream_t stream) {
+  if (d != fm::kFaD) {
+    fm_set_error("flash_attn_bwd: head_dim must be 128");
+    return -1;
+  }
+  const int hq = G * qpg;
+  if ((reinterpret_cast<uintptr_t>(qkv) & 15) || (reinterpret_cast<uintptr_t>(dout) & 15) ||
+      (reinterpret_cast<uintptr_t>(dq_accum) & 15) || (reinterpret_cast<uintptr_t>(dqkv) & 15)) {
+    fm_set_error("flash_attn_bwd: buffers must be 16-byte aligned");
+    return -1;
+  }
+  CUtensorMap tq, tdo;
+  if (!make_rows_tmap(&tq, qkv, (long long)b * G * (qpg + 2) * d, s) ||
+      !make_rows_tmap(&tdo, dout, (long long)b * hq * d, s)) {
+    fm_set_error("flash_attn_bwd: cuTensorMapEncodeTiled failed");
+    return -3;
+  }
+  const long long nrows = (long long)s * b * hq;
+  fm::attn_delta_kernel<<<(unsigned)((nrows + 7) / 8), 256, 0, stream>>>(
+      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, s, b, hq);
+  constexpr int smem = 6 * fm::kTileBytes + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(fm::flash_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) {
+      fm_set_error(cudaGetErrorString(e));
+      return (int)e;
+    }
+    configured = true;
+  }
+  fm::FlashBwdArgs a;
+  a.s = s; a.b = b; a.G = G; a.qpg = qpg;
+  a.scale = scale;
+  a.scale_log2 = scale * 1.4426950408889634f;
+  a.lse = lse;
+  a.delta = delta;
+  a.dq_accum = dq_accum;
+  a.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
+  a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
+  a.status = status;
+  dim3 grid((s + fm::kFaBN - 1) / fm::kFaBN, G, b);
+  fm::flash_bwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tq, tdo, a);
+  fm::attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(dq_accum, a.dqkv, (long long)s * b, G, qpg);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fm_set_error(cudaGetErrorString(e));

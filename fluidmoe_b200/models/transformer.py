@@ -268,19 +268,10 @@ class TransformerLayerFunction(torch.autograd.Function):
 
         # ---- attention backward (+ RoPE backward), packed per KV group ----
         with nvtx_range("bwd_attention"):
-            s_full = qkv_full.shape[0]
             G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
-            heads = qkv_full.view(s_full, b, G, qpg + 2, d)
-            q = heads[:, :, :, :qpg].reshape(s_full, b, G * qpg, d)
-            k = heads[:, :, :, qpg]
-            v = heads[:, :, :, qpg + 1]
-            dq, dk, dv = attn_ops.attention_bwd(d_attn.contiguous(), q, k, v, attn_out, lse,
-                                                1.0 / math.sqrt(d), True)
-            dqkv_hp = torch.empty_like(qkv_full)
-            dh = dqkv_hp.view(s_full, b, G, qpg + 2, d)
-            dh[:, :, :, :qpg].copy_(dq.view(s_full, b, G, qpg, d))
-            dh[:, :, :, qpg].copy_(dk)
-            dh[:, :, :, qpg + 1].copy_(dv)
+            dqkv_hp = attn_ops.attention_bwd_packed(d_attn, qkv_full, attn_out,
+                                                    lse if lse.dim() == 3 else None, qpg, d,
+                                                    1.0 / math.sqrt(d))
             if ctx.has_rotary:
                 rope.rope_packed_(dqkv_hp, rotary, qpg, d, backward=True)
 

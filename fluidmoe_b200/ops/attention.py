@@ -46,11 +46,10 @@ def attention_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch
     hkv = k.shape[2]
     rep = hq // hkv
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
-    if _native.use_native(q, k, v) and hasattr(_native.lib(), "flash_attn_bwd"):
-        from . import flash
-        return flash.flash_attn_bwd(dout, q, k, v, out, lse, scale, causal)
     if q.is_cuda:
         return _sdpa_bwd(dout, q, k, v, scale, causal, out, lse if (lse is not None and lse.dtype == torch.float32) else None)
+    if lse is None:
+        _, lse = attention_fwd(q, k, v, scale, causal)
     qf = q.float().permute(1, 2, 0, 3)
     kf = k.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
     vf = v.float().permute(1, 2, 0, 3).repeat_interleave(rep, dim=1)
@@ -85,6 +84,31 @@ def attention_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sca
     heads = qkv.view(s, b, G, q_per_group + 2, head_dim)
     q = heads[:, :, :, :q_per_group].reshape(s, b, G * q_per_group, head_dim)
     return attention_fwd(q, heads[:, :, :, q_per_group], heads[:, :, :, q_per_group + 1], scale, True)
+
+
+def attention_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse, q_per_group: int,
+                         head_dim: int, scale: float = None) -> torch.Tensor:
+    """Gradient of the packed projection buffer from the saved output (and log-sum-exp).
+    ``FLUIDMOE_ATTN_BWD=native`` selects this library's tcgen05 kernel, ``library`` (default) the
+    vendor attention backward."""
+    import os
+    from . import flash
+    s, b, G, gs = qkv.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
+    have_lse = lse is not None and lse.dim() == 3 and lse.dtype == torch.float32
+    if have_lse and flash.supported(qkv, head_dim) and os.environ.get("FLUIDMOE_ATTN_BWD", "library") == "native":
+        return flash.flash_attn_bwd_packed(dout, qkv, out, lse, q_per_group, head_dim, scale)
+    qpg, d = q_per_group, head_dim
+    heads = qkv.view(s, b, G, qpg + 2, d)
+    q = heads[:, :, :, :qpg].reshape(s, b, G * qpg, d)
+    dq, dk, dv = attention_bwd(dout.contiguous(), q, heads[:, :, :, qpg], heads[:, :, :, qpg + 1], out,
+                               lse if have_lse else None, scale, True)
+    dqkv = torch.empty_like(qkv)
+    dh = dqkv.view(s, b, G, qpg + 2, d)
+    dh[:, :, :, :qpg].copy_(dq.reshape(s, b, G, qpg, d))
+    dh[:, :, :, qpg].copy_(dk)
+    dh[:, :, :, qpg + 1].copy_(dv)
+    return dqkv
 
 
 # ---- library attention, used on CUDA where this library's own kernel does not apply ----

@@ -9,7 +9,7 @@ from .gemm import status_buffer
 import os
 
 LAUNCHES = 0
-VERSION = int(os.environ.get("FLUIDMOE_FLASH_VERSION", "1"))
+VERSION = int(os.environ.get("FLUIDMOE_FLASH_VERSION", "2"))
 
 
 def supported(qkv: torch.Tensor, head_dim: int) -> bool:
@@ -29,3 +29,21 @@ def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sc
                                  head_dim, float(scale), 0, status_buffer(qkv.device).data_ptr(),
                                  version or VERSION, _native.stream_ptr())
     return out, lse
+
+
+def flash_attn_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
+                          q_per_group: int, head_dim: int, scale: float) -> torch.Tensor:
+    """Gradient of the packed projection buffer, ``[s, b, G, (qpg + 2) * d]`` (dq heads, dk, dv per
+    KV group), from the saved output and log-sum-exp."""
+    global LAUNCHES
+    s, b, G, gs = qkv.shape
+    hq = G * q_per_group
+    dout = dout.contiguous()
+    delta = torch.empty(b, hq, s, dtype=torch.float32, device=qkv.device)
+    dq_accum = torch.zeros(s, b, hq, head_dim, dtype=torch.float32, device=qkv.device)
+    dqkv = torch.empty_like(qkv)
+    LAUNCHES += 3
+    _native.lib().flash_attn_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+                                 dq_accum.data_ptr(), dqkv.data_ptr(), s, b, G, q_per_group, head_dim, float(scale),
+                                 0, status_buffer(qkv.device).data_ptr(), _native.stream_ptr())
+    return dqkv

@@ -116,11 +116,25 @@ def case_wgrad(a):
 
 
 def case_flash(a):
+    from ..ops import attention
     s, G, qpg, d = a.seq, a.kv_heads, a.q_per_kv, 128
+    sc = 1.0 / math.sqrt(d)
     qkv = _r(s, 1, G, (qpg + 2) * d)
-    report(f"flash fwd causal s={s} heads={G * qpg}/{G}",
-           timed(lambda: flash.flash_attn_fwd_packed(qkv, qpg, d, 1.0 / math.sqrt(d))),
-           4.0 * s * s * G * qpg * d / 2)
+    fl = 4.0 * s * s * G * qpg * d / 2
+    for ver in (2, 1):
+        report(f"flash fwd v{ver} causal s={s} heads={G * qpg}/{G}",
+               timed(lambda: flash.flash_attn_fwd_packed(qkv, qpg, d, sc, version=ver)), fl)
+    out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, sc)
+    dout = torch.randn_like(out)
+    report("flash bwd (delta + main + dq store)",
+           timed(lambda: flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, sc)), 2.5 * fl)
+    heads = qkv.view(s, 1, G, qpg + 2, d)
+    q = heads[:, :, :, :qpg].reshape(s, 1, G * qpg, d).contiguous()
+    k, v = heads[:, :, :, qpg].contiguous(), heads[:, :, :, qpg + 1].contiguous()
+    report("  library fwd (cuDNN via torch), same shape", timed(lambda: attention._sdpa_fwd(q, k, v, sc, True)), fl)
+    lo, ll = attention._sdpa_fwd(q, k, v, sc, True)
+    report("  library bwd (cuDNN via torch), same shape",
+           timed(lambda: attention._sdpa_bwd(dout, q, k, v, sc, True, lo, ll)), 2.5 * fl)
 
 
 def case_norm(a):
@@ -147,7 +161,7 @@ def case_permute(a):
 
 
 def case_adam(a):
-    n = 1 << 28
+    n = a.elems
     p = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
     g = torch.randn(n, device="cuda")
     m, v = torch.zeros_like(p), torch.zeros_like(p)
@@ -234,6 +248,7 @@ def main(argv=None):
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--q-per-kv", type=int, default=4)
+    ap.add_argument("--elems", type=int, default=1 << 28)
     a = ap.parse_args(argv)
     torch.manual_seed(0)
     for name in (list(CASES) if a.case == "all" else [a.case]):

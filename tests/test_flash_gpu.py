@@ -69,3 +69,46 @@ def test_attention_backward_from_saved_output(fwd):
     for got, ref in ((dq, rdq), (dk, rdk), (dv, rdv)):
         err = (got.float().cpu() - ref).norm() / ref.norm()
         assert err < 3e-2, err
+
+
+@pytest.mark.parametrize("s,b,G,qpg", [(256, 1, 1, 1), (512, 1, 2, 2), (1000, 2, 1, 4)])
+def test_flash_bwd_native_matches_reference(s, b, G, qpg):
+    d = 128
+    torch.manual_seed(2)
+    qkv = torch.randn(s, b, G, (qpg + 2) * d, device="cuda").bfloat16()
+    scale = 1.0 / math.sqrt(d)
+    out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, scale)
+    dout = torch.randn_like(out)
+    dqkv = flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, scale)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    heads = qkv.float().cpu().view(s, b, G, qpg + 2, d)
+    q = heads[:, :, :, :qpg].reshape(s, b, G * qpg, d)
+    k, v = heads[:, :, :, qpg], heads[:, :, :, qpg + 1]
+    ro, rl = attention.attention_fwd(q, k, v, scale, True)
+    rdq, rdk, rdv = attention.attention_bwd(dout.float().cpu(), q, k, v, ro, rl, scale, True)
+    got = dqkv.float().cpu().view(s, b, G, qpg + 2, d)
+    for name, g_, r_ in (("dq", got[:, :, :, :qpg].reshape(s, b, G * qpg, d), rdq), ("dk", got[:, :, :, qpg], rdk),
+                         ("dv", got[:, :, :, qpg + 1], rdv)):
+        err = ((g_ - r_).norm() / r_.norm()).item()
+        assert err < 3e-2, (name, err)
+
+
+def test_flash_bwd_speed():
+    s, b, G, qpg, d = 8192, 1, 2, 4, 128
+    qkv = torch.randn(s, b, G, (qpg + 2) * d, device="cuda").bfloat16()
+    out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, 0.088)
+    dout = torch.randn_like(out)
+    for _ in range(2):
+        flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, 0.088)
+    torch.cuda.synchronize()
+    st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    st.record()
+    for _ in range(5):
+        flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, 0.088)
+    en.record()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    ms = st.elapsed_time(en) / 5
+    flops = 2.5 * 4 * s * s * G * qpg * d / 2
+    print(f"\nflash bwd s={s} heads={G*qpg}: {ms:.3f} ms, {flops / ms / 1e9:.1f} TFLOP/s")

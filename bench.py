@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--tiny", action="store_true", help="small shapes for a functional check")
     ap.add_argument("--opt-state", default="bf16", choices=["bf16", "fp32"],
                     help="dtype of the Adam moments (torch.optim.AdamW keeps bf16 moments for bf16 parameters)")
+    ap.add_argument("--fuse-optimizer", type=int, default=1,
+                    help="1: apply Adam to the expert weights in their weight-gradient GEMM epilogue "
+                         "(bf16 moments, scheduler on, one micro-batch per step)")
     ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file")
     return ap.parse_args()
 
@@ -184,6 +187,9 @@ def run_ours(args):
     opt = FluidOptimizerWrapper(
         FusedAdam(model.parameters(), lr=1e-4, weight_decay=0.0,
                   state_dtype=torch.bfloat16 if args.opt_state == "bf16" else torch.float32), sched)
+    fused_params = 0
+    if args.fuse_optimizer and args.mode != "F" and args.opt_state == "bf16":
+        fused_params = opt.fuse_into_backward()
     seq, batch = args.seq, m["batch"]
     n_batches = 4
     host = make_batches(torch, n_batches, seq, batch, m["vocab"], 100 + rank)

@@ -86,6 +86,16 @@ static void gemm_launch(const py::dict& d, uintptr_t stream) {
   g.k_rotate = get<int>(d, "k_rotate", 0);
   g.cols_per_rank = get<int>(d, "cols_per_rank", 0);
   g.dst_row_offset = get<long long>(d, "dst_row_offset", 0);
+  g.adam_p = ptr<void*>(d, "adam_p");
+  g.adam_m = ptr<void*>(d, "adam_m");
+  g.adam_v = ptr<void*>(d, "adam_v");
+  g.adam_lr = get<float>(d, "adam_lr", 0.f);
+  g.adam_beta1 = get<float>(d, "adam_beta1", 0.f);
+  g.adam_beta2 = get<float>(d, "adam_beta2", 0.f);
+  g.adam_eps = get<float>(d, "adam_eps", 0.f);
+  g.adam_wd = get<float>(d, "adam_wd", 0.f);
+  g.adam_rbc1 = get<float>(d, "adam_rbc1", 1.f);
+  g.adam_rbc2 = get<float>(d, "adam_rbc2", 1.f);
   g.max_ctas = get<int>(d, "max_ctas", 0);
   g.timeout_ns = get<unsigned long long>(d, "timeout_ns", 0ull);
   g.status = ptr<int*>(d, "status");
@@ -104,6 +114,7 @@ PYBIND11_MODULE(_C, m) {
   m.attr("EPI_SCATTER") = (int)FM_EPI_SCATTER;
   m.attr("EPI_DACT") = (int)FM_EPI_DACT;
   m.attr("EPI_COLSCATTER") = (int)FM_EPI_COLSCATTER;
+  m.attr("EPI_ADAM") = (int)FM_EPI_ADAM;
   m.attr("ACT_GELU") = (int)FM_ACT_GELU;
   m.attr("ACT_SILU") = (int)FM_ACT_SILU;
   m.attr("ACT_NONE") = (int)FM_ACT_NONE;

@@ -282,6 +282,103 @@ __device__ __forceinline__ void get_block_bf16(float* stg, int lane, float* v, i
 }
 
 // ----------------------------------------------------------------------------------------
+// Epilogue 5: optimizer in the weight-gradient epilogue.  The accumulator tile IS the gradient
+// of the matching tile of a bf16 parameter; instead of storing it, the epilogue reads the
+// parameter and its two bf16 Adam moments, applies the AdamW update and writes the three back
+// (12 bytes of traffic per element instead of a 4-byte gradient store here plus a 16-byte
+// optimizer pass later).  Only valid when the gradient is complete after this GEMM: a single
+// micro-batch per step and no data-parallel reduction of this parameter.
+// ----------------------------------------------------------------------------------------
+struct EpiAdam {
+  __nv_bfloat16* P;
+  __nv_bfloat16* Mo;
+  __nv_bfloat16* Vo;
+  long long ld;
+  long long group_stride;
+  float alpha;   // gradient scale
+  float lr, beta1, beta2, eps, weight_decay, rbc1, rbc2;
+
+  template <int BN>
+  __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
+                                      bool zero, int chalf, float* stg) const {
+    const int lane = r & 31;
+    const long long row = a.mode == 0 ? (long long)t.row_base + t.m0 + r : (long long)t.m0 + r;
+    const long long row0 = row - lane;
+    const long long goff = a.mode == 0 ? 0 : (long long)t.g * group_stride;
+    const bool row_ok = r < t.rows_valid;
+    const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
+#pragma unroll 1
+    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+      const int col = t.n_tile * BN + c * 32;
+      if (col >= a.N) break;
+      float g[32];
+      load_acc(taddr + c * 32, g, zero);
+      if (rows_ok == 0) continue;
+      const int ncols = min(32, a.N - col);
+      const long long off = goff + row0 * ld + col;
+      if (ncols == 32 && (ld & 7) == 0 && aligned16(P + off) && aligned16(Mo + off) && aligned16(Vo + off)) {
+        // the gradient block goes through the stage once; parameter and moments are then read,
+        // updated and written in the coalesced layout (4 lanes x 16 bytes per row)
+        stage_put(stg, lane, g);
+        const int sub = lane >> 2, c8 = (lane & 3) * 8;
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const int rr = pass * 8 + sub;
+          if (rr < rows_ok) {
+            const long long o = off + rr * ld + c8;
+            const float4 ga = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+            const float4 gb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+            const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+            uint4 pw = *reinterpret_cast<const uint4*>(P + o);
+            uint4 pm = *reinterpret_cast<const uint4*>(Mo + o);
+            uint4 pv = *reinterpret_cast<const uint4*>(Vo + o);
+            uint32_t* ww = reinterpret_cast<uint32_t*>(&pw);
+            uint32_t* wm = reinterpret_cast<uint32_t*>(&pm);
+            uint32_t* wv = reinterpret_cast<uint32_t*>(&pv);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const __nv_bfloat162 bw = *reinterpret_cast<const __nv_bfloat162*>(&ww[q]);
+              const __nv_bfloat162 bm = *reinterpret_cast<const __nv_bfloat162*>(&wm[q]);
+              const __nv_bfloat162 bv = *reinterpret_cast<const __nv_bfloat162*>(&wv[q]);
+              float w2[2] = {__low2float(bw), __high2float(bw)};
+              float m2[2] = {__low2float(bm), __high2float(bm)};
+              float v2[2] = {__low2float(bv), __high2float(bv)};
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const float gi = gg[2 * q + e] * alpha;
+                m2[e] = beta1 * m2[e] + (1.f - beta1) * gi;
+                v2[e] = beta2 * v2[e] + (1.f - beta2) * gi * gi;
+                w2[e] -= lr * ((m2[e] * rbc1) / (sqrtf(v2[e] * rbc2) + eps) + weight_decay * w2[e]);
+              }
+              ww[q] = pack_bf16x2(w2[0], w2[1]);
+              wm[q] = pack_bf16x2(m2[0], m2[1]);
+              wv[q] = pack_bf16x2(v2[0], v2[1]);
+            }
+            *reinterpret_cast<uint4*>(Mo + o) = pm;
+            *reinterpret_cast<uint4*>(Vo + o) = pv;
+            *reinterpret_cast<uint4*>(P + o) = pw;
+          }
+        }
+        __syncwarp();
+      } else if (row_ok) {
+        const long long o = off + (long long)lane * ld;
+        for (int i = 0; i < ncols; ++i) {
+          const float gi = g[i] * alpha;
+          float wi = __bfloat162float(P[o + i]);
+          const float mi = beta1 * __bfloat162float(Mo[o + i]) + (1.f - beta1) * gi;
+          const float vi = beta2 * __bfloat162float(Vo[o + i]) + (1.f - beta2) * gi * gi;
+          wi -= lr * ((mi * rbc1) / (sqrtf(vi * rbc2) + eps) + weight_decay * wi);
+          Mo[o + i] = __float2bfloat16(mi);
+          Vo[o + i] = __float2bfloat16(vi);
+          P[o + i] = __float2bfloat16(wi);
+        }
+      }
+    }
+  }
+  __device__ __forceinline__ void tile_done(const Tile&, const GemmArgs&, int) const {}
+};
+
+// ----------------------------------------------------------------------------------------
 // Epilogue 1: activation x routing probability (forward FC1).  Non-gated: out = act(x) * p.
 // Gated (SwiGLU): the tile holds 128 gate columns then 128 up columns; out = silu(g) * u * p.
 // Optionally keeps the pre-activation for the backward pass.
@@ -849,6 +946,17 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
       EpiColScatter e{reinterpret_cast<__nv_bfloat16* const*>(d->dst_base), d->cols_per_rank, d->ld_dst,
                       d->dst_row_offset, d->dst_flags};
       return dispatch_gate(d, ta, tb, args, e, grid, stream);
+    }
+    case FM_EPI_ADAM: {
+      if (d->adam_p == nullptr || d->adam_m == nullptr || d->adam_v == nullptr) {
+        set_err("optimizer epilogue needs parameter and moment pointers");
+        return -1;
+      }
+      EpiAdam e{reinterpret_cast<__nv_bfloat16*>(d->adam_p), reinterpret_cast<__nv_bfloat16*>(d->adam_m),
+                reinterpret_cast<__nv_bfloat16*>(d->adam_v), d->ldc, d->c_group_stride,
+                d->alpha == 0.f ? 1.0f : d->alpha, d->adam_lr, d->adam_beta1, d->adam_beta2, d->adam_eps,
+                d->adam_wd, d->adam_rbc1, d->adam_rbc2};
+      return dispatch_shape(d, ta, tb, args, e, GateNone{}, grid, stream);
     }
     default:
       set_err("unknown epilogue");

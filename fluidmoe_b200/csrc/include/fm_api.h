@@ -14,6 +14,7 @@ enum FmEpilogue {
   FM_EPI_SCATTER = 2,  // row r of the result goes to dst_base[dst_rank[r]] + dst_row[r] * ld
   FM_EPI_DACT = 3,     // backward of act * prob fused after the FC2 input-gradient GEMM
   FM_EPI_COLSCATTER = 4,  // column block p of the result goes to rank p's buffer
+  FM_EPI_ADAM = 5,        // the result is a weight gradient: apply AdamW to the parameter tile in place
 };
 enum FmAct { FM_ACT_GELU = 0, FM_ACT_SILU = 1, FM_ACT_NONE = 2 };
 
@@ -68,6 +69,11 @@ typedef struct FmGemmDesc {
   // FM_EPI_COLSCATTER (also uses dst_base, ld_dst, dst_flags)
   int cols_per_rank;
   long long dst_row_offset;
+  // FM_EPI_ADAM (bf16 parameter and moments laid out like C: ldc, c_group_stride; alpha scales the gradient)
+  void* adam_p;
+  void* adam_m;
+  void* adam_v;
+  float adam_lr, adam_beta1, adam_beta2, adam_eps, adam_wd, adam_rbc1, adam_rbc2;
   // ---- gate (producer waits until flags[...] >= expected before loading a row block) ----
   const int* gate_flags;
   const int* gate_group_base;

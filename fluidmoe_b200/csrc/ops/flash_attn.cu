@@ -638,6 +638,7 @@ struct FlashBwdArgs {
   __nv_bfloat16* dqkv;   // packed gradient buffer [s, b, G, (qpg + 2) * d]
   unsigned long long timeout_ns;
   int* status;
+  int flags;             // 1: skip the dQ reductions (timing experiments only)
 };
 
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
@@ -665,7 +666,7 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const _
 
 // dq_accum (fp32 [s, b, hq, d]) -> bf16 into the query-head columns of the packed buffer
 __global__ void attn_dq_store_kernel(const float* __restrict__ dq, __nv_bfloat16* __restrict__ dqkv,
-                                     long long rows /* s*b */, int G, int qpg) {
+                                     long long rows /* s*b */, int G, int qpg, float mul) {
   const int hq = G * qpg;
   const long long total = rows * hq * (kFaD / 8);
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -677,8 +678,8 @@ __global__ void attn_dq_store_kernel(const float* __restrict__ dq, __nv_bfloat16
     const float4 a = reinterpret_cast<const float4*>(dq + rh * kFaD)[v8 * 2];
     const float4 c = reinterpret_cast<const float4*>(dq + rh * kFaD)[v8 * 2 + 1];
     uint4 p;
-    p.x = pack_bf16x2(a.x, a.y); p.y = pack_bf16x2(a.z, a.w);
-    p.z = pack_bf16x2(c.x, c.y); p.w = pack_bf16x2(c.z, c.w);
+    p.x = pack_bf16x2(a.x * mul, a.y * mul); p.y = pack_bf16x2(a.z * mul, a.w * mul);
+    p.z = pack_bf16x2(c.x * mul, c.y * mul); p.w = pack_bf16x2(c.z * mul, c.w * mul);
     const int g = h / qpg, hi = h % qpg;
     __nv_bfloat16* dst = dqkv + ((row * G + g) * (qpg + 2) + hi) * kFaD;
     reinterpret_cast<uint4*>(dst)[v8] = p;
@@ -876,9 +877,8 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
         if (row_ok) {
 #pragma unroll
           for (int u = 0; u < 8; ++u)
-            atomicAdd(reinterpret_cast<float4*>(dq_row + c * 32) + u,
-                      make_float4(__uint_as_float(v[4 * u]), __uint_as_float(v[4 * u + 1]),
-                                  __uint_as_float(v[4 * u + 2]), __uint_as_float(v[4 * u + 3])));
+            red_add_v4_f32(dq_row + c * 32 + 4 * u, __uint_as_float(v[4 * u]), __uint_as_float(v[4 * u + 1]),
+                           __uint_as_float(v[4 * u + 2]), __uint_as_float(v[4 * u + 3]));
         }
       }
       tc_fence_before_sync();
@@ -914,6 +914,409 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
         }
       }
     }
+    tc_fence_before_sync();
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+
+// =========================================================================================
+// Second-generation backward: same ownership (one CTA per 128-position K/V block and KV head)
+// but in the transposed orientation, which lets the five MMAs of a step overlap with the
+// element-wise work of the neighbouring steps:
+//   S^T  = K Q^T,  dP^T = V dO^T       (key/value position on the TMEM lanes)
+//   P^T  = exp2(S^T c - lse[q])          written back to TMEM over S^T (bf16), A operand of
+//   dV  += P^T dO                        straight from TMEM
+//   dS^T = P^T (dP^T - delta[q])         staged once in swizzled shared memory: K-major A of
+//   dK  += dS^T Q                        and MN-major A of
+//   dQ   = dS K                          whose accumulator re-uses the dP^T columns
+// Q tiles are double buffered and S^T of step n+1 is issued before the tensor core waits for dS^T
+// of step n.  Eight softmax warps (two per TMEM lane quarter, 64 query positions each) keep two
+// warps per scheduler busy; four more warps drain dQ: TMEM -> swizzled shared-memory boxes ->
+// TMA reduce-add into the fp32 dQ buffer (whole 128-byte lines instead of per-thread atomics).
+// TMEM: S^T/P^T, dP^T/dQ, dV, dK = 512 columns.  The softmax scale is applied once at the end
+// (to dK here, to dQ in the store kernel).
+// =========================================================================================
+constexpr int kFaB2Threads = 448;   // TMA warp, MMA warp, 8 softmax warps, 4 dQ-drain warps
+constexpr int kKernelIdFlashBwd2 = 23;
+constexpr int kFaB2StageBytes = 4 * 2 * 4096;   // per drain warp: two [32 rows][32 fp32] boxes
+constexpr int kFaB2Smem = 6 * kTileBytes + kFaB2StageBytes + 2 * 2 * 128 * 4 + 256;
+
+__global__ void __launch_bounds__(kFaB2Threads, 1)
+flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_do,
+                  const __grid_constant__ CUtensorMap tmap_dq, const FlashBwdArgs a) {
+  extern __shared__ __align__(1024) uint8_t smem_b2[];
+  uint8_t* smem = smem_b2;
+  if ((smem_u32(smem) & 1023u) != 0) {   // the swizzled tiles need a 1024-byte aligned base
+    if (threadIdx.x == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 1, 0, 0);
+    return;
+  }
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + kTileBytes;
+  uint8_t* sQ = smem + 2 * kTileBytes;     // 2 stages
+  uint8_t* sdO = smem + 4 * kTileBytes;    // 1 stage
+  uint8_t* sdS = smem + 5 * kTileBytes;
+  uint8_t* sStage = smem + 6 * kTileBytes; // dQ boxes on their way to the TMA reduction
+  float* s_lse = reinterpret_cast<float*>(sStage + kFaB2StageBytes);   // [2][128]  lse * log2(e)
+  float* s_dl = s_lse + 256;                                           // [2][128]  delta
+  uint64_t* bars = reinterpret_cast<uint64_t*>(s_dl + 256);
+  uint64_t* kv_full = bars;
+  uint64_t* q_full = bars + 1;      // [2]
+  uint64_t* q_empty = bars + 3;     // [2]
+  uint64_t* do_full = bars + 5;
+  uint64_t* do_empty = bars + 6;
+  uint64_t* s_full = bars + 7;      // S^T(n) is in TMEM
+  uint64_t* p_full = bars + 8;      // P^T(n) is in TMEM (8 warps)
+  uint64_t* dp_full = bars + 9;     // dP^T(n) is in TMEM
+  uint64_t* ds_full = bars + 10;    // dS^T(n) is in shared memory (8 warps)
+  uint64_t* dq_full = bars + 11;    // dQ(n) is in TMEM
+  uint64_t* dq_read = bars + 12;    // dQ(n) has left TMEM (4 warps)
+  uint64_t* done_full = bars + 13;  // every MMA of this CTA has finished
+  uint64_t* stats_full = bars + 14; // [2] lse / delta of a step are in shared memory (128 threads)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int j = blockIdx.x, g = blockIdx.y, bb = blockIdx.z;
+  const int nq = (a.s + kFaBM - 1) / kFaBM;
+  const int hq = a.G * a.qpg;
+  const int hpg = a.qpg + 2;
+  const int col_k = ((bb * a.G + g) * hpg + a.qpg) * kFaD;
+  const int col_v = col_k + kFaD;
+  const int tiles = nq - j;                 // query tiles i = j .. nq-1
+  const int nsteps = tiles * a.qpg;
+  const uint64_t timeout = a.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&stats_full[i], 128);
+    }
+    mbar_init(do_full, 1);
+    mbar_init(do_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 8);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_full, 8);
+    mbar_init(dq_full, 1);
+    mbar_init(dq_read, 4);
+    mbar_init(done_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_qkv);
+    tma_prefetch_desc(&tmap_do);
+    tma_prefetch_desc(&tmap_dq);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t t_s = tmem_base, t_dp = tmem_base + 128, t_dv = tmem_base + 256, t_dk = tmem_base + 384;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * kTileBytes);
+      tma_load_2d(sK, &tmap_qkv, kv_full, col_k, j * kFaBN);
+      tma_load_2d(sK + kTileBytes / 2, &tmap_qkv, kv_full, col_k + 64, j * kFaBN);
+      tma_load_2d(sV, &tmap_qkv, kv_full, col_v, j * kFaBN);
+      tma_load_2d(sV + kTileBytes / 2, &tmap_qkv, kv_full, col_v + 64, j * kFaBN);
+      for (int n = 0; n < nsteps; ++n) {
+        const int st = n & 1;
+        const int hi = n / tiles, i = j + n % tiles;
+        if (!mbar_wait(&q_empty[st], ((n >> 1) & 1) ^ 1, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 100 + st, 0, 0);
+          break;
+        }
+        const int col_q = ((bb * a.G + g) * hpg + hi) * kFaD;
+        uint8_t* q_dst = sQ + st * kTileBytes;
+        mbar_expect_tx(&q_full[st], kTileBytes);
+        tma_load_2d(q_dst, &tmap_qkv, &q_full[st], col_q, i * kFaBM);
+        tma_load_2d(q_dst + kTileBytes / 2, &tmap_qkv, &q_full[st], col_q + 64, i * kFaBM);
+        if (!mbar_wait(do_empty, (n & 1) ^ 1, timeout, abort_flag)) {   // dV(n-1) has read dO(n-1)
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 110, 0, 0);
+          break;
+        }
+        const int col_do = (bb * hq + g * a.qpg + hi) * kFaD;
+        mbar_expect_tx(do_full, kTileBytes);
+        tma_load_2d(sdO, &tmap_do, do_full, col_do, i * kFaBM);
+        tma_load_2d(sdO + kTileBytes / 2, &tmap_do, do_full, col_do + 64, i * kFaBM);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, false, false);   // A K-major, B K-major
+      constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, true, true);     // A MN-major, B MN-major
+      constexpr uint32_t id_km = umma_idesc_bf16(128, 128, false, true);    // A K-major / TMEM, B MN-major
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aS = smem_u32(sdS), aO = smem_u32(sdO);
+      constexpr uint32_t HALF = kTileBytes / 2;
+      auto kdesc = [&](uint32_t base, int kk) {   // K-major operand, k-step kk of 8
+        return umma_smem_desc(base + (kk >> 2) * HALF + (kk & 3) * 32, 0, 1024);
+      };
+      auto mdesc = [&](uint32_t base, int kk) {   // MN-major operand ([128 k rows][64] slabs)
+        return umma_smem_desc(base + kk * 2048, HALF, 1024);
+      };
+      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
+        if (mbar_wait(bar, parity, timeout, abort_flag)) return true;
+        report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, what, 0, 0);
+        return false;
+      };
+      auto issue_s = [&](int n) {     // S^T(n) = K Q(n)^T
+        const uint32_t aQ = smem_u32(sQ + (n & 1) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_s, kdesc(aK, kk), kdesc(aQ, kk), id_kk, kk > 0);
+        umma_commit(s_full);
+      };
+      auto issue_dp = [&]() {         // dP^T(n) = V dO(n)^T
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dp, kdesc(aV, kk), kdesc(aO, kk), id_kk, kk > 0);
+        umma_commit(dp_full);
+      };
+      bool ok = wait_or_fail(kv_full, 0, 200);
+      if (ok && nsteps > 0) ok = wait_or_fail(&q_full[0], 0, 201);
+      if (ok && nsteps > 0) ok = wait_or_fail(do_full, 0, 202);
+      if (ok && nsteps > 0) {
+        tc_fence_after_sync();
+        issue_s(0);
+        issue_dp();
+      }
+      for (int n = 0; ok && n < nsteps; ++n) {
+        const uint32_t par = n & 1;
+        const uint32_t aQ = smem_u32(sQ + (n & 1) * kTileBytes);
+        if (!(ok = wait_or_fail(p_full, par, 210))) break;
+        tc_fence_after_sync();
+        // dV += P^T dO, A from TMEM: query positions 0-63 sit in columns [0, 32) of the S^T block,
+        // positions 64-127 in columns [64, 96) (each softmax warp writes over its own scores)
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ts(t_dv, t_s + (kk >> 2) * 64 + (kk & 3) * 8, mdesc(aO, kk), id_km, (n > 0 || kk > 0));
+        umma_commit(do_empty);
+        if (n + 1 < nsteps) {
+          if (!(ok = wait_or_fail(&q_full[(n + 1) & 1], ((n + 1) >> 1) & 1, 220))) break;
+          tc_fence_after_sync();
+          issue_s(n + 1);
+        }
+        if (!(ok = wait_or_fail(ds_full, par, 230))) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dk, kdesc(aS, kk), mdesc(aQ, kk), id_km, (n > 0 || kk > 0));
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dp, mdesc(aS, kk), mdesc(aK, kk), id_mm, kk > 0);
+        umma_commit(dq_full);
+        umma_commit(&q_empty[n & 1]);
+        if (n + 1 < nsteps) {
+          if (!(ok = wait_or_fail(do_full, par ^ 1, 235))) break;
+          if (!(ok = wait_or_fail(dq_read, par, 240))) break;
+          tc_fence_after_sync();
+          issue_dp();
+        }
+      }
+      if (ok) umma_commit(done_full);
+    }
+  } else if (warp < 10) {
+    // ---- softmax warps: thread (r, hf) owns key/value position j*128 + r and query positions
+    //      [hf*64, hf*64 + 64) of the step's tile ----
+    const int q = warp & 3;
+    const int hf = (warp - 2) >> 2;
+    const int r = q * 32 + lane;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t t_s_mine = t_s + lane_addr + hf * 64;     // my 64 score columns; P^T goes to the first 32
+    const uint32_t t_dp_mine = t_dp + lane_addr + hf * 64;
+    bool ok = true;
+    auto load_stats = [&](int n, float& l2, float& dl) {
+      const int hi = n / tiles, i = j + n % tiles;
+      const int row = i * kFaBM + r;
+      const long long off = ((long long)bb * hq + g * a.qpg + hi) * a.s + row;
+      const bool row_ok = row < a.s;
+      // rows past the end get lse = +inf, which turns their probabilities into exact zeros
+      l2 = row_ok ? a.lse[off] * 1.4426950408889634f : INFINITY;
+      dl = row_ok ? a.delta[off] : 0.f;
+    };
+    float nl2 = 0.f, ndl = 0.f;
+    if (hf == 0 && nsteps > 0) {     // the first four warps fetch the per-row statistics
+      load_stats(0, nl2, ndl);
+      s_lse[r] = nl2;
+      s_dl[r] = ndl;
+      mbar_arrive(&stats_full[0]);
+    }
+    for (int n = 0; n < nsteps; ++n) {
+      const uint32_t par = n & 1;
+      const int st = n & 1;
+      const bool diag = (n % tiles) == 0;
+      if (hf == 0 && n + 1 < nsteps) load_stats(n + 1, nl2, ndl);   // in flight during this step
+      if (!mbar_wait(&stats_full[st], (n >> 1) & 1, timeout, abort_flag) ||
+          !mbar_wait(s_full, par, timeout, abort_flag)) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 300, 0, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      uint32_t pk[32];    // my 64 P^T values, bf16 pairs along the query positions
+      {
+        uint32_t sv[2][32];
+        tmem_ld_32x32(t_s_mine, sv[0]);
+        tmem_ld_32x32(t_s_mine + 32, sv[1]);
+        tmem_ld_wait();
+        const float4* l4 = reinterpret_cast<const float4*>(s_lse + st * 128 + hf * 64);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const float4 l = l4[c * 8 + u];
+            float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][4 * u + 0]), a.scale_log2, -l.x));
+            float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][4 * u + 1]), a.scale_log2, -l.y));
+            float p2 = fast_exp2(fmaf(__uint_as_float(sv[c][4 * u + 2]), a.scale_log2, -l.z));
+            float p3 = fast_exp2(fmaf(__uint_as_float(sv[c][4 * u + 3]), a.scale_log2, -l.w));
+            if (diag) {   // causal: key position r may not exceed the query position
+              const int col = hf * 64 + c * 32 + 4 * u;
+              p0 = (r > col + 0) ? 0.f : p0;
+              p1 = (r > col + 1) ? 0.f : p1;
+              p2 = (r > col + 2) ? 0.f : p2;
+              p3 = (r > col + 3) ? 0.f : p3;
+            }
+            pk[c * 16 + 2 * u] = pack_bf16x2(p0, p1);
+            pk[c * 16 + 2 * u + 1] = pack_bf16x2(p2, p3);
+          }
+        }
+      }
+      tmem_st_32x32(t_s_mine, pk);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+
+      if (!mbar_wait(dp_full, par, timeout, abort_flag)) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 310, 0, 0);
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      {
+        uint32_t dv[2][32];
+        tmem_ld_32x32(t_dp_mine, dv[0]);
+        tmem_ld_32x32(t_dp_mine + 32, dv[1]);
+        tmem_ld_wait();
+        const float4* d4 = reinterpret_cast<const float4*>(s_dl + st * 128 + hf * 64);
+        uint8_t* drow = sdS + hf * (kTileBytes / 2) + r * 128;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {     // 8 query positions = one 16-byte chunk
+          const int c = w >> 2, e0 = (w & 3) * 8;
+          const float4 da = d4[w * 2], db = d4[w * 2 + 1];
+          const float dl[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
+          uint32_t o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 pp = *reinterpret_cast<const __nv_bfloat162*>(&pk[w * 4 + e]);
+            const float d0 = __low2float(pp) * (__uint_as_float(dv[c][e0 + 2 * e]) - dl[2 * e]);
+            const float d1 = __high2float(pp) * (__uint_as_float(dv[c][e0 + 2 * e + 1]) - dl[2 * e + 1]);
+            o[e] = pack_bf16x2(d0, d1);
+          }
+          const int chunk = w ^ (r & 7);
+          *reinterpret_cast<uint4*>(drow + chunk * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_full);
+      if (hf == 0 && n + 1 < nsteps) {   // stage (n+1)&1 was last read in step n-1, which every warp has left
+        s_lse[((n + 1) & 1) * 128 + r] = nl2;
+        s_dl[((n + 1) & 1) * 128 + r] = ndl;
+        mbar_arrive(&stats_full[(n + 1) & 1]);
+      }
+    }
+    if (ok && nsteps > 0 && mbar_wait(done_full, 0, timeout, abort_flag)) {
+      // dK / dV of this block: each warp converts its 64 columns
+      tc_fence_after_sync();
+      const int kvrow = j * kFaBN + r;
+      __nv_bfloat16* dk_dst = a.dqkv + (((long long)kvrow * a.b + bb) * a.G + g) * hpg * kFaD + a.qpg * kFaD;
+      __nv_bfloat16* dv_dst = dk_dst + kFaD;
+#pragma unroll 1
+      for (int c = hf * 2; c < hf * 2 + 2; ++c) {
+        uint32_t vk[32], vv[32];
+        tmem_ld_32x32(t_dk + lane_addr + c * 32, vk);
+        tmem_ld_32x32(t_dv + lane_addr + c * 32, vv);
+        tmem_ld_wait();
+        if (kvrow < a.s) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 k4, v4;
+            k4.x = pack_bf16x2(__uint_as_float(vk[8 * u]) * a.scale, __uint_as_float(vk[8 * u + 1]) * a.scale);
+            k4.y = pack_bf16x2(__uint_as_float(vk[8 * u + 2]) * a.scale, __uint_as_float(vk[8 * u + 3]) * a.scale);
+            k4.z = pack_bf16x2(__uint_as_float(vk[8 * u + 4]) * a.scale, __uint_as_float(vk[8 * u + 5]) * a.scale);
+            k4.w = pack_bf16x2(__uint_as_float(vk[8 * u + 6]) * a.scale, __uint_as_float(vk[8 * u + 7]) * a.scale);
+            v4.x = pack_bf16x2(__uint_as_float(vv[8 * u]), __uint_as_float(vv[8 * u + 1]));
+            v4.y = pack_bf16x2(__uint_as_float(vv[8 * u + 2]), __uint_as_float(vv[8 * u + 3]));
+            v4.z = pack_bf16x2(__uint_as_float(vv[8 * u + 4]), __uint_as_float(vv[8 * u + 5]));
+            v4.w = pack_bf16x2(__uint_as_float(vv[8 * u + 6]), __uint_as_float(vv[8 * u + 7]));
+            reinterpret_cast<uint4*>(dk_dst)[c * 4 + u] = k4;
+            reinterpret_cast<uint4*>(dv_dst)[c * 4 + u] = v4;
+          }
+        }
+      }
+    }
+    tc_fence_before_sync();
+  } else {
+    // ---- dQ drain warps: warp `q` owns query rows [32q, 32q + 32) of the step's tile.  Each round
+    //      moves 32 columns: TMEM -> registers -> a swizzled [32 rows][32 fp32] box in shared memory
+    //      -> TMA reduce-add into the fp32 dQ buffer.  Two boxes per warp alternate. ----
+    const int q = warp & 3;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    uint8_t* my_stage = sStage + q * 8192;
+    for (int n = 0; n < nsteps; ++n) {
+      const int hi = n / tiles, i = j + n % tiles;
+      const int h = g * a.qpg + hi;
+      const int row0 = i * kFaBM + q * 32;       // first query row of my box
+      if (!mbar_wait(dq_full, n & 1, timeout, abort_flag)) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 400, 0, 0);
+        break;
+      }
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int k = 0; k < 4; ++k) {
+        uint32_t v[32];
+        tmem_ld_32x32(t_dp + lane_addr + k * 32, v);
+        // the box written two rounds ago must have been read by its reduction
+        if (lane == 0) bulk_wait_group_read<1>();
+        tmem_ld_wait();
+        if (k == 3) {   // every value has left TMEM: the tensor core may overwrite the columns
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(dq_read);
+        } else {
+          __syncwarp();
+        }
+        uint8_t* box = my_stage + (k & 1) * 4096;
+        uint8_t* brow = box + lane * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c)
+          *reinterpret_cast<uint4*>(brow + ((c ^ (lane & 7)) * 16)) =
+              make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (row0 < a.s && a.flags == 0)
+            tma_reduce_add_2d(&tmap_dq, box, ((bb * hq + h) * kFaD) + k * 32, row0);
+          bulk_commit_group();
+        }
+      }
+    }
+    if (lane == 0) bulk_wait_group<0>();    // all reductions have been performed
     tc_fence_before_sync();
   }
 
@@ -1015,7 +1418,15 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
   return 0;
 }
 
+static bool make_rows_tmap_impl(CUtensorMap* m, const void* ptr, long long cols, long long rows, bool f32);
 static bool make_rows_tmap(CUtensorMap* m, const void* ptr, long long cols, long long rows) {
+  return make_rows_tmap_impl(m, ptr, cols, rows, false);
+}
+// fp32 [rows, cols] tensor, boxes of [32 rows][32 columns] (128 bytes per row, 128-byte swizzle)
+static bool make_f32_box_tmap(CUtensorMap* m, const void* ptr, long long cols, long long rows) {
+  return make_rows_tmap_impl(m, ptr, cols, rows, true);
+}
+static bool make_rows_tmap_impl(CUtensorMap* m, const void* ptr, long long cols, long long rows, bool f32) {
   static EncodeTiledFn2 enc = nullptr;
   if (!enc) {
     void* p = nullptr;
@@ -1026,10 +1437,11 @@ static bool make_rows_tmap(CUtensorMap* m, const void* ptr, long long cols, long
     enc = reinterpret_cast<EncodeTiledFn2>(p);
   }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {64, 128};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * (f32 ? 4 : 2)};
+  cuuint32_t box[2] = {f32 ? 32u : 64u, f32 ? 32u : 128u};
   cuuint32_t estr[2] = {1, 1};
-  return enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+  return enc(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+             const_cast<void*>(ptr), dims, strides, box, estr,
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -1037,7 +1449,7 @@ static bool make_rows_tmap(CUtensorMap* m, const void* ptr, long long cols, long
 extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
                                  float* delta, float* dq_accum, void* dqkv, int s, int b, int G, int qpg,
                                  int d, float scale, unsigned long long timeout_ns, int* status,
-                                 cudaStream_t stream) {
+                                 int version, cudaStream_t stream) {
   if (d != fm::kFaD) {
     fm_set_error("flash_attn_bwd: head_dim must be 128");
     return -1;
@@ -1077,9 +1489,30 @@ extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* d
   a.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
   a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
   a.status = status;
+  a.flags = 0;
   dim3 grid((s + fm::kFaBN - 1) / fm::kFaBN, G, b);
-  fm::flash_bwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tq, tdo, a);
-  fm::attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(dq_accum, a.dqkv, (long long)s * b, G, qpg);
+  if (version == 2) {
+    static bool configured2 = false;
+    if (!configured2) {
+      cudaError_t e2 = cudaFuncSetAttribute(fm::flash_bwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            fm::kFaB2Smem);
+      if (e2 != cudaSuccess) {
+        fm_set_error(cudaGetErrorString(e2));
+        return (int)e2;
+      }
+      configured2 = true;
+    }
+    CUtensorMap tdq;
+    if (!make_f32_box_tmap(&tdq, dq_accum, (long long)b * hq * d, s)) {
+      fm_set_error("flash_attn_bwd: cuTensorMapEncodeTiled failed (dQ)");
+      return -3;
+    }
+    fm::flash_bwd2_kernel<<<grid, fm::kFaB2Threads, fm::kFaB2Smem, stream>>>(tq, tdo, tdq, a);
+    fm::attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(dq_accum, a.dqkv, (long long)s * b, G, qpg, scale);
+  } else {
+    fm::flash_bwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tq, tdo, a);
+    fm::attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(dq_accum, a.dqkv, (long long)s * b, G, qpg, 1.0f);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fm_set_error(cudaGetErrorString(e));

@@ -62,10 +62,10 @@ void bind_ops(py::module_& m) {
         "cross_entropy");
   });
   m.def("flash_attn_bwd", [](u qkv, u out, u dout, u lse, u delta, u dq, u dqkv, int s_, int b, int G, int qpg,
-                             int d, float scale, unsigned long long timeout_ns, u status, u s) {
+                             int d, float scale, unsigned long long timeout_ns, u status, int version, u s) {
     chk(fm_flash_attn_bwd(p<const void*>(qkv), p<const void*>(out), p<const void*>(dout), p<const float*>(lse),
                           p<float*>(delta), p<float*>(dq), p<void*>(dqkv), s_, b, G, qpg, d, scale, timeout_ns,
-                          p<int*>(status), st(s)), "flash_attn_bwd");
+                          p<int*>(status), version, st(s)), "flash_attn_bwd");
   });
   m.def("adam", [](u prm, u master, u g, u mm, u v, long long n, float lr, float b1, float b2,
                    float eps, float wd, int step, float grad_scale, int zero_grad, int state_bf16, u s) {

@@ -94,26 +94,48 @@ __global__ void permute_dispatch_kernel(const __nv_bfloat16* __restrict__ x,
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const long long S = (long long)nle * cap;
-  for (long long s = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s < total_slots;
-       s += (long long)gridDim.x * warps_per_block) {
-    // Visit destinations starting from my right-hand neighbour (the local copy comes last).
-    const long long dst_rank_seq = s / S;
-    const int p = (int)((me + 1 + dst_rank_seq) % P);
-    const long long within = s % S;
-    const int j = (int)(within / cap);
-    const int i = (int)(within % cap);
-    const long long src_slot = (long long)p * S + within;
-    const long long tok = sorted_idx[src_slot];
-    const long long row_in_group = (long long)me * cap + i;
-    const long long drow = (long long)j * P * cap + row_in_group;
-    const uint4* src = reinterpret_cast<const uint4*>(x + tok * H);
-    uint4* dst = reinterpret_cast<uint4*>(dst_tokens[p] + drow * H);
-    for (int v = lane; v < nvec; v += 32) dst[v] = src[v];
-    if (lane == 0 && probs != nullptr) dst_probs[p][drow] = probs[src_slot];
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_system();
-      flag_release_add(dst_flags[p] + j * blocks_per_group + (int)(row_in_group / 128), 1);
+  // A warp takes kRowsPerFence consecutive slots; the system-scope fence and the counter update
+  // are issued once per run of rows that share a counter, not once per row.
+  constexpr int kRowsPerFence = 8;
+  const long long nchunks = (total_slots + kRowsPerFence - 1) / kRowsPerFence;
+  for (long long c = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); c < nchunks;
+       c += (long long)gridDim.x * warps_per_block) {
+    int* pending_flag = nullptr;
+    int pending = 0;
+    const long long s_end = min(total_slots, (c + 1) * kRowsPerFence);
+    for (long long s = c * kRowsPerFence; s < s_end; ++s) {
+      // Visit destinations starting from my right-hand neighbour (the local copy comes last).
+      const long long dst_rank_seq = s / S;
+      const int p = (int)((me + 1 + dst_rank_seq) % P);
+      const long long within = s % S;
+      const int j = (int)(within / cap);
+      const int i = (int)(within % cap);
+      const long long src_slot = (long long)p * S + within;
+      const long long tok = sorted_idx[src_slot];
+      const long long row_in_group = (long long)me * cap + i;
+      const long long drow = (long long)j * P * cap + row_in_group;
+      int* flag = dst_flags[p] + j * blocks_per_group + (int)(row_in_group / 128);
+      if (flag != pending_flag && pending > 0) {
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();
+          flag_release_add(pending_flag, pending);
+        }
+        pending = 0;
+      }
+      pending_flag = flag;
+      const uint4* src = reinterpret_cast<const uint4*>(x + tok * H);
+      uint4* dst = reinterpret_cast<uint4*>(dst_tokens[p] + drow * H);
+      for (int v = lane; v < nvec; v += 32) dst[v] = src[v];
+      if (lane == 0 && probs != nullptr) dst_probs[p][drow] = probs[src_slot];
+      ++pending;
+    }
+    if (pending > 0) {
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_system();
+        flag_release_add(pending_flag, pending);
+      }
     }
   }
 }
@@ -131,17 +153,37 @@ __global__ void rows_push_kernel(const __nv_bfloat16* __restrict__ src,
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   const long long total = rows_blk * P;
-  for (long long s = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s < total;
-       s += (long long)gridDim.x * warps_per_block) {
-    const int p = (int)((me + 1 + s / rows_blk) % P);   // right-hand neighbour first, self last
-    const long long i = s % rows_blk;
-    const uint4* from = reinterpret_cast<const uint4*>(src + ((long long)p * rows_blk + i) * W);
-    uint4* to = reinterpret_cast<uint4*>(dst_base[p] + i * (long long)P * W + (long long)me * W);
-    for (int v = lane; v < nvec; v += 32) to[v] = from[v];
-    __syncwarp();
-    if (lane == 0) {
-      __threadfence_system();
-      flag_release_add(dst_flags[p] + me * row_blocks + (int)(i / 128), 1);
+  constexpr int kRowsPerFence = 8;   // one fence + counter update per run of rows sharing a counter
+  const long long nchunks = (total + kRowsPerFence - 1) / kRowsPerFence;
+  for (long long c = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5); c < nchunks;
+       c += (long long)gridDim.x * warps_per_block) {
+    int* pending_flag = nullptr;
+    int pending = 0;
+    const long long s_end = min(total, (c + 1) * kRowsPerFence);
+    for (long long s = c * kRowsPerFence; s < s_end; ++s) {
+      const int p = (int)((me + 1 + s / rows_blk) % P);   // right-hand neighbour first, self last
+      const long long i = s % rows_blk;
+      int* flag = dst_flags[p] + me * row_blocks + (int)(i / 128);
+      if (flag != pending_flag && pending > 0) {
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_system();
+          flag_release_add(pending_flag, pending);
+        }
+        pending = 0;
+      }
+      pending_flag = flag;
+      const uint4* from = reinterpret_cast<const uint4*>(src + ((long long)p * rows_blk + i) * W);
+      uint4* to = reinterpret_cast<uint4*>(dst_base[p] + i * (long long)P * W + (long long)me * W);
+      for (int v = lane; v < nvec; v += 32) to[v] = from[v];
+      ++pending;
+    }
+    if (pending > 0) {
+      __syncwarp();
+      if (lane == 0) {
+        __threadfence_system();
+        flag_release_add(pending_flag, pending);
+      }
     }
   }
 }

@@ -522,12 +522,27 @@ def fc1_dispatch_backward(plan: EPPlan, dpre_em: torch.Tensor, w1: torch.Tensor,
 # ============================================================================================
 # weight-gradient tasks
 # ============================================================================================
+def fused_optimizer_of(param, sched):
+    """The optimizer that wants to run in this parameter's weight-gradient epilogue, or None.
+    Only taken on the first (and only) gradient write of a step, when the parameter has no
+    expert-data-parallel replicas."""
+    fa = getattr(param, "_fused_adam", None)
+    if fa is None or getattr(param, "_ar_buf_written", False):
+        return None
+    if getattr(sched, "expert_dp_world", 1) > 1:
+        return None
+    return fa
+
+
 def register_moe_dw_tasks(plan: EPPlan, state: MoEForwardState, dfc2_em: torch.Tensor,
                           dpre_em: torch.Tensor, w1_param, w2_param, layer_id: int = 0,
-                          layer_name: str = "moe") -> None:
+                          layer_name: str = "moe", which: str = "both") -> None:
     """Queue ``dW2[e] = actW[e]^T dFC2out[e]`` and ``dW1[e] = tokens[e]^T dFC1[e]``
     (fluid/moe/backward.py:487-613).  When the parameter lives in a flat gradient buffer the GEMM
-    accumulates straight into its fp32 slice."""
+    accumulates straight into its fp32 slice; when an optimizer asked to run in the epilogue
+    (``FusedAdam.fuse_into_backward``) the GEMM updates the parameter instead and stores nothing.
+    ``which`` selects the tasks to queue: a parameter that is updated in place may only be queued
+    once its last use of this backward pass (the FC1 dX GEMM for ``w1``) has been issued."""
     sched = get_backward_scheduler()
     nle = plan.num_local_experts
     rows_per = plan.ep_size * plan.expert_capacity if plan.ep_size > 1 else plan.expert_capacity
@@ -535,6 +550,11 @@ def register_moe_dw_tasks(plan: EPPlan, state: MoEForwardState, dfc2_em: torch.T
 
     def make(a, dy, param):
         def run():
+            fa = fused_optimizer_of(param, sched) if sched.is_enabled() else None
+            if fa is not None:
+                fa.wgrad_update(param, a, dy, nle, grad_scale=1.0 / max(1, sched.shared_dp_world),
+                                uniform_rows=rows_per, max_ctas=max_ctas)
+                return None
             buf = sched._buffer_of(param) if sched.is_enabled() else None
             if buf is not None and param.main_grad.dtype == torch.float32 and a.is_cuda:
                 first = not getattr(param, "_ar_buf_written", False)
@@ -544,8 +564,10 @@ def register_moe_dw_tasks(plan: EPPlan, state: MoEForwardState, dfc2_em: torch.T
             return gemm.grouped_gemm_wgrad(a, dy, nle, uniform_rows=rows_per)
         return run
 
-    sched.register_dw_task(f"{layer_name}.w2", layer_id, make(state.act_em, dfc2_em, w2_param), w2_param)
-    sched.register_dw_task(f"{layer_name}.w1", layer_id, make(state.tokens_em, dpre_em, w1_param), w1_param)
+    if which in ("both", "w2"):
+        sched.register_dw_task(f"{layer_name}.w2", layer_id, make(state.act_em, dfc2_em, w2_param), w2_param)
+    if which in ("both", "w1"):
+        sched.register_dw_task(f"{layer_name}.w1", layer_id, make(state.tokens_em, dpre_em, w1_param), w1_param)
 
 
 # ============================================================================================

@@ -138,6 +138,13 @@ def register_dw_tasks(plan: DroplessPlan, state, dfc2_em, dpre_em, w1_param, w2_
 
     def make(a, dy, param):
         def run():
+            from .moe import fused_optimizer_of
+            fa = fused_optimizer_of(param, sched) if sched.is_enabled() else None
+            if fa is not None:
+                fa.wgrad_update(param, a, dy, nle, grad_scale=1.0 / max(1, sched.shared_dp_world),
+                                group_rows=plan.group_rows, group_offs=plan.group_offs,
+                                max_ctas=sched.dw_max_ctas)
+                return None
             buf = sched._buffer_of(param) if sched.is_enabled() else None
             if buf is not None and param.main_grad.dtype == torch.float32 and a.is_cuda:
                 first = not getattr(param, "_ar_buf_written", False)

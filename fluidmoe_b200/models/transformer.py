@@ -213,7 +213,11 @@ class TransformerLayerFunction(torch.autograd.Function):
                 dfc2_em, dpre_em, dprobs_em = moe_mod.combine_fc2_backward(
                     ep, grad_combined, st, w2, act, cfg["moe_combine"].num_chunks, mode_moe,
                     fused_ctx=_FusedBwd(fused, dy2, rplan) if (mode_moe == "fused" and P > 1) else None)
-            moe_mod.register_moe_dw_tasks(ep, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe")
+            # w1 is still needed by the FC1 dX GEMM of R2: when its optimizer runs in the
+            # weight-gradient epilogue the task may only be queued after R2
+            w1_late = getattr(w1, "_fused_adam", None) is not None
+            moe_mod.register_moe_dw_tasks(ep, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe",
+                                          which="w2" if w1_late else "both")
 
             # ---- routing-probability gradient back to the token owners, router backward ----
             with nvtx_range("bwd_router"):
@@ -245,6 +249,8 @@ class TransformerLayerFunction(torch.autograd.Function):
                     d_ln2 = fused.unpermute(ep, dperm, rplan.slot_of_token, d_ln2_router)
                 else:
                     d_ln2 = permute.unpermute_reduce(dperm, rplan.slot_of_token, d_ln2_router)
+            if w1_late:
+                moe_mod.register_moe_dw_tasks(ep, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe", which="w1")
 
         # ---- shared experts (dense, local) ----
         if ctx.has_shared:

@@ -10,6 +10,7 @@ import os
 
 LAUNCHES = 0
 VERSION = int(os.environ.get("FLUIDMOE_FLASH_VERSION", "2"))
+BWD_VERSION = int(os.environ.get("FLUIDMOE_FLASH_BWD_VERSION", "1"))
 
 
 def supported(qkv: torch.Tensor, head_dim: int) -> bool:
@@ -32,7 +33,7 @@ def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sc
 
 
 def flash_attn_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
-                          q_per_group: int, head_dim: int, scale: float) -> torch.Tensor:
+                          q_per_group: int, head_dim: int, scale: float, version: int = 0) -> torch.Tensor:
     """Gradient of the packed projection buffer, ``[s, b, G, (qpg + 2) * d]`` (dq heads, dk, dv per
     KV group), from the saved output and log-sum-exp."""
     global LAUNCHES
@@ -45,5 +46,6 @@ def flash_attn_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tens
     LAUNCHES += 3
     _native.lib().flash_attn_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
                                  dq_accum.data_ptr(), dqkv.data_ptr(), s, b, G, q_per_group, head_dim, float(scale),
-                                 0, status_buffer(qkv.device).data_ptr(), _native.stream_ptr())
+                                 0, status_buffer(qkv.device).data_ptr(), version or BWD_VERSION,
+                                 _native.stream_ptr())
     return dqkv

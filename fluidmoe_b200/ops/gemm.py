@@ -376,3 +376,67 @@ def grouped_gemm_wgrad(
     desc.update(kw)
     _launch(desc)
     return out
+
+
+def grouped_gemm_wgrad_adam(
+    a: torch.Tensor,
+    dy: torch.Tensor,
+    num_groups: int,
+    param: torch.Tensor,
+    exp_avg: torch.Tensor,
+    exp_avg_sq: torch.Tensor,
+    *,
+    lr: float,
+    beta1: float,
+    beta2: float,
+    eps: float,
+    weight_decay: float,
+    step: int,
+    grad_scale: float = 1.0,
+    group_rows=None,
+    group_offs=None,
+    uniform_rows=None,
+    max_ctas: int = 0,
+) -> None:
+    """Weight gradient with the optimizer in the epilogue: ``g[g] = a[rows_g]^T @ dy[rows_g]`` is
+    never written; the AdamW update of ``param[g]`` ([G, M, N] bf16, moments bf16) is applied to
+    each output tile while it is still in TMEM.  Valid only when this GEMM produces the complete
+    gradient of the step (one micro-batch, no data-parallel reduction of ``param``).  The
+    reference stores the gradient (fluid/moe/backward.py:541-573) and runs the optimizer later."""
+    rows, M = a.shape
+    N = dy.shape[1]
+    G = num_groups
+    if uniform_rows is None and group_rows is None:
+        assert G == 1
+        uniform_rows = rows
+    rbc1 = 1.0 / (1.0 - beta1 ** step)
+    rbc2 = 1.0 / (1.0 - beta2 ** step)
+    p3, m3, v3 = param.view(G, M, N), exp_avg.view(G, M, N), exp_avg_sq.view(G, M, N)
+    if not (_native.use_native(a, dy) and param.dtype == torch.bfloat16 and exp_avg.dtype == torch.bfloat16):
+        for g, o, r in _groups(rows, G, group_rows, group_offs, uniform_rows):
+            gr = grad_scale * (a[o:o + r].float().t() @ dy[o:o + r].float())
+            m = m3[g].float().mul_(beta1).add_(gr, alpha=1 - beta1)
+            v = v3[g].float().mul_(beta2).addcmul_(gr, gr, value=1 - beta2)
+            w = p3[g].float()
+            w = w - lr * ((m * rbc1) / ((v * rbc2).sqrt() + eps) + weight_decay * w)
+            m3[g].copy_(m)
+            v3[g].copy_(v)
+            p3[g].copy_(w)
+        return
+    assert M % 8 == 0 and N % 8 == 0 and param.is_contiguous() and exp_avg.is_contiguous() and exp_avg_sq.is_contiguous()
+    ap, ai, ao, lda = _operand(a)
+    bp, bi, bo, ldb = _operand(dy)
+    desc = dict(
+        A=ap, a_inner=ai, a_outer=ao, lda=lda, a_mn=1,
+        B=bp, b_inner=bi, b_outer=bo, ldb=ldb, b_mn=1,
+        mode=1, num_groups=G, M=M, N=N, K=0, bn=_pick_bn(N), epi=_native.lib().EPI_ADAM,
+        ldc=N, c_group_stride=M * N, alpha=float(grad_scale),
+        adam_p=param.data_ptr(), adam_m=exp_avg.data_ptr(), adam_v=exp_avg_sq.data_ptr(),
+        adam_lr=float(lr), adam_beta1=float(beta1), adam_beta2=float(beta2), adam_eps=float(eps),
+        adam_wd=float(weight_decay), adam_rbc1=float(rbc1), adam_rbc2=float(rbc2),
+        max_ctas=max_ctas, status=status_buffer(a.device).data_ptr(),
+    )
+    kw = _group_kw(group_rows, group_offs, uniform_rows or 0)
+    kw.pop("num_groups", None)
+    desc.update(kw)
+    _launch(desc)

@@ -24,6 +24,39 @@ class FusedAdam:
         self.master_weights = master_weights
         self.state_dtype = state_dtype   # fp32, or bf16 moments as torch.optim.AdamW keeps for bf16 parameters
         self.param_groups = [dict(params=self.params, lr=lr)]
+        self.fused_wgrad_params = 0
+
+    # ------------------------------------------------------------------ optimizer in the backward pass
+    def fuse_into_backward(self, params: Optional[Iterable[torch.nn.Parameter]] = None) -> int:
+        """Let the weight-gradient GEMM of the given parameters (default: every expert weight,
+        i.e. parameters marked ``allreduce = False``) apply this optimizer in its epilogue
+        (``ops.gemm.grouped_gemm_wgrad_adam``): the gradient is never stored and ``step`` skips
+        those parameters.  The caller promises one micro-batch per optimizer step, no gradient
+        clipping and no data-parallel replicas of these parameters.  Needs bf16 parameters and bf16
+        moments without master weights; returns the number of parameters taken."""
+        if self.master_weights or self.state_dtype != torch.bfloat16:
+            return 0
+        chosen = list(params) if params is not None else [p for p in self.params
+                                                          if getattr(p, "allreduce", True) is False]
+        n = 0
+        for p in chosen:
+            if p.dtype == torch.bfloat16 and p.dim() == 3 and p.is_contiguous():
+                p._fused_adam = self
+                p._fused_update_done = False
+                n += 1
+        self.fused_wgrad_params = n
+        return n
+
+    def wgrad_update(self, p, a, dy, num_groups, grad_scale: float = 1.0, **rows_kw) -> None:
+        """Called by a weight-gradient task instead of storing the gradient of ``p``."""
+        from . import gemm
+        st = self._state(p)
+        b1, b2 = self.betas
+        with torch.no_grad():
+            gemm.grouped_gemm_wgrad_adam(a, dy, num_groups, p.data, st["m"], st["v"], lr=self.lr, beta1=b1,
+                                         beta2=b2, eps=self.eps, weight_decay=self.weight_decay,
+                                         step=self.step_count + 1, grad_scale=grad_scale, **rows_kw)
+        p._fused_update_done = True
 
     def _state(self, p):
         st = self.state.get(id(p))
@@ -46,6 +79,9 @@ class FusedAdam:
         self.step_count += 1
         b1, b2 = self.betas
         for p in self.params:
+            if getattr(p, "_fused_update_done", False):
+                p._fused_update_done = False      # updated by its weight-gradient GEMM already
+                continue
             g = self._grad_of(p)
             if g is None:
                 continue

@@ -180,6 +180,15 @@ class FlatGradBuffer:
                 total += buf.numel() * buf.element_size()
         return total
 
+    def skip_pending(self) -> None:
+        """Nothing in this buffer needs a reduction (its gradients were consumed in place)."""
+        if self.primary is not None:
+            self.read = self.committed
+
+    def consumed_in_backward(self) -> bool:
+        """True when every parameter of the buffer is updated by its weight-gradient GEMM."""
+        return bool(self.order) and all(getattr(p, "_fused_adam", None) is not None for p in self.order)
+
     def scale_pending(self, scale: float) -> None:
         for buf in self.buffers.values():
             buf.mul_(scale)
@@ -463,7 +472,9 @@ class BackwardScheduler:
             s_evt = make_event(self._device, True)
             s_evt.record(comm)
         with on_stream(comm):
-            if eb.has_pending() and (not budgeted or expert_budget > 0):
+            if eb.has_pending() and self._expert_grads_consumed():
+                eb.skip_pending()
+            elif eb.has_pending() and (not budgeted or expert_budget > 0):
                 # Expert gradients use the same pre-scale as shared ones even when there is a
                 # single expert-data-parallel replica (AVG convention of the whole model).
                 total += eb.submit_block(self.expert_reduce_fn, expert_budget, scale)
@@ -558,6 +569,11 @@ class BackwardScheduler:
         get_overhead_profiler().exit(tok)
         return result
 
+    def _expert_grads_consumed(self) -> bool:
+        """Expert gradients never reach their buffer when the optimizer runs in the weight-gradient
+        epilogue of every expert parameter and there are no expert-data-parallel replicas."""
+        return getattr(self, "expert_dp_world", 1) <= 1 and self.expert_buffer.consumed_in_backward()
+
     # ------------------------------------------------------------------ iteration boundaries
     def _reduce_all_sync(self) -> None:
         """F / FB tail: one synchronous reduction of everything that was produced."""
@@ -570,7 +586,11 @@ class BackwardScheduler:
         comm.wait_event(ev)
         with on_stream(comm):
             if self.expert_buffer.primary is not None:
-                self.expert_buffer.sync_allreduce(self.expert_reduce_fn, scale)
+                if self._expert_grads_consumed():
+                    self.expert_buffer.commit_all()
+                    self.expert_buffer.skip_pending()
+                else:
+                    self.expert_buffer.sync_allreduce(self.expert_reduce_fn, scale)
             if self.shared_buffer.primary is not None:
                 self.shared_buffer.sync_allreduce(self.shared_reduce_fn, scale)
             for p in self._pending_param_ar:

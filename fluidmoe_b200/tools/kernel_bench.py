@@ -126,8 +126,9 @@ def case_flash(a):
                timed(lambda: flash.flash_attn_fwd_packed(qkv, qpg, d, sc, version=ver)), fl)
     out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, sc)
     dout = torch.randn_like(out)
-    report("flash bwd (delta + main + dq store)",
-           timed(lambda: flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, sc)), 2.5 * fl)
+    for ver in (2, 1):
+        report(f"flash bwd v{ver} (delta + main + dq store)",
+               timed(lambda: flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, sc, version=ver)), 2.5 * fl)
     heads = qkv.view(s, 1, G, qpg + 2, d)
     q = heads[:, :, :, :qpg].reshape(s, 1, G * qpg, d).contiguous()
     k, v = heads[:, :, :, qpg].contiguous(), heads[:, :, :, qpg + 1].contiguous()

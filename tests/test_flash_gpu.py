@@ -71,15 +71,16 @@ def test_attention_backward_from_saved_output(fwd):
         assert err < 3e-2, err
 
 
+@pytest.mark.parametrize("version", [1, 2])
 @pytest.mark.parametrize("s,b,G,qpg", [(256, 1, 1, 1), (512, 1, 2, 2), (1000, 2, 1, 4)])
-def test_flash_bwd_native_matches_reference(s, b, G, qpg):
+def test_flash_bwd_native_matches_reference(s, b, G, qpg, version):
     d = 128
     torch.manual_seed(2)
     qkv = torch.randn(s, b, G, (qpg + 2) * d, device="cuda").bfloat16()
     scale = 1.0 / math.sqrt(d)
     out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, scale)
     dout = torch.randn_like(out)
-    dqkv = flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, scale)
+    dqkv = flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, scale, version=version)
     torch.cuda.synchronize()
     gemm.check_status()
     heads = qkv.float().cpu().view(s, b, G, qpg + 2, d)
@@ -94,21 +95,22 @@ def test_flash_bwd_native_matches_reference(s, b, G, qpg):
         assert err < 3e-2, (name, err)
 
 
-def test_flash_bwd_speed():
+@pytest.mark.parametrize("version", [1, 2])
+def test_flash_bwd_speed(version):
     s, b, G, qpg, d = 8192, 1, 2, 4, 128
     qkv = torch.randn(s, b, G, (qpg + 2) * d, device="cuda").bfloat16()
     out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, 0.088)
     dout = torch.randn_like(out)
     for _ in range(2):
-        flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, 0.088)
+        flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, 0.088, version=version)
     torch.cuda.synchronize()
     st, en = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     st.record()
     for _ in range(5):
-        flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, 0.088)
+        flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, 0.088, version=version)
     en.record()
     torch.cuda.synchronize()
     gemm.check_status()
     ms = st.elapsed_time(en) / 5
     flops = 2.5 * 4 * s * s * G * qpg * d / 2
-    print(f"\nflash bwd s={s} heads={G*qpg}: {ms:.3f} ms, {flops / ms / 1e9:.1f} TFLOP/s")
+    print(f"\nflash bwd v{version} s={s} heads={G*qpg}: {ms:.3f} ms, {flops / ms / 1e9:.1f} TFLOP/s")

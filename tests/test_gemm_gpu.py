@@ -186,3 +186,31 @@ def test_cta_pair_speed(cta_pair):
     gemm.check_status()
     ms = s.elapsed_time(e) / 10
     print(f"\n8192^3 bf16 (CTA pair): {ms:.3f} ms, {2 * 8192**3 / ms / 1e9:.1f} TFLOP/s")
+
+
+@pytest.mark.parametrize("cta_pair", [0, 1])
+@pytest.mark.parametrize("G,rows_per,M,N", [(2, 256, 256, 512), (3, 128, 384, 264)])
+def test_wgrad_adam_epilogue_matches_fp32_reference(G, rows_per, M, N, cta_pair, monkeypatch):
+    """Optimizer in the weight-gradient epilogue == fp32 gradient followed by an fp32 AdamW update
+    (the PyTorch reference of the same op), up to the bf16 rounding of parameter and moments."""
+    monkeypatch.setattr(gemm, "CTA_PAIR", cta_pair)
+    torch.manual_seed(5)
+    a = torch.randn(G * rows_per, M, device="cuda").bfloat16()
+    dy = torch.randn(G * rows_per, N, device="cuda").bfloat16()
+    p = (torch.randn(G, M, N, device="cuda") * 0.05).bfloat16()
+    m = (torch.randn(G, M, N, device="cuda") * 0.1).bfloat16()
+    v = (torch.rand(G, M, N, device="cuda") * 0.1).bfloat16()
+    lr, b1, b2, eps, wd, step, gs = 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, 0.25
+    g = torch.stack([a[i * rows_per:(i + 1) * rows_per].float().t() @ dy[i * rows_per:(i + 1) * rows_per].float()
+                     for i in range(G)]) * gs
+    m_ref = b1 * m.float() + (1 - b1) * g
+    v_ref = b2 * v.float() + (1 - b2) * g * g
+    w = p.float()
+    w_ref = w - lr * ((m_ref / (1 - b1 ** step)) / ((v_ref / (1 - b2 ** step)).sqrt() + eps) + wd * w)
+    gemm.grouped_gemm_wgrad_adam(a, dy, G, p, m, v, lr=lr, beta1=b1, beta2=b2, eps=eps, weight_decay=wd,
+                                 step=step, grad_scale=gs, uniform_rows=rows_per)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for name, got, ref in (("m", m, m_ref), ("v", v, v_ref), ("p", p, w_ref)):
+        err = ((got.float() - ref).norm() / ref.norm()).item()
+        assert err < 6e-3, (name, err)

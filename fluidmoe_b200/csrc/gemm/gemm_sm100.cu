@@ -298,65 +298,120 @@ struct EpiAdam {
   float alpha;   // gradient scale
   float lr, beta1, beta2, eps, weight_decay, rbc1, rbc2;
 
+  // One AdamW step on 8 consecutive elements held as bf16 pairs.  The epilogue has only eight
+  // warps per SM to hide latency with, so the square root and the division use the hardware
+  // approximations (2 ulp; parameter and moments are rounded to bf16 right after).
+  static __device__ __forceinline__ float sqrt_approx(float x) {
+    float y;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  static __device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+  }
+  __device__ __forceinline__ void update8(const float* gg, uint4& pw, uint4& pm, uint4& pv) const {
+    uint32_t* ww = reinterpret_cast<uint32_t*>(&pw);
+    uint32_t* wm = reinterpret_cast<uint32_t*>(&pm);
+    uint32_t* wv = reinterpret_cast<uint32_t*>(&pv);
+    const float c1 = (1.f - beta1) * alpha, c2 = (1.f - beta2) * alpha * alpha;
+    const float step_m = lr * rbc1, decay = 1.f - lr * weight_decay;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      // bf16 -> fp32 is a 16-bit shift of the bit pattern
+      float w2[2] = {__uint_as_float(ww[q] << 16), __uint_as_float(ww[q] & 0xffff0000u)};
+      float m2[2] = {__uint_as_float(wm[q] << 16), __uint_as_float(wm[q] & 0xffff0000u)};
+      float v2[2] = {__uint_as_float(wv[q] << 16), __uint_as_float(wv[q] & 0xffff0000u)};
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float gi = gg[2 * q + e];
+        m2[e] = fmaf(beta1, m2[e], c1 * gi);
+        v2[e] = fmaf(beta2, v2[e], c2 * gi * gi);
+        const float r = rcp_approx(sqrt_approx(v2[e] * rbc2) + eps);
+        w2[e] = fmaf(-step_m * m2[e], r, decay * w2[e]);
+      }
+      ww[q] = pack_bf16x2(w2[0], w2[1]);
+      wm[q] = pack_bf16x2(m2[0], m2[1]);
+      wv[q] = pack_bf16x2(v2[0], v2[1]);
+    }
+  }
+
+  static constexpr bool kPrefetch = true;
+  // Called one tile ahead: pull this warp's part of parameter and moments (32 rows x BN/2
+  // columns of three bf16 arrays) into L2 while the tensor core still works on the tile.
+  template <int BN>
+  __device__ __forceinline__ void prefetch(const Tile& t, const GemmArgs& a, int r, int chalf) const {
+    const int lane = r & 31;
+    if (r >= t.rows_valid) return;
+    const long long row = a.mode == 0 ? (long long)t.row_base + t.m0 + r : (long long)t.m0 + r;
+    const long long goff = a.mode == 0 ? 0 : (long long)t.g * group_stride;
+    const int col0 = t.n_tile * BN + chalf * (BN / 2);
+    const long long off = goff + row * ld + col0;
+    (void)lane;
+#pragma unroll
+    for (int l = 0; l < BN / 2; l += 64) {     // 64 bf16 = one 128-byte line
+      if (col0 + l >= a.N) break;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(P + off + l));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(Mo + off + l));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(Vo + off + l));
+    }
+  }
+
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
                                       bool zero, int chalf, float* stg) const {
+    constexpr int NB = BN / 64;          // 32-column blocks handled by this warp
     const int lane = r & 31;
     const long long row = a.mode == 0 ? (long long)t.row_base + t.m0 + r : (long long)t.m0 + r;
     const long long row0 = row - lane;
     const long long goff = a.mode == 0 ? 0 : (long long)t.g * group_stride;
     const bool row_ok = r < t.rows_valid;
     const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
+    const int sub = lane >> 2, c8 = (lane & 3) * 8;
+    const int c_begin = chalf * NB;
+    const long long off0 = goff + row0 * ld + (long long)t.n_tile * BN;
+    // coalesced path: whole 32-column blocks, 16-byte aligned rows (4 lanes x 16 bytes per row)
+    const bool vec_ok = (ld & 7) == 0 && aligned16(P + off0) && aligned16(Mo + off0) && aligned16(Vo + off0);
 #pragma unroll 1
-    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+    for (int k = 0; k < NB; ++k) {
+      const int c = c_begin + k;
       const int col = t.n_tile * BN + c * 32;
       if (col >= a.N) break;
-      float g[32];
-      load_acc(taddr + c * 32, g, zero);
-      if (rows_ok == 0) continue;
       const int ncols = min(32, a.N - col);
-      const long long off = goff + row0 * ld + col;
-      if (ncols == 32 && (ld & 7) == 0 && aligned16(P + off) && aligned16(Mo + off) && aligned16(Vo + off)) {
-        // the gradient block goes through the stage once; parameter and moments are then read,
-        // updated and written in the coalesced layout (4 lanes x 16 bytes per row)
-        stage_put(stg, lane, g);
-        const int sub = lane >> 2, c8 = (lane & 3) * 8;
+      const long long off = off0 + c * 32;
+      const bool fast = vec_ok && ncols == 32;
+      // parameter and moments do not depend on the accumulator: issue their loads first
+      uint4 b[12];
+      if (fast) {
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass) {
           const int rr = pass * 8 + sub;
           if (rr < rows_ok) {
-            const long long o = off + rr * ld + c8;
+            const long long o = off + (long long)rr * ld + c8;
+            b[pass * 3 + 0] = *reinterpret_cast<const uint4*>(P + o);
+            b[pass * 3 + 1] = *reinterpret_cast<const uint4*>(Mo + o);
+            b[pass * 3 + 2] = *reinterpret_cast<const uint4*>(Vo + o);
+          }
+        }
+      }
+      float g[32];
+      load_acc(taddr + c * 32, g, zero);
+      if (rows_ok == 0) continue;
+      if (fast) {
+        stage_put(stg, lane, g);
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const int rr = pass * 8 + sub;
+          if (rr < rows_ok) {
+            const long long o = off + (long long)rr * ld + c8;
             const float4 ga = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
             const float4 gb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
             const float gg[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-            uint4 pw = *reinterpret_cast<const uint4*>(P + o);
-            uint4 pm = *reinterpret_cast<const uint4*>(Mo + o);
-            uint4 pv = *reinterpret_cast<const uint4*>(Vo + o);
-            uint32_t* ww = reinterpret_cast<uint32_t*>(&pw);
-            uint32_t* wm = reinterpret_cast<uint32_t*>(&pm);
-            uint32_t* wv = reinterpret_cast<uint32_t*>(&pv);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const __nv_bfloat162 bw = *reinterpret_cast<const __nv_bfloat162*>(&ww[q]);
-              const __nv_bfloat162 bm = *reinterpret_cast<const __nv_bfloat162*>(&wm[q]);
-              const __nv_bfloat162 bv = *reinterpret_cast<const __nv_bfloat162*>(&wv[q]);
-              float w2[2] = {__low2float(bw), __high2float(bw)};
-              float m2[2] = {__low2float(bm), __high2float(bm)};
-              float v2[2] = {__low2float(bv), __high2float(bv)};
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const float gi = gg[2 * q + e] * alpha;
-                m2[e] = beta1 * m2[e] + (1.f - beta1) * gi;
-                v2[e] = beta2 * v2[e] + (1.f - beta2) * gi * gi;
-                w2[e] -= lr * ((m2[e] * rbc1) / (sqrtf(v2[e] * rbc2) + eps) + weight_decay * w2[e]);
-              }
-              ww[q] = pack_bf16x2(w2[0], w2[1]);
-              wm[q] = pack_bf16x2(m2[0], m2[1]);
-              wv[q] = pack_bf16x2(v2[0], v2[1]);
-            }
-            *reinterpret_cast<uint4*>(Mo + o) = pm;
-            *reinterpret_cast<uint4*>(Vo + o) = pv;
-            *reinterpret_cast<uint4*>(P + o) = pw;
+            update8(gg, b[pass * 3 + 0], b[pass * 3 + 1], b[pass * 3 + 2]);
+            *reinterpret_cast<uint4*>(Mo + o) = b[pass * 3 + 1];
+            *reinterpret_cast<uint4*>(Vo + o) = b[pass * 3 + 2];
+            *reinterpret_cast<uint4*>(P + o) = b[pass * 3 + 0];
           }
         }
         __syncwarp();

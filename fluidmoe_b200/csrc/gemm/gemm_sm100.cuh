@@ -117,6 +117,14 @@ struct TileWalker {
   }
 };
 
+// An epilogue may declare `static constexpr bool kPrefetch = true` and a member
+// `prefetch<BN>(tile, args, row, chalf)`; the epilogue warps then call it one tile ahead, before
+// they wait for the current accumulator, so that operands the epilogue reads are already in L2.
+template <class E, class = void>
+struct EpiHasPrefetch { static constexpr bool value = false; };
+template <class E>
+struct EpiHasPrefetch<E, decltype((void)E::kPrefetch)> { static constexpr bool value = true; };
+
 // No gating: every tile is ready when the kernel starts.
 struct GateNone {
   __device__ __forceinline__ bool wait(const Tile&, const GemmArgs&, volatile int*) const {
@@ -403,10 +411,16 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
     const int q = warp & 3;             // TMEM lane quarter this warp may read
     const int chalf = (warp - 2) >> 2;  // which half of the tile's columns this warp drains
     TileWalker<BN> walker(args);
+    TileWalker<BN> peek(args);
     Tile t;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int ti = blockIdx.x; walker.get(ti, t); ti += gridDim.x) {
+      if constexpr (EpiHasPrefetch<Epi>::value) {
+        Tile nx;
+        if (ti == (int)blockIdx.x) epi.template prefetch<BN>(t, args, q * 32 + lane, chalf);
+        if (peek.get(ti + gridDim.x, nx)) epi.template prefetch<BN>(nx, args, q * 32 + lane, chalf);
+      }
       if (!mbar_wait(&tfull[acc], acc_phase, timeout, abort_flag)) {
         if (lane == 0)
           report_status(args.status, kStatusMbarTimeout, kKernelIdGemm, 400 + acc, 0, 0);
@@ -627,6 +641,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
     const int q = warp & 3;
     const int chalf = (warp - 2) >> 2;
     TileWalker<BN, 2 * kBM> walker(args);
+    TileWalker<BN, 2 * kBM> peek(args);
     Tile t;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -634,6 +649,15 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
       Tile mine = t;
       mine.m0 = t.m0 + (int)cta_rank * kBM;
       mine.rows_valid = max(0, min(kBM, t.rows_valid - (int)cta_rank * kBM));
+      if constexpr (EpiHasPrefetch<Epi>::value) {
+        Tile nx;
+        if (ti == pair_id) epi.template prefetch<BN>(mine, args, q * 32 + lane, chalf);
+        if (peek.get(ti + num_pairs, nx)) {
+          nx.rows_valid = max(0, min(kBM, nx.rows_valid - (int)cta_rank * kBM));
+          nx.m0 += (int)cta_rank * kBM;
+          epi.template prefetch<BN>(nx, args, q * 32 + lane, chalf);
+        }
+      }
       if (!mbar_wait(&tfull[acc], acc_phase, timeout, abort_flag)) {
         if (lane == 0)
           report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 400 + acc, 0, 0);

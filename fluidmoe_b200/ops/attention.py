@@ -89,14 +89,14 @@ def attention_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sca
 def attention_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse, q_per_group: int,
                          head_dim: int, scale: float = None) -> torch.Tensor:
     """Gradient of the packed projection buffer from the saved output (and log-sum-exp).
-    ``FLUIDMOE_ATTN_BWD=native`` selects this library's tcgen05 kernel, ``library`` (default) the
+    ``FLUIDMOE_ATTN_BWD=native`` (default) selects this library's tcgen05 kernel, ``library`` the
     vendor attention backward."""
     import os
     from . import flash
     s, b, G, gs = qkv.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     have_lse = lse is not None and lse.dim() == 3 and lse.dtype == torch.float32
-    if have_lse and flash.supported(qkv, head_dim) and os.environ.get("FLUIDMOE_ATTN_BWD", "library") == "native":
+    if have_lse and flash.supported(qkv, head_dim) and os.environ.get("FLUIDMOE_ATTN_BWD", "native") == "native":
         return flash.flash_attn_bwd_packed(dout, qkv, out, lse, q_per_group, head_dim, scale)
     qpg, d = q_per_group, head_dim
     heads = qkv.view(s, b, G, qpg + 2, d)

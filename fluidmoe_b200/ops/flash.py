@@ -10,7 +10,7 @@ import os
 
 LAUNCHES = 0
 VERSION = int(os.environ.get("FLUIDMOE_FLASH_VERSION", "2"))
-BWD_VERSION = int(os.environ.get("FLUIDMOE_FLASH_BWD_VERSION", "1"))
+BWD_VERSION = int(os.environ.get("FLUIDMOE_FLASH_BWD_VERSION", "2"))
 
 
 def supported(qkv: torch.Tensor, head_dim: int) -> bool:

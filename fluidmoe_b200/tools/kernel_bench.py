@@ -115,6 +115,23 @@ def case_wgrad(a):
            2.0 * R * H * 2 * F, bytes_=out.numel() * 4.0)
 
 
+def case_wgrad_adam(a):
+    """Expert weight gradient with the optimizer in the epilogue, against gradient store + Adam pass."""
+    R, H, F, G = a.rows, a.hidden, a.ffn, a.experts
+    x, dy = _r(R, H), _r(R, 2 * F)
+    p = _r(G, H, 2 * F, scale=0.02)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    hyper = dict(lr=1e-4, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1)
+    fl, by = 2.0 * R * H * 2 * F, p.numel() * 12.0
+    report(f"wgrad + Adam epilogue G={G} {H}x{2 * F}, K={R // G}",
+           timed(lambda: gemm.grouped_gemm_wgrad_adam(x, dy, G, p, m, v, uniform_rows=R // G, **hyper)), fl, bytes_=by)
+    out = torch.zeros(G, H, 2 * F, device="cuda")
+    t1 = timed(lambda: gemm.grouped_gemm_wgrad(x, dy, G, uniform_rows=R // G, out=out, accumulate=False))
+    t2 = timed(lambda: ew.adam_step(p.view(-1), None, out.view(-1), m.view(-1), v.view(-1), 1e-4, 0.9, 0.999, 1e-8, 0.0, 1))
+    report("  gradient store (fp32) then Adam pass", t1 + t2, fl, bytes_=p.numel() * 20.0)
+    report("    of which Adam pass", t2, bytes_=p.numel() * 16.0)
+
+
 def case_flash(a):
     from ..ops import attention
     s, G, qpg, d = a.seq, a.kv_heads, a.q_per_kv, 128
@@ -232,7 +249,7 @@ def case_fused(a):
     report(f"FC2 + combine (scatter epilogue) + unpermute {rows}x{F}x{H}", timed(fc2), 2.0 * rows * F * H)
 
 
-CASES = dict(gemm=case_gemm, fc1=case_fc1, dact=case_dact, wgrad=case_wgrad, flash=case_flash, norm=case_norm,
+CASES = dict(gemm=case_gemm, fc1=case_fc1, dact=case_dact, wgrad=case_wgrad, wgrad_adam=case_wgrad_adam, flash=case_flash, norm=case_norm,
              permute=case_permute, adam=case_adam, ce=case_ce, rope=case_rope, fused=case_fused)
 
 

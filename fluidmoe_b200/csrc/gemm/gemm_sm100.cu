@@ -352,9 +352,9 @@ struct EpiAdam {
 #pragma unroll
     for (int l = 0; l < BN / 2; l += 64) {     // 64 bf16 = one 128-byte line
       if (col0 + l >= a.N) break;
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(P + off + l));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(Mo + off + l));
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(Vo + off + l));
+      asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(P + off + l));
+      asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(Mo + off + l));
+      asm volatile("prefetch.global.L2::evict_last [%0];" ::"l"(Vo + off + l));
     }
   }
 

@@ -17,6 +17,11 @@ int fm_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
                 int kind, cudaStream_t s);
 int fm_rope_packed(void* t, const float* freqs, long long rows, int heads_per_row, int rope_heads,
                    int d, int rot, int rows_per_pos, int backward, cudaStream_t s);
+// dlogits [T, E] fp32 from the slot-probability gradients (softmax-over-top-k backward, optional
+// load-balancing term aux_coef * tpe[e] and z-loss term z_coef * lse * softmax); tpe / logits may be null.
+int fm_router_bwd(const float* dprobs_slots, const int* slot_of_token, const long long* top_idx,
+                  const float* top_probs, const float* logits, const float* tpe, float aux_coef, float z_coef,
+                  int T, int k, int E, float* dlogits, cudaStream_t s);
 int fm_topk_softmax(const float* logits, long long* idx, float* probs, int T, int E, int k,
                     cudaStream_t s);
 int fm_gather_rows(const void* x, const long long* idx, void* out, long long rows, int H,

@@ -427,6 +427,49 @@ __global__ void adam_tail_kernel(__nv_bfloat16* p, float* master, float* g, ST* 
 }
 
 // --------------------------------------------------------------------------------------------
+// Router backward: gradient of the loss w.r.t. the router logits [T, E] (fp32).  One thread per
+// token gathers the gradient of its k slot probabilities (dropped choices have slot -1 and
+// contribute nothing), adds the load-balancing term coef * tokens_per_expert[e], runs the backward
+// of the softmax over the k selected logits, scatters into a zeroed row and adds the z-loss term
+// zc * logsumexp(logits) * softmax(logits).  Reference: fluid/moe/backward.py:1461-1530.
+// --------------------------------------------------------------------------------------------
+__global__ void router_bwd_kernel(const float* __restrict__ dprobs_slots, const int* __restrict__ slot_of_token,
+                                  const long long* __restrict__ top_idx, const float* __restrict__ top_probs,
+                                  const float* __restrict__ logits, const float* __restrict__ tpe,
+                                  float aux_coef, float z_coef, int T, int k, int E,
+                                  float* __restrict__ dlogits) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  float* out = dlogits + (long long)t * E;
+  if (z_coef != 0.f) {
+    const float* lg = logits + (long long)t * E;
+    float mx = -INFINITY;
+    for (int e = 0; e < E; ++e) mx = fmaxf(mx, lg[e]);
+    float sum = 0.f;
+    for (int e = 0; e < E; ++e) sum += __expf(lg[e] - mx);
+    const float lse = mx + __logf(sum);
+    const float f = z_coef * lse / sum;
+    for (int e = 0; e < E; ++e) out[e] = f * __expf(lg[e] - mx);
+  } else {
+    for (int e = 0; e < E; ++e) out[e] = 0.f;
+  }
+  float dot = 0.f;
+  for (int j = 0; j < k; ++j) {
+    const int slot = slot_of_token[(long long)t * k + j];
+    float g = slot >= 0 ? dprobs_slots[slot] : 0.f;
+    if (tpe != nullptr) g += aux_coef * tpe[top_idx[(long long)t * k + j]];
+    dot += top_probs[(long long)t * k + j] * g;
+  }
+  for (int j = 0; j < k; ++j) {
+    const int slot = slot_of_token[(long long)t * k + j];
+    const long long e = top_idx[(long long)t * k + j];
+    float g = slot >= 0 ? dprobs_slots[slot] : 0.f;
+    if (tpe != nullptr) g += aux_coef * tpe[e];
+    out[e] += top_probs[(long long)t * k + j] * (g - dot);
+  }
+}
+
+// --------------------------------------------------------------------------------------------
 // Routing plan for fixed (padded) capacity.  One CTA per expert:
 //   1. count the tokens routed to the expert;
 //   2. if there are more than `cap`, find the cap-th largest probability by radix select on the
@@ -779,6 +822,18 @@ extern "C" int fm_adam(void* p, float* master, float* g, void* m, void* v, long 
     return check_launch("adam_tail");
   }
   return 0;
+}
+
+extern "C" int fm_router_bwd(const float* dprobs_slots, const int* slot_of_token, const long long* top_idx,
+                             const float* top_probs, const float* logits, const float* tpe, float aux_coef,
+                             float z_coef, int T, int k, int E, float* dlogits, cudaStream_t s) {
+  if (z_coef != 0.f && logits == nullptr) {
+    fm_set_error("router_bwd: the z-loss term needs the logits");
+    return -1;
+  }
+  fm::router_bwd_kernel<<<(T + 127) / 128, 128, 0, s>>>(dprobs_slots, slot_of_token, top_idx, top_probs, logits,
+                                                       tpe, aux_coef, z_coef, T, k, E, dlogits);
+  return check_launch("router_bwd");
 }
 
 extern "C" int fm_moe_plan(const long long* top_idx, const float* top_probs, int T, int k, int E,

@@ -67,6 +67,12 @@ void bind_ops(py::module_& m) {
                           p<float*>(delta), p<float*>(dq), p<void*>(dqkv), s_, b, G, qpg, d, scale, timeout_ns,
                           p<int*>(status), version, st(s)), "flash_attn_bwd");
   });
+  m.def("router_bwd", [](u dprobs, u slot_of_token, u top_idx, u top_probs, u logits, u tpe, float aux_coef,
+                         float z_coef, int T, int k, int E, u dlogits, u s) {
+    chk(fm_router_bwd(p<const float*>(dprobs), p<const int*>(slot_of_token), p<const long long*>(top_idx),
+                      p<const float*>(top_probs), p<const float*>(logits), p<const float*>(tpe), aux_coef, z_coef,
+                      T, k, E, p<float*>(dlogits), st(s)), "router_bwd");
+  });
   m.def("adam", [](u prm, u master, u g, u mm, u v, long long n, float lr, float b1, float b2,
                    float eps, float wd, int step, float grad_scale, int zero_grad, int state_bf16, u s) {
     chk(fm_adam(p<void*>(prm), p<float*>(master), p<float*>(g), p<void*>(mm), p<void*>(v), n, lr,

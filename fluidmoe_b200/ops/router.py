@@ -135,6 +135,23 @@ def router_backward_logits(dprobs_slots: torch.Tensor, plan: RoutingPlan, top_id
     contributes ``2c/T * logsumexp(logits) * softmax(logits)`` (fluid/moe/backward.py:1461-1530).
     """
     T, k = top_idx.shape
+    use_aux = aux_loss_coeff > 0.0 and tokens_per_expert_global is not None
+    if (_native.use_native(dprobs_slots, top_idx) and hasattr(_native.lib(), "router_bwd")
+            and plan.slot_of_token.dtype == torch.int32 and top_idx.dtype == torch.int64
+            and (z_loss_coeff <= 0.0 or logits.dtype == torch.float32)):
+        tg = float(num_global_tokens if num_global_tokens is not None else T)
+        dlogits = torch.empty(T, num_experts, dtype=torch.float32, device=top_idx.device)
+        dps = dprobs_slots.float().contiguous()
+        tpe = tokens_per_expert_global.float().contiguous() if use_aux else None
+        lg = logits.contiguous() if z_loss_coeff > 0.0 else None
+        tp = top_probs.float().contiguous()
+        _native.lib().router_bwd(dps.data_ptr(), plan.slot_of_token.contiguous().data_ptr(),
+                                 top_idx.contiguous().data_ptr(), tp.data_ptr(),
+                                 lg.data_ptr() if lg is not None else 0, tpe.data_ptr() if tpe is not None else 0,
+                                 float(num_experts * aux_loss_coeff / (k * tg * tg)) if use_aux else 0.0,
+                                 float(2.0 * z_loss_coeff / T) if z_loss_coeff > 0.0 else 0.0,
+                                 T, k, num_experts, dlogits.data_ptr(), _native.stream_ptr())
+        return dlogits
     slots = plan.slot_of_token.long()
     g = torch.where(slots >= 0, dprobs_slots.float()[slots.clamp(min=0)], torch.zeros((), device=slots.device))
     p = top_probs.float()

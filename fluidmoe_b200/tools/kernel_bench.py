@@ -69,7 +69,10 @@ def report(name, ms, flops=0.0, bytes_=0.0):
     if bytes_:
         g = bytes_ / ms / 1e6
         parts.append(f"{g:8.1f} GB/s ({g / gb:5.2f} {label} copy bandwidth)")
-    print("  ".join(parts), flush=True)
+    try:
+        print("  ".join(parts), flush=True)
+    except BrokenPipeError:      # output piped into `head`
+        pass
 
 
 def _r(*shape, scale=1.0):

@@ -117,3 +117,20 @@ def test_fused_cross_entropy():
     loss = ew.cross_entropy_(work, labels, 1.0)
     _close(loss, ref, 1e-2)
     assert (work.float() - ref_in.grad).abs().max().item() < 1e-2
+
+
+@pytest.mark.parametrize("aux,z", [(0.0, 0.0), (0.01, 0.001)])
+def test_router_backward_kernel_matches_pytorch(aux, z, monkeypatch):
+    from fluidmoe_b200 import _native
+    T, E, k = 1000, 8, 2
+    torch.manual_seed(3)
+    logits = torch.randn(T, E, device="cuda")
+    ti, tp = router.topk_softmax(logits, k)
+    cap = router.expert_capacity(T, k, E, 1.0)
+    plan = router.build_padded_plan(ti, tp, E, cap)
+    dprobs = torch.randn(E * cap, device="cuda")
+    tpe = plan.routed_per_expert.float()
+    got = router.router_backward_logits(dprobs, plan, ti, tp, logits, E, aux, z, tpe, T)
+    monkeypatch.setattr(_native, "use_native", lambda *a: False)
+    ref = router.router_backward_logits(dprobs, plan, ti, tp, logits, E, aux, z, tpe, T)
+    assert (got - ref).abs().max().item() < 1e-5 * max(1.0, ref.abs().max().item())

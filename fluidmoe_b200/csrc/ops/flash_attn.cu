@@ -1113,11 +1113,13 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         }
         if (!(ok = wait_or_fail(ds_full, par, 230))) break;
         tc_fence_after_sync();
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dk, kdesc(aS, kk), mdesc(aQ, kk), id_km, (n > 0 || kk > 0));
+        // dQ first: its drain (and then dP^T of the next step, which re-uses the columns) is on the
+        // critical path, dK is not
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dp, mdesc(aS, kk), mdesc(aK, kk), id_mm, kk > 0);
         umma_commit(dq_full);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dk, kdesc(aS, kk), mdesc(aQ, kk), id_km, (n > 0 || kk > 0));
         umma_commit(&q_empty[n & 1]);
         if (n + 1 < nsteps) {
           if (!(ok = wait_or_fail(do_full, par ^ 1, 235))) break;
@@ -1272,9 +1274,9 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
     }
     tc_fence_before_sync();
   } else {
-    // ---- dQ drain warps: warp `q` owns query rows [32q, 32q + 32) of the step's tile.  Each round
-    //      moves 32 columns: TMEM -> registers -> a swizzled [32 rows][32 fp32] box in shared memory
-    //      -> TMA reduce-add into the fp32 dQ buffer.  Two boxes per warp alternate. ----
+    // ---- dQ drain warps: warp `q` owns query rows [32q, 32q + 32) of the step's tile and moves them
+    //      in two halves of 64 columns: TMEM -> registers -> two swizzled [32 rows][32 fp32] boxes in
+    //      shared memory -> TMA reduce-add into the fp32 dQ buffer. ----
     const int q = warp & 3;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     uint8_t* my_stage = sStage + q * 8192;
@@ -1287,34 +1289,48 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         break;
       }
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int k = 0; k < 4; ++k) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_dp + lane_addr + k * 32, v);
-        // the box written two rounds ago must have been read by its reduction
-        if (lane == 0) bulk_wait_group_read<1>();
-        tmem_ld_wait();
-        if (k == 3) {   // every value has left TMEM: the tensor core may overwrite the columns
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(dq_read);
-        } else {
-          __syncwarp();
-        }
-        uint8_t* box = my_stage + (k & 1) * 4096;
-        uint8_t* brow = box + lane * 128;
+      // Two halves of 64 columns: both boxes of the first half are filled and the second half is
+      // already in registers when the TMEM columns are released to the tensor core.
+      uint32_t va[2][32];
+      tmem_ld_32x32(t_dp + lane_addr, va[0]);
+      tmem_ld_32x32(t_dp + lane_addr + 32, va[1]);
+      if (lane == 0) bulk_wait_group_read<0>();   // both boxes of the previous step have been read
+      tmem_ld_wait();
+      __syncwarp();
+      auto put_box = [&](int slot, const uint32_t* v) {
+        uint8_t* brow = my_stage + slot * 4096 + lane * 128;
 #pragma unroll
         for (int c = 0; c < 8; ++c)
           *reinterpret_cast<uint4*>(brow + ((c ^ (lane & 7)) * 16)) =
               make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]);
+      };
+      auto reduce_boxes = [&](int first_col) {
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (row0 < a.s && a.flags == 0)
-            tma_reduce_add_2d(&tmap_dq, box, ((bb * hq + h) * kFaD) + k * 32, row0);
+          if (row0 < a.s && a.flags == 0) {
+            tma_reduce_add_2d(&tmap_dq, my_stage, ((bb * hq + h) * kFaD) + first_col, row0);
+            tma_reduce_add_2d(&tmap_dq, my_stage + 4096, ((bb * hq + h) * kFaD) + first_col + 32, row0);
+          }
           bulk_commit_group();
         }
+      };
+      put_box(0, va[0]);
+      put_box(1, va[1]);
+      tmem_ld_32x32(t_dp + lane_addr + 64, va[0]);
+      tmem_ld_32x32(t_dp + lane_addr + 96, va[1]);
+      reduce_boxes(0);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(dq_read);          // every value has left TMEM
+        bulk_wait_group_read<0>();     // the first half's boxes have been read
       }
+      __syncwarp();
+      put_box(0, va[0]);
+      put_box(1, va[1]);
+      reduce_boxes(64);
     }
     if (lane == 0) bulk_wait_group<0>();    // all reductions have been performed
     tc_fence_before_sync();

@@ -99,3 +99,53 @@ def test_checkpoint_round_trip(tmp_path):
     sd = {k.replace("qkv_weight", "te_qkv_linear.weight"): v for k, v in a.state_dict().items()}
     sd["layers.0.te_attn._extra_state"] = torch.zeros(1)
     load_reference_state_dict(b, sd)
+
+
+def test_comm_timer_counts_and_restores():
+    """The collective timers wrap the torch.distributed entry points only inside the context."""
+    import torch.distributed as dist
+    from fluidmoe_b200.tools import comm_ratio_table as crt
+    orig = dist.all_reduce
+    seen = []
+
+    def fake_all_reduce(t, *a, **k):
+        seen.append(t.numel())
+    dist.all_reduce = fake_all_reduce
+    try:
+        iter_ms, table = crt.measure(lambda: dist.all_reduce(torch.zeros(4)), 3, torch.device("cpu"))
+        assert dist.all_reduce is fake_all_reduce          # restored
+    finally:
+        dist.all_reduce = orig
+    assert seen == [4, 4, 4]
+    assert table["all_reduce"][0] == 1.0 and table["all_reduce"][1] >= 0.0
+    text = crt.format_table(max(iter_ms, 1e-6), table)
+    assert "all_reduce" in text and "iteration" in text
+
+
+def test_comm_ratio_table_runs_on_cpu(capsys):
+    from fluidmoe_b200.tools import comm_ratio_table as crt
+    crt.main(["--model", "tiny_test", "--iters", "1", "--warmup", "1"])
+    assert "iteration" in capsys.readouterr().out
+
+
+def test_profile_capture_writes_table(tmp_path, capsys):
+    from fluidmoe_b200.tools import profile_capture
+    out = tmp_path / "table.txt"
+    profile_capture.main(["--model", "tiny_test", "--impl", "fluidmoe-fb", "--warmup", "1", "--iters", "1",
+                          "--table", str(out)])
+    assert "captured 1 iteration" in capsys.readouterr().out
+    assert out.read_text().strip()
+
+
+def test_external_baselines_report_missing_packages():
+    from fluidmoe_b200.tools import external_baselines as eb
+    from fluidmoe_b200.tools.model_configs import get_model_config
+    avail = eb.available()
+    assert set(avail) == {"megatron", "deepspeed"}
+    cfg = get_model_config("tiny_test")
+    if not avail["megatron"]:
+        with pytest.raises(eb.BaselineUnavailable, match="package"):
+            eb.build_megatron_baseline(cfg, device="cpu")
+    if not avail["deepspeed"]:
+        with pytest.raises(eb.BaselineUnavailable, match="package"):
+            eb.build_deepspeed_ulysses_baseline(cfg, device="cpu")

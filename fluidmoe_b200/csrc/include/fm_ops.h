@@ -38,7 +38,8 @@ int fm_adam(void* p, float* master, float* g, void* m, void* v, long long n, flo
 // dqkv: packed gradient [s, b, G, (qpg + 2) * d] bf16 (every element is written).
 int fm_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
                       float* dq_accum, void* dqkv, int s, int b, int G, int qpg, int d, float scale,
-                      unsigned long long timeout_ns, int* status, int version, cudaStream_t stream);
+                      unsigned long long timeout_ns, int* status, int version, float* dkv_accum, int hsplit,
+                      cudaStream_t stream);
 
 // Cross-entropy forward + backward in place: loss_out[row] = lse - logit[label]; logits are
 // overwritten with (softmax - onehot) * grad_scale (rows with a negative label get zeros).

@@ -56,6 +56,14 @@ int fm_allreduce_p2p(void* const* buf_ptrs_dev, long long count, int dtype_fp32,
                      int* const* flag_ptrs_dev, int my_rank, int nranks, int epoch, int num_ctas,
                      unsigned long long timeout_ns, int* status, cudaStream_t stream);
 
+// In-switch (NVLS) sum all-reduce of `count` fp32 elements in place.  `multicast_ptr` is the
+// multicast address of a buffer that every rank bound to the same NVLink multicast object (the
+// caller obtains it from a VMM-based symmetric allocator); the flags live in this library's own
+// symmetric heap.  Rank r reduces slice r with multimem.ld_reduce and broadcasts it with multimem.st.
+int fm_allreduce_nvls(float* multicast_ptr, long long count, float scale, int* const* flag_ptrs_dev,
+                      int my_rank, int nranks, int epoch, int num_ctas, unsigned long long timeout_ns,
+                      int* status, cudaStream_t stream);
+
 // One-sided put + signal: copy `bytes` (16-byte multiple) from `src` to `dst` (a peer address),
 // then store `value` to `flag` (a peer address) with a system-scope release.
 int fm_put_signal(const void* src, long long bytes, void* dst, int* flag, int value, int num_ctas,

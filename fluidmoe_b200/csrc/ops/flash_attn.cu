@@ -638,7 +638,8 @@ struct FlashBwdArgs {
   __nv_bfloat16* dqkv;   // packed gradient buffer [s, b, G, (qpg + 2) * d]
   unsigned long long timeout_ns;
   int* status;
-  int flags;             // 1: skip the dQ reductions (timing experiments only)
+  int hsplit;            // CTAs per (K/V block, KV head): each takes qpg / hsplit query heads
+  float* dkv_accum;      // [s, b, G, 2, d] fp32, zero-initialised; used when hsplit > 1
 };
 
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
@@ -682,6 +683,26 @@ __global__ void attn_dq_store_kernel(const float* __restrict__ dq, __nv_bfloat16
     p.z = pack_bf16x2(c.x * mul, c.y * mul); p.w = pack_bf16x2(c.z * mul, c.w * mul);
     const int g = h / qpg, hi = h % qpg;
     __nv_bfloat16* dst = dqkv + ((row * G + g) * (qpg + 2) + hi) * kFaD;
+    reinterpret_cast<uint4*>(dst)[v8] = p;
+  }
+}
+
+// dkv_accum (fp32 [s*b, G, 2, d]) -> bf16 into the key / value columns of the packed buffer
+__global__ void attn_dkv_store_kernel(const float* __restrict__ dkv, __nv_bfloat16* __restrict__ dqkv,
+                                      long long rows /* s*b */, int G, int qpg) {
+  const long long total = rows * G * 2 * (kFaD / 8);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int v8 = (int)(i % (kFaD / 8));
+    const long long rgw = i / (kFaD / 8);          // (row, g, which)
+    const int which = (int)(rgw % 2);
+    const long long rg = rgw / 2;                  // row * G + g
+    const float4 a = reinterpret_cast<const float4*>(dkv + rgw * kFaD)[v8 * 2];
+    const float4 c = reinterpret_cast<const float4*>(dkv + rgw * kFaD)[v8 * 2 + 1];
+    uint4 p;
+    p.x = pack_bf16x2(a.x, a.y); p.y = pack_bf16x2(a.z, a.w);
+    p.z = pack_bf16x2(c.x, c.y); p.w = pack_bf16x2(c.z, c.w);
+    __nv_bfloat16* dst = dqkv + (rg * (qpg + 2) + qpg + which) * kFaD;
     reinterpret_cast<uint4*>(dst)[v8] = p;
   }
 }
@@ -987,14 +1008,17 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x, g = blockIdx.y, bb = blockIdx.z;
+  const int j = blockIdx.x, bb = blockIdx.z;
+  const int g = (int)blockIdx.y / a.hsplit;
+  const int heads_here = a.qpg / a.hsplit;                      // query heads of this CTA
+  const int head0 = ((int)blockIdx.y % a.hsplit) * heads_here;   // first of them within the group
   const int nq = (a.s + kFaBM - 1) / kFaBM;
   const int hq = a.G * a.qpg;
   const int hpg = a.qpg + 2;
   const int col_k = ((bb * a.G + g) * hpg + a.qpg) * kFaD;
   const int col_v = col_k + kFaD;
   const int tiles = nq - j;                 // query tiles i = j .. nq-1
-  const int nsteps = tiles * a.qpg;
+  const int nsteps = tiles * heads_here;
   const uint64_t timeout = a.timeout_ns;
 
   if (threadIdx.x == 0) {
@@ -1038,7 +1062,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       tma_load_2d(sV + kTileBytes / 2, &tmap_qkv, kv_full, col_v + 64, j * kFaBN);
       for (int n = 0; n < nsteps; ++n) {
         const int st = n & 1;
-        const int hi = n / tiles, i = j + n % tiles;
+        const int hi = head0 + n / tiles, i = j + n % tiles;
         if (!mbar_wait(&q_empty[st], ((n >> 1) & 1) ^ 1, timeout, abort_flag)) {
           report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 100 + st, 0, 0);
           break;
@@ -1141,7 +1165,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
     const uint32_t t_dp_mine = t_dp + lane_addr + hf * 64;
     bool ok = true;
     auto load_stats = [&](int n, float& l2, float& dl) {
-      const int hi = n / tiles, i = j + n % tiles;
+      const int hi = head0 + n / tiles, i = j + n % tiles;
       const int row = i * kFaBM + r;
       const long long off = ((long long)bb * hq + g * a.qpg + hi) * a.s + row;
       const bool row_ok = row < a.s;
@@ -1254,7 +1278,17 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         tmem_ld_32x32(t_dk + lane_addr + c * 32, vk);
         tmem_ld_32x32(t_dv + lane_addr + c * 32, vv);
         tmem_ld_wait();
-        if (kvrow < a.s) {
+        if (kvrow < a.s && a.hsplit > 1) {
+          // several CTAs share this K/V block: add into the fp32 accumulators
+          float* acc = a.dkv_accum + ((((long long)kvrow * a.b + bb) * a.G + g) * 2) * kFaD + c * 32;
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            red_add_v4_f32(acc + 4 * u, __uint_as_float(vk[4 * u]) * a.scale, __uint_as_float(vk[4 * u + 1]) * a.scale,
+                           __uint_as_float(vk[4 * u + 2]) * a.scale, __uint_as_float(vk[4 * u + 3]) * a.scale);
+            red_add_v4_f32(acc + kFaD + 4 * u, __uint_as_float(vv[4 * u]), __uint_as_float(vv[4 * u + 1]),
+                           __uint_as_float(vv[4 * u + 2]), __uint_as_float(vv[4 * u + 3]));
+          }
+        } else if (kvrow < a.s) {
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             uint4 k4, v4;
@@ -1281,7 +1315,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     uint8_t* my_stage = sStage + q * 8192;
     for (int n = 0; n < nsteps; ++n) {
-      const int hi = n / tiles, i = j + n % tiles;
+      const int hi = head0 + n / tiles, i = j + n % tiles;
       const int h = g * a.qpg + hi;
       const int row0 = i * kFaBM + q * 32;       // first query row of my box
       if (!mbar_wait(dq_full, n & 1, timeout, abort_flag)) {
@@ -1308,7 +1342,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (row0 < a.s && a.flags == 0) {
+          if (row0 < a.s) {
             tma_reduce_add_2d(&tmap_dq, my_stage, ((bb * hq + h) * kFaD) + first_col, row0);
             tma_reduce_add_2d(&tmap_dq, my_stage + 4096, ((bb * hq + h) * kFaD) + first_col + 32, row0);
           }
@@ -1465,7 +1499,7 @@ static bool make_rows_tmap_impl(CUtensorMap* m, const void* ptr, long long cols,
 extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const float* lse,
                                  float* delta, float* dq_accum, void* dqkv, int s, int b, int G, int qpg,
                                  int d, float scale, unsigned long long timeout_ns, int* status,
-                                 int version, cudaStream_t stream) {
+                                 int version, float* dkv_accum, int hsplit, cudaStream_t stream) {
   if (d != fm::kFaD) {
     fm_set_error("flash_attn_bwd: head_dim must be 128");
     return -1;
@@ -1505,7 +1539,8 @@ extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* d
   a.dqkv = reinterpret_cast<__nv_bfloat16*>(dqkv);
   a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
   a.status = status;
-  a.flags = 0;
+  a.hsplit = 1;
+  a.dkv_accum = nullptr;
   dim3 grid((s + fm::kFaBN - 1) / fm::kFaBN, G, b);
   if (version == 2) {
     static bool configured2 = false;
@@ -1523,8 +1558,16 @@ extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* d
       fm_set_error("flash_attn_bwd: cuTensorMapEncodeTiled failed (dQ)");
       return -3;
     }
+    if (hsplit > 1 && dkv_accum != nullptr && qpg % hsplit == 0 &&
+        (reinterpret_cast<uintptr_t>(dkv_accum) & 15) == 0) {
+      a.hsplit = hsplit;
+      a.dkv_accum = dkv_accum;
+      grid.y = G * hsplit;
+    }
     fm::flash_bwd2_kernel<<<grid, fm::kFaB2Threads, fm::kFaB2Smem, stream>>>(tq, tdo, tdq, a);
     fm::attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(dq_accum, a.dqkv, (long long)s * b, G, qpg, scale);
+    if (a.hsplit > 1)
+      fm::attn_dkv_store_kernel<<<148 * 4, 256, 0, stream>>>(dkv_accum, a.dqkv, (long long)s * b, G, qpg);
   } else {
     fm::flash_bwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tq, tdo, a);
     fm::attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(dq_accum, a.dqkv, (long long)s * b, G, qpg, 1.0f);

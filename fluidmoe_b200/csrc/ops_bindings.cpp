@@ -62,10 +62,10 @@ void bind_ops(py::module_& m) {
         "cross_entropy");
   });
   m.def("flash_attn_bwd", [](u qkv, u out, u dout, u lse, u delta, u dq, u dqkv, int s_, int b, int G, int qpg,
-                             int d, float scale, unsigned long long timeout_ns, u status, int version, u s) {
+                             int d, float scale, unsigned long long timeout_ns, u status, int version, u dkv, int hsplit, u s) {
     chk(fm_flash_attn_bwd(p<const void*>(qkv), p<const void*>(out), p<const void*>(dout), p<const float*>(lse),
                           p<float*>(delta), p<float*>(dq), p<void*>(dqkv), s_, b, G, qpg, d, scale, timeout_ns,
-                          p<int*>(status), version, st(s)), "flash_attn_bwd");
+                          p<int*>(status), version, p<float*>(dkv), hsplit, st(s)), "flash_attn_bwd");
   });
   m.def("router_bwd", [](u dprobs, u slot_of_token, u top_idx, u top_probs, u logits, u tpe, float aux_coef,
                          float z_coef, int T, int k, int E, u dlogits, u s) {

@@ -324,6 +324,44 @@ __global__ void allreduce_p2p_kernel(T* const* bufs, long long count, float scal
                     status);
 }
 
+// In-switch all-reduce (NVLS): `mc` is the multicast address of a buffer that every rank of the
+// group has bound to one NVLink multicast object.  Rank r owns the r-th slice of the buffer:
+// `multimem.ld_reduce` returns the sum over all ranks (the NVSwitch adds the copies), the thread
+// scales it, and `multimem.st` writes the result into every rank's copy.  The same bounded
+// peer barrier as the two-shot kernel brackets the data phase.
+__global__ void allreduce_nvls_kernel(float* mc, long long count, float scale, int* const* flag_ptrs,
+                                      int my_rank, int nranks, int epoch, unsigned long long timeout_ns,
+                                      int* status) {
+  int* local_sync = flag_ptrs[my_rank] + nranks;
+  if (!grid_peer_barrier(flag_ptrs, my_rank, nranks, 2 * epoch - 1, local_sync, 2 * epoch - 1,
+                         timeout_ns, status))
+    return;
+  const long long nvec = count / 4;
+  const long long per = (nvec + nranks - 1) / nranks;
+  const long long lo = per * my_rank;
+  const long long hi = min(nvec, lo + per);
+  for (long long j = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; j < hi;
+       j += (long long)gridDim.x * blockDim.x) {
+    float4 v;
+    float* addr = mc + j * 4;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(addr) : "memory");
+    v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                 :: "l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+  }
+  // tail (count not a multiple of 4): rank 0, one element at a time
+  if (my_rank == 0 && blockIdx.x == 0 && threadIdx.x < (int)(count - nvec * 4)) {
+    float* addr = mc + nvec * 4 + threadIdx.x;
+    float v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.f32 %0, [%1];" : "=f"(v) : "l"(addr) : "memory");
+    v *= scale;
+    asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" :: "l"(addr), "f"(v) : "memory");
+  }
+  __threadfence_system();
+  grid_peer_barrier(flag_ptrs, my_rank, nranks, 2 * epoch, local_sync, 2 * epoch, timeout_ns, status);
+}
+
 }  // namespace fm
 
 static int launch_check(const char* what) {
@@ -430,4 +468,22 @@ extern "C" int fm_allreduce_p2p(void* const* buf_ptrs_dev, long long count, int 
         reinterpret_cast<__nv_bfloat16* const*>(buf_ptrs_dev), count, scale, flag_ptrs_dev,
         my_rank, nranks, epoch, to, status);
   return launch_check("allreduce_p2p");
+}
+
+extern "C" int fm_allreduce_nvls(float* multicast_ptr, long long count, float scale,
+                                 int* const* flag_ptrs_dev, int my_rank, int nranks, int epoch,
+                                 int num_ctas, unsigned long long timeout_ns, int* status,
+                                 cudaStream_t stream) {
+  if (multicast_ptr == nullptr || (reinterpret_cast<uintptr_t>(multicast_ptr) & 15) != 0) {
+    fm_set_error("allreduce_nvls: needs a 16-byte aligned multicast address");
+    return -1;
+  }
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (num_ctas <= 0 || num_ctas > sms) num_ctas = sms / 4 > 0 ? sms / 4 : 1;
+  fm::allreduce_nvls_kernel<<<num_ctas, 512, 0, stream>>>(multicast_ptr, count, scale, flag_ptrs_dev, my_rank,
+                                                         nranks, epoch, timeout_ns ? timeout_ns : 4000000000ull,
+                                                         status);
+  return launch_check("allreduce_nvls");
 }

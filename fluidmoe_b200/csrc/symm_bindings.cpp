@@ -91,4 +91,11 @@ void bind_symm(py::module_& m) {
                          as_ptr<int*>(status), as_ptr<cudaStream_t>(stream)),
         "allreduce_p2p");
   });
+  m.def("allreduce_nvls", [](uintptr_t mc, long long count, float scale, uintptr_t flag_ptrs, int rank, int n,
+                             int epoch, int ctas, unsigned long long timeout_ns, uintptr_t status,
+                             uintptr_t stream) {
+    chk(fm_allreduce_nvls(as_ptr<float*>(mc), count, scale, as_ptr<int* const*>(flag_ptrs), rank, n, epoch,
+                          ctas, timeout_ns, as_ptr<int*>(status), as_ptr<cudaStream_t>(stream)),
+        "allreduce_nvls");
+  });
 }

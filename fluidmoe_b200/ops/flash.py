@@ -33,7 +33,8 @@ def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sc
 
 
 def flash_attn_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
-                          q_per_group: int, head_dim: int, scale: float, version: int = 0) -> torch.Tensor:
+                          q_per_group: int, head_dim: int, scale: float, version: int = 0,
+                          head_split=None) -> torch.Tensor:
     """Gradient of the packed projection buffer, ``[s, b, G, (qpg + 2) * d]`` (dq heads, dk, dv per
     KV group), from the saved output and log-sum-exp."""
     global LAUNCHES
@@ -43,9 +44,20 @@ def flash_attn_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tens
     delta = torch.empty(b, hq, s, dtype=torch.float32, device=qkv.device)
     dq_accum = torch.zeros(s, b, hq, head_dim, dtype=torch.float32, device=qkv.device)
     dqkv = torch.empty_like(qkv)
-    LAUNCHES += 3
+    ver = version or BWD_VERSION
+    # Causal work per CTA is triangular; with few (K/V block, KV head) pairs the query heads of a group
+    # are split over several CTAs, which then add their dK / dV parts into an fp32 buffer.
+    hsplit = 1
+    if ver == 2 and head_split is not False:
+        ctas = ((s + 127) // 128) * G * b
+        hsplit = head_split if head_split else 1
+        if not head_split:
+            while hsplit * 2 <= q_per_group and q_per_group % (hsplit * 2) == 0 and ctas * hsplit < 4 * 148:
+                hsplit *= 2
+    dkv = torch.zeros(s, b, G, 2, head_dim, dtype=torch.float32, device=qkv.device) if hsplit > 1 else None
+    LAUNCHES += 3 + (1 if hsplit > 1 else 0)
     _native.lib().flash_attn_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
                                  dq_accum.data_ptr(), dqkv.data_ptr(), s, b, G, q_per_group, head_dim, float(scale),
-                                 0, status_buffer(qkv.device).data_ptr(), version or BWD_VERSION,
-                                 _native.stream_ptr())
+                                 0, status_buffer(qkv.device).data_ptr(), ver,
+                                 dkv.data_ptr() if dkv is not None else 0, hsplit, _native.stream_ptr())
     return dqkv

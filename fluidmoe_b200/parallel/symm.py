@@ -225,3 +225,52 @@ class SymmAllReduce:
             self.flags.ptr_table, heap.rank, heap.world, self.epoch, self.num_ctas,
             int(timeout_ms * 1e6), status_buffer(heap.device).data_ptr(), _native.stream_ptr())
         return self.buf.local
+
+
+class NvlsAllReduce:
+    """In-switch (NVLS) sum all-reduce on an fp32 buffer (in place).
+
+    The buffer comes from PyTorch's VMM-based symmetric allocator, which binds every rank's copy to
+    one NVLink multicast object and hands back the multicast address; the reduction itself is this
+    library's kernel (``multimem.ld_reduce`` / ``multimem.st``, one slice per rank) bracketed by the
+    bounded peer barrier of the two-shot kernel.  ``available`` is False when the allocator or the
+    multicast mapping is missing (no NVSwitch, unsupported driver); callers then use
+    ``SymmAllReduce`` or the library collective.  Counterpart of the reference's reliance on NCCL's
+    all-reduce for the trickled gradient reduction (fluid/core/scheduler.py:188-213).
+
+    Not to be used in tests that let a rank leave while peers keep running: a rank that exits
+    while its memory is bound to a multicast object can fault the other ranks' GPUs.
+    """
+
+    def __init__(self, heap: SymmetricHeap, numel: int, group=None, num_ctas: int = 0):
+        self.heap = heap
+        self.numel = numel
+        self.num_ctas = num_ctas
+        self.epoch = 0
+        self.available = False
+        self.local = None
+        self._mc_ptr = 0
+        if heap.world <= 1 or heap.device.type != "cuda":
+            return
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            g = group if group is not None else dist.group.WORLD
+            self.local = symm_mem.empty(numel, dtype=torch.float32, device=heap.device)
+            self._handle = symm_mem.rendezvous(self.local, g.group_name)
+            self._mc_ptr = int(getattr(self._handle, "multicast_ptr", 0) or 0)
+        except Exception:  # noqa: BLE001 - allocator / multicast unsupported on this system
+            self._mc_ptr = 0
+        self.available = self._mc_ptr != 0
+        if self.available:
+            self.flags = heap.alloc((heap.world + 2,), torch.int32)
+            heap.sync_group()
+
+    def __call__(self, numel: Optional[int] = None, scale: float = 1.0, timeout_ms: float = 4000.0) -> torch.Tensor:
+        if not self.available:
+            raise RuntimeError("NVLS all-reduce is not available on this system")
+        n = self.numel if numel is None else numel
+        self.epoch += 1
+        _native.lib().allreduce_nvls(self._mc_ptr, n, float(scale), self.flags.ptr_table, self.heap.rank,
+                                     self.heap.world, self.epoch, self.num_ctas, int(timeout_ms * 1e6),
+                                     status_buffer(self.heap.device).data_ptr(), _native.stream_ptr())
+        return self.local

@@ -57,6 +57,27 @@ def main():
             assert (out - ref / world).abs().max().item() <= tol * (ref.abs().max().item() / world + 1), dtype
     gemm.check_status()
 
+    # ---- 2b. in-switch (NVLS) all-reduce, where the system offers a multicast mapping ----
+    from fluidmoe_b200.parallel.symm import NvlsAllReduce
+    nv = NvlsAllReduce(heap, (1 << 20) + 3) if os.environ.get("FLUIDMOE_TEST_NVLS", "0") == "1" else None
+    if nv is None:
+        pass
+    elif nv.available:
+        for it in range(2):
+            torch.manual_seed(200 * it + rank)
+            x = torch.randn((1 << 20) + 3, device=dev)
+            nv.local.copy_(x)
+            ref = x.clone()
+            dist.all_reduce(ref)
+            out = nv(scale=1.0 / world)
+            torch.cuda.synchronize()
+            assert (out - ref / world).abs().max().item() <= 1e-5 * (ref.abs().max().item() / world + 1)
+        gemm.check_status()
+        if rank == 0:
+            print("NVLS_ALLREDUCE_OK", flush=True)
+    elif rank == 0:
+        print("NVLS_ALLREDUCE_SKIPPED (no multicast mapping)", flush=True)
+
     # ---- 3. a wait that nothing satisfies returns a status (bounded wait) ----
     flag = torch.zeros(1, dtype=torch.int32, device=dev)
     st = gemm.status_buffer(dev)

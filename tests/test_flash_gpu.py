@@ -71,16 +71,18 @@ def test_attention_backward_from_saved_output(fwd):
         assert err < 3e-2, err
 
 
-@pytest.mark.parametrize("version", [1, 2])
+@pytest.mark.parametrize("version,head_split", [(1, None), (2, False), (2, 2), (2, None)])
 @pytest.mark.parametrize("s,b,G,qpg", [(256, 1, 1, 1), (512, 1, 2, 2), (1000, 2, 1, 4)])
-def test_flash_bwd_native_matches_reference(s, b, G, qpg, version):
+def test_flash_bwd_native_matches_reference(s, b, G, qpg, version, head_split):
+    if head_split == 2 and qpg % 2:
+        pytest.skip("query heads per group not divisible")
     d = 128
     torch.manual_seed(2)
     qkv = torch.randn(s, b, G, (qpg + 2) * d, device="cuda").bfloat16()
     scale = 1.0 / math.sqrt(d)
     out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, scale)
     dout = torch.randn_like(out)
-    dqkv = flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, scale, version=version)
+    dqkv = flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, scale, version=version, head_split=head_split)
     torch.cuda.synchronize()
     gemm.check_status()
     heads = qkv.float().cpu().view(s, b, G, qpg + 2, d)

@@ -219,8 +219,8 @@ def run_ours(args):
             gemm.check_status()
     torch.cuda.synchronize()
     gemm.check_status()
-    if args.profile and rank == 0:
-        _profile_one_step(torch, step_device, args.profile)
+    if args.profile:
+        _profile_one_step(torch, step_device, args.profile, rank)
     l0 = gemm.LAUNCHES + elementwise.LAUNCHES + _extra_launches()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -255,8 +255,13 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def _profile_one_step(torch, step_fn, path):
+def _profile_one_step(torch, step_fn, path, rank=0):
+    """Every rank runs the step (its kernels wait for the peers'); only rank 0 records it."""
     from torch.profiler import ProfilerActivity, profile
+    if rank != 0:
+        step_fn(0)
+        torch.cuda.synchronize()
+        return
     with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
         step_fn(0)
         torch.cuda.synchronize()
@@ -285,7 +290,7 @@ def run_reference(args):
     rank, local_rank, world = dist_env()
     if not os.path.isdir(os.path.join(ref_root, "fluid")):
         emit(0, {"impl": "reference", "unavailable": "baseline/_ref is empty: the reference has no setup.py / "
-                 "pyproject.toml; install it from a copy with a packaging shim (see DESIGN.md)"})
+                 "pyproject.toml; install it from a copy with a packaging shim (pip --no-index --target baseline/_ref)"})
         return
     sys.path.insert(0, ref_root)
     for k in [k for k in sys.modules if k == "fluid" or k.startswith("fluid.")]:
@@ -395,8 +400,8 @@ def run_reference(args):
     except Exception as e:  # noqa: BLE001
         emit(rank, {"impl": "reference", "unavailable": f"reference step failed: {type(e).__name__}: {e}"[:400]})
         return
-    if args.profile and rank == 0:
-        _profile_one_step(torch, step_device, args.profile)
+    if args.profile:
+        _profile_one_step(torch, step_device, args.profile, rank)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()

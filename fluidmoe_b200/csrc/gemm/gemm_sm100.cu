@@ -383,7 +383,15 @@ struct EpiAdam {
       const bool fast = vec_ok && ncols == 32;
       // parameter and moments do not depend on the accumulator: issue their loads first
       uint4 b[12];
-      if (fast) {
+      if (fast && rows_ok == 32) {
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const long long o = off + (long long)(pass * 8 + sub) * ld + c8;
+          b[pass * 3 + 0] = *reinterpret_cast<const uint4*>(P + o);
+          b[pass * 3 + 1] = *reinterpret_cast<const uint4*>(Mo + o);
+          b[pass * 3 + 2] = *reinterpret_cast<const uint4*>(Vo + o);
+        }
+      } else if (fast) {
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass) {
           const int rr = pass * 8 + sub;
@@ -398,7 +406,30 @@ struct EpiAdam {
       float g[32];
       load_acc(taddr + c * 32, g, zero);
       if (rows_ok == 0) continue;
-      if (fast) {
+      if (fast && rows_ok == 32) {
+        // all rows valid (the common case): branch-free, so that the 32 independent update chains
+        // of the four passes can be interleaved by the scheduler
+        stage_put(stg, lane, g);
+        float gg[4][8];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const int rr = pass * 8 + sub;
+          const float4 ga = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+          const float4 gb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+          gg[pass][0] = ga.x; gg[pass][1] = ga.y; gg[pass][2] = ga.z; gg[pass][3] = ga.w;
+          gg[pass][4] = gb.x; gg[pass][5] = gb.y; gg[pass][6] = gb.z; gg[pass][7] = gb.w;
+        }
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) update8(gg[pass], b[pass * 3 + 0], b[pass * 3 + 1], b[pass * 3 + 2]);
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const long long o = off + (long long)(pass * 8 + sub) * ld + c8;
+          *reinterpret_cast<uint4*>(Mo + o) = b[pass * 3 + 1];
+          *reinterpret_cast<uint4*>(Vo + o) = b[pass * 3 + 2];
+          *reinterpret_cast<uint4*>(P + o) = b[pass * 3 + 0];
+        }
+        __syncwarp();
+      } else if (fast) {
         stage_put(stg, lane, g);
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass) {

@@ -162,8 +162,7 @@ class FusedCommContext:
             epi=lib.EPI_SCATTER, dst_base=dst.ptr_table, dst_rank=plan.combine_dst_rank.data_ptr(),
             dst_row=plan.combine_dst_row.data_ptr(), ld_dst=plan.hidden_size,
             dst_flags=cnt_tbl.data_ptr(), num_ranks=plan.ep_size,
-            timeout_ns=self.timeout_ns, status=status_buffer(a.device).data_ptr())
-        gemm.LAUNCHES += 0
+            timeout_ns=self.timeout_ns, status=status_buffer(a.device).data_ptr(), cta_pair=gemm.CTA_PAIR)
         lib.gemm_launch(desc, _native.stream_ptr())
 
     def _wait_counters(self, cnt: SymmTensor, expected: int) -> None:

@@ -1164,27 +1164,10 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
     const uint32_t t_s_mine = t_s + lane_addr + hf * 64;     // my 64 score columns; P^T goes to the first 32
     const uint32_t t_dp_mine = t_dp + lane_addr + hf * 64;
     bool ok = true;
-    auto load_stats = [&](int n, float& l2, float& dl) {
-      const int hi = head0 + n / tiles, i = j + n % tiles;
-      const int row = i * kFaBM + r;
-      const long long off = ((long long)bb * hq + g * a.qpg + hi) * a.s + row;
-      const bool row_ok = row < a.s;
-      // rows past the end get lse = +inf, which turns their probabilities into exact zeros
-      l2 = row_ok ? a.lse[off] * 1.4426950408889634f : INFINITY;
-      dl = row_ok ? a.delta[off] : 0.f;
-    };
-    float nl2 = 0.f, ndl = 0.f;
-    if (hf == 0 && nsteps > 0) {     // the first four warps fetch the per-row statistics
-      load_stats(0, nl2, ndl);
-      s_lse[r] = nl2;
-      s_dl[r] = ndl;
-      mbar_arrive(&stats_full[0]);
-    }
     for (int n = 0; n < nsteps; ++n) {
       const uint32_t par = n & 1;
       const int st = n & 1;
       const bool diag = (n % tiles) == 0;
-      if (hf == 0 && n + 1 < nsteps) load_stats(n + 1, nl2, ndl);   // in flight during this step
       if (!mbar_wait(&stats_full[st], (n >> 1) & 1, timeout, abort_flag) ||
           !mbar_wait(s_full, par, timeout, abort_flag)) {
         if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 300, 0, 0);
@@ -1260,11 +1243,6 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_full);
-      if (hf == 0 && n + 1 < nsteps) {   // stage (n+1)&1 was last read in step n-1, which every warp has left
-        s_lse[((n + 1) & 1) * 128 + r] = nl2;
-        s_dl[((n + 1) & 1) * 128 + r] = ndl;
-        mbar_arrive(&stats_full[(n + 1) & 1]);
-      }
     }
     if (ok && nsteps > 0 && mbar_wait(done_full, 0, timeout, abort_flag)) {
       // dK / dV of this block: each warp converts its 64 columns
@@ -1314,8 +1292,44 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
     const int q = warp & 3;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     uint8_t* my_stage = sStage + q * 8192;
+    // These warps also fetch the per-row statistics (log-sum-exp, delta) of the query tiles for the
+    // softmax warps: one row per thread, loaded two steps ahead, published one step ahead.
+    const int r = q * 32 + lane;
+    int ld_tile = 0, ld_head = head0;          // (tile, head) of the next step to load
+    auto load_stats = [&](float& l2, float& dl) {
+      const int row = (j + ld_tile) * kFaBM + r;
+      const long long off = ((long long)bb * hq + g * a.qpg + ld_head) * a.s + row;
+      const bool row_ok = row < a.s;
+      // rows past the end get lse = +inf, which turns their probabilities into exact zeros
+      l2 = row_ok ? a.lse[off] : INFINITY;
+      dl = row_ok ? a.delta[off] : 0.f;
+      if (++ld_tile == tiles) {
+        ld_tile = 0;
+        ++ld_head;
+      }
+    };
+    float nl2 = 0.f, ndl = 0.f;
+    if (nsteps > 0) {
+      load_stats(nl2, ndl);
+      s_lse[r] = nl2 * 1.4426950408889634f;
+      s_dl[r] = ndl;
+      mbar_arrive(&stats_full[0]);
+      if (nsteps > 1) load_stats(nl2, ndl);     // statistics of step 1, published at the top of step 0
+    }
+    int cur_tile = 0, cur_head = head0;
     for (int n = 0; n < nsteps; ++n) {
-      const int hi = head0 + n / tiles, i = j + n % tiles;
+      // stage (n+1)&1 was last read in step n-1, which every softmax warp left before dQ(n-1) existed
+      if (n + 1 < nsteps) {
+        s_lse[((n + 1) & 1) * 128 + r] = nl2 * 1.4426950408889634f;
+        s_dl[((n + 1) & 1) * 128 + r] = ndl;
+        mbar_arrive(&stats_full[(n + 1) & 1]);
+        if (n + 2 < nsteps) load_stats(nl2, ndl);
+      }
+      const int hi = cur_head, i = j + cur_tile;
+      if (++cur_tile == tiles) {
+        cur_tile = 0;
+        ++cur_head;
+      }
       const int h = g * a.qpg + hi;
       const int row0 = i * kFaBM + q * 32;       // first query row of my box
       if (!mbar_wait(dq_full, n & 1, timeout, abort_flag)) {

@@ -520,11 +520,16 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
             if ((diag && col > row) || col >= a.s) sv[c][i] = 0xff800000u;   // -inf
           }
       }
-      float m_raw = -INFINITY;
+      // eight independent running maxima (one dependent chain of 128 would cost ~500 cycles)
+      float mx[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) mx[k] = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) m_raw = fmaxf(m_raw, __uint_as_float(sv[c][i]));
+        for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(sv[c][i]));
+      const float m_raw = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       const float m_blk = m_raw * a.scale_log2;   // scale > 0
       // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 above it.
       const float m_new = fmaxf(m_used, m_blk);
@@ -554,7 +559,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
           m_used = m_new;
         }
       }
-      float l_blk = 0.f;
+      float l_part[4] = {0.f, 0.f, 0.f, 0.f};     // independent partial row sums
       const float neg_m = -m_used;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -563,14 +568,14 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         for (int i = 0; i < 16; ++i) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i]), a.scale_log2, neg_m));
           const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i + 1]), a.scale_log2, neg_m));
-          l_blk += p0 + p1;
+          l_part[i & 3] += p0 + p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
         // P columns [16c, 16c+16) alias score columns; the scores are already in registers
         tmem_st_32x16(t_s + c * 16, pk);
       }
       tmem_st_wait();
-      l_run += l_blk;
+      l_run += (l_part[0] + l_part[1]) + (l_part[2] + l_part[3]);
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[w]);
@@ -1164,10 +1169,12 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
     const uint32_t t_s_mine = t_s + lane_addr + hf * 64;     // my 64 score columns; P^T goes to the first 32
     const uint32_t t_dp_mine = t_dp + lane_addr + hf * 64;
     bool ok = true;
+    int tile_in_head = 0;
     for (int n = 0; n < nsteps; ++n) {
       const uint32_t par = n & 1;
       const int st = n & 1;
-      const bool diag = (n % tiles) == 0;
+      const bool diag = tile_in_head == 0;     // first query tile of a head = the diagonal block
+      if (++tile_in_head == tiles) tile_in_head = 0;
       if (!mbar_wait(&stats_full[st], (n >> 1) & 1, timeout, abort_flag) ||
           !mbar_wait(s_full, par, timeout, abort_flag)) {
         if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, 300, 0, 0);

@@ -47,8 +47,9 @@ def parse_args():
     ap.add_argument("--opt-state", default="bf16", choices=["bf16", "fp32"],
                     help="dtype of the Adam moments (torch.optim.AdamW keeps bf16 moments for bf16 parameters)")
     ap.add_argument("--fuse-optimizer", type=int, default=1,
-                    help="1: apply Adam to the expert weights in their weight-gradient GEMM epilogue "
-                         "(bf16 moments, scheduler on, one micro-batch per step)")
+                    help="Adam for the expert weights inside the backward pass (bf16 moments, scheduler on, one "
+                         "micro-batch per step): 1 = in the weight-gradient GEMM epilogue, 2 = small-CTA kernel on "
+                         "a side stream behind each weight-gradient GEMM, 0 = off")
     ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file")
     return ap.parse_args()
 
@@ -189,7 +190,7 @@ def run_ours(args):
                   state_dtype=torch.bfloat16 if args.opt_state == "bf16" else torch.float32), sched)
     fused_params = 0
     if args.fuse_optimizer and args.mode != "F" and args.opt_state == "bf16":
-        fused_params = opt.fuse_into_backward()
+        fused_params = opt.fuse_into_backward(mode="stream" if args.fuse_optimizer == 2 else "epilogue")
     seq, batch = args.seq, m["batch"]
     n_batches = 4
     host = make_batches(torch, n_batches, seq, batch, m["vocab"], 100 + rank)

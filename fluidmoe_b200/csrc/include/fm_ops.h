@@ -29,6 +29,11 @@ int fm_gather_rows(const void* x, const long long* idx, void* out, long long row
 int fm_unpermute_reduce(const void* rows, const int* slot, const void* residual, void* out, int T,
                         int k, int H, cudaStream_t s);
 // Moments are fp32, or bf16 when state_bf16 != 0.
+// Adam for bf16 parameter / bf16 moments / fp32 gradient with small CTAs (128 threads, <= 80 registers)
+// that fit on an SM beside a resident tensor-core kernel; meant for a side stream.
+int fm_adam_background(void* p, const float* g, void* m, void* v, long long n, float lr, float beta1,
+                       float beta2, float eps, float weight_decay, int step, float grad_scale, int num_ctas,
+                       cudaStream_t s);
 int fm_adam(void* p, float* master, float* g, void* m, void* v, long long n, float lr, float beta1,
             float beta2, float eps, float weight_decay, int step, float grad_scale, int zero_grad,
             int state_bf16, cudaStream_t s);

@@ -407,6 +407,64 @@ adam_kernel(__nv_bfloat16* __restrict__ p, float* __restrict__ master, float* __
   }
 }
 
+// Background form of the Adam step for bf16 parameters with bf16 moments: 128-thread CTAs with at
+// most 80 registers, so that one CTA fits on an SM BESIDE a resident tensor-core kernel (GEMM /
+// attention CTAs leave about 11 K registers and no shared memory is needed here).  Every thread
+// keeps four independent 4-element groups in flight per iteration to cover DRAM latency with so
+// few threads.  Launched on a side stream, it runs under the tensor-bound kernels of the
+// following layers.  n4 = number of 4-element groups; pointers 16-byte aligned (8 for bf16).
+__global__ void __launch_bounds__(128, 6)   // at most 80 registers: 10 K per CTA
+adam_background_kernel(__nv_bfloat16* __restrict__ p, const float* __restrict__ g,
+                       __nv_bfloat16* __restrict__ m, __nv_bfloat16* __restrict__ v, long long n4, float lr,
+                       float beta1, float beta2, float eps, float weight_decay, float rbc1, float rbc2,
+                       float grad_scale) {
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += stride * U) {
+    float4 gr[U];
+    uint2 pw[U], pm[U], pv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < n4) {
+        gr[u] = *reinterpret_cast<const float4*>(g + i * 4);
+        pw[u] = *reinterpret_cast<const uint2*>(p + i * 4);
+        pm[u] = *reinterpret_cast<const uint2*>(m + i * 4);
+        pv[u] = *reinterpret_cast<const uint2*>(v + i * 4);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < n4) {
+        const float gg[4] = {gr[u].x, gr[u].y, gr[u].z, gr[u].w};
+        uint32_t* ww = reinterpret_cast<uint32_t*>(&pw[u]);
+        uint32_t* wm = reinterpret_cast<uint32_t*>(&pm[u]);
+        uint32_t* wv = reinterpret_cast<uint32_t*>(&pv[u]);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          float w2[2] = {__uint_as_float(ww[q] << 16), __uint_as_float(ww[q] & 0xffff0000u)};
+          float m2[2] = {__uint_as_float(wm[q] << 16), __uint_as_float(wm[q] & 0xffff0000u)};
+          float v2[2] = {__uint_as_float(wv[q] << 16), __uint_as_float(wv[q] & 0xffff0000u)};
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float gj = gg[2 * q + e] * grad_scale;
+            m2[e] = beta1 * m2[e] + (1.f - beta1) * gj;
+            v2[e] = beta2 * v2[e] + (1.f - beta2) * gj * gj;
+            w2[e] -= lr * ((m2[e] * rbc1) / (sqrtf(v2[e] * rbc2) + eps) + weight_decay * w2[e]);
+          }
+          ww[q] = pack_bf16x2(w2[0], w2[1]);
+          wm[q] = pack_bf16x2(m2[0], m2[1]);
+          wv[q] = pack_bf16x2(v2[0], v2[1]);
+        }
+        *reinterpret_cast<uint2*>(m + i * 4) = pm[u];
+        *reinterpret_cast<uint2*>(v + i * 4) = pv[u];
+        *reinterpret_cast<uint2*>(p + i * 4) = pw[u];
+      }
+    }
+  }
+}
+
 template <class ST>
 __global__ void adam_tail_kernel(__nv_bfloat16* p, float* master, float* g, ST* m, ST* v,
                                  long long lo, long long n, float lr, float beta1, float beta2,
@@ -834,6 +892,23 @@ extern "C" int fm_router_bwd(const float* dprobs_slots, const int* slot_of_token
   fm::router_bwd_kernel<<<(T + 127) / 128, 128, 0, s>>>(dprobs_slots, slot_of_token, top_idx, top_probs, logits,
                                                        tpe, aux_coef, z_coef, T, k, E, dlogits);
   return check_launch("router_bwd");
+}
+
+extern "C" int fm_adam_background(void* p, const float* g, void* m, void* v, long long n, float lr, float beta1,
+                                  float beta2, float eps, float weight_decay, int step, float grad_scale,
+                                  int num_ctas, cudaStream_t s) {
+  using bf = __nv_bfloat16;
+  if ((n & 3) != 0 || (reinterpret_cast<uintptr_t>(p) & 7) || (reinterpret_cast<uintptr_t>(g) & 15) ||
+      (reinterpret_cast<uintptr_t>(m) & 7) || (reinterpret_cast<uintptr_t>(v) & 7)) {
+    fm_set_error("adam_background: needs a multiple of 4 elements and aligned pointers");
+    return -1;
+  }
+  const float rbc1 = 1.f / (1.f - powf(beta1, (float)step));
+  const float rbc2 = 1.f / (1.f - powf(beta2, (float)step));
+  if (num_ctas <= 0) num_ctas = 148;
+  fm::adam_background_kernel<<<num_ctas, 128, 0, s>>>((bf*)p, g, (bf*)m, (bf*)v, n / 4, lr, beta1, beta2, eps,
+                                                     weight_decay, rbc1, rbc2, grad_scale);
+  return check_launch("adam_background");
 }
 
 extern "C" int fm_moe_plan(const long long* top_idx, const float* top_probs, int T, int k, int E,

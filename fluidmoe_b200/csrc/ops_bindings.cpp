@@ -73,6 +73,11 @@ void bind_ops(py::module_& m) {
                       p<const float*>(top_probs), p<const float*>(logits), p<const float*>(tpe), aux_coef, z_coef,
                       T, k, E, p<float*>(dlogits), st(s)), "router_bwd");
   });
+  m.def("adam_background", [](u prm, u g, u mm, u v, long long n, float lr, float b1, float b2, float eps,
+                              float wd, int step, float grad_scale, int ctas, u s) {
+    chk(fm_adam_background(p<void*>(prm), p<const float*>(g), p<void*>(mm), p<void*>(v), n, lr, b1, b2, eps, wd,
+                           step, grad_scale, ctas, st(s)), "adam_background");
+  });
   m.def("adam", [](u prm, u master, u g, u mm, u v, long long n, float lr, float b1, float b2,
                    float eps, float wd, int step, float grad_scale, int zero_grad, int state_bf16, u s) {
     chk(fm_adam(p<void*>(prm), p<float*>(master), p<float*>(g), p<void*>(mm), p<void*>(v), n, lr,

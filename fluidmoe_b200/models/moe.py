@@ -551,17 +551,20 @@ def register_moe_dw_tasks(plan: EPPlan, state: MoEForwardState, dfc2_em: torch.T
     def make(a, dy, param):
         def run():
             fa = fused_optimizer_of(param, sched) if sched.is_enabled() else None
-            if fa is not None:
-                fa.wgrad_update(param, a, dy, nle, grad_scale=1.0 / max(1, sched.shared_dp_world),
-                                uniform_rows=rows_per, max_ctas=max_ctas)
+            gscale = 1.0 / max(1, sched.shared_dp_world)
+            if fa is not None and getattr(fa, "fused_mode", "epilogue") == "epilogue":
+                fa.wgrad_update(param, a, dy, nle, grad_scale=gscale, uniform_rows=rows_per, max_ctas=max_ctas)
                 return None
             buf = sched._buffer_of(param) if sched.is_enabled() else None
             if buf is not None and param.main_grad.dtype == torch.float32 and a.is_cuda:
                 first = not getattr(param, "_ar_buf_written", False)
                 gemm.grouped_gemm_wgrad(a, dy, nle, uniform_rows=rows_per, out=param.main_grad,
-                                        accumulate=not first, max_ctas=max_ctas)
+                                        accumulate=not first, alpha=gscale if fa is not None else 1.0,
+                                        max_ctas=max_ctas)
+                if fa is not None:
+                    fa.update_on_stream(param)     # Adam for this parameter behind the GEMM, on a side stream
                 return None
-            return gemm.grouped_gemm_wgrad(a, dy, nle, uniform_rows=rows_per)
+            return gemm.grouped_gemm_wgrad(a, dy, nle, uniform_rows=rows_per, alpha=gscale if fa is not None else 1.0)
         return run
 
     if which in ("both", "w2"):

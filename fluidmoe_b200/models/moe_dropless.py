@@ -140,18 +140,23 @@ def register_dw_tasks(plan: DroplessPlan, state, dfc2_em, dpre_em, w1_param, w2_
         def run():
             from .moe import fused_optimizer_of
             fa = fused_optimizer_of(param, sched) if sched.is_enabled() else None
-            if fa is not None:
-                fa.wgrad_update(param, a, dy, nle, grad_scale=1.0 / max(1, sched.shared_dp_world),
-                                group_rows=plan.group_rows, group_offs=plan.group_offs,
-                                max_ctas=sched.dw_max_ctas)
+            gscale = 1.0 / max(1, sched.shared_dp_world)
+            if fa is not None and getattr(fa, "fused_mode", "epilogue") == "epilogue":
+                fa.wgrad_update(param, a, dy, nle, grad_scale=gscale, group_rows=plan.group_rows,
+                                group_offs=plan.group_offs, max_ctas=sched.dw_max_ctas)
                 return None
+            alpha = gscale if fa is not None else 1.0
             buf = sched._buffer_of(param) if sched.is_enabled() else None
             if buf is not None and param.main_grad.dtype == torch.float32 and a.is_cuda:
                 first = not getattr(param, "_ar_buf_written", False)
                 gemm.grouped_gemm_wgrad(a, dy, nle, group_rows=plan.group_rows, group_offs=plan.group_offs,
-                                        out=param.main_grad, accumulate=not first, max_ctas=sched.dw_max_ctas)
+                                        out=param.main_grad, accumulate=not first, alpha=alpha,
+                                        max_ctas=sched.dw_max_ctas)
+                if fa is not None:
+                    fa.update_on_stream(param)
                 return None
-            return gemm.grouped_gemm_wgrad(a, dy, nle, group_rows=plan.group_rows, group_offs=plan.group_offs)
+            return gemm.grouped_gemm_wgrad(a, dy, nle, group_rows=plan.group_rows, group_offs=plan.group_offs,
+                                           alpha=alpha)
         return run
     sched.register_dw_task(f"{layer_name}.w2", layer_id, make(state.act_em, dfc2_em, w2_param), w2_param)
     sched.register_dw_task(f"{layer_name}.w1", layer_id, make(state.tokens_em, dpre_em, w1_param), w1_param)

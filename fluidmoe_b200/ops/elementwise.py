@@ -109,6 +109,17 @@ def adam_step(p, master, g, m, v, lr, beta1, beta2, eps, weight_decay, step, gra
                        float(grad_scale), int(zero_grad), int(m.dtype == torch.bfloat16), _s())
 
 
+def adam_background(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0, num_ctas=0, stream=None):
+    """Adam on bf16 parameter / bf16 moments / fp32 gradient with the small-CTA kernel that fits on
+    an SM beside a resident tensor-core kernel.  ``stream`` is the raw stream handle to launch on."""
+    global LAUNCHES
+    assert p.dtype == torch.bfloat16 and m.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and g.dtype == torch.float32
+    LAUNCHES += 1
+    _native.lib().adam_background(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(), float(lr),
+                                  float(beta1), float(beta2), float(eps), float(weight_decay), int(step),
+                                  float(grad_scale), int(num_ctas), _s() if stream is None else stream)
+
+
 def moe_plan(top_idx, top_probs, num_experts, capacity):
     """Padded-capacity routing plan on the device (one CTA per expert, no sort, no host sync)."""
     T, k = top_idx.shape

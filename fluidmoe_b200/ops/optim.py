@@ -27,13 +27,21 @@ class FusedAdam:
         self.fused_wgrad_params = 0
 
     # ------------------------------------------------------------------ optimizer in the backward pass
-    def fuse_into_backward(self, params: Optional[Iterable[torch.nn.Parameter]] = None) -> int:
-        """Let the weight-gradient GEMM of the given parameters (default: every expert weight,
-        i.e. parameters marked ``allreduce = False``) apply this optimizer in its epilogue
-        (``ops.gemm.grouped_gemm_wgrad_adam``): the gradient is never stored and ``step`` skips
-        those parameters.  The caller promises one micro-batch per optimizer step, no gradient
-        clipping and no data-parallel replicas of these parameters.  Needs bf16 parameters and bf16
-        moments without master weights; returns the number of parameters taken."""
+    def fuse_into_backward(self, params: Optional[Iterable[torch.nn.Parameter]] = None,
+                           mode: str = "epilogue") -> int:
+        """Run this optimizer inside the backward pass for the given parameters (default: every
+        expert weight, i.e. parameters marked ``allreduce = False``); ``step`` then skips them.
+
+        ``mode="epilogue"``: the weight-gradient GEMM applies the update in its epilogue
+        (``ops.gemm.grouped_gemm_wgrad_adam``), the gradient is never stored.
+        ``mode="stream"``: the weight-gradient GEMM stores the gradient as usual and a small-CTA Adam
+        kernel is queued behind it on a side stream, where it runs under the tensor-bound kernels of
+        the following layers (``ops.elementwise.adam_background``).
+
+        The caller promises one micro-batch per optimizer step, no gradient clipping and no
+        data-parallel replicas of these parameters.  Needs bf16 parameters and bf16 moments without
+        master weights; returns the number of parameters taken."""
+        assert mode in ("epilogue", "stream")
         if self.master_weights or self.state_dtype != torch.bfloat16:
             return 0
         chosen = list(params) if params is not None else [p for p in self.params
@@ -45,7 +53,48 @@ class FusedAdam:
                 p._fused_update_done = False
                 n += 1
         self.fused_wgrad_params = n
+        self.fused_mode = mode
         return n
+
+    def update_on_stream(self, p) -> None:
+        """``p.main_grad`` holds the complete gradient (written by kernels already queued on the
+        current stream): queue the Adam kernel for ``p`` behind them on the optimizer stream."""
+        st = self._state(p)
+        b1, b2 = self.betas
+        g = p.main_grad
+        if not (p.is_cuda and _native.available() and g.dtype == torch.float32):
+            self._update_reference(p, g.float(), st, self.step_count + 1, 1.0)
+            p._fused_update_done = True
+            return
+        from . import elementwise
+        if getattr(self, "_opt_stream", None) is None:
+            self._opt_stream = torch.cuda.Stream(device=p.device)
+            self._pending_events = []
+        ready = torch.cuda.Event()
+        ready.record()
+        self._opt_stream.wait_event(ready)
+        elementwise.adam_background(p.data.view(-1), g.view(-1), st["m"].view(-1), st["v"].view(-1), self.lr, b1, b2,
+                                    self.eps, self.weight_decay, self.step_count + 1,
+                                    stream=self._opt_stream.cuda_stream)
+        done = torch.cuda.Event()
+        done.record(self._opt_stream)
+        self._pending_events.append(done)
+        p._fused_update_done = True
+
+    def _update_reference(self, p, gf, st, step, grad_scale) -> None:
+        b1, b2 = self.betas
+        gf = gf * grad_scale
+        w = st["master"] if st["master"] is not None else p.data.float()
+        m32 = st["m"].float().mul_(b1).add_(gf, alpha=1 - b1)
+        v32 = st["v"].float().mul_(b2).addcmul_(gf, gf, value=1 - b2)
+        st["m"].copy_(m32)
+        st["v"].copy_(v32)
+        bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+        upd = (m32 / bc1) / ((v32 / bc2).sqrt() + self.eps) + self.weight_decay * w
+        w = w - self.lr * upd
+        if st["master"] is not None:
+            st["master"].copy_(w)
+        p.data.copy_(w.to(p.dtype))
 
     def wgrad_update(self, p, a, dy, num_groups, grad_scale: float = 1.0, **rows_kw) -> None:
         """Called by a weight-gradient task instead of storing the gradient of ``p``."""
@@ -76,6 +125,10 @@ class FusedAdam:
 
     @torch.no_grad()
     def step(self, grad_scale: float = 1.0) -> None:
+        for ev in getattr(self, "_pending_events", []):     # updates queued on the optimizer stream
+            torch.cuda.current_stream().wait_event(ev)
+        if getattr(self, "_pending_events", None):
+            self._pending_events.clear()
         self.step_count += 1
         b1, b2 = self.betas
         for p in self.params:

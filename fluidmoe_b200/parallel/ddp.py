@@ -34,7 +34,7 @@ class FluidDDP(nn.Module):
                  dp_cp_group=None, expert_dp_group=None, accumulate_in_fp32: bool = True,
                  ar_enabled: bool = True, gap_budgets: Optional[dict] = None,
                  shared_ar_bw: Optional[float] = None, expert_ar_bw: Optional[float] = None,
-                 shared_reduce_fn=None, expert_reduce_fn=None, allocator=None):
+                 shared_reduce_fn=None, expert_reduce_fn=None, allocator=None, eager_ar: Optional[bool] = None):
         super().__init__()
         self.config = config
         self.module = module
@@ -49,6 +49,9 @@ class FluidDDP(nn.Module):
         self._configure_scheduler(accumulate_in_fp32, ar_enabled, gap_budgets, shared_ar_bw, expert_ar_bw,
                                   shared_reduce_fn, expert_reduce_fn, allocator)
         self._setup_other_params()
+        # With the device-initiated transports there are no all-to-all windows to trickle the gradient
+        # reduction into: start it as soon as gradients are committed instead.
+        self.scheduler.eager_ar = (self.fused_ctx is not None) if eager_ar is None else bool(eager_ar)
 
     # ------------------------------------------------------------------ configuration
     def _decoder_layers(self):

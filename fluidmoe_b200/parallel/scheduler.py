@@ -226,6 +226,11 @@ class BackwardScheduler:
         self.use_profiled_gaps = True
         self.fixed_ar_budget = 0          # bytes per gap when > 0 (overrides the model)
         self.pending_ar_enabled = True
+        # Reduce committed gradients as soon as a batch of weight-gradient tasks has run, without
+        # waiting for an all-to-all window: for the device-initiated (fused) transports, whose
+        # exchanges never occupy the communication stream.
+        self.eager_ar = False
+        self.eager_ar_min_bytes = 32 << 20
         self.profiling = False
         self.comm_metrics_enabled = False
         # all-reduce configuration
@@ -427,6 +432,10 @@ class BackwardScheduler:
             current_stream(self._device).wait_stream(self.dw_stream)
         if executed and not commit_per_task:
             self._commit()
+            if (self.eager_ar and self.ar_enabled and not self._in_finish and
+                    (self.shared_buffer.pending_bytes() >= self.eager_ar_min_bytes or
+                     (self.expert_dp_world > 1 and self.expert_buffer.pending_bytes() >= self.eager_ar_min_bytes))):
+                self._submit_ar_inline(budgeted=False)
         get_overhead_profiler().exit(tok)
         return executed
 

@@ -63,3 +63,24 @@ def test_fuse_into_backward_refuses_fp32_state():
     assert FusedAdam([p], state_dtype=torch.float32).fuse_into_backward() == 0
     assert FusedAdam([p], state_dtype=torch.bfloat16, master_weights=True).fuse_into_backward() == 0
     assert FusedAdam([p], state_dtype=torch.bfloat16).fuse_into_backward() == 1
+
+
+def test_stream_mode_is_the_plain_path_on_cpu():
+    """``mode="stream"`` needs CUDA streams; on CPU the gradient is stored and ``step`` updates the
+    parameter as usual, with the same result as the separate optimizer."""
+    torch.manual_seed(0)
+    model = fm.TransformerModel(1, 64, 4, 2, 128, 4, 2, None, None, activation_func="swiglu",
+                                norm_type="rmsnorm", dtype=torch.bfloat16, device="cpu")
+    sched = get_backward_scheduler()
+    sched.enable()
+    ddp = fm.FluidDDP(None, model, sched)
+    opt = fm.FluidOptimizerWrapper(FusedAdam(model.parameters(), lr=1e-2, state_dtype=torch.bfloat16), sched)
+    assert opt.fuse_into_backward(mode="stream") == 2
+    before = [p.detach().float().clone() for p in model.parameters()]
+    x = torch.randn(32, 1, 64).bfloat16().requires_grad_(True)
+    ddp.zero_grad_buffer()
+    ddp(x).float().pow(2).mean().backward()
+    ddp.finish_grad_sync()
+    opt.step()
+    changed = sum(int(not torch.equal(b, p.detach().float())) for b, p in zip(before, model.parameters()))
+    assert changed >= 4

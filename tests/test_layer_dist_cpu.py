@@ -10,7 +10,7 @@ import torch
 from tests.dist_utils import run_distributed
 
 
-def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act, capacity_factor=1.0):
+def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act, capacity_factor=1.0, eager_ar=False):
     import torch.distributed as dist
     from fluidmoe_b200.distributed import init_parallel
     from fluidmoe_b200.models.transformer import TransformerLayer
@@ -46,6 +46,8 @@ def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act, capa
     sched.configure_allreduce(sched_mode == "full", pc.dp_cp_group, pc.expert_dp_group,
                               gap_budgets={r: 1.0 for r in ("moe_combine", "moe_dispatch", "attn_proj", "attn_qkv")},
                               shared_ar_bw=1e6, expert_ar_bw=1e6)
+    sched.eager_ar = bool(eager_ar)
+    sched.eager_ar_min_bytes = 0
     if sched_mode == "F":
         sched.disable()
     else:
@@ -89,6 +91,20 @@ def test_overlap_matches_baseline_world2(mode, sched_mode, chunks):
         y, gx, g = got[r]
         assert torch.allclose(y, yb, atol=2e-5), (y - yb).abs().max()
         assert torch.allclose(gx, gxb, atol=2e-4), (gx - gxb).abs().max()
+        for n in gb:
+            scale = gb[n].abs().max().item() + 1e-6
+            assert (g[n] - gb[n]).abs().max().item() / scale < 1e-4, n
+
+
+def test_eager_allreduce_matches_baseline_world2():
+    """Gradient reduction started right after each batch of weight-gradient tasks (the policy used
+    with the device-initiated transports) gives the same gradients as the reduction at the end."""
+    base = run_distributed(_layer_vs_single, 2, "a2a", "F", 1, "rmsnorm", "gelu")
+    got = run_distributed(_layer_vs_single, 2, "p2p", "full", 2, "rmsnorm", "gelu", 1.0, True)
+    for r in range(2):
+        yb, gxb, gb = base[r]
+        y, gx, g = got[r]
+        assert torch.allclose(y, yb, atol=2e-5)
         for n in gb:
             scale = gb[n].abs().max().item() + 1e-6
             assert (g[n] - gb[n]).abs().max().item() / scale < 1e-4, n

@@ -134,3 +134,25 @@ def test_router_backward_kernel_matches_pytorch(aux, z, monkeypatch):
     monkeypatch.setattr(_native, "use_native", lambda *a: False)
     ref = router.router_backward_logits(dprobs, plan, ti, tp, logits, E, aux, z, tpe, T)
     assert (got - ref).abs().max().item() < 1e-5 * max(1.0, ref.abs().max().item())
+
+
+def test_adam_background_kernel_matches_fp32_reference():
+    n = (1 << 20) + 4 * 37
+    torch.manual_seed(7)
+    p = (torch.randn(n, device="cuda") * 0.05).bfloat16()
+    g = torch.randn(n, device="cuda")
+    m = (torch.randn(n, device="cuda") * 0.1).bfloat16()
+    v = (torch.rand(n, device="cuda") * 0.1).bfloat16()
+    lr, b1, b2, eps, wd, step, gs = 1e-2, 0.9, 0.95, 1e-8, 0.1, 3, 0.5
+    gf = g * gs
+    m_ref = b1 * m.float() + (1 - b1) * gf
+    v_ref = b2 * v.float() + (1 - b2) * gf * gf
+    w = p.float()
+    w_ref = w - lr * ((m_ref / (1 - b1 ** step)) / ((v_ref / (1 - b2 ** step)).sqrt() + eps) + wd * w)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    ew.adam_background(p, g, m, v, lr, b1, b2, eps, wd, step, grad_scale=gs, stream=side.cuda_stream)
+    side.synchronize()
+    for name, got, ref in (("m", m, m_ref), ("v", v, v_ref), ("p", p, w_ref)):
+        err = ((got.float() - ref).norm() / ref.norm()).item()
+        assert err < 6e-3, (name, err)

@@ -19,7 +19,8 @@ __device__ __forceinline__ float dgelu_f(float x) {
   const float pdf = 0.3989422804014327f * __expf(-0.5f * x * x);
   return cdf + x * pdf;
 }
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + __expf(-x)); }
+// Hardware reciprocal (1 ulp): the epilogue warps are latency-bound and the result is rounded to bf16.
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoid_f(x); }
 __device__ __forceinline__ float dsilu_f(float x) {
   const float s = sigmoid_f(x);
@@ -569,10 +570,11 @@ struct EpiDAct {
         get_block_bf16(stg, lane, u, rows_ok, row_ok, pre_in + row0 * ld_pre_in + n_half + col, ld_pre_in, ncols);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float s = silu_f(g[i]);
+          const float sg = sigmoid_f(g[i]);          // one sigmoid serves silu and its derivative
+          const float s = g[i] * sg;
           dp += v[i] * s * u[i];
           const float da = v[i] * p;
-          g[i] = da * u[i] * dsilu_f(g[i]);
+          g[i] = da * u[i] * (sg * (1.0f + g[i] * (1.0f - sg)));
           u[i] = da * s;
         }
         put_block_bf16(stg, lane, g, rows_ok, row_ok, dpre + row0 * ld_dpre + col, ld_dpre, ncols);

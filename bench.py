@@ -244,7 +244,11 @@ def run_ours(args):
                             % (args.layers, m["hidden"], m["heads"], m["kv_heads"], m["ffn"], m["vocab"]),
                    "global_batch": world * batch, "seq_len": seq * world, "seq_per_rank": seq,
                    "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
-                   "comm": args.comm, "adam_moments": args.opt_state, "grad_accum": "fp32", "l2": "working set of a step is several GB (>> 126 MB L2); no explicit flush",
+                   "comm": args.comm, "adam_moments": args.opt_state, "grad_accum": "fp32",
+                   "optimizer": ("AdamW every step inside the timed region; expert weights (%d tensors) updated in their "
+                                 "weight-gradient GEMM %s, all other parameters by the fused Adam kernel in step()"
+                                 % (fused_params, "epilogue" if args.fuse_optimizer != 2 else "stream")) if fused_params
+                   else "AdamW (fused kernel) every step inside the timed region", "l2": "working set of a step is several GB (>> 126 MB L2); no explicit flush",
                    "loss": float(last["loss_val"])},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": wall_e2e / args.steps,

@@ -81,6 +81,11 @@ def build(verbose: bool = True, force: bool = False) -> Path:
             f.unlink()
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 4)) as ex:
         objs = list(ex.map(lambda s: _compile(s, verbose), srcs))
+    # objects of earlier source versions are of no further use: keep the cache to one object per source
+    current = {o.name for o in objs}
+    for f in BUILD.glob("*.o"):
+        if f.name not in current:
+            f.unlink()
     out = target_path()
     stamp = BUILD / "link.stamp"
     key = " ".join(str(o) for o in objs)

@@ -53,6 +53,9 @@ class SymmTensor:
         return self.peer_table.data_ptr()
 
 
+_CANARY_BYTE = 0xC5
+
+
 class SymmetricHeap:
     def __init__(self, group=None, nbytes: int = 1 << 30, device=None):
         self.group = group
@@ -76,6 +79,11 @@ class SymmetricHeap:
         self._cursor = 0
         self._high_water = 0     # the slab is zero-filled at creation; bytes above this mark are still zero
         self._closed = False
+        # Debug aid (FLUIDMOE_SYMM_CANARY=1): a guard block filled with a byte pattern follows every
+        # allocation; ``check_canaries()`` tells which buffer a kernel (local or a peer's) overran.
+        import os
+        self._canary = os.environ.get("FLUIDMOE_SYMM_CANARY", "0") == "1"
+        self._guards: List[tuple] = []     # (start of guard, label)
         self._barrier_flags = self.alloc((max(self.world, 1),), torch.int32)
         self._barrier_epoch = 0
         self._marks: List[int] = []
@@ -88,10 +96,17 @@ class SymmetricHeap:
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
         start = self._cursor
         end = start + int(math.ceil(max(nbytes, 1) / _ALIGN) * _ALIGN)
+        data_end = end
+        if self._canary:
+            end += _ALIGN
         if end > self.nbytes:
             raise MemoryError(
                 f"symmetric heap exhausted: need {end - start} more bytes, {self.nbytes - start} left")
         self._cursor = end
+        if self._canary:
+            self._slab[data_end:end].fill_(_CANARY_BYTE)
+            self._guards = [g for g in self._guards if g[0] < start]     # guards of released regions
+            self._guards.append((data_end, f"allocation at byte {start} ({tuple(shape)} {dtype})"))
         # A tensor of its own over the slice (not a view of the slab): every allocation gets its
         # own autograd version counter, so an in-place update of one buffer (a counter reset, an
         # in-place RoPE) does not invalidate tensors saved for backward that live in another.
@@ -105,6 +120,21 @@ class SymmetricHeap:
         addrs = [b + start for b in self._peer_bases]
         table = torch.tensor(addrs, dtype=torch.int64, device=self.device)
         return SymmTensor(local, start, addrs, table)
+
+    def check_canaries(self) -> None:
+        """Host-synchronising check of every guard block; raises ``RuntimeError`` naming the first
+        allocation whose guard was overwritten.  No-op unless the heap was created with
+        ``FLUIDMOE_SYMM_CANARY=1``."""
+        if not self._canary:
+            return
+        for gstart, label in self._guards:
+            if gstart >= self._cursor:
+                continue
+            block = self._slab[gstart:gstart + _ALIGN]
+            if not bool((block == _CANARY_BYTE).all().item()):
+                bad = int((block != _CANARY_BYTE).nonzero()[0].item())
+                raise RuntimeError(f"symmetric heap guard overwritten {bad} bytes past the end of {label} "
+                                   f"on rank {self.rank}")
 
     def mark(self) -> None:
         self._marks.append(self._cursor)

@@ -156,3 +156,20 @@ def test_adam_background_kernel_matches_fp32_reference():
     for name, got, ref in (("m", m, m_ref), ("v", v, v_ref), ("p", p, w_ref)):
         err = ((got.float() - ref).norm() / ref.norm()).item()
         assert err < 6e-3, (name, err)
+
+
+def test_symmetric_heap_canaries_detect_an_overrun(monkeypatch):
+    """Debug guards of the symmetric heap: a write past the end of a buffer (simulated with an
+    in-heap store, nothing faults) is reported with the allocation it belongs to."""
+    from fluidmoe_b200.parallel.symm import SymmetricHeap
+    monkeypatch.setenv("FLUIDMOE_SYMM_CANARY", "1")
+    heap = SymmetricHeap(None, 1 << 20, torch.device("cuda", torch.cuda.current_device()))
+    a = heap.alloc((1000,), torch.float32)
+    b = heap.alloc((64, 8), torch.bfloat16)
+    a.local.fill_(1.0)
+    b.local.fill_(2.0)
+    heap.check_canaries()                              # intact
+    end_of_a = a.offset + 4096                         # 4000 bytes rounded up to the 1024-byte grain
+    heap._slab[end_of_a + 7] = 0                       # one byte past the end of `a`
+    with pytest.raises(RuntimeError, match="7 bytes past the end of allocation"):
+        heap.check_canaries()

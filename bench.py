@@ -30,6 +30,8 @@ REPO = os.path.dirname(os.path.abspath(__file__))
 MODEL = dict(hidden=4096, heads=32, kv_heads=8, ffn=14336, experts=8, top_k=2, vocab=32000, layers=4,
              seq_per_rank=4096, batch=1)
 BASELINE_TOKENS_PER_S = None  # the reference publishes no tokens/s figure for this configuration
+METRIC_TRAIN = "MoE transformer training tokens/s (fwd+bwd+optimizer, 4-layer Mixtral-shaped block stack)"
+METRIC_FWD = "MoE transformer forward (inference) tokens/s (4-layer Mixtral-shaped block stack, loss included)"
 
 
 def parse_args():
@@ -51,6 +53,13 @@ def parse_args():
                          "micro-batch per step): 1 = in the weight-gradient GEMM epilogue, 2 = small-CTA kernel on "
                          "a side stream behind each weight-gradient GEMM, 0 = off")
     ap.add_argument("--profile", default="", help="write a torch-profiler kernel table of one step to this file")
+    ap.add_argument("--arch", default="native", choices=["native", "matched"],
+                    help="native: SwiGLU 14336 + RMSNorm (this repository's arm of the headline); matched: the "
+                         "reference's own architecture (GELU ffn 21504, LayerNorm, padded capacity 1.0) so that "
+                         "both arms run the identical model")
+    ap.add_argument("--forward-only", action="store_true",
+                    help="time the forward pass alone (inference latency): no backward, no optimizer")
+    ap.add_argument("--loss-trace", action="store_true", help="add the loss of every timed end-to-end step to the JSON line")
     return ap.parse_args()
 
 
@@ -170,9 +179,12 @@ def run_ours(args):
     heap = (6 << 30) if (world > 1 and args.comm in ("auto", "fused")) else 0
     pc = init_parallel(ep_size=world, device=device, symmetric_heap_bytes=heap)
     torch.manual_seed(1234)
-    model = MoEGPT(m["vocab"], args.layers, m["hidden"], m["heads"], m["kv_heads"], m["ffn"], m["experts"],
+    matched = args.arch == "matched"
+    ffn = m["ffn"] * 3 // 2 if matched else m["ffn"]
+    act_name, norm_name = ("gelu", "layernorm") if matched else ("swiglu", "rmsnorm")
+    model = MoEGPT(m["vocab"], args.layers, m["hidden"], m["heads"], m["kv_heads"], ffn, m["experts"],
                    m["top_k"], pc.cp_group, pc.ep_group, dtype=torch.bfloat16, device=device,
-                   router_dtype=torch.float32, activation_func="swiglu", norm_type="rmsnorm",
+                   router_dtype=torch.float32, activation_func=act_name, norm_type=norm_name,
                    moe_combine_chunks=args.chunks, moe_dispatch_chunks=args.chunks,
                    attn_proj_chunks=args.chunks, attn_qkv_chunks=args.chunks, comm_mode=args.comm,
                    parallel_ctx=pc)
@@ -197,7 +209,12 @@ def run_ours(args):
     dev_batches = [b.to(device) for b in host]
     last = {}
 
+    trace = []
+
     def train_step(ids_full):
+        if args.forward_only:
+            with torch.no_grad():
+                return ddp(ids_full[:-1], ids_full[1:])
         ddp.zero_grad_buffer()
         loss = ddp(ids_full[:-1], ids_full[1:])
         loss.backward()
@@ -211,6 +228,7 @@ def run_ours(args):
     def step_e2e(i):
         ids = host[i % n_batches].to(device, non_blocking=True)
         last["loss_val"] = train_step(ids).item()
+        trace.append(last["loss_val"])
 
     for i in range(args.warmup):
         step_device(i)
@@ -235,21 +253,23 @@ def run_ours(args):
     value = tokens / (ms / 1e3)
     e2e = tokens / (wall_e2e / 1e3)
     emit(rank, {
-        "metric": "MoE transformer training tokens/s (fwd+bwd+optimizer, 4-layer Mixtral-shaped block stack)",
+        "metric": METRIC_FWD if args.forward_only else METRIC_TRAIN,
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
         "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)", "impl": "ours",
-        "config": {"model": "mixtral-8x7b-shaped, %d layers, hidden %d, %d/%d heads, 8 experts top-2 SwiGLU ffn %d, vocab %d"
-                            % (args.layers, m["hidden"], m["heads"], m["kv_heads"], m["ffn"], m["vocab"]),
-                   "global_batch": world * batch, "seq_len": seq * world, "seq_per_rank": seq,
+        "config": {"model": "mixtral-8x7b-shaped, %d layers, hidden %d, %d/%d heads, 8 experts top-2 %s ffn %d, %s, vocab %d"
+                            % (args.layers, m["hidden"], m["heads"], m["kv_heads"],
+                               "GELU" if matched else "SwiGLU", ffn, "LayerNorm" if matched else "RMSNorm", m["vocab"]),
+                   "arch": args.arch, "forward_only": bool(args.forward_only),
+                   "global_batch": batch, "seq_len": seq * world, "seq_per_rank": seq,
                    "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
                    "comm": args.comm, "adam_moments": args.opt_state, "grad_accum": "fp32",
                    "optimizer": ("AdamW every step inside the timed region; expert weights (%d tensors) updated in their "
                                  "weight-gradient GEMM %s, all other parameters by the fused Adam kernel in step()"
                                  % (fused_params, "epilogue" if args.fuse_optimizer != 2 else "stream")) if fused_params
                    else "AdamW (fused kernel) every step inside the timed region", "l2": "working set of a step is several GB (>> 126 MB L2); no explicit flush",
-                   "loss": float(last["loss_val"])},
+                   "loss": float(last["loss_val"]), **({"loss_trace": trace} if args.loss_trace else {})},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": wall_e2e / args.steps,
                 "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4},
@@ -365,17 +385,26 @@ def run_reference(args):
     dev_batches = [b.to(device) for b in host]
     last = {}
 
-    def train_step(ids_full):
-        for p in params:
-            p.grad = None
-            if hasattr(p, "_ar_buf_written"):
-                p._ar_buf_written = False
+    trace = []
+    converted = {"n": 0, "bytes": 0}
+
+    def forward_loss(ids_full):
         ids, labels = ids_full[:-1], ids_full[1:]
         x = emb(ids)
         for layer in model.layers:
             x = layer(x, rotary)
         logits = head(final_norm(x))
-        loss = F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), labels.reshape(-1))
+        return F.cross_entropy(logits.view(-1, logits.shape[-1]).float(), labels.reshape(-1))
+
+    def train_step(ids_full):
+        if args.forward_only:
+            with torch.no_grad():
+                return forward_loss(ids_full)
+        for p in params:
+            p.grad = None
+            if hasattr(p, "_ar_buf_written"):
+                p._ar_buf_written = False
+        loss = forward_loss(ids_full)
         loss.backward()
         sched.finish_batch()
         if world > 1:
@@ -383,10 +412,19 @@ def run_reference(args):
                 if p.grad is not None:
                     p.grad.div_(world)
                     dist.all_reduce(p.grad, group=all_group)
+        # The reference's flat buffers hold gradients in the parameter's dtype (its default,
+        # accumulate_in_fp32=False), so handing them to the optimizer is a pointer assignment; a
+        # dtype conversion, should one ever be needed, is counted and reported in the config record.
+        converted["n"] = converted["bytes"] = 0
         for p in model.parameters():
             mg = getattr(p, "main_grad", None)
             if mg is not None and getattr(p, "_ar_buf_written", False):
-                p.grad = mg if mg.dtype == p.dtype else mg.to(p.dtype)
+                if mg.dtype == p.dtype:
+                    p.grad = mg
+                else:
+                    p.grad = mg.to(p.dtype)
+                    converted["n"] += 1
+                    converted["bytes"] += mg.numel() * mg.element_size()
         opt.step()
         sched.clear_iteration()
         return loss
@@ -397,6 +435,7 @@ def run_reference(args):
     def step_e2e(i):
         ids = host[i % n_batches].to(device, non_blocking=True)
         last["loss_val"] = train_step(ids).item()
+        trace.append(last["loss_val"])
 
     try:
         for i in range(args.warmup):
@@ -416,7 +455,7 @@ def run_reference(args):
     tokens = world * seq * batch * args.steps
     value = tokens / (ms / 1e3)
     emit(rank, {
-        "metric": "MoE transformer training tokens/s (fwd+bwd+optimizer, 4-layer Mixtral-shaped block stack)",
+        "metric": METRIC_FWD if args.forward_only else METRIC_TRAIN,
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (uniform random token ids, random-init weights)",
@@ -424,9 +463,11 @@ def run_reference(args):
         "config": {"model": "reference TransformerLayer x%d, hidden %d, %d/%d heads, 8 experts top-2 GELU ffn %d "
                             "(FLOP-matched to SwiGLU %d), LayerNorm, vocab %d; embedding / head / loss / AdamW from torch"
                             % (args.layers, m["hidden"], m["heads"], m["kv_heads"], ffn_ref, m["ffn"], m["vocab"]),
-                   "global_batch": world * batch, "seq_len": seq * world, "seq_per_rank": seq,
+                   "arch": "matched", "forward_only": bool(args.forward_only),
+                   "global_batch": batch, "seq_len": seq * world, "seq_per_rank": seq,
                    "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
-                   "loss": float(last["loss_val"])},
+                   "grad_dtype_conversions_per_step": converted["n"], "grad_bytes_converted_per_step": converted["bytes"],
+                   "loss": float(last["loss_val"]), **({"loss_trace": trace} if args.loss_trace else {})},
         "clocks": clocks,
         "e2e": {"value": tokens / (wall_e2e / 1e3), "unit": "tokens/s", "ms_per_step": wall_e2e / args.steps,
                 "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4},

@@ -62,7 +62,7 @@ def main():
     ddp = FluidDDP(None, model, sched, dp_cp_group=pc.dp_cp_group, expert_dp_group=pc.expert_dp_group)
     opt = FluidOptimizerWrapper(FusedAdam(model.parameters(), lr=args.lr), sched)
     if args.load:
-        load_checkpoint(model, args.load, pc.ep_group)
+        load_checkpoint(model, args.load, pc.ep_group, optimizer=opt.optimizer)
     if args.data:
         from text_dataset import TokenFileDataset
         data = TokenFileDataset(args.data, args.seq * world + 1)
@@ -89,9 +89,9 @@ def main():
             print(f" iteration {step:6d}/{args.steps} | elapsed time per iteration (ms): "
                   f"{(time.perf_counter() - t0) * 1e3:.1f} | lm loss: {lv.item():.6E}", flush=True)
         if args.save and args.save_interval and step % args.save_interval == 0:
-            save_checkpoint(model, args.save, pc.ep_group, step=step)
+            save_checkpoint(model, args.save, pc.ep_group, optimizer=opt.optimizer, step=step)
     if args.save:
-        save_checkpoint(model, args.save, pc.ep_group, step=args.steps)
+        save_checkpoint(model, args.save, pc.ep_group, optimizer=opt.optimizer, step=args.steps)
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

@@ -77,6 +77,8 @@ static void gemm_launch(const py::dict& d, uintptr_t stream) {
   g.ld_dst = get<long long>(d, "ld_dst", 0);
   g.dst_flags = ptr<int* const*>(d, "dst_flags");
   g.num_ranks = get<int>(d, "num_ranks", 1);
+  g.row_aux = ptr<const float*>(d, "row_aux");
+  g.row_aux_dst = ptr<float* const*>(d, "row_aux_dst");
   g.gate_flags = ptr<const int*>(d, "gate_flags");
   g.gate_group_base = ptr<const int*>(d, "gate_group_base");
   g.gate_blocks_per_group = get<int>(d, "gate_blocks_per_group", 0);

@@ -611,6 +611,12 @@ struct EpiScatter {
   long long ld_dst;
   int* const* dst_flags;  // per destination rank: pointer to the counter this rank bumps
   int num_ranks;
+  // One fp32 per row that rides along (the routing-probability gradient on the way back to the
+  // token owner, which the reference sends through a separate small all-to-all,
+  // fluid/layer/transformer.py:526-538): stored by the first column tile's first warp group,
+  // before the release that publishes the row.
+  const float* row_aux;
+  float* const* row_aux_dst;
 
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
@@ -624,6 +630,8 @@ struct EpiScatter {
       rank = dst_rank[row];
       drow = dst_row[row];
     }
+    if (row_aux != nullptr && t.n_tile == 0 && chalf == 0 && rank >= 0)
+      row_aux_dst[rank][drow] = row_aux[row];
     __nv_bfloat16* base = rank >= 0 ? dst_base[rank] + drow * ld_dst : nullptr;
     const bool fast = (ld_dst & 7) == 0 &&
                       __all_sync(0xffffffffu, base == nullptr || aligned16(base));
@@ -1023,7 +1031,7 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
     }
     case FM_EPI_SCATTER: {
       EpiScatter e{reinterpret_cast<__nv_bfloat16* const*>(d->dst_base), d->dst_rank, d->dst_row,
-                   d->ld_dst, d->dst_flags, d->num_ranks};
+                   d->ld_dst, d->dst_flags, d->num_ranks, d->row_aux, d->row_aux_dst};
       return dispatch_gate(d, ta, tb, args, e, grid, stream);
     }
     case FM_EPI_COLSCATTER: {

@@ -1,11 +1,13 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a.
 //
-// One CTA per SM walks a static list of 128 x BN output tiles.  Warp 0 feeds a 4-stage
-// shared-memory ring with TMA tiled loads (128-byte swizzle), warp 1 issues tcgen05.mma
-// with the accumulator in TMEM (two accumulators, so the epilogue of tile i overlaps the
-// main loop of tile i+1), warps 2-5 drain TMEM with tcgen05.ld and run a pluggable
-// epilogue.  A pluggable gate lets the producer wait (bounded) for a flag before it touches
-// the rows of a tile, which is how arriving peer data is consumed tile by tile.
+// One CTA (or a CTA pair sharing a 256 x BN tile through tcgen05.mma.cta_group::2) per SM walks a
+// static list of output tiles.  Warp 0 feeds a shared-memory ring (5 stages for the CTA pair, 4 or 3
+// for a single CTA) with TMA tiled loads
+// (128-byte swizzle), warp 1 issues tcgen05.mma with the accumulator in TMEM (two accumulators, so
+// the epilogue of tile i overlaps the main loop of tile i+1), warps 2-9 (two per TMEM lane quarter,
+// each half of the columns) drain TMEM with tcgen05.ld and run a pluggable epilogue.  A pluggable
+// gate lets the producer wait (bounded) for a flag before it touches the rows of a tile, which is
+// how arriving peer data is consumed tile by tile.
 //
 // Two problem shapes share the kernel:
 //   mode 0 (grouped-M): C[rows_g, N] = A[rows_g, K] * B_g, groups partition the rows of A;

@@ -66,6 +66,8 @@ typedef struct FmGemmDesc {
   long long ld_dst;
   int* const* dst_flags;   // device array [num_ranks]: counter this rank bumps on each peer (may be null)
   int num_ranks;
+  const float* row_aux;       // optional: one fp32 per source row that travels with the row ...
+  float* const* row_aux_dst;  // ... into row_aux_dst[dst_rank[r]][dst_row[r]] (device array [num_ranks])
   // FM_EPI_COLSCATTER (also uses dst_base, ld_dst, dst_flags)
   int cols_per_rank;
   long long dst_row_offset;

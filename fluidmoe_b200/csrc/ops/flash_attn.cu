@@ -351,8 +351,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nq = (a.s + kFaBM - 1) / kFaBM;
   const int npairs = (nq + 1) / 2;
-  const int pair = npairs - 1 - (int)blockIdx.x;   // longest rows first
-  const int h = blockIdx.y, bb = blockIdx.z;
+  // One-dimensional grid ordered by work: every (head, batch) of the longest tile pair comes
+  // first, the shortest pairs last, so that the hardware's in-order CTA dispatch is a
+  // longest-job-first schedule over the whole launch (a causal tile pair p costs 4p + 3 blocks).
+  // Neighbouring CTAs are the query heads of one KV group: they share K/V in L2.
+  const int hq_all = a.G * a.qpg;
+  const int per_pair = hq_all * a.b;
+  const int pair = npairs - 1 - (int)blockIdx.x / per_pair;
+  const int rem_lin = (int)blockIdx.x % per_pair;
+  const int h = rem_lin % hq_all, bb = rem_lin / hq_all;
   const int g = h / a.qpg, hi = h % a.qpg;
   const int heads_per_group = a.qpg + 2;
   const int col_q = ((bb * a.G + g) * heads_per_group + hi) * kFaD;
@@ -1013,10 +1020,14 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int j = blockIdx.x, bb = blockIdx.z;
-  const int g = (int)blockIdx.y / a.hsplit;
+  // One-dimensional grid, longest job first over the whole launch: K/V block j (tiles = nq - j
+  // query tiles to walk) of every (KV head, head split, batch) before block j + 1 of any.
+  const int ny = a.G * a.hsplit;
+  const int j = (int)blockIdx.x / (ny * a.b);
+  const int y_lin = (int)blockIdx.x % ny, bb = ((int)blockIdx.x / ny) % a.b;
+  const int g = y_lin / a.hsplit;
   const int heads_here = a.qpg / a.hsplit;                      // query heads of this CTA
-  const int head0 = ((int)blockIdx.y % a.hsplit) * heads_here;   // first of them within the group
+  const int head0 = (y_lin % a.hsplit) * heads_here;             // first of them within the group
   const int nq = (a.s + kFaBM - 1) / kFaBM;
   const int hq = a.G * a.qpg;
   const int hpg = a.qpg + 2;
@@ -1475,7 +1486,7 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
       configured2 = true;
     }
     const int nq = (s + fm::kFaBM - 1) / fm::kFaBM;
-    dim3 grid2((nq + 1) / 2, G * qpg, b);
+    dim3 grid2((unsigned)(((nq + 1) / 2) * G * qpg * b), 1, 1);
     fm::flash_fwd2_kernel<<<grid2, fm::kFa2Threads, smem, stream>>>(tmap, a);
   } else {
     dim3 grid((s + fm::kFaBM - 1) / fm::kFaBM, G * qpg, b);
@@ -1585,7 +1596,8 @@ extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* d
       a.dkv_accum = dkv_accum;
       grid.y = G * hsplit;
     }
-    fm::flash_bwd2_kernel<<<grid, fm::kFaB2Threads, fm::kFaB2Smem, stream>>>(tq, tdo, tdq, a);
+    dim3 grid_lin(grid.x * grid.y * grid.z, 1, 1);
+    fm::flash_bwd2_kernel<<<grid_lin, fm::kFaB2Threads, fm::kFaB2Smem, stream>>>(tq, tdo, tdq, a);
     fm::attn_dq_store_kernel<<<148 * 8, 256, 0, stream>>>(dq_accum, a.dqkv, (long long)s * b, G, qpg, scale);
     if (a.hsplit > 1)
       fm::attn_dkv_store_kernel<<<148 * 4, 256, 0, stream>>>(dkv_accum, a.dqkv, (long long)s * b, G, qpg);

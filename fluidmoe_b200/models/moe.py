@@ -128,7 +128,7 @@ class EPPlan:
 def router_forward(hidden_states: torch.Tensor, router_weight: torch.Tensor, num_experts: int,
                    top_k: int, ep_group=None, capacity_factor: float = 1.0,
                    ep_plan: Optional[EPPlan] = None, router_dtype: torch.dtype = torch.float32,
-                   gather_tokens: bool = True):
+                   gather_tokens: bool = True, forced_top_idx: Optional[torch.Tensor] = None):
     """Route ``hidden_states [T, H]``.
 
     Returns ``(permuted_tokens, permuted_probs, sorted_indices, tokens_per_expert, top_indices,
@@ -140,7 +140,7 @@ def router_forward(hidden_states: torch.Tensor, router_weight: torch.Tensor, num
     with nvtx_range("router_forward"):
         T = hidden_states.shape[0]
         logits = router_ops.router_logits(hidden_states, router_weight, router_dtype)
-        top_idx, top_probs = router_ops.topk_softmax(logits, top_k)
+        top_idx, top_probs = router_ops.topk_softmax(logits, top_k, forced_top_idx)
         cap = (ep_plan.expert_capacity if ep_plan is not None
                else router_ops.expert_capacity(T, top_k, num_experts, capacity_factor))
         plan = router_ops.build_padded_plan(top_idx, top_probs, num_experts, cap)
@@ -467,7 +467,8 @@ def _dact_blocks(dfc2, w2, state, activation, rows, offs, experts, P, dpre, dpro
 # backward R2: FC1 dX + dispatch-grad all-to-all
 # ============================================================================================
 def fc1_dispatch_backward(plan: EPPlan, dpre_em: torch.Tensor, w1: torch.Tensor,
-                          num_chunks: int = 1, mode: str = "a2a", fused_ctx=None) -> torch.Tensor:
+                          num_chunks: int = 1, mode: str = "a2a", fused_ctx=None,
+                          dprobs_em: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Region ``moe_dispatch``: ``dTok = dpre @ W1^T`` per expert, sent back to the token owners.
     Returns the gradient of the permuted tokens ``[E*cap, H]`` (fluid/moe/backward.py:1075-1411).
     """
@@ -482,7 +483,7 @@ def fc1_dispatch_backward(plan: EPPlan, dpre_em: torch.Tensor, w1: torch.Tensor,
                 sched.execute_dw_tasks(max_defer_tasks=2)
             return out
         if mode == "fused":
-            return fused_ctx.fc1_dispatch_backward(plan, dpre_em, w1)
+            return fused_ctx.fc1_dispatch_backward(plan, dpre_em, w1, dprobs_em)
         cfg = build_region_chunk_config(num_chunks, nle, cap)
         dev, dt = dpre_em.device, dpre_em.dtype
         if cfg.num_chunks == 1 or not sched.is_enabled():

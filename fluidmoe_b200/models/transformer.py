@@ -55,10 +55,12 @@ class LayerRuntime:
         self.ep_plan: Optional[moe_mod.EPPlan] = None
         self.cp_plan: Optional[attn_mod.CPPlan] = None
         self.sig = None
+        self.grad_enabled = True     # grad mode of the current forward call (set by the module)
 
     def ensure(self, x: torch.Tensor) -> None:
         L = self.layer
-        sig = (x.shape[0], x.shape[1], x.dtype, x.device)
+        gen = L.fused_ctx.generation if L.fused_ctx is not None else 0
+        sig = (x.shape[0], x.shape[1], x.dtype, x.device, gen)
         if sig == self.sig:
             return
         self.sig = sig
@@ -74,6 +76,8 @@ class LayerRuntime:
             self.ep_plan.expert_capacity)
         if L.fused_ctx is not None:
             L.fused_ctx.prepare(self.ep_plan, self.cp_plan, L)
+            # a new shape released every layer's buffers: remember the generation now current
+            self.sig = sig[:4] + (L.fused_ctx.generation,)
 
 
 class TransformerLayerFunction(torch.autograd.Function):
@@ -90,11 +94,16 @@ class TransformerLayerFunction(torch.autograd.Function):
         s_loc, b, H = x.shape
         T = s_loc * b
         x2 = x.reshape(T, H)
-        needs_grad = any(ctx.needs_input_grad)
+        # ``needs_input_grad`` ignores torch.no_grad(); the module records the grad mode it was
+        # called in, so that an inference pass neither keeps activations nor the FC1 pre-activation
+        needs_grad = any(ctx.needs_input_grad) and rt.grad_enabled
         act = L.activation
         mode_attn = L.resolve_mode(cp.cp_size, attention=True, cp_plan=cp)
         mode_moe = L.resolve_mode(ep.ep_size)
         fused = L.fused_ctx
+        uses_fused = fused is not None and "fused" in (mode_attn, mode_moe)
+        if uses_fused:
+            fused.layer_forward_begin(ep, needs_grad)
 
         # ---- attention half ----
         with nvtx_range("ln1"):
@@ -116,7 +125,7 @@ class TransformerLayerFunction(torch.autograd.Function):
         if L.dropless:
             mode_moe = "dropless"
             logits = router_ops.router_logits(ln2_out, router_w, L.router_dtype)
-            top_idx, top_probs = router_ops.topk_softmax(logits, L.top_k)
+            top_idx, top_probs = router_ops.topk_softmax(logits, L.top_k, L.forced_top_idx)
             rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
             with nvtx_range("dropless_moe"):
                 combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, needs_grad)
@@ -124,7 +133,8 @@ class TransformerLayerFunction(torch.autograd.Function):
             gather = not (mode_moe == "fused" and ep.ep_size > 1)
             (permuted, probs, sorted_idx, _tpe, top_idx, top_probs, logits, _rmap, rplan) = \
                 moe_mod.router_forward(ln2_out, router_w, L.num_experts, L.top_k, L.ep_group,
-                                       L.capacity_factor, ep, L.router_dtype, gather_tokens=gather)
+                                       L.capacity_factor, ep, L.router_dtype, gather_tokens=gather,
+                                       forced_top_idx=L.forced_top_idx)
             with nvtx_range("dispatch_fc1"):
                 st = moe_mod.dispatch_fc1_forward(ep, permuted, probs, w1, act, mode_moe, save_pre=needs_grad,
                                                   fused_ctx=fused, hidden_states=ln2_out,
@@ -146,6 +156,7 @@ class TransformerLayerFunction(torch.autograd.Function):
         if needs_grad:
             ctx.rt = rt
             ctx.modes = (mode_attn, mode_moe)
+            ctx.uses_fused = uses_fused
             ctx.has_rotary = rotary is not None
             ctx.has_shared = shared_w1 is not None
             ctx.rplan = rplan
@@ -219,13 +230,11 @@ class TransformerLayerFunction(torch.autograd.Function):
             moe_mod.register_moe_dw_tasks(ep, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe",
                                           which="w2" if w1_late else "both")
 
-            # ---- routing-probability gradient back to the token owners, router backward ----
-            with nvtx_range("bwd_router"):
-                if P > 1:
-                    send = moe_mod.expert_to_rank_major(dprobs_em, P, nle, cap).contiguous()
-                    dprobs_perm = comm.all_to_all(send, ep.group)
-                else:
-                    dprobs_perm = dprobs_em
+            fused_moe = mode_moe == "fused" and P > 1
+
+            def router_backward(dprobs_perm):
+                """Routing-probability gradient (permuted order, on the token owner) -> gradient of
+                the router input; queues the router weight gradient."""
                 tpe_global = None
                 if L.aux_loss_coeff > 0.0:
                     tpe_global = rplan.routed_per_expert.float()
@@ -234,19 +243,36 @@ class TransformerLayerFunction(torch.autograd.Function):
                 dlogits = router_ops.router_backward_logits(
                     dprobs_perm, rplan, top_idx, top_probs, logits, L.num_experts, L.aux_loss_coeff,
                     L.z_loss_coeff, tpe_global, T * cp.cp_size)
-                d_ln2_router = (dlogits.to(router_w.dtype) @ router_w.detach().t()).to(dy2.dtype)
+                d_router = (dlogits.to(router_w.dtype) @ router_w.detach().t()).to(dy2.dtype)
                 ln2_for_dw = ln2_out
 
                 def router_dw():
                     return (ln2_for_dw.float().t() @ dlogits).to(torch.float32)
                 sched.register_dw_task(f"layer{lid}.router", lid, router_dw, router_w)
+                return d_router
+
+            # ---- routing-probability gradient back to the token owners, router backward ----
+            # Device-initiated transport: the probability gradient of a row rides with the row's
+            # dispatch gradient in the FC1 input-gradient epilogue (region moe_dispatch), so the
+            # router backward runs after that exchange.  Other transports: a small all-to-all now.
+            d_ln2_router = None
+            if not fused_moe:
+                with nvtx_range("bwd_router"):
+                    if P > 1:
+                        send = moe_mod.expert_to_rank_major(dprobs_em, P, nle, cap).contiguous()
+                        dprobs_perm = comm.all_to_all(send, ep.group)
+                    else:
+                        dprobs_perm = dprobs_em
+                    d_ln2_router = router_backward(dprobs_perm)
 
             # ---- R2: FC1 dX -> dispatch gradient -> token order ----
             with nvtx_range("bwd_moe_dispatch"):
                 dperm = moe_mod.fc1_dispatch_backward(ep, dpre_em, w1, cfg["moe_dispatch"].num_chunks, mode_moe,
-                                                      fused_ctx=fused)
-                if mode_moe == "fused" and P > 1:
-                    d_ln2 = fused.unpermute(ep, dperm, rplan.slot_of_token, d_ln2_router)
+                                                      fused_ctx=fused, dprobs_em=dprobs_em if fused_moe else None)
+                if fused_moe:
+                    with nvtx_range("bwd_router"):
+                        d_ln2_router = router_backward(fused.wait_dispatch_grad(ep))
+                    d_ln2 = fused.unpermute(ep, dperm, rplan.slot_of_token, d_ln2_router, waited=True)
                 else:
                     d_ln2 = permute.unpermute_reduce(dperm, rplan.slot_of_token, d_ln2_router)
             if w1_late:
@@ -293,6 +319,8 @@ class TransformerLayerFunction(torch.autograd.Function):
         if is_ln:
             sched.register_dw_task(f"layer{lid}.ln1_b", lid, lambda: dln1_b, ln1_b)
         ctx.st = ctx.rplan = None
+        if ctx.uses_fused:
+            fused.layer_backward_end(ep)
         return (dx.view(s_loc, b, H),) + (None,) * 13
 
 
@@ -353,6 +381,7 @@ class TransformerLayer(nn.Module):
         self.comm_mode = comm_mode
         self.fused_ctx = parallel_ctx.fused_ctx if (parallel_ctx is not None and hasattr(parallel_ctx, "fused_ctx")) else None
         self._moe_chunk_config = None
+        self.forced_top_idx = None   # [T, k] expert ids replacing the router's selection (see force_routing)
 
         cp_size, ep_size = comm.group_size(cp_group), comm.group_size(ep_group)
         assert num_experts % ep_size == 0
@@ -426,12 +455,19 @@ class TransformerLayer(nn.Module):
             return "fused" if fused_ok else "p2p"
         return self.comm_mode
 
+    def force_routing(self, top_idx: Optional[torch.Tensor]) -> None:
+        """Replace the router's top-k selection by ``top_idx`` (``[tokens, k]`` expert ids) until
+        called with None.  Probabilities still come from this layer's logits, so gradients flow as
+        usual; used to compare two precisions of the same layer under identical routing."""
+        self.forced_top_idx = top_idx
+
     def attach_fused(self, fused_ctx) -> None:
         self.fused_ctx = fused_ctx
         self._rt.sig = None
 
     def forward(self, x: torch.Tensor, rotary_pos_emb: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: ``[seq_local, batch, hidden]``; rotary_pos_emb: ``[seq_full, 1, 1, rot_dim]`` or None."""
+        self._rt.grad_enabled = torch.is_grad_enabled()
         return TransformerLayerFunction.apply(
             x, self.ln1_weight, self.ln1_bias, self.ln2_weight, self.ln2_bias, self.qkv_weight,
             self.proj_weight, self.router_weight, self.moe_w1, self.moe_w2, self.shared_w1,

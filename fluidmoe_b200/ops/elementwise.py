@@ -102,8 +102,19 @@ def unpermute_reduce(rows, slot_of_token, residual=None):
     return out
 
 
+def _same_cuda_device(p, *others) -> None:
+    """The kernels below take raw addresses: every operand must live on the parameter's GPU."""
+    if not p.is_cuda:
+        raise ValueError("native optimizer kernels need CUDA tensors")
+    for t in others:
+        if t is not None and (not t.is_cuda or t.device != p.device):
+            raise ValueError(f"optimizer operand on {t.device}, parameter on {p.device}: load optimizer state "
+                             "with FusedAdam.load_state_dict, which moves it to the parameter's device")
+
+
 def adam_step(p, master, g, m, v, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0, zero_grad=False):
     assert p.dtype == torch.bfloat16 and g.dtype == torch.float32 and m.dtype == v.dtype
+    _same_cuda_device(p, master, g, m, v)
     _native.lib().adam(p.data_ptr(), _ptr(master), g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(),
                        float(lr), float(beta1), float(beta2), float(eps), float(weight_decay), int(step),
                        float(grad_scale), int(zero_grad), int(m.dtype == torch.bfloat16), _s())
@@ -114,6 +125,7 @@ def adam_background(p, g, m, v, lr, beta1, beta2, eps, weight_decay, step, grad_
     an SM beside a resident tensor-core kernel.  ``stream`` is the raw stream handle to launch on."""
     global LAUNCHES
     assert p.dtype == torch.bfloat16 and m.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and g.dtype == torch.float32
+    _same_cuda_device(p, g, m, v)
     LAUNCHES += 1
     _native.lib().adam_background(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), p.numel(), float(lr),
                                   float(beta1), float(beta2), float(eps), float(weight_decay), int(step),

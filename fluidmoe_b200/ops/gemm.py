@@ -424,6 +424,11 @@ def grouped_gemm_wgrad_adam(
             p3[g].copy_(w)
         return
     assert M % 8 == 0 and N % 8 == 0 and param.is_contiguous() and exp_avg.is_contiguous() and exp_avg_sq.is_contiguous()
+    for t in (param, exp_avg, exp_avg_sq):
+        # raw addresses go to the kernel: a host tensor here (moments loaded from a checkpoint
+        # without moving them) would be dereferenced on the device
+        if not t.is_cuda or t.device != a.device:
+            raise ValueError(f"optimizer operand on {t.device}, activations on {a.device}")
     ap, ai, ao, lda = _operand(a)
     bp, bi, bo, ldb = _operand(dy)
     desc = dict(

@@ -165,11 +165,37 @@ class FusedAdam:
                 p._ar_buf_written = False
 
     def state_dict(self):
-        return dict(step=self.step_count, state={i: {k: v for k, v in self.state.get(id(p), {}).items()}
-                                                 for i, p in enumerate(self.params)})
+        """Step count and per-parameter moments, keyed by the parameter's position; tensors are
+        detached host copies so that the result can be written with ``torch.save`` as is."""
+        return dict(step=self.step_count,
+                    state={i: {k: (v.detach().cpu() if torch.is_tensor(v) else v)
+                               for k, v in self.state.get(id(p), {}).items()}
+                           for i, p in enumerate(self.params)})
 
     def load_state_dict(self, sd) -> None:
-        self.step_count = sd["step"]
+        """Install saved moments (and master copies).  Every tensor is moved to its parameter's
+        device and to this optimizer's state dtype first: a checkpoint is read with
+        ``map_location='cpu'``, and the kernels take raw pointers, so a host tensor left in the state
+        of a CUDA parameter would be dereferenced on the device."""
+        self.step_count = int(sd["step"])
         for i, p in enumerate(self.params):
-            if i in sd["state"] and sd["state"][i]:
-                self.state[id(p)] = sd["state"][i]
+            saved = sd["state"].get(i) or sd["state"].get(str(i))
+            if not saved:
+                continue
+            st = {}
+            for key in ("m", "v"):
+                t = saved[key]
+                if tuple(t.shape) != tuple(p.shape):
+                    raise ValueError(f"optimizer state '{key}' of parameter {i} has shape {tuple(t.shape)}, "
+                                     f"the parameter has {tuple(p.shape)}")
+                st[key] = t.to(device=p.device, dtype=self.state_dtype).contiguous()
+            master = saved.get("master")
+            if self.master_weights:
+                if master is not None and tuple(master.shape) != tuple(p.shape):
+                    raise ValueError(f"master copy of parameter {i} has shape {tuple(master.shape)}, "
+                                     f"the parameter has {tuple(p.shape)}")
+                st["master"] = (master.to(device=p.device, dtype=torch.float32).contiguous()
+                                if master is not None else p.detach().float().clone())
+            else:
+                st["master"] = None
+            self.state[id(p)] = st

@@ -47,8 +47,13 @@ def router_logits(x: torch.Tensor, router_weight: torch.Tensor, router_dtype: to
     return x @ w
 
 
-def topk_softmax(logits: torch.Tensor, top_k: int):
-    """Top-k over experts, then softmax over the k selected logits in fp32."""
+def topk_softmax(logits: torch.Tensor, top_k: int, forced_idx: Optional[torch.Tensor] = None):
+    """Top-k over experts, then softmax over the k selected logits in fp32.  ``forced_idx``
+    (``[T, k]`` expert ids) replaces the selection and keeps the probabilities a function of the
+    logits: used to replay one run's routing in another precision."""
+    if forced_idx is not None:
+        top_idx = forced_idx.to(device=logits.device, dtype=torch.int64)
+        return top_idx, torch.softmax(logits.gather(1, top_idx).float(), dim=-1, dtype=torch.float32)
     if _native.use_native(logits) and logits.dtype == torch.float32 and hasattr(_native.lib(), "topk_softmax"):
         from . import elementwise
         return elementwise.topk_softmax(logits, top_k)

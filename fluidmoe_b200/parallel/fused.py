@@ -16,6 +16,26 @@ peers write into:
 
 Every wait is bounded and reports through the status word; counters are reset by their consumer
 after use and a kernel-side barrier at the end of each iteration keeps iterations apart.
+
+Buffer reuse.  The buffers are persistent per layer, so the same memory carries every iteration.
+Three rules keep a write of iteration n+1 from landing on data of iteration n that is still needed:
+
+1. *Exchange order.*  Every exchange is an all-to-all and every consumer kernel precedes, in its
+   rank's stream, the next kernel that rank pushes with.  A rank reaches exchange k+1 only after its
+   consumer of exchange k received the rows of every peer, i.e. after every peer launched its
+   producer of exchange k, and that producer follows the peer's consumer of exchange k-1 in stream
+   order.  So no rank can be more than one exchange ahead of another, and when a peer writes into a
+   buffer of this rank for the second time, the kernel that read the first contents (and the
+   ``zero_()`` of its counters, queued right behind it) has already been launched before the kernel
+   whose output the peer waited for.  This holds for forward-only loops as well; no barrier is
+   needed between forward passes.
+2. *Deferred weight-gradient tasks* read ``tokens_em``, ``dfc2_em``, ``attn_in`` and ``dqkv_sp``
+   after the backward pass that filled them.  ``layer_forward_begin`` therefore drains the
+   scheduler's queue before a layer launches its first push of a new forward pass (gradient
+   accumulation over micro-batches needs no barrier either).
+3. *Tensors saved for backward* are views of these buffers.  A second forward pass of a layer
+   before the backward pass of the first (two forwards then two backwards, or an evaluation pass
+   in between) would overwrite them; ``layer_forward_begin`` raises instead.
 """
 from __future__ import annotations
 
@@ -53,6 +73,7 @@ class _LayerBuffers:
         self.combined = heap.alloc((P * plan.S, H), dtype, zero=False)
         self.cnt_combine = heap.alloc((P,), torch.int32)
         self.dperm = heap.alloc((P * plan.S, H), dtype, zero=False)
+        self.dprobs_perm = heap.alloc((P * plan.S,), torch.float32, zero=False)   # rides with dperm rows
         self.cnt_dperm = heap.alloc((P,), torch.int32)
         me = heap.rank
         # entry p = address of rank p's counter for rows coming from this rank
@@ -95,6 +116,9 @@ class FusedCommContext:
         self._layers: Dict[int, _LayerBuffers] = {}
         self._attn: Dict[int, _AttnBuffers] = {}
         self._sig: Dict[int, tuple] = {}
+        self._awaiting_backward: Dict[int, bool] = {}
+        self.generation = 0          # bumped whenever every buffer is released (a new input shape)
+        self.heap.mark()
 
     @staticmethod
     def attention_supported(cp_plan) -> bool:
@@ -103,23 +127,56 @@ class FusedCommContext:
 
     # ------------------------------------------------------------------ set-up
     def prepare(self, ep_plan, cp_plan, layer) -> None:
-        lid = layer.layer_id
-        sig = ep_plan.signature()
-        if self._sig.get(lid) == sig:
+        """Allocate (first call) or re-allocate (new input shape) the buffers of ``layer``.  The heap
+        is a bump allocator, so a new shape releases the buffers of every layer; each layer notices
+        through ``generation`` and allocates again at its next forward pass.  Collective: every rank
+        of the group must see the same shapes in the same order."""
+        key = id(layer)
+        sig = (ep_plan.signature(), cp_plan.signature() if cp_plan is not None else None)
+        if self._sig.get(key) == sig and key in self._layers:
             return
-        if lid in self._layers:
-            raise RuntimeError("input shape changed after symmetric buffers were allocated; "
-                               "create a new parallel context for a new shape")
-        self._sig[lid] = sig
-        self._layers[lid] = _LayerBuffers(self.heap, ep_plan, ep_plan.dtype, layer.ffn_hidden_size)
-        ep_plan._fused_layer = lid
+        if key in self._layers:
+            self._release_all()
+        self._sig[key] = sig
+        self._layers[key] = _LayerBuffers(self.heap, ep_plan, ep_plan.dtype, layer.ffn_hidden_size)
+        ep_plan._fused_layer = key
         if cp_plan is not None and cp_plan.cp_size > 1 and self.attention_supported(cp_plan):
-            self._attn[lid] = _AttnBuffers(self.heap, cp_plan, cp_plan.dtype)
-            cp_plan._fused_layer = lid
+            self._attn[key] = _AttnBuffers(self.heap, cp_plan, cp_plan.dtype)
+            cp_plan._fused_layer = key
+        self._awaiting_backward[key] = False
         # every rank must finish allocating (and zeroing counters) before anyone pushes
-        torch.cuda.synchronize(self.device)
-        if dist.is_initialized() and self.world > 1:
-            dist.barrier(group=self.group)
+        self.heap.sync_group()
+
+    def _release_all(self) -> None:
+        if any(self._awaiting_backward.values()):
+            raise RuntimeError("input shape changed between the forward and the backward pass of a layer")
+        self.heap.sync_group()          # nobody is still reading or writing the old buffers
+        self._layers.clear()
+        self._attn.clear()
+        self._sig.clear()
+        self._awaiting_backward.clear()
+        self.heap.release_to_mark()
+        self.heap.mark()
+        self.generation += 1
+
+    def layer_forward_begin(self, ep_plan, needs_grad: bool) -> None:
+        """First thing a layer does in a forward pass that uses these buffers (rules 2 and 3 of the
+        module docstring)."""
+        key = ep_plan._fused_layer
+        if self._awaiting_backward.get(key, False):
+            raise RuntimeError(
+                "fused transport: this layer ran a forward pass whose backward pass has not run yet; its "
+                "saved activations live in per-layer symmetric buffers that a second forward pass would "
+                "overwrite. Run forward and backward alternately (gradient accumulation does), or use "
+                "comm_mode='p2p' / 'a2a' for this pattern.")
+        from .scheduler import get_backward_scheduler
+        sched = get_backward_scheduler()
+        if sched.is_enabled() and sched.num_queued_dw_tasks() > 0:
+            sched.execute_dw_tasks()
+        self._awaiting_backward[key] = bool(needs_grad)
+
+    def layer_backward_end(self, ep_plan) -> None:
+        self._awaiting_backward[ep_plan._fused_layer] = False
 
     def _buf(self, plan) -> _LayerBuffers:
         return self._layers[plan._fused_layer]
@@ -143,9 +200,12 @@ class FusedCommContext:
         return dict(gate_flags=flags.local.data_ptr(), gate_blocks_per_group=bpg, gate_expected=1,
                     timeout_ns=self.timeout_ns)
 
-    def _scatter_gemm(self, plan, a, w, b_layout, dst: SymmTensor, cnt_tbl: torch.Tensor) -> None:
+    def _scatter_gemm(self, plan, a, w, b_layout, dst: SymmTensor, cnt_tbl: torch.Tensor,
+                      row_aux: Optional[torch.Tensor] = None, row_aux_dst: Optional[SymmTensor] = None) -> None:
         """Grouped GEMM over the expert-major rows whose epilogue stores each result row into the
-        owner's buffer (``plan.combine_dst_rank`` / ``combine_dst_row``)."""
+        owner's buffer (``plan.combine_dst_rank`` / ``combine_dst_row``).  ``row_aux`` (fp32, one
+        value per source row) travels with its row into ``row_aux_dst`` at the same destination
+        row and is published by the same counter."""
         _count()
         G = w.shape[0]
         K = a.shape[1]
@@ -163,6 +223,9 @@ class FusedCommContext:
             dst_row=plan.combine_dst_row.data_ptr(), ld_dst=plan.hidden_size,
             dst_flags=cnt_tbl.data_ptr(), num_ranks=plan.ep_size,
             timeout_ns=self.timeout_ns, status=status_buffer(a.device).data_ptr(), cta_pair=gemm.CTA_PAIR)
+        if row_aux is not None:
+            assert row_aux.dtype == torch.float32 and row_aux.is_contiguous() and row_aux.numel() == a.shape[0]
+            desc.update(row_aux=row_aux.data_ptr(), row_aux_dst=row_aux_dst.ptr_table)
         lib.gemm_launch(desc, _native.stream_ptr())
 
     def _wait_counters(self, cnt: SymmTensor, expected: int) -> None:
@@ -191,14 +254,17 @@ class FusedCommContext:
         self._scatter_gemm(plan, state.act_em, w2, "kn", b.combined, b.cnt_combine_tbl)
         return b.combined.local
 
-    def unpermute(self, plan, rows, slot_of_token, residual):
+    def unpermute(self, plan, rows, slot_of_token, residual, waited: bool = False):
         """Wait until every source's rows are in ``rows`` (the combine or dispatch-gradient buffer
-        of this layer), then gather-sum them into token order."""
+        of this layer), then gather-sum them into token order.  ``waited``: the caller has already
+        waited for (and reset) the counters with ``wait_dispatch_grad``."""
         b = self._buf(plan)
         cnt = b.cnt_combine if rows.data_ptr() == b.combined.local.data_ptr() else b.cnt_dperm
-        self._wait_counters(cnt, plan.S * self._n_tiles(plan.hidden_size) * EPI_SPLIT)
+        if not waited:
+            self._wait_counters(cnt, plan.S * self._n_tiles(plan.hidden_size) * EPI_SPLIT)
         out = permute.unpermute_reduce(rows, slot_of_token, residual)
-        cnt.local.zero_()
+        if not waited:
+            cnt.local.zero_()
         return out
 
     # ------------------------------------------------------------------ backward
@@ -216,14 +282,27 @@ class FusedCommContext:
         b.flags_bwd.local.zero_()
         return b.dfc2_em.local, dpre, dprobs
 
-    def fc1_dispatch_backward(self, plan, dpre_em, w1):
+    def fc1_dispatch_backward(self, plan, dpre_em, w1, dprobs_em=None):
+        """Region moe_dispatch: ``dTok = dpre @ W1^T`` whose epilogue stores every row into the
+        token owner's ``dperm`` buffer; with ``dprobs_em`` the routing-probability gradient of the
+        row goes with it (the reference sends it through a separate synchronous all-to-all,
+        fluid/layer/transformer.py:526-538)."""
         from .scheduler import get_backward_scheduler
         b = self._buf(plan)
-        self._scatter_gemm(plan, dpre_em, w1, "nk", b.dperm, b.cnt_dperm_tbl)
+        self._scatter_gemm(plan, dpre_em, w1, "nk", b.dperm, b.cnt_dperm_tbl,
+                           row_aux=dprobs_em, row_aux_dst=b.dprobs_perm if dprobs_em is not None else None)
         sched = get_backward_scheduler()
         if sched.is_enabled():
             sched.execute_dw_tasks(max_defer_tasks=2)
         return b.dperm.local
+
+    def wait_dispatch_grad(self, plan) -> torch.Tensor:
+        """Block the stream until every source's dispatch-gradient rows (and the probability
+        gradients that came with them) are in; returns the probability gradients in permuted order."""
+        b = self._buf(plan)
+        self._wait_counters(b.cnt_dperm, plan.S * self._n_tiles(plan.hidden_size) * EPI_SPLIT)
+        b.cnt_dperm.local.zero_()
+        return b.dprobs_perm.local
 
 
     # ------------------------------------------------------------------ Ulysses exchanges

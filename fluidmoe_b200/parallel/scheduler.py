@@ -356,6 +356,9 @@ class BackwardScheduler:
         self._dw_queue.append(task)
         get_overhead_profiler().exit(tok)
 
+    def num_queued_dw_tasks(self) -> int:
+        return len(self._dw_queue)
+
     def _run_task(self, task: DWTask) -> None:
         grad = task.compute_fn()
         param = task.weight_param
@@ -397,9 +400,6 @@ class BackwardScheduler:
         if not self.stage2_enabled and not self._in_finish:
             # Ablation: nothing runs inside windows except tasks that must not be deferred.
             max_defer_tasks = 0
-        if not self.cross_region_flow and not self._in_finish and max_defer_tasks is not None:
-            # Ablation: a window may only run tasks of the layer that is currently in backward.
-            pass
         tok = get_overhead_profiler().enter("overhead.bwd_execute_dw")
         ran_deferrable = 0
         executed = 0
@@ -685,6 +685,10 @@ class BackwardScheduler:
             self._last_a2a_end = None
 
     def end_region(self) -> None:
+        if not self.cross_region_flow and self.enabled and self._dw_queue and not self._in_finish:
+            # Ablation: no weight-gradient task outlives the region that queued or inherited it;
+            # the queue is drained at every region boundary (fluid/core/scheduler.py:1048-1052).
+            self.execute_dw_tasks(commit_per_task=False)
         if self.profiling and self._region_start is not None:
             name, s_ev, first_pair = self._region_start
             e_ev = make_event(self._device, True)

@@ -38,8 +38,7 @@ def main(argv=None):
     device, cfg, pc = common.setup(args.model, overrides, comm_mode)
     model = common.build_model(cfg, bench, pc, device, comm_mode)
     x = common.make_input(cfg, pc, device)
-    for msg_region, n in model.prepare_chunk_status(x).items():
-        pass
+    chunk_status = model.prepare_chunk_status(x)     # warns once per region that falls back
     sched = get_backward_scheduler()
     if args.impl == "fluidmoe-f":
         sched.disable()

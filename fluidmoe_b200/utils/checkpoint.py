@@ -24,25 +24,40 @@ def _is_expert_key(key: str) -> bool:
     return key.rsplit(".", 1)[-1] in EXPERT_KEYS
 
 
+def _writes_shards(ep_group) -> bool:
+    """With data-parallel replicas of the expert-parallel group every replica holds the same shards:
+    only the replica whose first member is global rank 0 writes them."""
+    if not dist.is_initialized() or ep_group is None:
+        return True
+    return dist.get_global_rank(ep_group, 0) == 0
+
+
 def save_checkpoint(model: torch.nn.Module, directory: str, ep_group=None, optimizer=None,
                     step: int = 0, extra: Optional[dict] = None) -> str:
+    """One ``shard_epNNN.pt`` per expert-parallel rank (expert tensors, the rank's optimizer state;
+    rank 0 also the dense tensors) and ``manifest.json``.  Only the first data-parallel replica
+    writes; the closing barrier spans every rank of the job."""
     os.makedirs(directory, exist_ok=True)
     rank = dist.get_rank(ep_group) if dist.is_initialized() else 0
     world = dist.get_world_size(ep_group) if dist.is_initialized() else 1
+    writer = _writes_shards(ep_group)
     sd = {k: v.detach().cpu() for k, v in model.state_dict().items()}
     shard = {k: v for k, v in sd.items() if _is_expert_key(k) or rank == 0}
     payload = {"model": shard}
     if optimizer is not None:
         payload["optimizer"] = optimizer.state_dict()
-    torch.save(payload, os.path.join(directory, f"shard_ep{rank:03d}.pt"))
-    if rank == 0:
+        names = {id(p): n for n, p in model.named_parameters()}
+        payload["optimizer_param_names"] = [names.get(id(p), "") for p in getattr(optimizer, "params", [])]
+    if writer:
+        torch.save(payload, os.path.join(directory, f"shard_ep{rank:03d}.pt"))
+    if rank == 0 and writer:
         manifest = dict(format="fluidmoe_b200.sharded.v1", step=step, ep_size=world,
                         keys={k: dict(shape=list(v.shape), dtype=str(v.dtype), expert=_is_expert_key(k))
                               for k, v in sd.items()}, extra=extra or {})
         with open(os.path.join(directory, "manifest.json"), "w") as f:
             json.dump(manifest, f, indent=1)
     if dist.is_initialized():
-        dist.barrier(group=ep_group)
+        dist.barrier()
     return directory
 
 
@@ -72,14 +87,41 @@ def reshard_experts(directory: str, out_directory: str, new_ep_size: int) -> Non
         manifest = json.load(f)
     old = manifest["ep_size"]
     shards = [torch.load(os.path.join(directory, f"shard_ep{r:03d}.pt"), map_location="cpu")["model"] for r in range(old)]
+    payloads = [torch.load(os.path.join(directory, f"shard_ep{r:03d}.pt"), map_location="cpu") for r in range(old)]
+    shards = [p["model"] for p in payloads]
     dense = {k: v for k, v in shards[0].items() if not _is_expert_key(k)}
     full = {k: torch.cat([s[k] for s in shards], dim=0) for k in shards[0] if _is_expert_key(k)}
+    # optimizer state: expert moments are split along the expert dimension like the weights, every
+    # other entry is replicated and taken from rank 0
+    opt_parts = None
+    if all("optimizer" in p for p in payloads):
+        names = payloads[0].get("optimizer_param_names")
+        if names is None:
+            raise ValueError("checkpoint holds optimizer state without parameter names; it cannot be resharded")
+        opt_parts = [dict(step=payloads[0]["optimizer"]["step"], state={}) for _ in range(new_ep_size)]
+        for i, name in enumerate(names):
+            per_rank = [p["optimizer"]["state"].get(i) for p in payloads]
+            if not per_rank[0]:
+                continue
+            for r in range(new_ep_size):
+                if _is_expert_key(name):
+                    opt_parts[r]["state"][i] = {
+                        k: (torch.cat([st[k] for st in per_rank], dim=0).chunk(new_ep_size, dim=0)[r].clone()
+                            if torch.is_tensor(per_rank[0][k]) else per_rank[0][k]) for k in per_rank[0]}
+                else:
+                    opt_parts[r]["state"][i] = per_rank[0]
+    elif any("optimizer" in p for p in payloads):
+        raise ValueError("only some shards hold optimizer state")
     os.makedirs(out_directory, exist_ok=True)
     for r in range(new_ep_size):
         part = {k: v.chunk(new_ep_size, dim=0)[r].clone() for k, v in full.items()}
         if r == 0:
             part.update(dense)
-        torch.save({"model": part}, os.path.join(out_directory, f"shard_ep{r:03d}.pt"))
+        out = {"model": part}
+        if opt_parts is not None:
+            out["optimizer"] = opt_parts[r]
+            out["optimizer_param_names"] = payloads[0]["optimizer_param_names"]
+        torch.save(out, os.path.join(out_directory, f"shard_ep{r:03d}.pt"))
     manifest["ep_size"] = new_ep_size
     with open(os.path.join(out_directory, "manifest.json"), "w") as f:
         json.dump(manifest, f, indent=1)

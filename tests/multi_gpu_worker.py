@@ -1,9 +1,12 @@
 """Worker run under torchrun by the multi-GPU tests (one process per GPU, NCCL).
 
 Checks, in order: bit-exact device-initiated all-to-all against a computed pattern and against
-NCCL; the kernel-side barrier; the peer-memory all-reduce against NCCL; the fused MoE exchange
-(forward and backward of a whole layer) against the plain all-to-all transport; and that a wait
-nobody satisfies returns a status instead of hanging.
+NCCL; the kernel-side barrier; the peer-memory all-reduce against NCCL; that a wait nobody
+satisfies returns a status instead of hanging; the pairwise put + flag back-end (bit-exact pattern
+over a full round-robin tournament); the fused exchanges inside a whole layer (forward and
+backward) against the plain all-to-all transport, with dense routing and with the flagship top-2
+routing replayed; forward-only loops and micro-batch accumulation without a barrier in between;
+the guard against a second forward pass before the backward pass; re-allocation on a new shape.
 """
 import os
 import sys
@@ -140,6 +143,157 @@ def main():
         assert fro(gx, gxb) < 3e-2, (mode, "dx", fro(gx, gxb))
         for n_ in gb:
             assert fro(g[n_], gb[n_]) < 3e-2, (mode, n_, fro(g[n_], gb[n_]))
+    # ---- 5. flagship routing (top-2 of 8, capacity 1.0): fused vs all-to-all, routing replayed ----
+    from fluidmoe_b200.ops import router as router_ops
+
+    def make_layer(mode, k_, cf, seed=7, **extra):
+        torch.manual_seed(seed)
+        lay = TransformerLayer(H, nh, nkv, F, E, k_, pc.cp_group, pc.ep_group, comm_mode=mode,
+                               parallel_ctx=pc if mode == "fused" else None, capacity_factor=cf, **kw, **extra)
+        with torch.no_grad():
+            g_ = torch.Generator(device=dev).manual_seed(1000 + rank)
+            lay.moe_w1.copy_((torch.randn(lay.moe_w1.shape, device=dev, generator=g_) * 0.05).bfloat16())
+            lay.moe_w2.copy_((torch.randn(lay.moe_w2.shape, device=dev, generator=g_) * 0.05).bfloat16())
+        return lay
+
+    def run_once(lay, x_, gy_, rot_):
+        x_.grad = None
+        for p_ in lay.parameters():
+            p_.grad = None
+        y_ = lay(x_, rot_)
+        y_.backward(gy_)
+        return y_
+
+    sched.disable()
+    seen = {}
+    orig_topk = router_ops.topk_softmax
+
+    def recording(logits, top_k, forced_idx=None):
+        idx, probs = orig_topk(logits, top_k, forced_idx)
+        seen["idx"] = idx.clone()
+        return idx, probs
+    la = make_layer("a2a", 2, 1.0)
+    router_ops.topk_softmax = recording
+    try:
+        ya = run_once(la, x, gy, rot)
+    finally:
+        router_ops.topk_softmax = orig_topk
+    ga = {n_: p_.grad.float().clone() for n_, p_ in la.named_parameters()}
+    gxa = x.grad.float().clone()
+    lf = make_layer("fused", 2, 1.0)
+    lf.force_routing(seen["idx"])
+    for it in range(2):
+        yf = run_once(lf, x, gy, rot)
+        pc.fused_ctx.iteration_barrier()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert fro(yf.float(), ya.float()) < 2e-2, ("top2 y", fro(yf.float(), ya.float()))
+    assert fro(x.grad.float(), gxa) < 4e-2, ("top2 dx", fro(x.grad.float(), gxa))
+    for n_, p_ in lf.named_parameters():
+        assert fro(p_.grad.float(), ga[n_]) < 4e-2, ("top2", n_, fro(p_.grad.float(), ga[n_]))
+
+    # ---- 6. forward-only loop in fused mode, no barrier between passes ----
+    with torch.no_grad():
+        y_ref = la(x, rot).float()
+        la.force_routing(None)
+        for it in range(5):
+            y_it = lf(x, rot)
+        torch.cuda.synchronize()
+        gemm.check_status()
+        assert fro(y_it.float(), y_ref) < 2e-2, ("forward-only", fro(y_it.float(), y_ref))
+
+    # ---- 7. a second forward pass before the backward pass of the first is refused ----
+    y1 = lf(x, rot)
+    try:
+        lf(x, rot)
+        raise AssertionError("expected the fused transport to refuse a second forward pass")
+    except RuntimeError as e:
+        assert "backward pass has not run" in str(e)
+    y1.backward(gy)                       # completes the pending pass; buffers are free again
+    pc.fused_ctx.iteration_barrier()
+    torch.cuda.synchronize()
+    gemm.check_status()
+
+    # ---- 8. two micro-batches accumulated, scheduler on, no barrier between them ----
+    def accumulate(lay, fused_mode):
+        from fluidmoe_b200.parallel.scheduler import BackwardScheduler
+        BackwardScheduler.reset()
+        sc = get_backward_scheduler()
+        sc.enable(dev)
+        sc.configure_allreduce(True, pc.dp_cp_group, pc.expert_dp_group, {}, 3e8, 3e8)
+        sc.eager_ar = fused_mode
+        expert = [lay.moe_w2, lay.moe_w1]
+        sc.setup_ar_buffer([p_ for p_ in lay.parameters() if all(p_ is not e_ for e_ in expert)], True)
+        sc.setup_expert_ar_buffer(expert, True)
+        for p_ in lay.parameters():
+            p_.grad = None
+            p_._ar_buf_written = False
+        torch.manual_seed(31 + rank)
+        for mb in range(2):
+            xm = torch.randn(s_loc, b, H, device=dev).bfloat16().requires_grad_(True)
+            gm = torch.randn(s_loc, b, H, device=dev).bfloat16()
+            lay(xm, rot).backward(gm)
+        sc.finish_batch()
+        if fused_mode:
+            pc.fused_ctx.iteration_barrier()
+        torch.cuda.synchronize()
+        out = {n_: p_.main_grad.float().clone() for n_, p_ in lay.named_parameters()}
+        sc.clear_iteration()
+        BackwardScheduler.reset()
+        return out
+    # dense routing here: each micro-batch routes on its own, nothing to replay
+    acc_a = accumulate(make_layer("a2a", E, 1.0), False)
+    acc_f = accumulate(make_layer("fused", E, 1.0), True)
+    gemm.check_status()
+    for n_ in acc_a:
+        assert fro(acc_f[n_], acc_a[n_]) < 3e-2, ("accumulate", n_, fro(acc_f[n_], acc_a[n_]))
+    sched = get_backward_scheduler()
+    sched.disable()
+
+    # ---- 9. a new input shape re-allocates the symmetric buffers ----
+    s2 = s_loc // 2
+    torch.manual_seed(55 + rank)
+    x2 = torch.randn(s2, b, H, device=dev).bfloat16().requires_grad_(True)
+    gy2 = torch.randn(s2, b, H, device=dev).bfloat16()
+    rot2 = make_rope_freqs(s2 * world, 64, device=dev)
+    lda, ldf = make_layer("a2a", E, 1.0), make_layer("fused", E, 1.0)
+    run_once(ldf, x, gy, rot)             # first shape
+    pc.fused_ctx.iteration_barrier()
+    gen0 = pc.fused_ctx.generation
+    y2a = run_once(lda, x2, gy2, rot2)
+    g2a = x2.grad.float().clone()
+    y2f = run_once(ldf, x2, gy2, rot2)    # second shape: buffers are released and rebuilt
+    pc.fused_ctx.iteration_barrier()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert pc.fused_ctx.generation == gen0 + 1
+    assert fro(y2f.float(), y2a.float()) < 2e-2 and fro(x2.grad.float(), g2a) < 3e-2
+
+    # ---- 10. pairwise put + flag back-end: bit-exact pattern over a whole tournament ----
+    from fluidmoe_b200.parallel.p2p_backend import SymmetricP2PBackend
+    from fluidmoe_b200.parallel.schedule import partner_table
+    backend = SymmetricP2PBackend(heap_bytes=64 << 20)
+    comm_stream = torch.cuda.Stream(device=dev)
+    table = partner_table(world)[rank]
+    nel = 1 << 16
+    idx = torch.arange(nel, device=dev, dtype=torch.int32)
+    for it in range(2):
+        for rnd, q in enumerate(table):
+            recv = backend.alloc_recv_buffer(f"t{rnd}", nel, torch.int32, dev, group=None)   # collective
+            if q < 0:
+                continue
+            send = (rank * 1000003 + q * 7919 + 13 * it + rnd) + idx
+            ev = torch.cuda.Event()
+            comm_stream.wait_stream(torch.cuda.current_stream())
+            backend.exchange(send, recv, q, q, None, comm_stream, ev)
+            torch.cuda.current_stream().wait_event(ev)
+            exp = (q * 1000003 + rank * 7919 + 13 * it + rnd) + idx
+            assert torch.equal(recv, exp), f"put+flag mismatch from {q} on {rank} round {rnd}"
+        torch.cuda.synchronize()
+        dist.barrier()                    # a receive buffer is reused only after both sides read it
+    gemm.check_status()
+    backend.finalize()
+
     dist.barrier()
     if rank == 0:
         print("MULTI_GPU_OK", world, flush=True)

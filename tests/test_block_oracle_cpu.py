@@ -1,0 +1,171 @@
+"""The block's hand-written forward and backward against an independent autograd oracle
+(``tests/oracle.py``: torch operators only, no library code), in one process and on two gloo ranks
+(sequence- and expert-parallel), for LayerNorm / RMSNorm, GELU / SwiGLU, shared experts on and off,
+and with the router's load-balancing and z losses on.
+"""
+import pytest
+import torch
+
+from tests import oracle
+from tests.dist_utils import run_distributed
+
+DIMS = dict(H=64, nh=4, nkv=2, F=96, E=4, k=2, s_loc=16, b=2)
+# the anchor configuration: hidden 256, 8 heads x 32, 4 experts (2 per rank) 256 -> 512 -> 256 GELU, top-2,
+# RMSNorm, RoPE, batch 2, 128 positions per rank, weights ~ N(0, 0.02)
+CONFIG1 = dict(H=256, nh=8, nkv=8, F=512, E=4, k=2, s_loc=128, b=2, init_std=0.02)
+
+
+def _layer_kwargs(norm_type, act, nsh, aux, cf, D=DIMS):
+    return dict(dtype=torch.float32, device="cpu", router_dtype=torch.float32, activation_func=act,
+                norm_type=norm_type, init_std=D.get("init_std", 0.2), capacity_factor=cf, num_shared_experts=nsh,
+                aux_loss_coeff=1e-2 if aux else 0.0, z_loss_coeff=1e-3 if aux else 0.0)
+
+
+def _build_full(norm_type, act, nsh, aux, cf, groups=(None, None), D=DIMS):
+    from fluidmoe_b200.models.transformer import TransformerLayer
+    torch.manual_seed(1)
+    layer = TransformerLayer(D["H"], D["nh"], D["nkv"], D["F"], D["E"], D["k"], groups[0], groups[1],
+                             **_layer_kwargs(norm_type, act, nsh, aux, cf, D))
+    with torch.no_grad():   # norms away from identity so that their gradients are exercised
+        g = torch.Generator().manual_seed(5)
+        for n, p in layer.named_parameters():
+            if n.startswith("ln"):
+                p.add_(0.3 * torch.randn(p.shape, generator=g))
+    return layer
+
+
+def _inputs(world, D=DIMS):
+    torch.manual_seed(2)
+    S = world * D["s_loc"]
+    return torch.randn(S, D["b"], D["H"]), torch.randn(S, D["b"], D["H"])
+
+
+def _sharded_run(rank, world, norm_type, act, nsh, aux, cf, mode, sched_mode, D=DIMS):
+    import torch.distributed as dist
+    from fluidmoe_b200.distributed import init_parallel
+    from fluidmoe_b200.models.transformer import TransformerLayer
+    from fluidmoe_b200.ops.rope import make_rope_freqs
+    from fluidmoe_b200.parallel.scheduler import get_backward_scheduler
+
+    pc = init_parallel()
+    solo = [dist.new_group([r]) for r in range(world)][rank]
+    full = _build_full(norm_type, act, nsh, aux, cf, (solo, solo), D)
+    layer = TransformerLayer(D["H"], D["nh"], D["nkv"], D["F"], D["E"], D["k"], pc.cp_group, pc.ep_group,
+                             comm_mode=mode, moe_combine_chunks=2, moe_dispatch_chunks=2, attn_proj_chunks=2,
+                             attn_qkv_chunks=2, **_layer_kwargs(norm_type, act, nsh, aux, cf, D))
+    nle = D["E"] // world
+    with torch.no_grad():
+        src = dict(full.named_parameters())
+        for n, p in layer.named_parameters():
+            p.copy_(src[n][rank * nle:(rank + 1) * nle] if n in ("moe_w1", "moe_w2") else src[n])
+    x_full, g_full = _inputs(world, D)
+    rot = make_rope_freqs(world * D["s_loc"], D["H"] // D["nh"])
+    sched = get_backward_scheduler()
+    sched.configure_allreduce(sched_mode == "full", pc.dp_cp_group, pc.expert_dp_group,
+                              gap_budgets={r: 1.0 for r in ("moe_combine", "moe_dispatch", "attn_proj", "attn_qkv")},
+                              shared_ar_bw=1e6, expert_ar_bw=1e6)
+    if sched_mode == "F":
+        sched.disable()
+    else:
+        sched.enable(torch.device("cpu"))
+        expert = [layer.moe_w2, layer.moe_w1]
+        sched.setup_ar_buffer([p for p in layer.parameters() if all(p is not e for e in expert)], True)
+        sched.setup_expert_ar_buffer(expert, True)
+    sl = slice(rank * D["s_loc"], (rank + 1) * D["s_loc"])
+    x = x_full[sl].clone().requires_grad_(True)
+    y = layer(x, rot)
+    y.backward(g_full[sl])
+    if sched_mode == "F":
+        sched.sync_allreduce_params(list(layer.parameters()))
+        grads = {n: p.grad.clone() for n, p in layer.named_parameters()}
+    else:
+        sched.finish_batch()
+        grads = {n: p.main_grad.clone() for n, p in layer.named_parameters()}
+    sched.clear_iteration()
+    return y.detach(), x.grad, grads
+
+
+def _oracle(world, norm_type, act, nsh, aux, cf, D=DIMS):
+    from fluidmoe_b200.ops.rope import make_rope_freqs
+    full = _build_full(norm_type, act, nsh, aux, cf, D=D)
+    P = oracle.full_params_from_layers([full])
+    x_full, g_full = _inputs(world, D)
+    x = x_full.clone().requires_grad_(True)
+    rot = make_rope_freqs(world * D["s_loc"], D["H"] // D["nh"])
+    y, reg = oracle.block_forward(x, P, num_heads=D["nh"], num_kv_heads=D["nkv"], top_k=D["k"], world=world,
+                                  activation=act, norm_type=norm_type, capacity_factor=cf, rotary=rot,
+                                  aux_loss_coeff=1e-2 if aux else 0.0, z_loss_coeff=1e-3 if aux else 0.0)
+    ((y * g_full).sum() + reg).backward()
+    return y.detach(), x.grad, {n: p.grad for n, p in P.items()}
+
+
+def _close(a, b, what, tol=2e-4):
+    scale = b.abs().max().item() + 1e-9
+    err = (a - b).abs().max().item() / scale
+    assert err < tol, (what, err)
+
+
+CASES = [("layernorm", "gelu", 0, False, 1.0), ("rmsnorm", "swiglu", 1, False, 1.0),
+         ("rmsnorm", "gelu", 0, True, 1.0), ("layernorm", "swiglu", 1, True, 2.0),
+         ("rmsnorm", "swiglu", 0, False, 0.0)]
+
+
+@pytest.mark.parametrize("norm_type,act,nsh,aux,cf", CASES)
+def test_block_matches_autograd_oracle_single_process(norm_type, act, nsh, aux, cf):
+    from fluidmoe_b200.ops.rope import make_rope_freqs
+    from fluidmoe_b200.parallel.scheduler import BackwardScheduler, get_backward_scheduler
+    BackwardScheduler.reset()
+    get_backward_scheduler().disable()
+    D = DIMS
+    layer = _build_full(norm_type, act, nsh, aux, cf)
+    x_full, g_full = _inputs(1)
+    x = x_full.clone().requires_grad_(True)
+    y = layer(x, make_rope_freqs(D["s_loc"], D["H"] // D["nh"]))
+    y.backward(g_full)
+    yo, dxo, go = _oracle(1, norm_type, act, nsh, aux, cf)
+    _close(y.detach(), yo, "y")
+    _close(x.grad, dxo, "dx")
+    for n, p in layer.named_parameters():
+        _close(p.grad, go[n], n)
+    BackwardScheduler.reset()
+
+
+@pytest.mark.parametrize("norm_type,act,nsh,aux,cf,mode,sched_mode", [
+    ("layernorm", "gelu", 0, False, 1.0, "a2a", "F"),
+    ("rmsnorm", "swiglu", 1, True, 1.0, "p2p", "full"),
+    ("rmsnorm", "swiglu", 0, False, 0.0, "a2a", "FB"),
+])
+def test_block_matches_autograd_oracle_world2(norm_type, act, nsh, aux, cf, mode, sched_mode):
+    """Sequence- and expert-parallel over two ranks.  Gradients come back averaged over the
+    data-parallel group (pre-scale 1/world, then sum), so they are compared after scaling by the
+    world size."""
+    world = 2
+    D = DIMS
+    res = run_distributed(_sharded_run, world, norm_type, act, nsh, aux, cf, mode, sched_mode)
+    yo, dxo, go = _oracle(world, norm_type, act, nsh, aux, cf)
+    nle = D["E"] // world
+    for r in range(world):
+        y, dx, grads = res[r]
+        sl = slice(r * D["s_loc"], (r + 1) * D["s_loc"])
+        _close(y, yo[sl], f"y rank {r}")
+        _close(dx, dxo[sl], f"dx rank {r}")
+        for n, g in grads.items():
+            ref = go[n][r * nle:(r + 1) * nle] if n in ("moe_w1", "moe_w2") else go[n]
+            _close(g * world, ref, f"{n} rank {r}")
+
+
+def test_anchor_configuration_world2_against_oracle():
+    """The anchor configuration exactly as stated (fp32, gloo, EP = SP = 2): pairwise-overlap
+    transport with the scheduler in full mode against the autograd oracle."""
+    world, D = 2, CONFIG1
+    res = run_distributed(_sharded_run, world, "rmsnorm", "gelu", 0, False, 1.0, "p2p", "full", D)
+    yo, dxo, go = _oracle(world, "rmsnorm", "gelu", 0, False, 1.0, D)
+    nle = D["E"] // world
+    for r in range(world):
+        y, dx, grads = res[r]
+        sl = slice(r * D["s_loc"], (r + 1) * D["s_loc"])
+        _close(y, yo[sl], f"y rank {r}")
+        _close(dx, dxo[sl], f"dx rank {r}")
+        for n, g in grads.items():
+            ref = go[n][r * nle:(r + 1) * nle] if n in ("moe_w1", "moe_w2") else go[n]
+            _close(g * world, ref, f"{n} rank {r}", tol=5e-4)

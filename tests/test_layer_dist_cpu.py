@@ -1,8 +1,10 @@
 """Multi-process CPU (gloo) checks: the overlapped layer against plain baselines.
 
-Covers the anchor configuration: one MoE transformer layer, fp32, world 2 (EP = SP = 2), hidden
-256, 8 heads x 32, causal, RoPE, RMSNorm, 4 experts with FFN 512, GELU, top-2, batch 2,
-128 positions per rank.
+One MoE transformer layer, fp32, world 2 (EP = SP = 2), hidden 256, 8 query / 4 KV heads x 32,
+causal, RoPE, RMSNorm, 4 experts with FFN 512, GELU, top-2, batch 2, 32 positions per rank: every
+transport and scheduler mode against the plain all-to-all path.  (The anchor configuration with
+128 positions per rank and 8 x 32 heads is checked against an independent autograd oracle in
+``test_block_oracle_cpu.py``.)
 """
 import pytest
 import torch
@@ -69,15 +71,6 @@ def _layer_vs_single(rank, world, mode, sched_mode, chunks, norm_type, act, capa
         assert stats["pending_dw_at_finish"] == 0 and stats["completed_dw_tasks"] == stats["total_dw_tasks"]
     sched.clear_iteration()
     return (y.detach(), x.grad, grads)
-
-
-def _single_reference(norm_type, act, world):
-    """Run the same problem in one process the way ``world`` ranks would route it: routing and
-    capacity are per-rank, so each rank's tokens go through the layer separately except for
-    attention, which sees the whole sequence.  Done by running the sharded layer math with
-    world-size-1 groups on the full sequence is not equivalent; instead gather results from a
-    world-size run in 'a2a' mode with the scheduler off, which is plain autograd-free baseline."""
-    raise NotImplementedError
 
 
 @pytest.mark.parametrize("mode,sched_mode,chunks", [("p2p", "F", 1), ("p2p", "FB", 2), ("a2a", "full", 4), ("p2p", "full", 2)])

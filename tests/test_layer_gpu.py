@@ -51,11 +51,69 @@ def test_layer_forward_backward_matches_cpu(norm_type, act, nsh, E, k):
     tok_err = (yg.float().cpu() - yc).abs().amax(-1) / (yc.abs().amax(-1) + 1e-6)
     assert (tok_err < 5e-2).float().mean().item() > 0.97, (tok_err < 5e-2).float().mean().item()
     if k < E:
-        return
+        return      # gradients under sparse routing: test_layer_gradients_sparse_routing_replayed
     assert fro(yg, yc) < 5e-2, fro(yg, yc)
     assert fro(xg.grad, xc.grad) < 8e-2, fro(xg.grad, xc.grad)
     for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
         assert fro(pg.grad, pc.grad) < 8e-2, (n, fro(pg.grad, pc.grad))
+
+
+@pytest.mark.parametrize("norm_type,act,cf", [("rmsnorm", "swiglu", 4.0), ("layernorm", "gelu", 1.0)])
+def test_layer_gradients_sparse_routing_replayed(norm_type, act, cf):
+    """Top-2 of 8 experts (the flagship routing): the fp32 run's expert selection is replayed on
+    the GPU (``force_routing``), which removes the discrete disagreement, so the output, ``dx`` and
+    every weight gradient must agree.  ``cf = 4`` keeps every routed pair; ``cf = 1`` also drops by
+    capacity, where a pair whose probability sits at an expert's cut can still differ, so that case
+    compares with a looser bound."""
+    from fluidmoe_b200.models.transformer import TransformerLayer
+    from fluidmoe_b200.ops import gemm, router as router_ops
+    from fluidmoe_b200.ops.rope import make_rope_freqs
+    from fluidmoe_b200.parallel.scheduler import get_backward_scheduler
+
+    get_backward_scheduler().disable()
+    torch.manual_seed(1)
+    H, nh, nkv, F, E, k = 512, 4, 2, 768, 8, 2
+    s, b = 256, 2
+    kw = dict(router_dtype=torch.float32, activation_func=act, norm_type=norm_type, init_std=0.05,
+              capacity_factor=cf)
+    cpu = TransformerLayer(H, nh, nkv, F, E, k, None, None, dtype=torch.float32, device="cpu", **kw)
+    with torch.no_grad():
+        for p in cpu.parameters():
+            p.copy_(p.bfloat16().float())
+    gpu = TransformerLayer(H, nh, nkv, F, E, k, None, None, dtype=torch.bfloat16, device="cuda", **kw)
+    gpu.load_state_dict({n: v.bfloat16() for n, v in cpu.state_dict().items()})
+    x = torch.randn(s, b, H).bfloat16().float()
+    g = torch.randn(s, b, H).bfloat16().float()
+    rot = make_rope_freqs(s, 128)
+    seen = {}
+    orig = router_ops.topk_softmax
+
+    def recording(logits, top_k, forced_idx=None):
+        idx, probs = orig(logits, top_k, forced_idx)
+        seen["idx"] = idx.clone()
+        return idx, probs
+    router_ops.topk_softmax = recording
+    try:
+        xc = x.clone().requires_grad_(True)
+        yc = cpu(xc, rot)
+        yc.backward(g)
+    finally:
+        router_ops.topk_softmax = orig
+    gpu.force_routing(seen["idx"].cuda())
+    xg = x.cuda().bfloat16().requires_grad_(True)
+    yg = gpu(xg, rot.cuda())
+    yg.backward(g.cuda().bfloat16())
+    torch.cuda.synchronize()
+    gemm.check_status()
+
+    def fro(a, b_):
+        a, b_ = a.float().cpu(), b_.float()
+        return ((a - b_).norm() / (b_.norm() + 1e-9)).item()
+    tol_y, tol_g = (5e-2, 8e-2) if cf >= 4.0 else (1e-1, 1.5e-1)
+    assert fro(yg, yc) < tol_y, fro(yg, yc)
+    assert fro(xg.grad, xc.grad) < tol_g, fro(xg.grad, xc.grad)
+    for (n, pg), (_, pc) in zip(gpu.named_parameters(), cpu.named_parameters()):
+        assert fro(pg.grad, pc.grad) < tol_g, (n, fro(pg.grad, pc.grad))
 
 
 def test_dropless_fine_grained_layer_runs_and_matches_cpu():

@@ -101,6 +101,60 @@ def test_checkpoint_round_trip(tmp_path):
     load_reference_state_dict(b, sd)
 
 
+def _train_steps(model, opt, xs):
+    for x in xs:
+        for p in model.parameters():
+            p.grad = None
+        model(x).square().mean().backward()
+        opt.step()
+
+
+def test_checkpoint_resume_with_optimizer_matches_uninterrupted_run(tmp_path):
+    """Two steps, save, load into a fresh model + optimizer, two more steps == four steps in one go;
+    the loaded moments live on the parameter's device in the optimizer's state dtype."""
+    from fluidmoe_b200.models.transformer import TransformerModel
+    from fluidmoe_b200.ops.optim import FusedAdam
+    from fluidmoe_b200.parallel.scheduler import BackwardScheduler
+    from fluidmoe_b200.utils.checkpoint import load_checkpoint, reshard_experts, save_checkpoint
+    BackwardScheduler.reset()
+    kw = dict(dtype=torch.float32, device="cpu")
+    torch.manual_seed(3)
+    xs = [torch.randn(8, 1, 64) for _ in range(4)]
+    torch.manual_seed(4)
+    a = TransformerModel(1, 64, 4, 2, 96, 4, 2, **kw)
+    oa = FusedAdam(a.parameters(), lr=1e-2)
+    _train_steps(a, oa, xs[:2])
+    save_checkpoint(a, str(tmp_path / "ck"), optimizer=oa, step=2)
+    _train_steps(a, oa, xs[2:])
+    torch.manual_seed(5)
+    b = TransformerModel(1, 64, 4, 2, 96, 4, 2, **kw)
+    ob = FusedAdam(b.parameters(), lr=1e-2)
+    load_checkpoint(b, str(tmp_path / "ck"), optimizer=ob)
+    assert ob.step_count == 2
+    for p in ob.params:
+        st = ob.state[id(p)]
+        assert st["m"].device == p.device and st["m"].dtype == ob.state_dtype and st["m"].shape == p.shape
+    _train_steps(b, ob, xs[2:])
+    for (n, pa), (_, pb) in zip(a.named_parameters(), b.named_parameters()):
+        assert torch.allclose(pa, pb, atol=1e-6), n
+    # a state tensor of the wrong shape is refused
+    bad = oa.state_dict()
+    bad["state"][0]["m"] = torch.zeros(3)
+    with pytest.raises(ValueError, match="shape"):
+        FusedAdam(b.parameters()).load_state_dict(bad)
+    # resharding keeps the optimizer state and splits expert moments along the expert dimension
+    reshard_experts(str(tmp_path / "ck"), str(tmp_path / "ck2"), 2)
+    s0 = torch.load(str(tmp_path / "ck2" / "shard_ep000.pt"))
+    s1 = torch.load(str(tmp_path / "ck2" / "shard_ep001.pt"))
+    names = s0["optimizer_param_names"]
+    i = names.index("layers.0.moe_w1")
+    full = torch.load(str(tmp_path / "ck" / "shard_ep000.pt"))["optimizer"]["state"][i]["m"]
+    assert torch.equal(torch.cat([s0["optimizer"]["state"][i]["m"], s1["optimizer"]["state"][i]["m"]]), full)
+    j = names.index("layers.0.qkv_weight")
+    assert torch.equal(s0["optimizer"]["state"][j]["v"], s1["optimizer"]["state"][j]["v"])
+    BackwardScheduler.reset()
+
+
 def test_comm_timer_counts_and_restores():
     """The collective timers wrap the torch.distributed entry points only inside the context."""
     import torch.distributed as dist
@@ -149,3 +203,73 @@ def test_external_baselines_report_missing_packages():
     if not avail["deepspeed"]:
         with pytest.raises(eb.BaselineUnavailable, match="package"):
             eb.build_deepspeed_ulysses_baseline(cfg, device="cpu")
+
+
+def test_external_baselines_build_with_stub_packages(monkeypatch):
+    """With stand-ins for megatron-core / transformer_engine / deepspeed on the import path both
+    builders run to the end for every preset: the preset keys they read exist and the arguments
+    they pass are the ones the packages' constructors take."""
+    import sys
+    import types
+    from fluidmoe_b200.tools import external_baselines as eb
+    from fluidmoe_b200.tools.model_configs import get_model_config, list_model_names
+
+    seen = {}
+
+    def module(name, **attrs):
+        m = types.ModuleType(name)
+        m.__dict__.update(attrs)
+        monkeypatch.setitem(sys.modules, name, m)
+        return m
+
+    class TransformerConfig:
+        def __init__(self, **kw):
+            seen["tc"] = kw
+
+    class TransformerBlock(torch.nn.Module):
+        def __init__(self, config, spec, post_layer_norm=True):
+            super().__init__()
+            seen["block"] = (config, spec, post_layer_norm)
+
+    module("megatron")
+    module("megatron.core")
+    module("transformer_engine")
+    module("megatron.core.models")
+    module("megatron.core.models.gpt")
+    module("megatron.core.models.gpt.gpt_layer_specs",
+           get_gpt_layer_with_transformer_engine_spec=lambda **kw: ("spec", kw))
+    module("megatron.core.transformer")
+    module("megatron.core.transformer.transformer_block", TransformerBlock=TransformerBlock)
+    module("megatron.core.transformer.transformer_config", TransformerConfig=TransformerConfig)
+
+    class MoE(torch.nn.Module):
+        def __init__(self, hidden, expert, num_experts, ep_size, k, capacity_factor, drop_tokens):
+            super().__init__()
+            seen["moe"] = dict(hidden=hidden, num_experts=num_experts, ep_size=ep_size, k=k,
+                               capacity_factor=capacity_factor, ffn=expert[0].out_features)
+
+    class DistributedAttention(torch.nn.Module):
+        def __init__(self, local, group, scatter_idx, gather_idx):
+            super().__init__()
+            self.local = local
+
+    module("deepspeed")
+    module("deepspeed.moe")
+    module("deepspeed.moe.layer", MoE=MoE)
+    module("deepspeed.sequence")
+    module("deepspeed.sequence.layer", DistributedAttention=DistributedAttention)
+
+    assert eb.available() == {"megatron": True, "deepspeed": True}
+    for name in list_model_names():
+        cfg = get_model_config(name)
+        eb.build_megatron_baseline(cfg, device="cpu")
+        tc = seen["tc"]
+        assert tc["ffn_hidden_size"] == cfg["ffn_hidden"] and tc["num_query_groups"] == cfg["num_kv_heads"]
+        assert tc["normalization"] == ("RMSNorm" if cfg.get("norm_type") == "rmsnorm" else "LayerNorm")
+        assert tc["gated_linear_unit"] == (cfg.get("activation") == "swiglu")
+        assert tc["moe_token_dispatcher_type"] == "alltoall" and tc["cp_comm_type"] == "a2a"
+    small = get_model_config("tiny_test")
+    model = eb.build_deepspeed_ulysses_baseline(small, ep_size=1, dtype=torch.float32, device="cpu")
+    assert len(model) == small["num_layers"]
+    assert seen["moe"] == dict(hidden=small["hidden_size"], num_experts=small["num_experts"], ep_size=1,
+                               k=small["top_k"], capacity_factor=1.0, ffn=small["ffn_hidden"])

@@ -47,8 +47,8 @@ def _import_reference(ref_root: str):
     import fluid  # noqa: F401 - the reference package, not this repository's alias package
     assert os.path.abspath(fluid.__file__).startswith(ref_root), fluid.__file__
     from fluid.core.scheduler import get_backward_scheduler as ref_sched
-    from fluid.layer.transformer import TransformerModel as RefModel
-    return RefModel, ref_sched
+    import fluid.layer.transformer as ref_mod
+    return ref_mod.TransformerModel, ref_sched, ref_mod
 
 
 class _Arm:
@@ -155,15 +155,22 @@ def main(argv=None) -> int:
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--lr", type=float, default=1e-4)
     ap.add_argument("--chunks", type=int, default=2)
-    ap.add_argument("--ref-qkv-chunks", type=int, default=1,
-                    help="chunk count of the reference's attn_qkv region.  Its chunked path slices the FULL "
-                         "sequence (fluid/attention/backward.py:330-349) and lets the all-to-all split each slice "
-                         "over the ranks, which hands a rank gradient rows of positions it does not own whenever "
-                         "the count exceeds 1 on more than one rank; 1 keeps the reference on its correct path")
+    ap.add_argument("--ref-attn-chunks", type=int, default=1,
+                    help="chunk count of the reference's two attention regions.  Both of its chunked paths "
+                         "misplace sequence rows on more than one rank: attn_proj writes the all-to-all output of "
+                         "chunk c at rows [c*P*sc, (c+1)*P*sc), i.e. in (chunk, rank, row) order instead of the "
+                         "(rank, chunk, row) order of the full sequence (fluid/attention/backward.py:131-162), and "
+                         "attn_qkv slices the FULL sequence and lets the all-to-all split every slice over the ranks "
+                         "(fluid/attention/backward.py:330-349).  1 keeps the reference on its correct paths; any "
+                         "other value reproduces its wrong attention gradients")
     ap.add_argument("--comm", default="auto", choices=["auto", "a2a", "p2p", "fused"])
     ap.add_argument("--tol-out", type=float, default=2e-2)
     ap.add_argument("--tol-grad", type=float, default=5e-2)
     ap.add_argument("--tol-loss", type=float, default=1e-2)
+    ap.add_argument("--own-routing", action="store_true",
+                    help="let this framework's router pick experts itself in the one-step comparison; by default "
+                         "the reference's top-k selection is replayed (force_routing), which removes the few tokens "
+                         "whose near-tied logits the two bf16 pipelines order differently")
     ap.add_argument("--diagnose", action="store_true",
                     help="also compare the first layer's attention half and MoE half in isolation (by zeroing "
                          "the other half's output weights in both models) and print the norms of the differences")
@@ -171,7 +178,7 @@ def main(argv=None) -> int:
 
     os.environ.setdefault("FLUIDMOE_P2P_BACKEND", "nccl")
     os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "1")
-    RefModel, ref_sched_fn = _import_reference(args.ref_root)
+    RefModel, ref_sched_fn, ref_mod = _import_reference(args.ref_root)
     from ..distributed import init_parallel
     from ..models.transformer import TransformerModel
     from ..ops import gemm
@@ -205,7 +212,7 @@ def main(argv=None) -> int:
     ref = RefModel(num_layers=args.layers, hidden_size=H, num_heads=args.heads, num_kv_heads=args.kv_heads,
                    ffn_hidden_size=args.ffn, num_experts=args.experts, top_k=args.top_k, cp_group=ref_group,
                    ep_group=ref_group, capacity_factor=1.0, dtype=torch.bfloat16, device=device,
-                   router_dtype=torch.float32, **{**chunk_kw, "attn_qkv_chunks": args.ref_qkv_chunks})
+                   router_dtype=torch.float32, **{**chunk_kw, "attn_qkv_chunks": args.ref_attn_chunks, "attn_proj_chunks": args.ref_attn_chunks})
     ours = TransformerModel(args.layers, H, args.heads, args.kv_heads, args.ffn, args.experts, args.top_k,
                             pc.cp_group, pc.ep_group, activation_func="gelu", capacity_factor=1.0,
                             dtype=torch.bfloat16, device=device, router_dtype=torch.float32,
@@ -243,8 +250,21 @@ def main(argv=None) -> int:
     x0 = torch.randn(s_loc, b, H, device=device, generator=g).bfloat16()
     dy = (torch.randn(s_loc, b, H, device=device, generator=g) / (s_loc * world)).bfloat16()
     res = {}
+    # record the reference's expert selection (one call of its router per layer) to replay it
+    picked = []
+    ref_router = ref_mod.router_forward
+
+    def recording_router(*a, **kw):
+        out = ref_router(*a, **kw)
+        picked.append(out[4].detach().clone())        # top_indices [tokens, k]
+        return out
     for name, model, begin, finish, sched in (("reference", ref, lambda: None, rs.finish_batch, rs),
                                               ("ours", ours, ours_begin, ours_finish, os_)):
+        if name == "reference":
+            ref_mod.router_forward = recording_router
+        elif not args.own_routing:
+            for layer, idx in zip(model.layers, picked):
+                layer.force_routing(idx)
         for p in model.parameters():
             p.grad = None
             if hasattr(p, "_ar_buf_written"):
@@ -261,12 +281,23 @@ def main(argv=None) -> int:
                  for n, p in model.named_parameters()}
         res[name] = (y.detach().float(), x.grad.float(), grads)
         sched.clear_iteration()
+        if name == "reference":
+            ref_mod.router_forward = ref_router
+        else:
+            for layer in model.layers:
+                layer.force_routing(None)
     gemm.check_status()
     yr, dxr, gr = res["reference"]
     yo, dxo, go = res["ours"]
     errs = {"y": _fro(yo, yr), "dx": _fro(dxo, dxr)}
     for n in gr:
         errs["grad:" + n] = _fro(go[n], gr[n])
+    if args.diagnose:
+        for n in gr:
+            a_, b_ = go[n].flatten(), gr[n].flatten()
+            cos = torch.dot(a_, b_) / (a_.norm() * b_.norm() + 1e-30)
+            print(f"PARITY rank {rank} {n:28s} err {errs['grad:' + n]:.3e}  |ours|/|ref| "
+                  f"{(a_.norm() / (b_.norm() + 1e-30)).item():.4f}  cosine {cos.item():.4f}", flush=True)
     t = torch.tensor(list(errs.values()), device=device, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -289,7 +320,7 @@ def main(argv=None) -> int:
     batches = [torch.randint(0, args.vocab, (s_loc + 1, b), generator=gh).to(device) for _ in range(4)]
     curves = {a.name: [] for a in arms}
     norms = {a.name: [] for a in arms}
-    for i in range(args.steps):
+    for i in range(max(args.steps, 1)):
         for a in arms:
             lv, gn = a.step(batches[i % len(batches)])
             curves[a.name].append(lv)

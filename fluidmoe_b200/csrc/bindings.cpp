@@ -100,6 +100,7 @@ static void gemm_launch(const py::dict& d, uintptr_t stream) {
   g.adam_rbc2 = get<float>(d, "adam_rbc2", 1.f);
   g.max_ctas = get<int>(d, "max_ctas", 0);
   g.timeout_ns = get<unsigned long long>(d, "timeout_ns", 0ull);
+  g.wait_ns = ptr<unsigned long long*>(d, "wait_ns");
   g.status = ptr<int*>(d, "status");
   check(fm_gemm_launch(&g, reinterpret_cast<cudaStream_t>(stream)), "fm_gemm_launch");
 }

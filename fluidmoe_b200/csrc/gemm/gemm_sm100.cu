@@ -1005,6 +1005,7 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   args.k_rotate = d->k_rotate;
   args.timeout_ns = d->timeout_ns ? d->timeout_ns : 4000000000ull;
   args.status = d->status;
+  args.wait_ns = d->wait_ns;
 
   int grid = sm_count();
   if (d->max_ctas > 0 && d->max_ctas < grid) grid = d->max_ctas;

@@ -52,6 +52,10 @@ struct GemmArgs {
   int k_rotate;           // the K loop starts at this 64-wide block (local source first)
   unsigned long long timeout_ns;
   int* status;
+  // Optional device counter (nullptr = off): nanoseconds the producers of all CTAs spent
+  // waiting in a gate for rows that had not arrived yet.  Divided by the number of CTAs it
+  // bounds the communication time this kernel could not hide.
+  unsigned long long* wait_ns;
 };
 
 struct Tile {
@@ -152,7 +156,10 @@ struct GateRowBlockFlags {
     int observed = 0;
     // One arrival per row: a block is ready when as many rows arrived as it holds.
     const int want = t.rows_valid * expected;
-    if (flag_wait_ge(flags + idx, want, a.timeout_ns, abort_flag, &observed)) return true;
+    const uint64_t t0 = a.wait_ns ? global_timer_ns() : 0;
+    const bool ok = flag_wait_ge(flags + idx, want, a.timeout_ns, abort_flag, &observed);
+    if (a.wait_ns) atomicAdd(a.wait_ns, (unsigned long long)(global_timer_ns() - t0));
+    if (ok) return true;
     report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, idx, want, observed);
     return false;
   }
@@ -179,7 +186,10 @@ struct GateKSource {
     const int src = kb / kblocks_per_src;
     const int idx = src * row_blocks + (t.row_base + t.m0) / kBM;
     int observed = 0;
-    if (flag_wait_ge(flags + idx, t.rows_valid, a.timeout_ns, abort_flag, &observed)) return true;
+    const uint64_t t0 = a.wait_ns ? global_timer_ns() : 0;
+    const bool ok = flag_wait_ge(flags + idx, t.rows_valid, a.timeout_ns, abort_flag, &observed);
+    if (a.wait_ns) atomicAdd(a.wait_ns, (unsigned long long)(global_timer_ns() - t0));
+    if (ok) return true;
     report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, 10000 + idx, t.rows_valid, observed);
     return false;
   }

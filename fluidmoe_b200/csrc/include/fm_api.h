@@ -88,6 +88,7 @@ typedef struct FmGemmDesc {
   int max_ctas;  // 0 = one per SM
   unsigned long long timeout_ns;
   int* status;   // device int32[8], may be null
+  unsigned long long* wait_ns;  // optional device counter: time producers spent waiting in a gate
 } FmGemmDesc;
 
 // Returns 0 on success, a cudaError_t / negative code otherwise.  Never allocates.

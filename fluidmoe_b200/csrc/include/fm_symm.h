@@ -48,6 +48,11 @@ int fm_rows_push(const void* src, void* const* dst_base, int* const* dst_flags, 
 // Wait (bounded) until every peer's arrival word in `my_flags` reached `epoch`.
 int fm_a2a_wait(const int* my_flags, int my_rank, int nranks, int epoch,
                 unsigned long long timeout_ns, int* status, cudaStream_t stream);
+// Same, with per-source thresholds read from device memory (`expected[p]`, may be null: then
+// `epoch`) and an optional device counter that accumulates the nanoseconds waited.
+int fm_a2a_wait_counts(const int* my_flags, int nranks, int epoch, const int* expected,
+                       unsigned long long* wait_ns, unsigned long long timeout_ns, int* status,
+                       cudaStream_t stream);
 
 // Two-shot all-reduce (sum) over peer memory: every rank's `buf_ptrs[p]` points at its copy of
 // the same symmetric buffer of `count` elements (fp32 or bf16, in place).  Rank r reduces

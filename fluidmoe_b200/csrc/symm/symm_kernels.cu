@@ -188,13 +188,27 @@ __global__ void rows_push_kernel(const __nv_bfloat16* __restrict__ src,
   }
 }
 
+// Thread p waits until the arrival word of source p reached `epoch` (or `expected[p]`, when the
+// amount every source sends is only known on the device).  With `wait_ns` the time the slowest
+// thread waited is added to a device counter: this kernel sits alone on its stream, so that time
+// is communication the step could not hide.
 __global__ void a2a_wait_kernel(const int* my_flags, int my_rank, int nranks, int epoch,
+                                const int* expected, unsigned long long* wait_ns,
                                 unsigned long long timeout_ns, int* status) {
+  __shared__ unsigned long long slowest;
   const int p = threadIdx.x;
-  if (p >= nranks) return;
-  int observed = 0;
-  if (!flag_wait_ge(my_flags + p, epoch, timeout_ns, nullptr, &observed))
-    report_status(status, kStatusFlagTimeout, kKernelIdA2AWait, p, epoch, observed);
+  if (p == 0) slowest = 0;
+  __syncthreads();
+  if (p < nranks) {
+    const int want = expected ? expected[p] : epoch;
+    int observed = 0;
+    const uint64_t t0 = wait_ns ? global_timer_ns() : 0;
+    if (!flag_wait_ge(my_flags + p, want, timeout_ns, nullptr, &observed))
+      report_status(status, kStatusFlagTimeout, kKernelIdA2AWait, p, want, observed);
+    if (wait_ns) atomicMax(&slowest, (unsigned long long)(global_timer_ns() - t0));
+  }
+  __syncthreads();
+  if (p == 0 && wait_ns) atomicAdd(wait_ns, slowest);
 }
 
 __global__ void wait_flag_kernel(const int* flag, int expected, unsigned long long timeout_ns,
@@ -440,8 +454,16 @@ extern "C" int fm_rows_push(const void* src, void* const* dst_base, int* const* 
 extern "C" int fm_a2a_wait(const int* my_flags, int my_rank, int nranks, int epoch,
                            unsigned long long timeout_ns, int* status, cudaStream_t stream) {
   fm::a2a_wait_kernel<<<1, 32 * ((nranks + 31) / 32), 0, stream>>>(
-      my_flags, my_rank, nranks, epoch, timeout_ns ? timeout_ns : 4000000000ull, status);
+      my_flags, my_rank, nranks, epoch, nullptr, nullptr, timeout_ns ? timeout_ns : 4000000000ull, status);
   return launch_check("a2a_wait");
+}
+
+extern "C" int fm_a2a_wait_counts(const int* my_flags, int nranks, int epoch, const int* expected,
+                                  unsigned long long* wait_ns, unsigned long long timeout_ns, int* status,
+                                  cudaStream_t stream) {
+  fm::a2a_wait_kernel<<<1, 32 * ((nranks + 31) / 32), 0, stream>>>(
+      my_flags, 0, nranks, epoch, expected, wait_ns, timeout_ns ? timeout_ns : 4000000000ull, status);
+  return launch_check("a2a_wait_counts");
 }
 
 extern "C" int fm_wait_flag(const int* flag, int expected, unsigned long long timeout_ns,

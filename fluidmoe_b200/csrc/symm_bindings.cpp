@@ -71,6 +71,13 @@ void bind_symm(py::module_& m) {
                     as_ptr<cudaStream_t>(stream)),
         "a2a_wait");
   });
+  m.def("a2a_wait_counts", [](uintptr_t flags, int n, int epoch, uintptr_t expected, uintptr_t wait_ns,
+                              unsigned long long timeout_ns, uintptr_t status, uintptr_t stream) {
+    chk(fm_a2a_wait_counts(as_ptr<const int*>(flags), n, epoch, as_ptr<const int*>(expected),
+                           as_ptr<unsigned long long*>(wait_ns), timeout_ns, as_ptr<int*>(status),
+                           as_ptr<cudaStream_t>(stream)),
+        "a2a_wait_counts");
+  });
   m.def("put_signal", [](uintptr_t src, long long bytes, uintptr_t dst, uintptr_t flag, int value,
                          int ctas, uintptr_t counter, uintptr_t stream) {
     chk(fm_put_signal(as_ptr<const void*>(src), bytes, as_ptr<void*>(dst), as_ptr<int*>(flag), value,

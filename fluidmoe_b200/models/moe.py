@@ -128,7 +128,8 @@ class EPPlan:
 def router_forward(hidden_states: torch.Tensor, router_weight: torch.Tensor, num_experts: int,
                    top_k: int, ep_group=None, capacity_factor: float = 1.0,
                    ep_plan: Optional[EPPlan] = None, router_dtype: torch.dtype = torch.float32,
-                   gather_tokens: bool = True, forced_top_idx: Optional[torch.Tensor] = None):
+                   gather_tokens: bool = True, forced_top_idx: Optional[torch.Tensor] = None,
+                   logit_bias: Optional[torch.Tensor] = None):
     """Route ``hidden_states [T, H]``.
 
     Returns ``(permuted_tokens, permuted_probs, sorted_indices, tokens_per_expert, top_indices,
@@ -140,6 +141,8 @@ def router_forward(hidden_states: torch.Tensor, router_weight: torch.Tensor, num
     with nvtx_range("router_forward"):
         T = hidden_states.shape[0]
         logits = router_ops.router_logits(hidden_states, router_weight, router_dtype)
+        if logit_bias is not None:
+            logits = logits + logit_bias.to(logits.dtype)
         top_idx, top_probs = router_ops.topk_softmax(logits, top_k, forced_top_idx)
         cap = (ep_plan.expert_capacity if ep_plan is not None
                else router_ops.expert_capacity(T, top_k, num_experts, capacity_factor))

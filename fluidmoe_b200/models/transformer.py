@@ -101,57 +101,68 @@ class TransformerLayerFunction(torch.autograd.Function):
         mode_attn = L.resolve_mode(cp.cp_size, attention=True, cp_plan=cp)
         mode_moe = L.resolve_mode(ep.ep_size)
         fused = L.fused_ctx
-        uses_fused = fused is not None and "fused" in (mode_attn, mode_moe)
+        uses_fused = fused is not None and (("fused" == mode_attn and L.has_attention) or
+                                            ("fused" == mode_moe and L.has_moe))
         if uses_fused:
             fused.layer_forward_begin(ep, needs_grad)
 
         # ---- attention half ----
-        with nvtx_range("ln1"):
-            ln1_out, mean1, rstd1 = norm.norm_fwd(x2, ln1_w, ln1_b, L.norm_eps, L.norm_type)
-        with nvtx_range("qkv_sp2hp"):
-            qkv_full = attn_mod.qkv_projection_forward(ln1_out, qkv_w, cp, mode_attn, fused)
-        if rotary is not None:
-            rope.rope_packed_(qkv_full, rotary, cp.q_per_group, cp.head_dim)
-        G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
-        with nvtx_range("attention"):
-            attn_out, lse = attn_ops.attention_fwd_packed(qkv_full, qpg, d, 1.0 / math.sqrt(d))
-        with nvtx_range("hp2sp_outproj"):
-            h1, attn_in_full = attn_mod.output_projection_forward(attn_out, proj_w, cp, mode_attn, fused,
-                                                                  residual=x2)
+        mean1 = rstd1 = ln1_out = qkv_full = attn_out = lse = attn_in_full = None
+        if L.has_attention:
+            with nvtx_range("ln1"):
+                ln1_out, mean1, rstd1 = norm.norm_fwd(x2, ln1_w, ln1_b, L.norm_eps, L.norm_type)
+            with nvtx_range("qkv_sp2hp"):
+                qkv_full = attn_mod.qkv_projection_forward(ln1_out, qkv_w, cp, mode_attn, fused)
+            if rotary is not None:
+                rope.rope_packed_(qkv_full, rotary, cp.q_per_group, cp.head_dim)
+            G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
+            with nvtx_range("attention"):
+                attn_out, lse = attn_ops.attention_fwd_packed(qkv_full, qpg, d, 1.0 / math.sqrt(d))
+            with nvtx_range("hp2sp_outproj"):
+                h1, attn_in_full = attn_mod.output_projection_forward(attn_out, proj_w, cp, mode_attn, fused,
+                                                                      residual=x2)
+        else:
+            h1 = x2
 
         # ---- MoE half ----
-        with nvtx_range("ln2"):
-            ln2_out, mean2, rstd2 = norm.norm_fwd(h1, ln2_w, ln2_b, L.norm_eps, L.norm_type)
-        if L.dropless:
-            mode_moe = "dropless"
-            logits = router_ops.router_logits(ln2_out, router_w, L.router_dtype)
-            top_idx, top_probs = router_ops.topk_softmax(logits, L.top_k, L.forced_top_idx)
-            rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
-            with nvtx_range("dropless_moe"):
-                combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, needs_grad)
-        else:
-            gather = not (mode_moe == "fused" and ep.ep_size > 1)
-            (permuted, probs, sorted_idx, _tpe, top_idx, top_probs, logits, _rmap, rplan) = \
-                moe_mod.router_forward(ln2_out, router_w, L.num_experts, L.top_k, L.ep_group,
-                                       L.capacity_factor, ep, L.router_dtype, gather_tokens=gather,
-                                       forced_top_idx=L.forced_top_idx)
-            with nvtx_range("dispatch_fc1"):
-                st = moe_mod.dispatch_fc1_forward(ep, permuted, probs, w1, act, mode_moe, save_pre=needs_grad,
-                                                  fused_ctx=fused, hidden_states=ln2_out,
-                                                  sorted_indices=sorted_idx)
-            with nvtx_range("fc2_combine"):
-                combined = moe_mod.fc2_combine_forward(ep, st, w2, mode_moe, fused)
-        residual = h1
+        mean2 = rstd2 = ln2_out = top_idx = top_probs = logits = rplan = st = None
         sh_pre = sh_act = None
-        if shared_w1 is not None:
-            sh_act, sh_pre = gemm.grouped_gemm_act(ln2_out, shared_w1.unsqueeze(0), None,
-                                                   activation=L.shared_activation, save_pre=needs_grad)
-            residual = gemm.gemm_nn(sh_act, shared_w2, out=h1.clone(), accumulate=True)
-        with nvtx_range("unpermute"):
-            if mode_moe == "fused" and ep.ep_size > 1:
-                out = fused.unpermute(ep, combined, rplan.slot_of_token, residual)
+        if not L.has_moe:
+            out = h1
+        else:
+            with nvtx_range("ln2"):
+                ln2_out, mean2, rstd2 = norm.norm_fwd(h1, ln2_w, ln2_b, L.norm_eps, L.norm_type)
+            if L.dropless:
+                mode_moe = "dropless"
+                logits = router_ops.router_logits(ln2_out, router_w, L.router_dtype)
+                if L.router_logit_bias is not None:
+                    logits = logits + L.router_logit_bias
+                top_idx, top_probs = router_ops.topk_softmax(logits, L.top_k, L.forced_top_idx)
+                rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
+                with nvtx_range("dropless_moe"):
+                    combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, needs_grad)
             else:
-                out = permute.unpermute_reduce(combined, rplan.slot_of_token, residual)
+                gather = not (mode_moe == "fused" and ep.ep_size > 1)
+                (permuted, probs, sorted_idx, _tpe, top_idx, top_probs, logits, _rmap, rplan) = \
+                    moe_mod.router_forward(ln2_out, router_w, L.num_experts, L.top_k, L.ep_group,
+                                           L.capacity_factor, ep, L.router_dtype, gather_tokens=gather,
+                                           forced_top_idx=L.forced_top_idx, logit_bias=L.router_logit_bias)
+                with nvtx_range("dispatch_fc1"):
+                    st = moe_mod.dispatch_fc1_forward(ep, permuted, probs, w1, act, mode_moe, save_pre=needs_grad,
+                                                      fused_ctx=fused, hidden_states=ln2_out,
+                                                      sorted_indices=sorted_idx)
+                with nvtx_range("fc2_combine"):
+                    combined = moe_mod.fc2_combine_forward(ep, st, w2, mode_moe, fused)
+            residual = h1
+            if shared_w1 is not None:
+                sh_act, sh_pre = gemm.grouped_gemm_act(ln2_out, shared_w1.unsqueeze(0), None,
+                                                       activation=L.shared_activation, save_pre=needs_grad)
+                residual = gemm.gemm_nn(sh_act, shared_w2, out=h1.clone(), accumulate=True)
+            with nvtx_range("unpermute"):
+                if mode_moe == "fused" and ep.ep_size > 1:
+                    out = fused.unpermute(ep, combined, rplan.slot_of_token, residual)
+                else:
+                    out = permute.unpermute_reduce(combined, rplan.slot_of_token, residual)
 
         if needs_grad:
             ctx.rt = rt
@@ -162,13 +173,13 @@ class TransformerLayerFunction(torch.autograd.Function):
             ctx.rplan = rplan
             ctx.st = st
             ctx.params = (ln1_w, ln1_b, ln2_w, ln2_b, qkv_w, proj_w, router_w, w1, w2, shared_w1, shared_w2)
-            ctx.save_for_backward(x2, mean1 if mean1 is not None else rstd1, rstd1, ln1_out, qkv_full,
-                                  attn_out, lse if lse is not None else rstd1, attn_in_full, h1,
-                                  mean2 if mean2 is not None else rstd2, rstd2, ln2_out, top_idx,
-                                  top_probs, logits,
-                                  rotary if rotary is not None else rstd1,
-                                  sh_pre if sh_pre is not None else rstd1,
-                                  sh_act if sh_act is not None else rstd1)
+            ph = x2      # placeholder for tensors a skipped half or option does not produce
+            opt = lambda t: t if t is not None else ph   # noqa: E731
+            ctx.save_for_backward(x2, opt(mean1 if mean1 is not None else rstd1), opt(rstd1), opt(ln1_out),
+                                  opt(qkv_full), opt(attn_out), opt(lse), opt(attn_in_full), h1,
+                                  opt(mean2 if mean2 is not None else rstd2), opt(rstd2), opt(ln2_out),
+                                  opt(top_idx), opt(top_probs), opt(logits), opt(rotary), opt(sh_pre), opt(sh_act))
+            ctx.has_lse = lse is not None
         return out.view(s_loc, b, H)
 
     @staticmethod
@@ -194,7 +205,9 @@ class TransformerLayerFunction(torch.autograd.Function):
         nle, cap = ep.num_local_experts, ep.expert_capacity
         cfg = L._moe_chunk_config
 
-        if mode_moe == "dropless":
+        if not L.has_moe:
+            dh1 = dy2
+        elif mode_moe == "dropless":
             # variable-split path: all-to-all-v in, grouped GEMMs over device-sized groups, all-to-all-v out
             with nvtx_range("bwd_dropless_moe"):
                 grad_combined = permute.permute_rows(dy2, rplan.sorted_indices)
@@ -279,7 +292,7 @@ class TransformerLayerFunction(torch.autograd.Function):
                 moe_mod.register_moe_dw_tasks(ep, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe", which="w1")
 
         # ---- shared experts (dense, local) ----
-        if ctx.has_shared:
+        if ctx.has_shared and L.has_moe:
             dsh_pre, _ = gemm.grouped_gemm_dact(dy2, shared_w2.unsqueeze(0), sh_pre, None,
                                                 activation=L.shared_activation)
             d_ln2 = gemm.gemm_nt(dsh_pre, shared_w1, out=d_ln2, accumulate=True)
@@ -287,11 +300,17 @@ class TransformerLayerFunction(torch.autograd.Function):
             attn_mod._register_dense_dw(f"layer{lid}.shared_w1", lid, ln2_out, dsh_pre, shared_w1, transpose_out=True)
 
         # ---- norm2 backward (+ residual gradient) ----
-        dh1, dln2_w, dln2_b = norm.norm_bwd(d_ln2, h1, ln2_w, mean2 if is_ln else None, rstd2,
-                                            L.norm_type, is_ln, residual_grad=dy2)
-        sched.register_dw_task(f"layer{lid}.ln2_w", lid, lambda: dln2_w, ln2_w)
-        if is_ln:
-            sched.register_dw_task(f"layer{lid}.ln2_b", lid, lambda: dln2_b, ln2_b)
+        if L.has_moe:
+            dh1, dln2_w, dln2_b = norm.norm_bwd(d_ln2, h1, ln2_w, mean2 if is_ln else None, rstd2,
+                                                L.norm_type, is_ln, residual_grad=dy2)
+            sched.register_dw_task(f"layer{lid}.ln2_w", lid, lambda: dln2_w, ln2_w)
+            if is_ln:
+                sched.register_dw_task(f"layer{lid}.ln2_b", lid, lambda: dln2_b, ln2_b)
+        if not L.has_attention:
+            ctx.st = ctx.rplan = None
+            if ctx.uses_fused:
+                fused.layer_backward_end(ep)
+            return (dh1.view(s_loc, b, H),) + (None,) * 13
 
         # ---- R3: out-proj dX -> SP->HP ----
         attn_mod.output_projection_register_dw(lid, attn_in_full, dh1, proj_w)
@@ -302,7 +321,7 @@ class TransformerLayerFunction(torch.autograd.Function):
         with nvtx_range("bwd_attention"):
             G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
             dqkv_hp = attn_ops.attention_bwd_packed(d_attn, qkv_full, attn_out,
-                                                    lse if lse.dim() == 3 else None, qpg, d,
+                                                    lse if ctx.has_lse else None, qpg, d,
                                                     1.0 / math.sqrt(d))
             if ctx.has_rotary:
                 rope.rope_packed_(dqkv_hp, rotary, qpg, d, backward=True)
@@ -352,8 +371,13 @@ class TransformerLayer(nn.Module):
                  router_dtype: torch.dtype = torch.bfloat16, aux_loss_coeff: float = 0.0,
                  z_loss_coeff: float = 0.0, *, norm_type: str = "layernorm", norm_eps: float = 1e-5,
                  num_shared_experts: int = 0, shared_ffn_hidden_size: Optional[int] = None,
-                 comm_mode: str = "auto", parallel_ctx=None):
+                 comm_mode: str = "auto", parallel_ctx=None, has_attention: bool = True, has_moe: bool = True):
         super().__init__()
+        assert has_attention or has_moe
+        # Either half can be switched off (its parameters stay in the state dict and receive no
+        # gradient): the block benchmarks time the MoE half and the attention half on their own.
+        self.has_attention, self.has_moe = bool(has_attention), bool(has_moe)
+        self.router_logit_bias = None   # optional fp32 [E] prior added to the router logits (set_router_bias)
         if parallel_ctx is not None:
             cp_group = cp_group if cp_group is not None else parallel_ctx.cp_group
             ep_group = ep_group if ep_group is not None else parallel_ctx.ep_group
@@ -460,6 +484,12 @@ class TransformerLayer(nn.Module):
         called with None.  Probabilities still come from this layer's logits, so gradients flow as
         usual; used to compare two precisions of the same layer under identical routing."""
         self.forced_top_idx = top_idx
+
+    def set_router_bias(self, bias: Optional[torch.Tensor]) -> None:
+        """A fixed (not trained) prior ``[num_experts]`` added to the router logits before the top-k
+        selection, e.g. a Zipf prior that makes the expert load skewed."""
+        self.router_logit_bias = None if bias is None else bias.detach().to(
+            device=self.router_weight.device, dtype=torch.float32)
 
     def attach_fused(self, fused_ctx) -> None:
         self.fused_ctx = fused_ctx

@@ -118,6 +118,12 @@ class FusedCommContext:
         self._sig: Dict[int, tuple] = {}
         self._awaiting_backward: Dict[int, bool] = {}
         self.generation = 0          # bumped whenever every buffer is released (a new input shape)
+        # exposed-communication accounting (off by default): [0] ns producers of gated GEMMs waited
+        # for rows (summed over CTAs), [1] ns the stand-alone wait kernels waited
+        self._wait_ns = torch.zeros(2, dtype=torch.int64, device=self.device)
+        self.metrics_enabled = False
+        self._push_events: list = []
+        self._gated_ctas = 0
         self.heap.mark()
 
     @staticmethod
@@ -146,6 +152,12 @@ class FusedCommContext:
         self._awaiting_backward[key] = False
         # every rank must finish allocating (and zeroing counters) before anyone pushes
         self.heap.sync_group()
+
+    def release_all(self) -> None:
+        """Give every layer's buffers back to the heap (collective).  Layers that are used again
+        allocate anew at their next forward pass."""
+        if self._layers:
+            self._release_all()
 
     def _release_all(self) -> None:
         if any(self._awaiting_backward.values()):
@@ -178,6 +190,48 @@ class FusedCommContext:
     def layer_backward_end(self, ep_plan) -> None:
         self._awaiting_backward[ep_plan._fused_layer] = False
 
+    # ------------------------------------------------------------------ exposed-communication metrics
+    def enable_comm_metrics(self, enabled: bool = True) -> None:
+        """Count, from now on, the communication time the compute stream could not hide: time the
+        producers of the gated GEMMs waited for rows, time the stand-alone wait kernels waited and
+        the run time of the push kernels (measured with events)."""
+        self.metrics_enabled = bool(enabled)
+        self.reset_comm_metrics()
+
+    def reset_comm_metrics(self) -> None:
+        self._wait_ns.zero_()
+        self._push_events.clear()
+        self._gated_launches = 0
+
+    def comm_metrics(self, num_ctas: int = 148) -> dict:
+        """Milliseconds since the last reset (synchronises the device).  ``gated_gemm_wait`` is the
+        per-CTA average of the producers' waits, an upper bound of what the tensor cores lost
+        (the shared-memory ring keeps them fed for a few blocks while a producer waits)."""
+        torch.cuda.synchronize(self.device)
+        w = self._wait_ns.tolist()
+        push = sum(s.elapsed_time(e) for s, e in self._push_events)
+        out = dict(gated_gemm_wait_ms=w[0] / 1e6 / max(1, num_ctas), wait_kernels_ms=w[1] / 1e6, push_kernels_ms=push)
+        out["exposed_comm_ms"] = out["gated_gemm_wait_ms"] + out["wait_kernels_ms"] + out["push_kernels_ms"]
+        return out
+
+    def _wait_ptr(self, slot: int) -> int:
+        return self._wait_ns.data_ptr() + 8 * slot if self.metrics_enabled else 0
+
+    class _Timed:
+        def __init__(self, ctx):
+            self.ctx = ctx
+
+        def __enter__(self):
+            if self.ctx.metrics_enabled:
+                self.s = torch.cuda.Event(enable_timing=True)
+                self.s.record()
+
+        def __exit__(self, *exc):
+            if self.ctx.metrics_enabled:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                self.ctx._push_events.append((self.s, e))
+
     def _buf(self, plan) -> _LayerBuffers:
         return self._layers[plan._fused_layer]
 
@@ -190,15 +244,16 @@ class FusedCommContext:
     def _push(self, plan, x, sorted_indices, probs, dst_tokens: SymmTensor, dst_probs: Optional[SymmTensor],
               flags: SymmTensor, bpg: int) -> None:
         _count()
-        _native.lib().permute_dispatch(
-            x.data_ptr(), sorted_indices.data_ptr(), probs.data_ptr() if probs is not None else 0,
-            dst_tokens.ptr_table, dst_probs.ptr_table if dst_probs is not None else 0, flags.ptr_table,
-            plan.num_experts * plan.expert_capacity, plan.hidden_size, plan.expert_capacity,
-            plan.num_local_experts, plan.ep_size, plan.ep_rank, bpg, 0, _native.stream_ptr())
+        with self._Timed(self):
+            _native.lib().permute_dispatch(
+                x.data_ptr(), sorted_indices.data_ptr(), probs.data_ptr() if probs is not None else 0,
+                dst_tokens.ptr_table, dst_probs.ptr_table if dst_probs is not None else 0, flags.ptr_table,
+                plan.num_experts * plan.expert_capacity, plan.hidden_size, plan.expert_capacity,
+                plan.num_local_experts, plan.ep_size, plan.ep_rank, bpg, 0, _native.stream_ptr())
 
     def _gate(self, flags: SymmTensor, bpg: int) -> dict:
         return dict(gate_flags=flags.local.data_ptr(), gate_blocks_per_group=bpg, gate_expected=1,
-                    timeout_ns=self.timeout_ns)
+                    timeout_ns=self.timeout_ns, wait_ns=self._wait_ptr(0))
 
     def _scatter_gemm(self, plan, a, w, b_layout, dst: SymmTensor, cnt_tbl: torch.Tensor,
                       row_aux: Optional[torch.Tensor] = None, row_aux_dst: Optional[SymmTensor] = None) -> None:
@@ -228,10 +283,14 @@ class FusedCommContext:
             desc.update(row_aux=row_aux.data_ptr(), row_aux_dst=row_aux_dst.ptr_table)
         lib.gemm_launch(desc, _native.stream_ptr())
 
-    def _wait_counters(self, cnt: SymmTensor, expected: int) -> None:
+    def _wait_counters(self, cnt: SymmTensor, expected: int, expected_dev: Optional[torch.Tensor] = None) -> None:
+        """Stand-alone wait for per-source arrival counters: ``expected`` for every source, or the
+        per-source values of ``expected_dev`` (int32 on the device)."""
         _count()
-        _native.lib().a2a_wait(cnt.local.data_ptr(), self.rank, self.world, expected, self.timeout_ns,
-                               status_buffer(self.device).data_ptr(), _native.stream_ptr())
+        _native.lib().a2a_wait_counts(cnt.local.data_ptr(), self.world, expected,
+                                      expected_dev.data_ptr() if expected_dev is not None else 0,
+                                      self._wait_ptr(1), self.timeout_ns,
+                                      status_buffer(self.device).data_ptr(), _native.stream_ptr())
 
     @staticmethod
     def _n_tiles(n: int) -> int:
@@ -333,13 +392,14 @@ class FusedCommContext:
     def _rows_push(self, src2d, P, dst: SymmTensor, flags: SymmTensor, row_blocks):
         _count()
         rows_blk = src2d.shape[0] // P
-        _native.lib().rows_push(src2d.data_ptr(), dst.ptr_table, flags.ptr_table, rows_blk, src2d.shape[1],
-                                P, self.rank, row_blocks, 0, _native.stream_ptr())
+        with self._Timed(self):
+            _native.lib().rows_push(src2d.data_ptr(), dst.ptr_table, flags.ptr_table, rows_blk, src2d.shape[1],
+                                    P, self.rank, row_blocks, 0, _native.stream_ptr())
 
     def _ksource_gate(self, flags: SymmTensor, cols_per_src: int, row_blocks: int) -> dict:
         return dict(gate_flags=flags.local.data_ptr(), gate_k_blocks_per_src=cols_per_src // 64,
                     gate_blocks_per_group=row_blocks, k_rotate=self.rank * (cols_per_src // 64),
-                    timeout_ns=self.timeout_ns)
+                    timeout_ns=self.timeout_ns, wait_ns=self._wait_ptr(0))
 
     def qkv_sp2hp(self, x, qkv_weight, plan):
         """QKV projection whose epilogue performs the SP->HP exchange (fluid/attention/forward.py:130-277)."""

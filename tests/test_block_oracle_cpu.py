@@ -169,3 +169,50 @@ def test_anchor_configuration_world2_against_oracle():
         for n, g in grads.items():
             ref = go[n][r * nle:(r + 1) * nle] if n in ("moe_w1", "moe_w2") else go[n]
             _close(g * world, ref, f"{n} rank {r}", tol=5e-4)
+
+
+@pytest.mark.parametrize("half", ["attention", "moe"])
+def test_single_half_layer_matches_full_layer_with_the_other_half_silenced(half):
+    """``has_moe=False`` / ``has_attention=False`` must equal the full block whose other half
+    contributes nothing (its output weights set to zero), in output, ``dx`` and the gradients of
+    the active half; with a router logit prior on."""
+    from fluidmoe_b200.models.transformer import TransformerLayer
+    from fluidmoe_b200.ops.rope import make_rope_freqs
+    from fluidmoe_b200.parallel.scheduler import BackwardScheduler, get_backward_scheduler
+    BackwardScheduler.reset()
+    get_backward_scheduler().disable()
+    D = DIMS
+    kw = _layer_kwargs("rmsnorm", "swiglu", 1, False, 1.0)
+    full = _build_full("rmsnorm", "swiglu", 1, False, 1.0)
+    torch.manual_seed(1)
+    part = TransformerLayer(D["H"], D["nh"], D["nkv"], D["F"], D["E"], D["k"], None, None,
+                            has_attention=half == "attention", has_moe=half == "moe", **kw)
+    part.load_state_dict(full.state_dict())
+    bias = torch.log(1.0 / torch.arange(1, D["E"] + 1, dtype=torch.float32) ** 1.1)
+    full.set_router_bias(bias)
+    part.set_router_bias(bias)
+    with torch.no_grad():
+        if half == "attention":
+            full.moe_w2.zero_()
+            full.shared_w2.zero_()
+        else:
+            full.proj_weight.zero_()
+    x_full, g_full = _inputs(1)
+    rot = make_rope_freqs(D["s_loc"], D["H"] // D["nh"])
+    outs = []
+    for layer in (full, part):
+        x = x_full.clone().requires_grad_(True)
+        y = layer(x, rot)
+        y.backward(g_full)
+        outs.append((y.detach(), x.grad, {n: p.grad for n, p in layer.named_parameters()}))
+    (yf, dxf, gf), (yp, dxp, gp) = outs
+    _close(yp, yf, "y", 1e-5)
+    _close(dxp, dxf, "dx", 1e-5)
+    active = (("ln1_weight", "qkv_weight", "proj_weight") if half == "attention" else
+              ("ln2_weight", "router_weight", "moe_w1", "moe_w2", "shared_w1", "shared_w2"))
+    for n in active:
+        _close(gp[n], gf[n], n, 1e-5)
+    idle = ("ln2_weight", "router_weight", "moe_w1") if half == "attention" else ("ln1_weight", "qkv_weight")
+    for n in idle:
+        assert gp[n] is None or float(gp[n].abs().max()) == 0.0, n
+    BackwardScheduler.reset()

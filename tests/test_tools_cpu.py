@@ -273,3 +273,25 @@ def test_external_baselines_build_with_stub_packages(monkeypatch):
     assert len(model) == small["num_layers"]
     assert seen["moe"] == dict(hidden=small["hidden_size"], num_experts=small["num_experts"], ep_size=1,
                                k=small["top_k"], capacity_factor=1.0, ffn=small["ffn_hidden"])
+
+
+def test_block_benchmark_runs_several_presets_and_halves(capsys, monkeypatch):
+    """Several presets in one run: a MoE-only layer with a Zipf router prior and dropless routing,
+    an attention-only block with RoPE, and the reference-expressible variant of a SwiGLU preset."""
+    from fluidmoe_b200.parallel.scheduler import BackwardScheduler
+    from fluidmoe_b200.tools import model_configs, run_block_benchmark
+    tiny = dict(hidden_size=128, num_heads=4, num_kv_heads=2, ffn_hidden=96, num_experts=8, top_k=2, num_layers=1,
+                seq_len=64, seq_per_rank=64, batch_size=1, activation="swiglu", norm_type="rmsnorm")
+    monkeypatch.setitem(model_configs.MODEL_CONFIGS, "t_moe", dict(tiny, capacity_factor=0.0, num_shared_experts=1,
+                                                                   has_attention=False, zipf_s=1.1))
+    monkeypatch.setitem(model_configs.MODEL_CONFIGS, "t_attn", dict(tiny, capacity_factor=1.0, has_moe=False, rope=True))
+    BackwardScheduler.reset()
+    run_block_benchmark.main(["--model", "t_moe,t_attn", "--impl", "fluidmoe-full", "--warmup", "1", "--iters", "1"])
+    out = capsys.readouterr().out
+    assert out.count("RESULT impl=fluidmoe-full") == 2 and "model=t_moe" in out and "model=t_attn" in out
+    run_block_benchmark.main(["--model", "t_moe", "--impl", "fluidmoe-fb", "--matched", "--warmup", "1", "--iters", "1"])
+    assert "RESULT impl=fluidmoe-fb-matched model=t_moe" in capsys.readouterr().out
+    ref = model_configs.reference_variant(model_configs.get_model_config("t_moe"))
+    assert ref["activation"] == "gelu" and ref["ffn_hidden"] == 144 and ref["capacity_factor"] == 1.0
+    assert ref["num_shared_experts"] == 0 and ref["has_attention"] and ref["norm_type"] == "layernorm"
+    BackwardScheduler.reset()

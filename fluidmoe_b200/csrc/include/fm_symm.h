@@ -54,6 +54,39 @@ int fm_a2a_wait_counts(const int* my_flags, int nranks, int epoch, const int* ex
                        unsigned long long* wait_ns, unsigned long long timeout_ns, int* status,
                        cudaStream_t stream);
 
+// ---- dropless (variable-split) expert exchange: see symm/dropless_kernels.cu ----
+// Device arrays the plan kernel fills (all int32, owned by the caller).
+typedef struct {
+  int* counts_all;       // [P * E]   pairs rank r routes to global expert e
+  int* group_rows;       // [nle]     rows of every local expert (all sources)
+  int* group_offs;       // [nle]     first row of every local expert (multiple of 128)
+  int* group_flag_base;  // [nle]     group_offs / 128: first arrival counter of the expert
+  int* dst_base;         // [E]       row in the owner's buffer where this rank's run for expert e starts
+  int* slot_start;       // [E + 1]   first slot of expert e in this rank's permuted order
+  int* before;           // [P * nle] rows of local expert j that come from ranks < r
+  int* src_prefix;       // [P * E]   slot_start of every rank
+  int* recv_expected;    // [P]       rows coming back from rank p, times `expected_mult`
+  int* totals;           // [2]       rows of the local expert-major buffer in use; 1 if the plan was refused
+} FmDroplessPlan;
+// Exchange the per-expert counts with every peer (peer stores + flag, bounded wait) and derive the
+// plan; then fill, for every local expert-major row, the rank and permuted-order row it returns to
+// (-1 for padding rows).  `table_ptrs[p]`: rank p's int[2][P][E]; `flag_ptrs[p]`: rank p's int[P];
+// `epoch` must grow by one per call.  A plan needing more than `max_rows` rows on any rank is
+// refused by all ranks alike: nothing is sent and a status record is written.
+int fm_dropless_plan(const int* counts, int* const* table_ptrs, int* const* flag_ptrs, int epoch, int P,
+                     int me, int E, int nle, int expected_mult, int max_rows, const FmDroplessPlan* out,
+                     int* row_dst_rank, int* row_dst_row, unsigned long long timeout_ns, int* status,
+                     cudaStream_t stream);
+// Gather the routed rows and store them into their owners' buffers, one arrival per row on the
+// counter of the row's 128-row block; probs may be null.
+int fm_dropless_dispatch(const void* x, const long long* sorted_idx, const float* probs,
+                         const FmDroplessPlan* pl, void* const* dst_tokens, float* const* dst_probs,
+                         int* const* dst_flags, long long total_slots, int H, int E, int nle, int P, int me,
+                         int num_ctas, cudaStream_t stream);
+// Zero the rows that pad every group to a whole 128-row block.
+int fm_zero_group_padding(void* buf, long long row_bytes, const int* group_rows, const int* group_offs,
+                          int num_groups, cudaStream_t stream);
+
 // Two-shot all-reduce (sum) over peer memory: every rank's `buf_ptrs[p]` points at its copy of
 // the same symmetric buffer of `count` elements (fp32 or bf16, in place).  Rank r reduces
 // chunk r by reading all peers, scales by `scale`, and writes the result to every peer.

@@ -4,6 +4,7 @@
 
 #include <stdexcept>
 #include <string>
+#include <vector>
 
 #include "include/fm_api.h"
 #include "include/fm_symm.h"
@@ -18,7 +19,49 @@ static P as_ptr(uintptr_t v) {
   return reinterpret_cast<P>(v);
 }
 
+static FmDroplessPlan plan_from(const std::vector<uintptr_t>& v) {
+  if (v.size() != 10) throw std::runtime_error("dropless plan needs 10 device pointers");
+  FmDroplessPlan p;
+  p.counts_all = as_ptr<int*>(v[0]);
+  p.group_rows = as_ptr<int*>(v[1]);
+  p.group_offs = as_ptr<int*>(v[2]);
+  p.group_flag_base = as_ptr<int*>(v[3]);
+  p.dst_base = as_ptr<int*>(v[4]);
+  p.slot_start = as_ptr<int*>(v[5]);
+  p.before = as_ptr<int*>(v[6]);
+  p.src_prefix = as_ptr<int*>(v[7]);
+  p.recv_expected = as_ptr<int*>(v[8]);
+  p.totals = as_ptr<int*>(v[9]);
+  return p;
+}
+
 void bind_symm(py::module_& m) {
+  m.def("dropless_plan", [](uintptr_t counts, uintptr_t table_ptrs, uintptr_t flag_ptrs, int epoch, int P, int me,
+                            int E, int nle, int mult, int max_rows, const std::vector<uintptr_t>& plan,
+                            uintptr_t row_rank, uintptr_t row_row, unsigned long long timeout_ns, uintptr_t status,
+                            uintptr_t stream) {
+    FmDroplessPlan pl = plan_from(plan);
+    chk(fm_dropless_plan(as_ptr<const int*>(counts), as_ptr<int* const*>(table_ptrs), as_ptr<int* const*>(flag_ptrs),
+                         epoch, P, me, E, nle, mult, max_rows, &pl, as_ptr<int*>(row_rank), as_ptr<int*>(row_row),
+                         timeout_ns, as_ptr<int*>(status), as_ptr<cudaStream_t>(stream)),
+        "dropless_plan");
+  });
+  m.def("dropless_dispatch", [](uintptr_t x, uintptr_t sorted_idx, uintptr_t probs, const std::vector<uintptr_t>& plan,
+                                uintptr_t dst_tokens, uintptr_t dst_probs, uintptr_t dst_flags, long long total_slots,
+                                int H, int E, int nle, int P, int me, int ctas, uintptr_t stream) {
+    FmDroplessPlan pl = plan_from(plan);
+    chk(fm_dropless_dispatch(as_ptr<const void*>(x), as_ptr<const long long*>(sorted_idx), as_ptr<const float*>(probs),
+                             &pl, as_ptr<void* const*>(dst_tokens), as_ptr<float* const*>(dst_probs),
+                             as_ptr<int* const*>(dst_flags), total_slots, H, E, nle, P, me, ctas,
+                             as_ptr<cudaStream_t>(stream)),
+        "dropless_dispatch");
+  });
+  m.def("zero_group_padding", [](uintptr_t buf, long long row_bytes, uintptr_t rows, uintptr_t offs, int n,
+                                 uintptr_t stream) {
+    chk(fm_zero_group_padding(as_ptr<void*>(buf), row_bytes, as_ptr<const int*>(rows), as_ptr<const int*>(offs), n,
+                              as_ptr<cudaStream_t>(stream)),
+        "zero_group_padding");
+  });
   m.def("symm_alloc", [](size_t bytes) {
     void* p = nullptr;
     unsigned char h[FM_IPC_HANDLE_BYTES];

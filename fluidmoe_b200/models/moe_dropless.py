@@ -130,8 +130,12 @@ def backward(plan: DroplessPlan, grad_combined: torch.Tensor, state, w1: torch.T
     return dfc2, dpre, dprobs, from_experts(plan, dtok, ep_group)
 
 
-def register_dw_tasks(plan: DroplessPlan, state, dfc2_em, dpre_em, w1_param, w2_param, layer_id: int,
-                      layer_name: str) -> None:
+def register_dw_tasks(plan, state, dfc2_em, dpre_em, w1_param, w2_param, layer_id: int,
+                      layer_name: str, which: str = "both") -> None:
+    """Queue the expert weight gradients over device-sized row groups (``plan.group_rows`` /
+    ``plan.group_offs``).  ``which``: ``both``, ``w1`` or ``w2`` (the task of ``w1`` may only be
+    queued after the FC1 input-gradient GEMM when its optimizer runs in the weight-gradient
+    epilogue, because that epilogue overwrites ``w1``)."""
     from ..parallel.scheduler import get_backward_scheduler
     sched = get_backward_scheduler()
     nle = plan.group_rows.numel()
@@ -158,5 +162,7 @@ def register_dw_tasks(plan: DroplessPlan, state, dfc2_em, dpre_em, w1_param, w2_
             return gemm.grouped_gemm_wgrad(a, dy, nle, group_rows=plan.group_rows, group_offs=plan.group_offs,
                                            alpha=alpha)
         return run
-    sched.register_dw_task(f"{layer_name}.w2", layer_id, make(state.act_em, dfc2_em, w2_param), w2_param)
-    sched.register_dw_task(f"{layer_name}.w1", layer_id, make(state.tokens_em, dpre_em, w1_param), w1_param)
+    if which in ("both", "w2"):
+        sched.register_dw_task(f"{layer_name}.w2", layer_id, make(state.act_em, dfc2_em, w2_param), w2_param)
+    if which in ("both", "w1"):
+        sched.register_dw_task(f"{layer_name}.w1", layer_id, make(state.tokens_em, dpre_em, w1_param), w1_param)

@@ -102,7 +102,7 @@ class TransformerLayerFunction(torch.autograd.Function):
         mode_moe = L.resolve_mode(ep.ep_size)
         fused = L.fused_ctx
         uses_fused = fused is not None and (("fused" == mode_attn and L.has_attention) or
-                                            ("fused" == mode_moe and L.has_moe))
+                                            ("fused" == mode_moe and L.has_moe and ep.ep_size > 1))
         if uses_fused:
             fused.layer_forward_begin(ep, needs_grad)
 
@@ -133,14 +133,22 @@ class TransformerLayerFunction(torch.autograd.Function):
             with nvtx_range("ln2"):
                 ln2_out, mean2, rstd2 = norm.norm_fwd(h1, ln2_w, ln2_b, L.norm_eps, L.norm_type)
             if L.dropless:
-                mode_moe = "dropless"
+                fused_dropless = mode_moe == "fused" and ep.ep_size > 1
+                mode_moe = "dropless_fused" if fused_dropless else "dropless"
                 logits = router_ops.router_logits(ln2_out, router_w, L.router_dtype)
                 if L.router_logit_bias is not None:
                     logits = logits + L.router_logit_bias
                 top_idx, top_probs = router_ops.topk_softmax(logits, L.top_k, L.forced_top_idx)
-                rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
                 with nvtx_range("dropless_moe"):
-                    combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, needs_grad)
+                    if fused_dropless:
+                        # device-initiated: counts exchanged by peer stores, no host read anywhere
+                        from ..parallel.fused_dropless import build_device_plan
+                        rplan = build_device_plan(top_idx, top_probs, L.num_experts)
+                        combined, st = fused.dropless.forward(fused._buf(ep), ep, rplan, ln2_out, w1, w2, act,
+                                                              needs_grad)
+                    else:
+                        rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
+                        combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, needs_grad)
             else:
                 gather = not (mode_moe == "fused" and ep.ep_size > 1)
                 (permuted, probs, sorted_idx, _tpe, top_idx, top_probs, logits, _rmap, rplan) = \
@@ -159,7 +167,9 @@ class TransformerLayerFunction(torch.autograd.Function):
                                                        activation=L.shared_activation, save_pre=needs_grad)
                 residual = gemm.gemm_nn(sh_act, shared_w2, out=h1.clone(), accumulate=True)
             with nvtx_range("unpermute"):
-                if mode_moe == "fused" and ep.ep_size > 1:
+                if mode_moe == "dropless_fused":
+                    out = fused.dropless.unpermute(fused._buf(ep), rplan, combined, residual, "combined")
+                elif mode_moe == "fused" and ep.ep_size > 1:
                     out = fused.unpermute(ep, combined, rplan.slot_of_token, residual)
                 else:
                     out = permute.unpermute_reduce(combined, rplan.slot_of_token, residual)
@@ -207,6 +217,43 @@ class TransformerLayerFunction(torch.autograd.Function):
 
         if not L.has_moe:
             dh1 = dy2
+        elif mode_moe == "dropless_fused":
+            # variable-split path on the device-initiated transport: same regions as the padded
+            # path, row ranges and arrival thresholds come from the device-side plan
+            dl, db = fused.dropless, fused._buf(ep)
+            with nvtx_range("bwd_moe_combine"):
+                sched.begin_region("moe_combine")
+                try:
+                    dfc2_em, dpre_em, dprobs_em = dl.combine_fc2_backward(db, ep, rplan, dy2, st, w2, act)
+                finally:
+                    sched.end_region()
+            w1_late = getattr(w1, "_fused_adam", None) is not None
+            if not w1_late:
+                moe_dropless.register_dw_tasks(rplan, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe")
+            else:
+                moe_dropless.register_dw_tasks(rplan, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe", which="w2")
+            with nvtx_range("bwd_moe_dispatch"):
+                sched.begin_region("moe_dispatch")
+                try:
+                    dperm = dl.fc1_dispatch_backward(db, ep, dpre_em, w1, dprobs_em)
+                finally:
+                    sched.end_region()
+                dl.wait_rows(db, "dperm")
+                tpe_global = None
+                if L.aux_loss_coeff > 0.0:
+                    tpe_global = rplan.routed_per_expert.float()
+                    if cp.cp_size > 1:
+                        dist.all_reduce(tpe_global, group=cp.group)
+                dlogits = router_ops.router_backward_logits(
+                    db.dprobs_perm.local, rplan, top_idx, top_probs, logits, L.num_experts, L.aux_loss_coeff,
+                    L.z_loss_coeff, tpe_global, T * cp.cp_size)
+                d_ln2_router = (dlogits.to(router_w.dtype) @ router_w.detach().t()).to(dy2.dtype)
+                ln2_for_dw = ln2_out
+                sched.register_dw_task(f"layer{lid}.router", lid,
+                                       lambda: (ln2_for_dw.float().t() @ dlogits).to(torch.float32), router_w)
+                d_ln2 = dl.unpermute(db, rplan, dperm, d_ln2_router, "dperm", waited=True)
+            if w1_late:
+                moe_dropless.register_dw_tasks(rplan, st, dfc2_em, dpre_em, w1, w2, lid, f"layer{lid}.moe", which="w1")
         elif mode_moe == "dropless":
             # variable-split path: all-to-all-v in, grouped GEMMs over device-sized groups, all-to-all-v out
             with nvtx_range("bwd_dropless_moe"):

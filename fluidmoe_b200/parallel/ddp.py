@@ -129,6 +129,12 @@ class FluidDDP(nn.Module):
         if self._grad_buffer is not None:
             self._grad_buffer.zero_()
 
+    def no_sync(self):
+        """Context for every micro-batch but the last of an accumulated step: gradients add up in
+        the flat buffers and nothing is reduced (see ``BackwardScheduler.no_sync``).  Call
+        ``finish_grad_sync`` once, after the last micro-batch."""
+        return self.scheduler.no_sync()
+
     def finish_grad_sync(self) -> None:
         self.scheduler.finish_batch()
         fused = getattr(self, "fused_ctx", None)

@@ -118,6 +118,8 @@ class FusedCommContext:
         self._sig: Dict[int, tuple] = {}
         self._awaiting_backward: Dict[int, bool] = {}
         self.generation = 0          # bumped whenever every buffer is released (a new input shape)
+        from .fused_dropless import DroplessExchange
+        self.dropless = DroplessExchange(self)
         # exposed-communication accounting (off by default): [0] ns producers of gated GEMMs waited
         # for rows (summed over CTAs), [1] ns the stand-alone wait kernels waited
         self._wait_ns = torch.zeros(2, dtype=torch.int64, device=self.device)
@@ -144,7 +146,12 @@ class FusedCommContext:
         if key in self._layers:
             self._release_all()
         self._sig[key] = sig
-        self._layers[key] = _LayerBuffers(self.heap, ep_plan, ep_plan.dtype, layer.ffn_hidden_size)
+        if getattr(layer, "dropless", False):
+            # variable-split routing: worst-case sized receive buffers and the device-side plan
+            from .fused_dropless import _DroplessBuffers
+            self._layers[key] = _DroplessBuffers(self.heap, ep_plan, ep_plan.dtype, self.dropless.buffer_factor)
+        else:
+            self._layers[key] = _LayerBuffers(self.heap, ep_plan, ep_plan.dtype, layer.ffn_hidden_size)
         ep_plan._fused_layer = key
         if cp_plan is not None and cp_plan.cp_size > 1 and self.attention_supported(cp_plan):
             self._attn[key] = _AttnBuffers(self.heap, cp_plan, cp_plan.dtype)

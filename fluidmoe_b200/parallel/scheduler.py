@@ -19,6 +19,7 @@ On CPU tensors streams and events degrade to no-ops and the same code runs synch
 from __future__ import annotations
 
 import collections
+import contextlib
 import os
 from dataclasses import dataclass, field
 from typing import Callable, Deque, Dict, List, Optional
@@ -231,6 +232,8 @@ class BackwardScheduler:
         # exchanges never occupy the communication stream.
         self.eager_ar = False
         self.eager_ar_min_bytes = 32 << 20
+        # Inside ``no_sync()``: gradients accumulate in the flat buffers, nothing is reduced.
+        self.ar_suspended = False
         self.profiling = False
         self.comm_metrics_enabled = False
         # all-reduce configuration
@@ -460,7 +463,7 @@ class BackwardScheduler:
 
     def _submit_ar_inline(self, budgeted: bool = True) -> int:
         """Reduce committed gradients on the communication stream (behind the dW that made them)."""
-        if not self.ar_enabled:
+        if not self.ar_enabled or self.ar_suspended:
             return 0
         sb, eb = self.shared_buffer, self.expert_buffer
         if not (sb.has_pending() or eb.has_pending() or self._pending_param_ar):
@@ -656,6 +659,29 @@ class BackwardScheduler:
         finally:
             self._in_finish = False
             self._current_region = prev_region
+
+    @contextlib.contextmanager
+    def no_sync(self):
+        """Gradient accumulation: run every micro-batch but the last inside this context.
+
+        A slice of the flat buffer is reduced once, as soon as its gradients are committed; a
+        micro-batch that adds to it afterwards would be left out of the reduction.  Inside the
+        context nothing is reduced.  On exit the weight-gradient queue is drained (so that no task
+        of an earlier micro-batch can mark a parameter as produced during the last one) and the
+        cursors start over: the last micro-batch then commits and reduces every parameter after its
+        final accumulation.  The reference reduces during every backward pass and has no
+        accumulation mode (fluid/core/scheduler.py:188-213)."""
+        prev = self.ar_suspended
+        self.ar_suspended = True
+        try:
+            yield self
+        finally:
+            self.ar_suspended = prev
+            if self.enabled and not prev:
+                if self._dw_queue:
+                    self.execute_dw_tasks()
+                self.shared_buffer.reset_cursors()
+                self.expert_buffer.reset_cursors()
 
     def clear_iteration(self) -> None:
         """Wait for anything outstanding and reset per-iteration state."""

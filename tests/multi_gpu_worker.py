@@ -232,7 +232,11 @@ def main():
         for mb in range(2):
             xm = torch.randn(s_loc, b, H, device=dev).bfloat16().requires_grad_(True)
             gm = torch.randn(s_loc, b, H, device=dev).bfloat16()
-            lay(xm, rot).backward(gm)
+            if mb == 0:
+                with sc.no_sync():          # nothing is reduced before the last micro-batch
+                    lay(xm, rot).backward(gm)
+            else:
+                lay(xm, rot).backward(gm)
         sc.finish_batch()
         if fused_mode:
             pc.fused_ctx.iteration_barrier()
@@ -268,6 +272,52 @@ def main():
     gemm.check_status()
     assert pc.fused_ctx.generation == gen0 + 1
     assert fro(y2f.float(), y2a.float()) < 2e-2 and fro(x2.grad.float(), g2a) < 3e-2
+
+    # ---- 9b. dropless (variable-split) routing on the device-initiated transport ----
+    # MoE half only, so that both transports see bit-identical router inputs and route alike;
+    # skewed expert load (Zipf prior), shared experts, top-4 of 16.
+    from fluidmoe_b200.tools.common import zipf_logit_prior
+    E2, k2 = 16, 4
+
+    def make_dropless(mode):
+        torch.manual_seed(9)
+        lay = TransformerLayer(H, nh, nkv, 512, E2, k2, pc.cp_group, pc.ep_group, comm_mode=mode,
+                               parallel_ctx=pc if mode == "fused" else None, capacity_factor=0.0,
+                               num_shared_experts=2, has_attention=False, **kw)
+        with torch.no_grad():
+            g_ = torch.Generator(device=dev).manual_seed(2000 + rank)
+            lay.moe_w1.copy_((torch.randn(lay.moe_w1.shape, device=dev, generator=g_) * 0.05).bfloat16())
+            lay.moe_w2.copy_((torch.randn(lay.moe_w2.shape, device=dev, generator=g_) * 0.05).bfloat16())
+        lay.set_router_bias(zipf_logit_prior(E2, 1.1, dev))
+        return lay
+    sched.disable()
+    lda2, ldf2 = make_dropless("a2a"), make_dropless("fused")
+    yda = run_once(lda2, x, gy, None)
+    gda = {n_: p_.grad.float().clone() for n_, p_ in lda2.named_parameters() if p_.grad is not None}
+    gxda = x.grad.float().clone()
+    for it in range(3):
+        if it == 2:      # a steady-state step must not synchronise with the host anywhere
+            torch.cuda.synchronize()
+            dist.barrier()
+            torch.cuda.set_sync_debug_mode("error")
+        try:
+            ydf = run_once(ldf2, x, gy, None)
+            pc.fused_ctx.iteration_barrier()
+        finally:
+            torch.cuda.set_sync_debug_mode("default")
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert fro(ydf.float(), yda.float()) < 2e-2, ("dropless y", fro(ydf.float(), yda.float()))
+    assert fro(x.grad.float(), gxda) < 3e-2, ("dropless dx", fro(x.grad.float(), gxda))
+    for n_, p_ in ldf2.named_parameters():
+        if n_ in gda:
+            assert fro(p_.grad.float(), gda[n_]) < 3e-2, ("dropless", n_, fro(p_.grad.float(), gda[n_]))
+    with torch.no_grad():          # inference passes back to back
+        for it in range(3):
+            y_inf = ldf2(x, None)
+        torch.cuda.synchronize()
+        gemm.check_status()
+        assert fro(y_inf.float(), yda.float()) < 2e-2
 
     # ---- 10. pairwise put + flag back-end: bit-exact pattern over a whole tournament ----
     from fluidmoe_b200.parallel.p2p_backend import SymmetricP2PBackend

@@ -172,3 +172,58 @@ def test_dropless_matches_padded_without_drops_world2():
         for n in gb:
             scale = gb[n].abs().max().item() + 1e-6
             assert (g[n] - gb[n]).abs().max().item() / scale < 1e-4, n
+
+
+def _accumulate(rank, world, use_scheduler):
+    """Two micro-batches accumulated into one gradient: with the scheduler (full mode, trickled
+    all-reduce) the first runs inside ``no_sync()``; without it gradients add up in ``param.grad``
+    and are reduced once at the end."""
+    from fluidmoe_b200.distributed import init_parallel
+    from fluidmoe_b200.models.transformer import TransformerLayer
+    from fluidmoe_b200.ops.rope import make_rope_freqs
+    from fluidmoe_b200.parallel.scheduler import get_backward_scheduler
+
+    H, nh, nkv, F, E, k, s_loc, b = 64, 4, 2, 96, 4, 2, 16, 2
+    pc = init_parallel()
+    torch.manual_seed(1)
+    layer = TransformerLayer(H, nh, nkv, F, E, k, pc.cp_group, pc.ep_group, comm_mode="p2p", moe_combine_chunks=2,
+                             moe_dispatch_chunks=2, attn_proj_chunks=2, attn_qkv_chunks=2, dtype=torch.float32,
+                             device="cpu", router_dtype=torch.float32, norm_type="rmsnorm", init_std=0.2)
+    rot = make_rope_freqs(world * s_loc, H // nh)
+    sched = get_backward_scheduler()
+    sched.configure_allreduce(use_scheduler, pc.dp_cp_group, pc.expert_dp_group,
+                              gap_budgets={r: 1.0 for r in ("moe_combine", "moe_dispatch", "attn_proj", "attn_qkv")},
+                              shared_ar_bw=1e6, expert_ar_bw=1e6)
+    if use_scheduler:
+        sched.enable(torch.device("cpu"))
+        expert = [layer.moe_w2, layer.moe_w1]
+        sched.setup_ar_buffer([p for p in layer.parameters() if all(p is not e for e in expert)], True)
+        sched.setup_expert_ar_buffer(expert, True)
+    else:
+        sched.disable()
+    torch.manual_seed(20 + rank)
+    batches = [(torch.randn(s_loc, b, H), torch.randn(s_loc, b, H)) for _ in range(2)]
+    for i, (x, g) in enumerate(batches):
+        x = x.requires_grad_(True)
+        if use_scheduler and i == 0:
+            with sched.no_sync():
+                layer(x, rot).backward(g)
+        else:
+            layer(x, rot).backward(g)
+    if use_scheduler:
+        sched.finish_batch()
+        grads = {n: p.main_grad.clone() for n, p in layer.named_parameters()}
+    else:
+        sched.sync_allreduce_params(list(layer.parameters()))
+        grads = {n: p.grad.clone() for n, p in layer.named_parameters()}
+    sched.clear_iteration()
+    return grads
+
+
+def test_gradient_accumulation_with_no_sync_world2():
+    base = run_distributed(_accumulate, 2, False)
+    got = run_distributed(_accumulate, 2, True)
+    for r in range(2):
+        for n in base[r]:
+            scale = base[r][n].abs().max().item() + 1e-9
+            assert (got[r][n] - base[r][n]).abs().max().item() / scale < 1e-4, (n, r)

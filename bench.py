@@ -59,6 +59,9 @@ def parse_args():
                          "both arms run the identical model")
     ap.add_argument("--forward-only", action="store_true",
                     help="time the forward pass alone (inference latency): no backward, no optimizer")
+    ap.add_argument("--grad-reduce", default="", choices=["", "nccl", "symm"],
+                    help="dense-gradient all-reduce: library (nccl) or this repository's two-shot kernel over peer "
+                         "memory (symm); default: FLUIDMOE_GRAD_REDUCE or nccl")
     ap.add_argument("--loss-trace", action="store_true", help="add the loss of every timed end-to-end step to the JSON line")
     return ap.parse_args()
 
@@ -177,6 +180,8 @@ def run_ours(args):
         m.update(hidden=512, heads=8, kv_heads=8, ffn=1024, vocab=2048)
         args.seq = min(args.seq, 512)
     heap = (6 << 30) if (world > 1 and args.comm in ("auto", "fused")) else 0
+    if heap and (args.grad_reduce or os.environ.get("FLUIDMOE_GRAD_REDUCE", "")) == "symm":
+        heap += 2 << 30        # the dense flat gradient buffer moves into the symmetric heap
     pc = init_parallel(ep_size=world, device=device, symmetric_heap_bytes=heap)
     torch.manual_seed(1234)
     matched = args.arch == "matched"
@@ -196,7 +201,7 @@ def run_ours(args):
     ddp = FluidDDP(None, model, sched, dp_cp_group=pc.dp_cp_group, expert_dp_group=pc.expert_dp_group,
                    ar_enabled=args.mode == "full",
                    gap_budgets={"moe_combine": 0.5, "moe_dispatch": 0.5, "attn_proj": 0.3, "attn_qkv": 0.3},
-                   shared_ar_bw=3.0e8, expert_ar_bw=3.0e8)
+                   shared_ar_bw=3.0e8, expert_ar_bw=3.0e8, grad_reduce=args.grad_reduce or None)
     opt = FluidOptimizerWrapper(
         FusedAdam(model.parameters(), lr=1e-4, weight_decay=0.0,
                   state_dtype=torch.bfloat16 if args.opt_state == "bf16" else torch.float32), sched)
@@ -265,6 +270,7 @@ def run_ours(args):
                    "global_batch": batch, "seq_len": seq * world, "seq_per_rank": seq,
                    "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
                    "comm": args.comm, "adam_moments": args.opt_state, "grad_accum": "fp32",
+                   "grad_reduce": ddp.grad_reduce_mode,
                    "optimizer": ("AdamW every step inside the timed region; expert weights (%d tensors) updated in their "
                                  "weight-gradient GEMM %s, all other parameters by the fused Adam kernel in step()"
                                  % (fused_params, "epilogue" if args.fuse_optimizer != 2 else "stream")) if fused_params

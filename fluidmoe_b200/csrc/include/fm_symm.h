@@ -94,6 +94,12 @@ int fm_allreduce_p2p(void* const* buf_ptrs_dev, long long count, int dtype_fp32,
                      int* const* flag_ptrs_dev, int my_rank, int nranks, int epoch, int num_ctas,
                      unsigned long long timeout_ns, int* status, cudaStream_t stream);
 
+// Same on the slice [elem_offset, elem_offset + count) of the buffers (the slice must start on a
+// 16-byte boundary): what a scheduler that reduces a flat gradient buffer piece by piece calls.
+int fm_allreduce_p2p_slice(void* const* buf_ptrs_dev, long long elem_offset, long long count, int dtype_fp32,
+                           float scale, int* const* flag_ptrs_dev, int my_rank, int nranks, int epoch,
+                           int num_ctas, unsigned long long timeout_ns, int* status, cudaStream_t stream);
+
 // In-switch (NVLS) sum all-reduce of `count` fp32 elements in place.  `multicast_ptr` is the
 // multicast address of a buffer that every rank bound to the same NVLink multicast object (the
 // caller obtains it from a VMM-based symmetric allocator); the flags live in this library's own

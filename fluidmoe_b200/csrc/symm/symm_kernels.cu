@@ -299,10 +299,15 @@ __device__ __forceinline__ bool grid_peer_barrier(int* const* flag_ptrs, int my_
 }
 
 template <class T>
-__global__ void allreduce_p2p_kernel(T* const* bufs, long long count, float scale,
+__global__ void allreduce_p2p_kernel(T* const* bufs_in, long long elem_offset, long long count, float scale,
                                      int* const* flag_ptrs, int my_rank, int nranks, int epoch,
                                      unsigned long long timeout_ns, int* status) {
   constexpr int VN = Vec16<T>::N;
+  constexpr int kMaxRanks = 32;
+  // the slice [elem_offset, elem_offset + count) of every rank's buffer
+  __shared__ T* bufs[kMaxRanks];
+  if (threadIdx.x < nranks) bufs[threadIdx.x] = bufs_in[threadIdx.x] + elem_offset;
+  __syncthreads();
   // local_sync words live right after the nranks barrier words of my flag block.
   int* local_sync = flag_ptrs[my_rank] + nranks;
   if (!grid_peer_barrier(flag_ptrs, my_rank, nranks, 2 * epoch - 1, local_sync, 2 * epoch - 1,
@@ -476,6 +481,22 @@ extern "C" int fm_allreduce_p2p(void* const* buf_ptrs_dev, long long count, int 
                                 float scale, int* const* flag_ptrs_dev, int my_rank, int nranks,
                                 int epoch, int num_ctas, unsigned long long timeout_ns,
                                 int* status, cudaStream_t stream) {
+  return fm_allreduce_p2p_slice(buf_ptrs_dev, 0, count, dtype_fp32, scale, flag_ptrs_dev, my_rank, nranks,
+                                epoch, num_ctas, timeout_ns, status, stream);
+}
+
+extern "C" int fm_allreduce_p2p_slice(void* const* buf_ptrs_dev, long long elem_offset, long long count,
+                                      int dtype_fp32, float scale, int* const* flag_ptrs_dev, int my_rank,
+                                      int nranks, int epoch, int num_ctas, unsigned long long timeout_ns,
+                                      int* status, cudaStream_t stream) {
+  if (nranks > 32) {
+    fm_set_error("allreduce_p2p: at most 32 ranks");
+    return -1;
+  }
+  if ((elem_offset * (dtype_fp32 ? 4 : 2)) % 16 != 0) {
+    fm_set_error("allreduce_p2p: the slice must start on a 16-byte boundary");
+    return -1;
+  }
   int dev = 0, sms = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
@@ -483,11 +504,11 @@ extern "C" int fm_allreduce_p2p(void* const* buf_ptrs_dev, long long count, int 
   const unsigned long long to = timeout_ns ? timeout_ns : 4000000000ull;
   if (dtype_fp32)
     fm::allreduce_p2p_kernel<float><<<num_ctas, 512, 0, stream>>>(
-        reinterpret_cast<float* const*>(buf_ptrs_dev), count, scale, flag_ptrs_dev, my_rank,
+        reinterpret_cast<float* const*>(buf_ptrs_dev), elem_offset, count, scale, flag_ptrs_dev, my_rank,
         nranks, epoch, to, status);
   else
     fm::allreduce_p2p_kernel<__nv_bfloat16><<<num_ctas, 512, 0, stream>>>(
-        reinterpret_cast<__nv_bfloat16* const*>(buf_ptrs_dev), count, scale, flag_ptrs_dev,
+        reinterpret_cast<__nv_bfloat16* const*>(buf_ptrs_dev), elem_offset, count, scale, flag_ptrs_dev,
         my_rank, nranks, epoch, to, status);
   return launch_check("allreduce_p2p");
 }

@@ -133,6 +133,14 @@ void bind_symm(py::module_& m) {
                      as_ptr<cudaStream_t>(stream)),
         "wait_flag");
   });
+  m.def("allreduce_p2p_slice", [](uintptr_t bufs, long long elem_offset, long long count, int fp32, float scale,
+                                  uintptr_t flags, int rank, int n, int epoch, int ctas,
+                                  unsigned long long timeout_ns, uintptr_t status, uintptr_t stream) {
+    chk(fm_allreduce_p2p_slice(as_ptr<void* const*>(bufs), elem_offset, count, fp32, scale,
+                               as_ptr<int* const*>(flags), rank, n, epoch, ctas, timeout_ns,
+                               as_ptr<int*>(status), as_ptr<cudaStream_t>(stream)),
+        "allreduce_p2p_slice");
+  });
   m.def("allreduce_p2p", [](uintptr_t bufs, long long count, int fp32, float scale,
                             uintptr_t flag_ptrs, int rank, int n, int epoch, int ctas,
                             unsigned long long timeout_ns, uintptr_t status, uintptr_t stream) {

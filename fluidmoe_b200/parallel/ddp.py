@@ -34,7 +34,8 @@ class FluidDDP(nn.Module):
                  dp_cp_group=None, expert_dp_group=None, accumulate_in_fp32: bool = True,
                  ar_enabled: bool = True, gap_budgets: Optional[dict] = None,
                  shared_ar_bw: Optional[float] = None, expert_ar_bw: Optional[float] = None,
-                 shared_reduce_fn=None, expert_reduce_fn=None, allocator=None, eager_ar: Optional[bool] = None):
+                 shared_reduce_fn=None, expert_reduce_fn=None, allocator=None, eager_ar: Optional[bool] = None,
+                 grad_reduce: Optional[str] = None):
         super().__init__()
         self.config = config
         self.module = module
@@ -46,8 +47,25 @@ class FluidDDP(nn.Module):
             if getattr(mod, "fused_ctx", None) is not None:
                 self.fused_ctx = mod.fused_ctx
                 break
+        # Dense-gradient reduction: "nccl" (library all-reduce) or "symm" (this library's two-shot
+        # kernel over peer memory on a flat buffer that lives in the symmetric heap); the latter
+        # needs the device-initiated transport and a dense data-parallel group equal to its group.
+        mode = (grad_reduce or os.environ.get("FLUIDMOE_GRAD_REDUCE", "nccl")).lower()
+        self.grad_reducer = None
+        if mode == "symm" and shared_reduce_fn is None and allocator is None and self.fused_ctx is not None \
+                and self.dp_world == self.fused_ctx.world and self.dp_world > 1:
+            from .scheduler import _default_reduce
+            from .symm import SymmGradReducer
+            self.grad_reducer = SymmGradReducer(self.fused_ctx.heap, fallback=_default_reduce(dp_cp_group))
+            shared_reduce_fn = self.grad_reducer.reduce
+            shared_allocator = self.grad_reducer.allocator
+        else:
+            shared_allocator = allocator
+        self.grad_reduce_mode = "symm" if self.grad_reducer is not None else "nccl"
         self._configure_scheduler(accumulate_in_fp32, ar_enabled, gap_budgets, shared_ar_bw, expert_ar_bw,
-                                  shared_reduce_fn, expert_reduce_fn, allocator)
+                                  shared_reduce_fn, expert_reduce_fn, allocator, shared_allocator)
+        if self.grad_reducer is not None:
+            self.fused_ctx.heap.sync_group()
         self._setup_other_params()
         # With the device-initiated transports there are no all-to-all windows to trickle the gradient
         # reduction into: start it as soon as gradients are committed instead.
@@ -66,7 +84,8 @@ class FluidDDP(nn.Module):
                 continue
         return []
 
-    def _configure_scheduler(self, fp32, ar_enabled, gap_budgets, shared_bw, expert_bw, s_fn, e_fn, allocator):
+    def _configure_scheduler(self, fp32, ar_enabled, gap_budgets, shared_bw, expert_bw, s_fn, e_fn, allocator,
+                             shared_allocator=None):
         sched = self.scheduler
         gaps = dict(gap_budgets or {})
         for region, env in _GAP_ENV.items():
@@ -94,7 +113,7 @@ class FluidDDP(nn.Module):
                      "qkv_weight", "ln1_weight", "ln1_bias")
             shared += [getattr(inner, n) for n in order if getattr(inner, n, None) is not None]
         self._scheduler_params = {id(p) for p in shared + expert}
-        sched.setup_ar_buffer(shared, fp32, allocator)
+        sched.setup_ar_buffer(shared, fp32, shared_allocator if shared_allocator is not None else allocator)
         sched.setup_expert_ar_buffer(expert, fp32, allocator)
 
     def _setup_other_params(self) -> None:

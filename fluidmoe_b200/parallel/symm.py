@@ -257,6 +257,67 @@ class SymmAllReduce:
         return self.buf.local
 
 
+class SymmGradReducer:
+    """Flat gradient buffers in symmetric memory, reduced slice by slice by the two-shot kernel.
+
+    ``allocator(n, dtype)`` has the signature ``FlatGradBuffer.setup`` takes and returns this rank's
+    instance of a symmetric buffer; ``reduce(chunk, pre_scale)`` has the signature of the
+    scheduler's reduce functions: ``chunk`` must be a slice of a buffer handed out by the allocator.
+    Every rank reads the peers' copies of its 1/P of the slice over NVLink, adds, scales and writes
+    the result into every copy (``fm_allreduce_p2p_slice``), so the pre-scale of the average costs
+    nothing extra.  A slice that does not start on a 16-byte boundary, or a group other than the
+    heap's, goes through ``fallback`` (the library collective).  This is the counterpart of the
+    NCCL all-reduce the reference trickles into its communication gaps
+    (fluid/core/scheduler.py:553-695)."""
+
+    def __init__(self, heap: SymmetricHeap, fallback=None, num_ctas: int = 24, timeout_ms: float = 8000.0):
+        self.heap = heap
+        self.fallback = fallback
+        self.num_ctas = num_ctas
+        self.timeout_ns = int(timeout_ms * 1e6)
+        self._bufs: List[SymmTensor] = []
+        self.flags = heap.alloc((heap.world + 2,), torch.int32)
+        self.epoch = 0
+        self.calls = 0
+        self.fallback_calls = 0
+
+    def allocator(self, n: int, dtype: torch.dtype) -> torch.Tensor:
+        t = self.heap.alloc((max(int(n), 4),), dtype)
+        self._bufs.append(t)
+        return t.local[:n]
+
+    def _locate(self, chunk: torch.Tensor):
+        addr = chunk.data_ptr()
+        for t in self._bufs:
+            lo = t.local.data_ptr()
+            if lo <= addr < lo + t.local.numel() * t.local.element_size():
+                return t, (addr - lo) // t.local.element_size()
+        return None, 0
+
+    def reduce(self, chunk: torch.Tensor, pre_scale: float = 1.0) -> None:
+        heap = self.heap
+        if heap.world == 1:
+            if pre_scale != 1.0:
+                chunk.mul_(pre_scale)
+            return
+        t, off = self._locate(chunk)
+        ok = t is not None and chunk.is_contiguous() and (off * chunk.element_size()) % 16 == 0 \
+            and chunk.dtype in (torch.float32, torch.bfloat16)
+        if not ok:
+            self.fallback_calls += 1
+            if self.fallback is None:
+                raise ValueError("gradient slice is not in a symmetric buffer (or not 16-byte aligned) and no "
+                                 "fallback reduce function was given")
+            self.fallback(chunk, pre_scale)
+            return
+        self.epoch += 1
+        self.calls += 1
+        _native.lib().allreduce_p2p_slice(
+            t.ptr_table, int(off), chunk.numel(), int(chunk.dtype == torch.float32), float(pre_scale),
+            self.flags.ptr_table, heap.rank, heap.world, self.epoch, self.num_ctas, self.timeout_ns,
+            status_buffer(heap.device).data_ptr(), _native.stream_ptr())
+
+
 class NvlsAllReduce:
     """In-switch (NVLS) sum all-reduce on an fp32 buffer (in place).
 

@@ -4,6 +4,12 @@ round-robin order, and this library's device-initiated all-to-all over symmetric
 Every transport first moves a pattern derived from (sender, receiver, index) and must reproduce it
 bit for bit before it is timed (as in the reference's tests/bench_comm.py:57-93).
     torchrun --nproc-per-node N -m fluidmoe_b200.tools.bench_comm --sizes-mib 1 8 32
+
+``--allreduce`` times the gradient all-reduce instead: the library collective against this
+library's two-shot kernel over peer memory (``SymmGradReducer``: the form the scheduler calls, on
+slices of a flat fp32 buffer), each checked against the other before it is timed; sizes are the
+slice sizes in MiB.  Bus bandwidth is ``2 (P-1)/P * bytes / time``.
+    torchrun --nproc-per-node N -m fluidmoe_b200.tools.bench_comm --allreduce --sizes-mib 32 128 512
 """
 from __future__ import annotations
 
@@ -44,12 +50,56 @@ def _time(fn, iters=20, warmup=5):
     return t.item()
 
 
+def bench_allreduce(args, device, rank, world):
+    from ..parallel.symm import SymmGradReducer, SymmetricHeap
+    biggest = int(max(args.sizes_mib) * (1 << 20))
+    heap = SymmetricHeap(None, biggest + (64 << 20), device)
+    for ctas in args.ctas:
+        red = SymmGradReducer(heap, num_ctas=ctas)
+        heap.mark()
+        flat = red.allocator(biggest // 4, torch.float32)
+        heap.sync_group()
+        for mib in args.sizes_mib:
+            n = int(mib * (1 << 20)) // 4
+            torch.manual_seed(7 + rank)
+            vals = torch.randn(n, device=device)
+            ref = vals.clone()
+            dist.all_reduce(ref)
+            ref /= world
+            flat[:n].copy_(vals)
+            red.reduce(flat[:n], 1.0 / world)
+            torch.cuda.synchronize()
+            err = (flat[:n] - ref).abs().max().item()
+            if err > 1e-5 * (ref.abs().max().item() + 1):
+                raise AssertionError(f"two-shot all-reduce differs from the library's by {err}")
+            scratch = vals.clone()
+            t_nccl = _time(lambda: dist.all_reduce(scratch.mul_(1.0 / world)))
+            t_symm = _time(lambda: red.reduce(flat[:n], 1.0 / world))
+            bus = lambda ms: 2 * (world - 1) / world * n * 4 / ms / 1e6       # noqa: E731
+            common.p0(f"allreduce {mib} MiB fp32, {ctas} CTAs: nccl={t_nccl:.3f}ms({bus(t_nccl):.0f}GB/s bus) "
+                      f"symm_two_shot={t_symm:.3f}ms({bus(t_symm):.0f}GB/s bus)")
+        heap.release_to_mark()
+    gemm_status()
+
+
+def gemm_status():
+    from ..ops import gemm
+    gemm.check_status()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--sizes-mib", type=float, nargs="+", default=[0.5, 2, 8, 32, 128])
+    ap.add_argument("--allreduce", action="store_true")
+    ap.add_argument("--ctas", type=int, nargs="+", default=[24], help="CTA counts of the two-shot kernel to try")
     args = ap.parse_args(argv)
     device = init_distributed()
     rank, world = dist.get_rank(), dist.get_world_size()
+    if args.allreduce:
+        bench_allreduce(args, device, rank, world)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     from ..parallel.symm import SymmAllToAll, SymmetricHeap
     heap = SymmetricHeap(None, int(max(args.sizes_mib) * (1 << 20) * world * 2 + (64 << 20)), device)
     partners = partner_table(world)[rank]

@@ -60,6 +60,36 @@ def main():
             assert (out - ref / world).abs().max().item() <= tol * (ref.abs().max().item() / world + 1), dtype
     gemm.check_status()
 
+    # ---- 2a. flat gradient buffer in symmetric memory, reduced slice by slice ----
+    from fluidmoe_b200.parallel.symm import SymmGradReducer
+    calls = []
+
+    def nccl_avg(chunk, pre_scale):
+        calls.append(chunk.numel())
+        chunk.mul_(pre_scale)
+        dist.all_reduce(chunk)
+    red = SymmGradReducer(heap, fallback=nccl_avg)
+    flat = red.allocator(3 * (1 << 18) + 8, torch.float32)
+    heap.sync_group()
+    torch.manual_seed(300 + rank)
+    vals = torch.randn(flat.numel(), device=dev)
+    flat.copy_(vals)
+    ref = vals.clone()
+    dist.all_reduce(ref)
+    ref /= world
+    cuts = [0, 1 << 18, (1 << 18) + 4096, 3 * (1 << 18) + 8]       # three slices, 16-byte aligned starts
+    for lo, hi in zip(cuts[:-1], cuts[1:]):
+        red.reduce(flat[lo:hi], 1.0 / world)
+    torch.cuda.synchronize()
+    assert (flat - ref).abs().max().item() <= 1e-5 * (ref.abs().max().item() + 1), "symmetric gradient reduce"
+    assert red.calls == 3 and red.fallback_calls == 0
+    flat.copy_(vals)
+    red.reduce(flat[2:1026], 1.0 / world)       # unaligned start: goes through the fallback
+    torch.cuda.synchronize()
+    assert red.fallback_calls == 1 and calls == [1024]
+    assert (flat[2:1026] - ref[2:1026]).abs().max().item() <= 1e-5 * (ref.abs().max().item() + 1)
+    gemm.check_status()
+
     # ---- 2b. in-switch (NVLS) all-reduce, where the system offers a multicast mapping ----
     from fluidmoe_b200.parallel.symm import NvlsAllReduce
     nv = NvlsAllReduce(heap, (1 << 20) + 3) if os.environ.get("FLUIDMOE_TEST_NVLS", "0") == "1" else None
@@ -215,15 +245,21 @@ def main():
     gemm.check_status()
 
     # ---- 8. two micro-batches accumulated, scheduler on, no barrier between them ----
-    def accumulate(lay, fused_mode):
-        from fluidmoe_b200.parallel.scheduler import BackwardScheduler
+    def accumulate(lay, fused_mode, symm_reduce=False):
+        from fluidmoe_b200.parallel.scheduler import BackwardScheduler, _default_reduce
         BackwardScheduler.reset()
         sc = get_backward_scheduler()
         sc.enable(dev)
-        sc.configure_allreduce(True, pc.dp_cp_group, pc.expert_dp_group, {}, 3e8, 3e8)
+        reducer = SymmGradReducer(pc.fused_ctx.heap, fallback=_default_reduce(pc.dp_cp_group)) if symm_reduce else None
+        sc.configure_allreduce(True, pc.dp_cp_group, pc.expert_dp_group, {}, 3e8, 3e8,
+                               shared_reduce_fn=reducer.reduce if reducer else None)
         sc.eager_ar = fused_mode
+        sc.eager_ar_min_bytes = 1 << 20 if symm_reduce else sc.eager_ar_min_bytes     # several slices per pass
         expert = [lay.moe_w2, lay.moe_w1]
-        sc.setup_ar_buffer([p_ for p_ in lay.parameters() if all(p_ is not e_ for e_ in expert)], True)
+        sc.setup_ar_buffer([p_ for p_ in lay.parameters() if all(p_ is not e_ for e_ in expert)], True,
+                           reducer.allocator if reducer else None)
+        if reducer:
+            pc.fused_ctx.heap.sync_group()
         sc.setup_expert_ar_buffer(expert, True)
         for p_ in lay.parameters():
             p_.grad = None
@@ -251,6 +287,11 @@ def main():
     gemm.check_status()
     for n_ in acc_a:
         assert fro(acc_f[n_], acc_a[n_]) < 3e-2, ("accumulate", n_, fro(acc_f[n_], acc_a[n_]))
+    # the same with the dense flat buffer in symmetric memory and the two-shot kernel reducing it
+    acc_s = accumulate(make_layer("fused", E, 1.0), True, symm_reduce=True)
+    gemm.check_status()
+    for n_ in acc_a:
+        assert fro(acc_s[n_], acc_a[n_]) < 3e-2, ("accumulate, symmetric reduce", n_, fro(acc_s[n_], acc_a[n_]))
     sched = get_backward_scheduler()
     sched.disable()
 

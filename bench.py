@@ -59,6 +59,9 @@ def parse_args():
                          "both arms run the identical model")
     ap.add_argument("--forward-only", action="store_true",
                     help="time the forward pass alone (inference latency): no backward, no optimizer")
+    ap.add_argument("--dw-side-ctas", type=int, default=0,
+                    help="> 0: deferred weight-gradient GEMMs run on a low-priority side stream with at most this "
+                         "many CTAs, concurrently with the critical path (0: on the compute stream, the default)")
     ap.add_argument("--grad-reduce", default="", choices=["", "nccl", "symm"],
                     help="dense-gradient all-reduce: library (nccl) or this repository's two-shot kernel over peer "
                          "memory (symm); default: FLUIDMOE_GRAD_REDUCE or nccl")
@@ -205,6 +208,8 @@ def run_ours(args):
     opt = FluidOptimizerWrapper(
         FusedAdam(model.parameters(), lr=1e-4, weight_decay=0.0,
                   state_dtype=torch.bfloat16 if args.opt_state == "bf16" else torch.float32), sched)
+    if args.dw_side_ctas > 0:
+        sched.dw_on_side_stream, sched.dw_max_ctas = True, args.dw_side_ctas
     fused_params = 0
     if args.fuse_optimizer and args.mode != "F" and args.opt_state == "bf16":
         fused_params = opt.fuse_into_backward(mode="stream" if args.fuse_optimizer == 2 else "epilogue")
@@ -270,7 +275,7 @@ def run_ours(args):
                    "global_batch": batch, "seq_len": seq * world, "seq_per_rank": seq,
                    "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
                    "comm": args.comm, "adam_moments": args.opt_state, "grad_accum": "fp32",
-                   "grad_reduce": ddp.grad_reduce_mode,
+                   "grad_reduce": ddp.grad_reduce_mode, "dw_side_stream_ctas": args.dw_side_ctas,
                    "optimizer": ("AdamW every step inside the timed region; expert weights (%d tensors) updated in their "
                                  "weight-gradient GEMM %s, all other parameters by the fused Adam kernel in step()"
                                  % (fused_params, "epilogue" if args.fuse_optimizer != 2 else "stream")) if fused_params

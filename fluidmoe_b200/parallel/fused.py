@@ -192,6 +192,8 @@ class FusedCommContext:
         sched = get_backward_scheduler()
         if sched.is_enabled() and sched.num_queued_dw_tasks() > 0:
             sched.execute_dw_tasks()
+        if sched.is_enabled():
+            sched.join_dw_stream()      # side-stream tasks read this layer's buffers too
         self._awaiting_backward[key] = bool(needs_grad)
 
     def layer_backward_end(self, ep_plan) -> None:

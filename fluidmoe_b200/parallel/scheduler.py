@@ -253,6 +253,7 @@ class BackwardScheduler:
         self.dw_max_ctas = 0
         # queues
         self._dw_queue: Deque[DWTask] = collections.deque()
+        self._side_inflight: List[DWTask] = []
         self._pending_param_ar: List[torch.nn.Parameter] = []
         self._a2a_tasks: Dict[int, tuple] = {}
         self._next_task_id = 0
@@ -384,8 +385,21 @@ class BackwardScheduler:
         if task.needs_ar and self.enabled:
             self._pending_param_ar.append(param)
 
+    def join_dw_stream(self) -> None:
+        """The compute stream waits for every weight-gradient task issued on the side stream; their
+        input tensors may be released afterwards."""
+        if self._side_inflight:
+            current_stream(self._device).wait_stream(self.dw_stream)
+            self._side_inflight.clear()
+
     def _commit(self) -> None:
-        self._dw_sync_event.record(current_stream(self._device))
+        cur = current_stream(self._device)
+        if self._side_inflight:
+            # committed gradients may have been produced on either stream
+            self.dw_stream.wait_stream(cur)
+            self._dw_sync_event.record(self.dw_stream)
+        else:
+            self._dw_sync_event.record(cur)
         self.shared_buffer.commit()
         self.expert_buffer.commit()
 
@@ -407,7 +421,13 @@ class BackwardScheduler:
         ran_deferrable = 0
         executed = 0
         kept: List[DWTask] = []
-        side = self.dw_on_side_stream and not isinstance(self.dw_stream, NullStream)
+        # Side-stream policy: deferrable tasks run on a low-priority stream behind the work queued so
+        # far (their inputs) and the compute stream does NOT wait for them here; it joins at the end
+        # of the backward pass (``join_dw_stream``).  Until then the tasks are kept alive, because
+        # the tensors their kernels read were allocated on the compute stream and must not be
+        # handed out again while those kernels are pending.  The gradient reduction waits for the
+        # side stream through ``_dw_sync_event``.
+        side = self.dw_on_side_stream and not isinstance(self.dw_stream, NullStream) and not self._in_finish
         if side:
             self.dw_stream.wait_stream(current_stream(self._device))
         while self._dw_queue:
@@ -418,21 +438,18 @@ class BackwardScheduler:
             if side and task.defer:
                 with on_stream(self.dw_stream):
                     self._run_task(task)
+                self._side_inflight.append(task)
             else:
                 self._run_task(task)
             executed += 1
             if task.defer:
                 ran_deferrable += 1
             if commit_per_task:
-                if side:
-                    current_stream(self._device).wait_stream(self.dw_stream)
                 self._commit()
                 if self.ar_enabled:
                     self._submit_ar_inline(budgeted=False)
         for task in reversed(kept):
             self._dw_queue.appendleft(task)
-        if side:
-            current_stream(self._device).wait_stream(self.dw_stream)
         if executed and not commit_per_task:
             self._commit()
             if (self.eager_ar and self.ar_enabled and not self._in_finish and
@@ -633,6 +650,7 @@ class BackwardScheduler:
         self._ensure_device()
         self._in_finish = True
         prev_region, self._current_region = self._current_region, "dp_tail"
+        self.join_dw_stream()
         try:
             if self.ar_enabled:
                 self.execute_dw_tasks(commit_per_task=True)
@@ -676,12 +694,12 @@ class BackwardScheduler:
         try:
             yield self
         finally:
-            self.ar_suspended = prev
             if self.enabled and not prev:
                 if self._dw_queue:
-                    self.execute_dw_tasks()
+                    self.execute_dw_tasks()          # still suspended: this commit reduces nothing
                 self.shared_buffer.reset_cursors()
                 self.expert_buffer.reset_cursors()
+            self.ar_suspended = prev
 
     def clear_iteration(self) -> None:
         """Wait for anything outstanding and reset per-iteration state."""
@@ -693,6 +711,8 @@ class BackwardScheduler:
                 cur.wait_event(self._ar_done_event)
         self._a2a_tasks.clear()
         self._next_task_id = 0
+        if self._cuda_ready:
+            self.join_dw_stream()
         self._dw_queue.clear()
         self._pending_param_ar.clear()
         self.shared_buffer.reset_cursors()
@@ -783,11 +803,16 @@ class BackwardScheduler:
         self._a2a_event_pairs.append((region, start_evt, end_evt))
 
     def record_fwd_wait(self, region: str, end_evt) -> None:
-        """Bracket a compute-stream wait on ``end_evt`` so that its exposed part can be measured."""
-        cur = current_stream(self._device) if self._cuda_ready else None
-        if not self.comm_metrics_enabled or cur is None:
-            if cur is not None and end_evt is not None:
-                cur.wait_event(end_evt)
+        """Make the compute stream wait for ``end_evt`` (always: the forward pairwise exchanges
+        rely on it, whether or not the scheduler was ever enabled) and, with metrics on, bracket
+        the wait so that its exposed part can be measured."""
+        if end_evt is None:
+            return
+        if not self._cuda_ready:
+            self._ensure_device()
+        cur = current_stream(self._device)
+        if not self.comm_metrics_enabled:
+            cur.wait_event(end_evt)
             return
         w0 = make_event(self._device, True)
         w0.record(cur)

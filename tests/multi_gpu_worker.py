@@ -245,7 +245,7 @@ def main():
     gemm.check_status()
 
     # ---- 8. two micro-batches accumulated, scheduler on, no barrier between them ----
-    def accumulate(lay, fused_mode, symm_reduce=False):
+    def accumulate(lay, fused_mode, symm_reduce=False, side_ctas=0):
         from fluidmoe_b200.parallel.scheduler import BackwardScheduler, _default_reduce
         BackwardScheduler.reset()
         sc = get_backward_scheduler()
@@ -255,6 +255,8 @@ def main():
                                shared_reduce_fn=reducer.reduce if reducer else None)
         sc.eager_ar = fused_mode
         sc.eager_ar_min_bytes = 1 << 20 if symm_reduce else sc.eager_ar_min_bytes     # several slices per pass
+        if side_ctas:
+            sc.dw_on_side_stream, sc.dw_max_ctas = True, side_ctas
         expert = [lay.moe_w2, lay.moe_w1]
         sc.setup_ar_buffer([p_ for p_ in lay.parameters() if all(p_ is not e_ for e_ in expert)], True,
                            reducer.allocator if reducer else None)
@@ -292,6 +294,11 @@ def main():
     gemm.check_status()
     for n_ in acc_a:
         assert fro(acc_s[n_], acc_a[n_]) < 3e-2, ("accumulate, symmetric reduce", n_, fro(acc_s[n_], acc_a[n_]))
+    # and with the deferred weight-gradient GEMMs on the CTA-capped side stream
+    acc_d = accumulate(make_layer("fused", E, 1.0), True, side_ctas=32)
+    gemm.check_status()
+    for n_ in acc_a:
+        assert fro(acc_d[n_], acc_a[n_]) < 3e-2, ("accumulate, side stream", n_, fro(acc_d[n_], acc_a[n_]))
     sched = get_backward_scheduler()
     sched.disable()
 

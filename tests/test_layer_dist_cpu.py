@@ -196,6 +196,7 @@ def _accumulate(rank, world, use_scheduler):
                               shared_ar_bw=1e6, expert_ar_bw=1e6)
     if use_scheduler:
         sched.enable(torch.device("cpu"))
+        sched.eager_ar, sched.eager_ar_min_bytes = True, 0     # reduce as early as the policy allows
         expert = [layer.moe_w2, layer.moe_w1]
         sched.setup_ar_buffer([p for p in layer.parameters() if all(p is not e for e in expert)], True)
         sched.setup_expert_ar_buffer(expert, True)

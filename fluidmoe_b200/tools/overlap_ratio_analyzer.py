@@ -1,5 +1,13 @@
-"""Exposed-communication report: total vs visible all-to-all and all-reduce time per region,
-MAX over ranks (counterpart of the reference's tests/overlap_ratio_analyzer.py:43-182)."""
+"""Exposed-communication report, MAX over ranks (counterpart of the reference's
+tests/overlap_ratio_analyzer.py:43-182).
+
+Host-submitted transports (``--comm p2p`` / ``a2a``): total vs visible all-to-all and all-reduce
+time per region, from the scheduler's event pairs.  Device-initiated transport (``--comm fused`` /
+``auto`` with a symmetric heap): there are no host-submitted all-to-alls to bracket; the report is
+the time the compute stream could not hide, from the counters inside the kernels
+(``FusedCommContext.comm_metrics``: waits of the gated GEMM producers, stand-alone wait kernels,
+push kernels), next to the iteration time.
+"""
 from __future__ import annotations
 
 import argparse
@@ -27,7 +35,28 @@ def main(argv=None):
     sched.configure_allreduce(True, pc.dp_cp_group, pc.expert_dp_group, bench.get("gap_budgets"),
                               bench.get("shared_ar_bw"), bench.get("expert_ar_bw"))
     model.setup_ar_buffer()
-    common.run_iters(model, x, 3, pc)
+    rotary = common.make_rotary(cfg, pc, device)
+    common.run_iters(model, x, 3, pc, rotary=rotary)
+    if pc.fused_ctx is not None and args.comm in ("auto", "fused"):
+        sched.eager_ar = True
+        iter_ms = common.time_iters(model, x, args.iters, pc, rotary=rotary)
+        pc.fused_ctx.enable_comm_metrics(True)
+        common.run_iters(model, x, args.iters, pc, rotary=rotary)
+        m = pc.fused_ctx.comm_metrics()
+        pc.fused_ctx.enable_comm_metrics(False)
+        keys = sorted(m)
+        vals = torch.tensor([m[k] / args.iters for k in keys], dtype=torch.float64, device=device)
+        if dist.is_initialized() and dist.get_world_size() > 1:
+            dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+        m = dict(zip(keys, vals.tolist()))
+        common.p0(f"iter_ms={iter_ms:.3f} exposed_comm_ms={m['exposed_comm_ms']:.3f} "
+                  f"exposed_comm_frac={m['exposed_comm_ms'] / max(iter_ms, 1e-9):.4f}")
+        common.p0(f"  gated_gemm_wait_ms={m['gated_gemm_wait_ms']:.3f} wait_kernels_ms={m['wait_kernels_ms']:.3f} "
+                  f"push_kernels_ms={m['push_kernels_ms']:.3f}")
+        if dist.is_initialized():
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     sched.set_comm_metrics_enabled(True)
     sched.reset_comm_metrics()
     common.run_iters(model, x, args.iters, pc)

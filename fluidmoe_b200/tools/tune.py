@@ -4,6 +4,11 @@ Step 1: greedy search of the per-region backward chunk counts over powers of two
 saving drops below ``min_saving_ms``), timing backward + ``finish_batch``.
 Step 2a: all-reduce bandwidth sweep (the largest size gives the bytes/ms used for gap budgeting).
 Step 2b: gap profiling: inter-all-to-all gaps per region, budget = p10 x 0.8.
+Step 3 (device-initiated transport only, ``--comm fused``): the knobs that replace the gap model
+there: the smallest slice the eager gradient reduction sends (``eager_ar_min_bytes``), the
+reduction kernel (``grad_reduce``: library or two-shot over peer memory) and the CTA cap of the
+weight-gradient side stream (``dw_side_ctas``, 0 = compute stream); each is kept only when it saves
+at least ``min_saving_ms``.
 Results are persisted with ``persist_block_benchmark_defaults`` (a JSON file; no source rewriting).
 """
 from __future__ import annotations
@@ -79,6 +84,41 @@ def tune_allreduce(cfg, bench, pc, device, comm, td) -> dict:
     return dict(shared_ar_bw=bytes_per_ms, expert_ar_bw=bytes_per_ms, gap_budgets=budgets)
 
 
+def _time_fused(cfg, bench, pc, device, td, eager_min_bytes, grad_reduce, side_ctas):
+    from ..parallel.ddp import FluidDDP
+    from ..parallel.scheduler import BackwardScheduler
+    BackwardScheduler.reset()
+    sched = get_backward_scheduler()
+    sched.enable(device)
+    model = common.build_model(cfg, bench, pc, device, "fused")
+    x = common.make_input(cfg, pc, device)
+    ddp = FluidDDP(None, model, sched, dp_cp_group=pc.dp_cp_group, expert_dp_group=pc.expert_dp_group,
+                   grad_reduce=grad_reduce)
+    sched.eager_ar_min_bytes = int(eager_min_bytes)
+    sched.dw_on_side_stream, sched.dw_max_ctas = side_ctas > 0, side_ctas
+    common.run_iters(ddp.module, x, td["warmup"], pc)
+    ms = common.time_iters(ddp.module, x, td["iters"], pc)
+    del ddp, model
+    if pc.fused_ctx is not None:
+        pc.fused_ctx.release_all()
+    return ms
+
+
+def tune_fused(cfg, bench, pc, device, td) -> dict:
+    best = dict(eager_ar_min_bytes=32 << 20, grad_reduce="nccl", dw_side_ctas=0)
+    best_ms = _time_fused(cfg, bench, pc, device, td, **best)
+    common.p0(f"[tune] fused defaults {best}: {best_ms:.3f} ms")
+    trials = [("eager_ar_min_bytes", v) for v in (8 << 20, 128 << 20)] + [("grad_reduce", "symm")] + \
+             [("dw_side_ctas", v) for v in td.get("side_ctas", (48,))]
+    for key, val in trials:
+        trial = dict(best, **{key: val})
+        ms = _time_fused(cfg, bench, pc, device, td, **trial)
+        common.p0(f"[tune] fused {key}={val}: {ms:.3f} ms (best {best_ms:.3f})")
+        if best_ms - ms >= td["min_saving_ms"]:
+            best, best_ms = trial, ms
+    return {"fused_" + k: v for k, v in best.items()}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="mixtral_8x7b")
@@ -93,7 +133,10 @@ def main(argv=None):
     if not args.skip_chunks:
         result.update(tune_chunks(cfg, bench, pc, device, args.comm, td))
         bench.update(result)
-    result.update(tune_allreduce(cfg, bench, pc, device, args.comm, td))
+    if args.comm in ("fused", "auto") and pc.fused_ctx is not None:
+        result.update(tune_fused(cfg, bench, pc, device, td))
+    else:
+        result.update(tune_allreduce(cfg, bench, pc, device, args.comm, td))
     if not dist.is_initialized() or dist.get_rank() == 0:
         path = persist_block_benchmark_defaults(result, args.node)
         print(f"[tune] wrote {path}: {result}", flush=True)

@@ -295,3 +295,26 @@ def test_block_benchmark_runs_several_presets_and_halves(capsys, monkeypatch):
     assert ref["activation"] == "gelu" and ref["ffn_hidden"] == 144 and ref["capacity_factor"] == 1.0
     assert ref["num_shared_experts"] == 0 and ref["has_attention"] and ref["norm_type"] == "layernorm"
     BackwardScheduler.reset()
+
+
+def test_tuner_searches_chunks_and_persists(tmp_path, monkeypatch, capsys):
+    """The tuner's chunk search and gap profiling on one CPU process; results go to the JSON file."""
+    import json
+    from fluidmoe_b200.parallel.scheduler import BackwardScheduler
+    from fluidmoe_b200.tools import experiment_configs, tune
+    monkeypatch.setenv("FLUIDMOE_TUNED_DEFAULTS", str(tmp_path / "tuned.json"))
+    monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "max_chunks", 2)
+    monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "iters", 1)
+    monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "warmup", 1)
+    monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "ar_sizes_mb", (1,))
+    monkeypatch.setattr(tune, "TUNE_DEFAULTS", experiment_configs.TUNE_DEFAULTS)
+    BackwardScheduler.reset()
+    tune.main(["--model", "tiny_test", "--comm", "p2p", "--node", "testbox"])
+    out = capsys.readouterr().out
+    assert "[tune] all regions 1 chunk" in out and "[tune] wrote" in out
+    saved = json.loads((tmp_path / "tuned.json").read_text())["testbox"]
+    assert {"moe_combine_chunks", "moe_dispatch_chunks", "attn_proj_chunks", "attn_qkv_chunks",
+            "shared_ar_bw", "gap_budgets"} <= set(saved)
+    merged = experiment_configs.get_block_benchmark_defaults("testbox")
+    assert merged["moe_combine_chunks"] == saved["moe_combine_chunks"]
+    BackwardScheduler.reset()

@@ -65,6 +65,8 @@ def parse_args():
     ap.add_argument("--grad-reduce", default="", choices=["", "nccl", "symm"],
                     help="dense-gradient all-reduce: library (nccl) or this repository's two-shot kernel over peer "
                          "memory (symm); default: FLUIDMOE_GRAD_REDUCE or nccl")
+    ap.add_argument("--recompute-fc1", action="store_true",
+                    help="do not keep the FC1 pre-activation; rebuild it in the backward pass (saves memory, costs one GEMM)")
     ap.add_argument("--loss-trace", action="store_true", help="add the loss of every timed end-to-end step to the JSON line")
     return ap.parse_args()
 
@@ -195,7 +197,7 @@ def run_ours(args):
                    router_dtype=torch.float32, activation_func=act_name, norm_type=norm_name,
                    moe_combine_chunks=args.chunks, moe_dispatch_chunks=args.chunks,
                    attn_proj_chunks=args.chunks, attn_qkv_chunks=args.chunks, comm_mode=args.comm,
-                   parallel_ctx=pc)
+                   parallel_ctx=pc, recompute_fc1=args.recompute_fc1)
     sched = get_backward_scheduler()
     if args.mode == "F":
         sched.disable()
@@ -276,6 +278,7 @@ def run_ours(args):
                    "parallelism": f"sp{world}ep{world}", "scheduler_mode": args.mode, "dx_chunks": args.chunks,
                    "comm": args.comm, "adam_moments": args.opt_state, "grad_accum": "fp32",
                    "grad_reduce": ddp.grad_reduce_mode, "dw_side_stream_ctas": args.dw_side_ctas,
+                   "recompute_fc1": bool(args.recompute_fc1),
                    "optimizer": ("AdamW every step inside the timed region; expert weights (%d tensors) updated in their "
                                  "weight-gradient GEMM %s, all other parameters by the fused Adam kernel in step()"
                                  % (fused_params, "epilogue" if args.fuse_optimizer != 2 else "stream")) if fused_params

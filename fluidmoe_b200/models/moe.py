@@ -170,13 +170,35 @@ def expert_to_rank_major(x: torch.Tensor, P: int, nle: int, cap: int) -> torch.T
     return x.view(nle, P, cap, *tail).transpose(0, 1).reshape(P * nle * cap, *tail)
 
 
-@dataclass
 class MoEForwardState:
-    """What the backward pass needs from the forward pass of the expert block."""
-    tokens_em: torch.Tensor            # [R, H] dispatched tokens, expert-major
-    probs_em: torch.Tensor             # [R] fp32
-    pre_em: Optional[torch.Tensor]     # [R, F or 2F] FC1 pre-activation
-    act_em: torch.Tensor               # [R, F] act * prob
+    """What the backward pass needs from the forward pass of the expert block.
+
+    ``pre_em`` (the FC1 pre-activation, ``[R, F or 2F]``) is the largest saved tensor of a layer.
+    With ``set_recompute`` it is not kept: the first read in the backward pass runs the FC1 GEMM
+    again on the saved tokens, which happens right before the activation backward needs it, i.e.
+    while the combine-gradient exchange is in flight (the reference has the same memory-saving
+    fallback, fluid/moe/backward.py:616-646)."""
+
+    def __init__(self, tokens_em: torch.Tensor, probs_em: torch.Tensor, pre_em: Optional[torch.Tensor],
+                 act_em: torch.Tensor):
+        self.tokens_em = tokens_em          # [R, H] dispatched tokens, expert-major
+        self.probs_em = probs_em            # [R] fp32
+        self.act_em = act_em                # [R, F] act * prob
+        self._pre_em = pre_em
+        self._recompute = None
+
+    def set_recompute(self, fn) -> None:
+        self._recompute = fn
+
+    @property
+    def pre_em(self) -> Optional[torch.Tensor]:
+        if self._pre_em is None and self._recompute is not None:
+            self._pre_em = self._recompute()
+        return self._pre_em
+
+    @pre_em.setter
+    def pre_em(self, value) -> None:
+        self._pre_em = value
 
 
 # ============================================================================================

@@ -132,6 +132,7 @@ class TransformerLayerFunction(torch.autograd.Function):
         else:
             with nvtx_range("ln2"):
                 ln2_out, mean2, rstd2 = norm.norm_fwd(h1, ln2_w, ln2_b, L.norm_eps, L.norm_type)
+            save_pre = needs_grad and not L.recompute_fc1
             if L.dropless:
                 fused_dropless = mode_moe == "fused" and ep.ep_size > 1
                 mode_moe = "dropless_fused" if fused_dropless else "dropless"
@@ -145,10 +146,10 @@ class TransformerLayerFunction(torch.autograd.Function):
                         from ..parallel.fused_dropless import build_device_plan
                         rplan = build_device_plan(top_idx, top_probs, L.num_experts)
                         combined, st = fused.dropless.forward(fused._buf(ep), ep, rplan, ln2_out, w1, w2, act,
-                                                              needs_grad)
+                                                              save_pre)
                     else:
                         rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
-                        combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, needs_grad)
+                        combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, save_pre)
             else:
                 gather = not (mode_moe == "fused" and ep.ep_size > 1)
                 (permuted, probs, sorted_idx, _tpe, top_idx, top_probs, logits, _rmap, rplan) = \
@@ -156,11 +157,17 @@ class TransformerLayerFunction(torch.autograd.Function):
                                            L.capacity_factor, ep, L.router_dtype, gather_tokens=gather,
                                            forced_top_idx=L.forced_top_idx, logit_bias=L.router_logit_bias)
                 with nvtx_range("dispatch_fc1"):
-                    st = moe_mod.dispatch_fc1_forward(ep, permuted, probs, w1, act, mode_moe, save_pre=needs_grad,
+                    st = moe_mod.dispatch_fc1_forward(ep, permuted, probs, w1, act, mode_moe, save_pre=save_pre,
                                                       fused_ctx=fused, hidden_states=ln2_out,
                                                       sorted_indices=sorted_idx)
                 with nvtx_range("fc2_combine"):
                     combined = moe_mod.fc2_combine_forward(ep, st, w2, mode_moe, fused)
+            if needs_grad and L.recompute_fc1:
+                # the FC1 pre-activation is rebuilt in the backward pass from the saved tokens
+                groups = (dict(group_rows=rplan.group_rows, group_offs=rplan.group_offs) if L.dropless else
+                          dict(uniform_rows=(ep.ep_size if ep.ep_size > 1 else 1) * ep.expert_capacity))
+                st.set_recompute(lambda st=st, w1=w1, groups=groups: gemm.grouped_gemm(
+                    st.tokens_em, w1.detach(), b_layout="kn", **groups))
             residual = h1
             if shared_w1 is not None:
                 sh_act, sh_pre = gemm.grouped_gemm_act(ln2_out, shared_w1.unsqueeze(0), None,
@@ -418,12 +425,16 @@ class TransformerLayer(nn.Module):
                  router_dtype: torch.dtype = torch.bfloat16, aux_loss_coeff: float = 0.0,
                  z_loss_coeff: float = 0.0, *, norm_type: str = "layernorm", norm_eps: float = 1e-5,
                  num_shared_experts: int = 0, shared_ffn_hidden_size: Optional[int] = None,
-                 comm_mode: str = "auto", parallel_ctx=None, has_attention: bool = True, has_moe: bool = True):
+                 comm_mode: str = "auto", parallel_ctx=None, has_attention: bool = True, has_moe: bool = True,
+                 recompute_fc1: bool = False):
         super().__init__()
         assert has_attention or has_moe
         # Either half can be switched off (its parameters stay in the state dict and receive no
         # gradient): the block benchmarks time the MoE half and the attention half on their own.
         self.has_attention, self.has_moe = bool(has_attention), bool(has_moe)
+        # Drop the FC1 pre-activation after the forward pass and rebuild it in the backward pass
+        # (one more FC1 GEMM per layer for [rows, F or 2F] less saved memory).
+        self.recompute_fc1 = bool(recompute_fc1)
         self.router_logit_bias = None   # optional fp32 [E] prior added to the router logits (set_router_bias)
         if parallel_ctx is not None:
             cp_group = cp_group if cp_group is not None else parallel_ctx.cp_group

@@ -367,6 +367,37 @@ def main():
         gemm.check_status()
         assert fro(y_inf.float(), yda.float()) < 2e-2
 
+    # ---- 9c. FC1 recompute: the rebuilt pre-activation is the same product on the same rows, so the
+    # gradients agree with the ones of the pass that kept it to rounding (padded and dropless) ----
+    def same(a_, b_):
+        return fro(a_.float(), b_.float()) < 2e-3
+    ldr2 = make_dropless("fused")
+    ldr2.recompute_fc1 = True
+    gkeep = {n_: p_.grad.clone() for n_, p_ in ldf2.named_parameters() if p_.grad is not None}
+    gxkeep = x.grad.clone()
+    run_once(ldr2, x, gy, None)
+    pc.fused_ctx.iteration_barrier()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert same(x.grad, gxkeep), "dropless recompute dx"
+    for n_, p_ in ldr2.named_parameters():
+        if n_ in gkeep:
+            assert same(p_.grad, gkeep[n_]), ("dropless recompute", n_)
+    lpk, lpr = make_layer("fused", E, 1.0, has_attention=False), make_layer("fused", E, 1.0, has_attention=False,
+                                                                           recompute_fc1=True)
+    run_once(lpk, x, gy, None)
+    pc.fused_ctx.iteration_barrier()
+    gkeep = {n_: p_.grad.clone() for n_, p_ in lpk.named_parameters() if p_.grad is not None}
+    gxkeep = x.grad.clone()
+    run_once(lpr, x, gy, None)
+    pc.fused_ctx.iteration_barrier()
+    torch.cuda.synchronize()
+    gemm.check_status()
+    assert same(x.grad, gxkeep), "recompute dx"
+    for n_, p_ in lpr.named_parameters():
+        if n_ in gkeep:
+            assert same(p_.grad, gkeep[n_]), ("recompute", n_)
+
     # ---- 10. pairwise put + flag back-end: bit-exact pattern over a whole tournament ----
     from fluidmoe_b200.parallel.p2p_backend import SymmetricP2PBackend
     from fluidmoe_b200.parallel.schedule import partner_table

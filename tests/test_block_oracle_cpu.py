@@ -18,7 +18,8 @@ CONFIG1 = dict(H=256, nh=8, nkv=8, F=512, E=4, k=2, s_loc=128, b=2, init_std=0.0
 def _layer_kwargs(norm_type, act, nsh, aux, cf, D=DIMS):
     return dict(dtype=torch.float32, device="cpu", router_dtype=torch.float32, activation_func=act,
                 norm_type=norm_type, init_std=D.get("init_std", 0.2), capacity_factor=cf, num_shared_experts=nsh,
-                aux_loss_coeff=1e-2 if aux else 0.0, z_loss_coeff=1e-3 if aux else 0.0)
+                aux_loss_coeff=1e-2 if aux else 0.0, z_loss_coeff=1e-3 if aux else 0.0,
+                recompute_fc1=D.get("recompute_fc1", False))
 
 
 def _build_full(norm_type, act, nsh, aux, cf, groups=(None, None), D=DIMS):
@@ -216,3 +217,35 @@ def test_single_half_layer_matches_full_layer_with_the_other_half_silenced(half)
     for n in idle:
         assert gp[n] is None or float(gp[n].abs().max()) == 0.0, n
     BackwardScheduler.reset()
+
+
+@pytest.mark.parametrize("act,cf,world,mode", [("swiglu", 1.0, 1, "a2a"), ("gelu", 0.0, 1, "a2a"),
+                                               ("swiglu", 1.0, 2, "p2p"), ("gelu", 0.0, 2, "a2a")])
+def test_fc1_recompute_gives_the_same_gradients(act, cf, world, mode):
+    """With ``recompute_fc1`` the FC1 pre-activation is not saved; the backward pass rebuilds it
+    from the saved tokens and must still match the oracle (padded and dropless routing)."""
+    D = dict(DIMS, recompute_fc1=True)
+    if world == 1:
+        from fluidmoe_b200.ops.rope import make_rope_freqs
+        from fluidmoe_b200.parallel.scheduler import BackwardScheduler, get_backward_scheduler
+        BackwardScheduler.reset()
+        get_backward_scheduler().disable()
+        layer = _build_full("rmsnorm", act, 0, False, cf, D=D)
+        assert layer.recompute_fc1
+        x_full, g_full = _inputs(1)
+        x = x_full.clone().requires_grad_(True)
+        y = layer(x, make_rope_freqs(D["s_loc"], D["H"] // D["nh"]))
+        y.backward(g_full)
+        results = [(y.detach(), x.grad, {n: p.grad for n, p in layer.named_parameters()})]
+        BackwardScheduler.reset()
+    else:
+        results = run_distributed(_sharded_run, world, "rmsnorm", act, 0, False, cf, mode, "full", D)
+    yo, dxo, go = _oracle(world, "rmsnorm", act, 0, False, cf)
+    nle = DIMS["E"] // world
+    for r, (y, dx, grads) in enumerate(results):
+        sl = slice(r * DIMS["s_loc"], (r + 1) * DIMS["s_loc"])
+        _close(y, yo[sl], "y")
+        _close(dx, dxo[sl], "dx")
+        for n, g in grads.items():
+            ref = go[n][r * nle:(r + 1) * nle] if n in ("moe_w1", "moe_w2") else go[n]
+            _close(g * world, ref, n)

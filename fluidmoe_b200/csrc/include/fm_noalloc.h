@@ -19,6 +19,8 @@
 //     non-zero return code and a message in fm_last_error();
 //   * the function never calls cudaMalloc, cudaFree or any allocating library routine; the
 //     caller passes every input and output buffer;
+//   * the buffers must live on the device that is current at the call (checked on dx; a
+//     mismatch is rejected with a non-zero return code);
 //   * the first call on a device looks up the device address of the scratch array (once per
 //     device, with that device current).  Make that first call before starting any stream
 //     capture on the device;

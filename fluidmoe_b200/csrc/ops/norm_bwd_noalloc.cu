@@ -169,7 +169,13 @@ extern "C" int fm_norm_bwd_static(const void* dy, const void* x, const void* w, 
                                   const float* rstd, const void* res_grad, void* dx, float* dw,
                                   float* db, int T, int H, int kind, cudaStream_t stream) {
   using namespace fm_noalloc;
-  if (T <= 0 || H <= 0 || H % 8 != 0 || H > FM_NOALLOC_MAX_H) {
+  if (T <= 0) {
+    char buf[120];
+    snprintf(buf, sizeof(buf), "norm_bwd_static: T=%d rows; at least one row is needed", T);
+    fm_set_error(buf);
+    return -1;
+  }
+  if (H <= 0 || H % 8 != 0 || H > FM_NOALLOC_MAX_H) {
     char buf[200];
     snprintf(buf, sizeof(buf),
              "norm_bwd_static: H=%d is not supported (a multiple of 8, at most %d; the scratch array has a fixed size)",
@@ -183,6 +189,19 @@ extern "C" int fm_norm_bwd_static(const void* dy, const void* x, const void* w, 
   }
   float* scratch = scratch_for_current_device();
   if (scratch == nullptr) return -2;
+  {
+    // the scratch looked up above belongs to the current device; the buffers must live there too
+    int dev = -1;
+    cudaPointerAttributes attr;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaPointerGetAttributes(&attr, dx) == cudaSuccess &&
+        attr.type == cudaMemoryTypeDevice && attr.device != dev) {
+      char buf[160];
+      snprintf(buf, sizeof(buf), "norm_bwd_static: dx lives on device %d but device %d is current", attr.device, dev);
+      fm_set_error(buf);
+      return -3;
+    }
+    (void)cudaGetLastError();
+  }
   using bf = __nv_bfloat16;
   const int nb = T < FM_NOALLOC_MAX_BLOCKS ? T : FM_NOALLOC_MAX_BLOCKS;
   bwd_kernel<<<nb, kThreads, 0, stream>>>((const bf*)dy, (const bf*)x, (const bf*)w, mean, rstd,

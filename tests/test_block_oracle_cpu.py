@@ -61,6 +61,10 @@ def _sharded_run(rank, world, norm_type, act, nsh, aux, cf, mode, sched_mode, D=
             p.copy_(src[n][rank * nle:(rank + 1) * nle] if n in ("moe_w1", "moe_w2") else src[n])
     x_full, g_full = _inputs(world, D)
     rot = make_rope_freqs(world * D["s_loc"], D["H"] // D["nh"])
+    if D.get("overhead"):
+        from fluidmoe_b200.utils import overhead_profiler as op
+        op.set_enabled(True)
+        op.reset()
     sched = get_backward_scheduler()
     sched.configure_allreduce(sched_mode == "full", pc.dp_cp_group, pc.expert_dp_group,
                               gap_budgets={r: 1.0 for r in ("moe_combine", "moe_dispatch", "attn_proj", "attn_qkv")},
@@ -69,6 +73,9 @@ def _sharded_run(rank, world, norm_type, act, nsh, aux, cf, mode, sched_mode, D=
         sched.disable()
     else:
         sched.enable(torch.device("cpu"))
+        for key, val in D.get("sched_toggles", {}).items():
+            assert hasattr(sched, key), key
+            setattr(sched, key, val)
         expert = [layer.moe_w2, layer.moe_w1]
         sched.setup_ar_buffer([p for p in layer.parameters() if all(p is not e for e in expert)], True)
         sched.setup_expert_ar_buffer(expert, True)
@@ -83,6 +90,11 @@ def _sharded_run(rank, world, norm_type, act, nsh, aux, cf, mode, sched_mode, D=
         sched.finish_batch()
         grads = {n: p.main_grad.clone() for n, p in layer.named_parameters()}
     sched.clear_iteration()
+    if D.get("overhead"):
+        from fluidmoe_b200.utils import overhead_profiler as op
+        buckets = op.summary_by_bucket()
+        op.set_enabled(False)
+        return y.detach(), x.grad, grads, buckets
     return y.detach(), x.grad, grads
 
 
@@ -249,3 +261,32 @@ def test_fc1_recompute_gives_the_same_gradients(act, cf, world, mode):
         for n, g in grads.items():
             ref = go[n][r * nle:(r + 1) * nle] if n in ("moe_w1", "moe_w2") else go[n]
             _close(g * world, ref, n)
+
+
+@pytest.mark.parametrize("toggles", [
+    dict(stage2_enabled=False),                          # weight gradients only at the end of backward
+    dict(cross_region_flow=False),                       # every region drains its own queue
+    dict(use_profiled_gaps=False),                       # no gap model: reductions wait for finish_batch
+    dict(fixed_ar_budget=4096),                          # a fixed number of bytes per gap
+    dict(pending_ar_enabled=False),                      # no trickled reductions after the exchanges
+    dict(stage2_enabled=False, pending_ar_enabled=False, cross_region_flow=False),
+])
+def test_scheduler_ablation_switches_keep_the_gradients(toggles):
+    """The switches the reference's ablation runs flip (tests/run_block_benchmark.py:286-323: stage-2
+    weight gradients, cross-region flow, profiled gaps, fixed reduction budget, trickled
+    reductions) change when work is submitted, never what is computed."""
+    world = 2
+    D = dict(DIMS, sched_toggles=toggles, overhead=True)
+    res = run_distributed(_sharded_run, world, "rmsnorm", "swiglu", 1, False, 1.0, "p2p", "full", D)
+    yo, dxo, go = _oracle(world, "rmsnorm", "swiglu", 1, False, 1.0)
+    nle = DIMS["E"] // world
+    for r in range(world):
+        y, dx, grads, buckets = res[r]
+        sl = slice(r * DIMS["s_loc"], (r + 1) * DIMS["s_loc"])
+        _close(y, yo[sl], f"y rank {r}")
+        _close(dx, dxo[sl], f"dx rank {r}")
+        for n, g in grads.items():
+            ref = go[n][r * nle:(r + 1) * nle] if n in ("moe_w1", "moe_w2") else go[n]
+            _close(g * world, ref, f"{n} rank {r} {toggles}")
+        # the host-overhead buckets of the scheduler were filled while it ran
+        assert any(v > 0 for v in buckets.values()), buckets

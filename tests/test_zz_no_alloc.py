@@ -33,7 +33,8 @@ def test_norm_bwd_static_matches_regular_entry_point(kind):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     stream = torch.cuda.current_stream().cuda_stream
-    for call, (T, H) in enumerate([(777, 4096), (64, 1024)]):      # two calls in a row share the scratch
+    for call, (T, H) in enumerate([(777, 4096), (64, 1024), (300, 8192), (5, 8)]):   # calls in a row share the scratch;
+        # the largest width with more rows than blocks, and the smallest width
         torch.manual_seed(10 + call)
         x = torch.randn(T, H, device=dev).bfloat16()
         w = (1 + 0.1 * torch.randn(H, device=dev)).bfloat16()
@@ -66,3 +67,6 @@ def test_norm_bwd_static_rejects_sizes_beyond_the_scratch():
     rc = fn(None, None, None, None, None, None, None, None, None, 16, 8192 + 8, 1, None)
     assert rc != 0
     assert b"not supported" in lib.fm_last_error()
+    rc = fn(None, None, None, None, None, None, None, None, None, 0, 1024, 1, None)
+    assert rc != 0
+    assert b"at least one row" in lib.fm_last_error()

@@ -24,6 +24,8 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]
+# extra nvcc flags of developer builds, e.g. FLUIDMOE_BUILD_DEFINES=-DFM_FLASH_PROFILE
+NVCC_FLAGS += os.environ.get("FLUIDMOE_BUILD_DEFINES", "").split()
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden"]
 
 

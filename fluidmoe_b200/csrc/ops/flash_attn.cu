@@ -15,6 +15,9 @@
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
 #include <math.h>
 #include <stdio.h>
 
@@ -39,7 +42,19 @@ struct FlashFwdArgs {
   float* lse;            // [b, G*qpg, s]
   unsigned long long timeout_ns;
   int* status;
+  long long* prof;       // developer builds (FM_FLASH_PROFILE): per-CTA cycle counters, else null
+  const __nv_bfloat16* qkv;   // packed projection buffer (third-generation kernel reads Q rows itself)
+  long long row_stride;       // elements between consecutive sequence positions
 };
+
+// Cycle counters of one softmax thread and of the MMA thread, per CTA (developer builds only).
+#ifdef FM_FLASH_PROFILE
+#define FA_PROF_NOW() clock64()
+#define FA_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#else
+#define FA_PROF_NOW() 0ll
+#define FA_PROF_ADD(acc, t0) (void)(t0)
+#endif
 
 __global__ void __launch_bounds__(kFaThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
@@ -325,9 +340,34 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 2^x on the FMA pipe: x = j + f with j = rint(x), f in [-0.5, 0.5]; 2^f by a cubic (relative
+// error 7.5e-5, far below bf16 resolution), 2^j by adding j to the exponent field.  The
+// special-function unit delivers 16 ex2 per clock and SM, which for head dim 128 is as many
+// clocks per key block as the tensor core needs for the two products; moving a share of the
+// exponentials here takes the unit off the critical path.
+__device__ __forceinline__ float poly_exp2(float x) {
+  constexpr float kMagic = 12582912.0f;   // 1.5 * 2^23: adding it leaves rint(x) in the low mantissa bits
+  x = fmaxf(x, -126.0f);
+  const float t = x + kMagic;
+  const float f = x - (t - kMagic);
+  float p = fmaf(f, 0.055171649903059006f, 0.2426111251115799f);
+  p = fmaf(p, f, 0.6932609677314758f);
+  p = fmaf(p, f, 0.9999280571937561f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 constexpr int kFa2Threads = 320;   // TMA warp, MMA warp, 4 + 4 softmax warps
 constexpr int kKernelIdFlashFwd2 = 21;
+constexpr int kFa2DefaultPoly = 0;
 
+// kPoly: of every four value pairs, how many take their exponential from poly_exp2x2.
+template <int kPoly>
 __global__ void __launch_bounds__(kFa2Threads, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -432,6 +472,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       auto issue_qk = [&](int w, int j) {
         const uint32_t q_addr = smem_u32(sQ + w * kTileBytes);
         const uint32_t k_addr = smem_u32(sK + (j & 1) * kTileBytes);
+#ifdef FM_FLASH_PROFILE
+        if constexpr (kPoly != 7)       // timing experiment: P.V only
+#endif
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint32_t off = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
@@ -442,6 +485,9 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       };
       auto issue_pv = [&](int w, int j) {
         const uint32_t v_addr = smem_u32(sV + (j & 1) * kTileBytes);
+#ifdef FM_FLASH_PROFILE
+        if constexpr (kPoly != 6)       // timing experiment: Q.K^T only
+#endif
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           umma_bf16_ts(tmem_base + 256 + w * 128, tmem_base + w * 128 + kk * 8,
@@ -454,6 +500,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd2, what, 0, 0);
         return false;
       };
+      [[maybe_unused]] long long pm_total = FA_PROF_NOW(), pm_wait_p = 0, pm_wait_kv = 0;
       // prologue: S_w(0) for both tiles
       for (int w = 0; ok && w < 2; ++w)
         if (nblk[w] > 0) ok = wait_or_fail(&q_full[w], 0, 200 + w);
@@ -467,17 +514,23 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       for (int j = 0; ok && j < nmax; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
+        [[maybe_unused]] long long t0 = FA_PROF_NOW();
         ok = wait_or_fail(&v_full[st], ph, 230 + st);
+        FA_PROF_ADD(pm_wait_kv, t0);
         bool k_next_ready = false;
         for (int w = 0; ok && w < 2; ++w) {
           if (j >= nblk[w]) continue;
+          t0 = FA_PROF_NOW();
           ok = wait_or_fail(&p_full[w], j & 1, 220 + w);
+          FA_PROF_ADD(pm_wait_p, t0);
           if (!ok) break;
           tc_fence_after_sync();
           issue_pv(w, j);
           if (j + 1 < nblk[w]) {
             if (!k_next_ready) {
+              t0 = FA_PROF_NOW();
               ok = wait_or_fail(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 240);
+              FA_PROF_ADD(pm_wait_kv, t0);
               if (!ok) break;
               tc_fence_after_sync();
               k_next_ready = true;
@@ -489,10 +542,25 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         umma_commit(&v_empty[st]);
         if (j + 1 < nmax) umma_commit(&k_empty[(j + 1) & 1]);
       }
+#ifdef FM_FLASH_PROFILE
+      if (a.prof != nullptr) {
+        long long* pr = a.prof + (long long)blockIdx.x * 16;
+        pr[0] = clock64() - pm_total;
+        pr[1] = pm_wait_p;
+        pr[2] = pm_wait_kv;
+        pr[3] = nblk[0] + nblk[1];
+      }
+#endif
     }
   } else {
-    // ------------------------------- softmax warps (two groups of 4) -------------------------------
-    const int w = (warp - 2) >> 2;       // which query tile this warp group owns
+    // ------------------------------- softmax warps -------------------------------
+    // One thread per query row.  The score row (128 fp32 values in TMEM) is streamed twice in
+    // chunks of 32 columns with the next chunk's load in flight behind the current chunk's
+    // arithmetic: once for the row maximum, once for the exponentials.  Holding only two chunks
+    // in registers (instead of the whole row) leaves the compiler room to interleave the
+    // special-function and the polynomial exponentials of many value pairs.
+    const int sw = warp - 2;
+    const int w = sw >> 2;               // which query tile this warp owns
     const int q = warp & 3;              // TMEM lane quarter
     const int r = q * 32 + lane;
     const int qt = 2 * pair + w;
@@ -503,41 +571,50 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
     const int nb = nblk[w];
     float m_used = -INFINITY, l_run = 0.f;
     bool ok = true;
+    [[maybe_unused]] long long ps_total = FA_PROF_NOW(), ps_wait = 0, ps_max = 0, ps_exp = 0, ps_resc = 0;
     for (int j = 0; j < nb; ++j) {
-      if (!mbar_wait(&s_full[w], j & 1, timeout, abort_flag)) {
+      [[maybe_unused]] long long t0 = FA_PROF_NOW();
+      if (!__all_sync(0xffffffffu, mbar_wait(&s_full[w], j & 1, timeout, abort_flag))) {
         if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd2, 300 + w, 0, 0);
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      const bool diag = (j == qt);
+      FA_PROF_ADD(ps_wait, t0);
+      t0 = FA_PROF_NOW();
       const int kv0 = j * kFaBN;
+      // only the diagonal block and a ragged last block need masking
+      const bool diag = (j == qt);
+      const bool masked = diag || kv0 + kFaBN > a.s;
+      auto mask_chunk = [&](uint32_t* v, int c) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = kv0 + c * 32 + i;
+          if ((diag && col > row) || col >= a.s) v[i] = 0xff800000u;   // -inf
+        }
+      };
       // The whole score row (128 values) is kept in registers: one TMEM read per block.
       uint32_t sv[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
       tmem_ld_wait();
-      if (diag || kv0 + kFaBN > a.s) {
-        // only the diagonal block and a ragged last block need masking
+      if (masked) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = kv0 + c * 32 + i;
-            if ((diag && col > row) || col >= a.s) sv[c][i] = 0xff800000u;   // -inf
-          }
+        for (int c = 0; c < 4; ++c) mask_chunk(sv[c], c);
       }
-      // eight independent running maxima (one dependent chain of 128 would cost ~500 cycles)
+      // row maximum: eight independent chains of three-input maxima
       float mx[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) mx[k] = -INFINITY;
 #pragma unroll
       for (int c = 0; c < 4; ++c)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(sv[c][i]));
-      const float m_raw = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                                fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        for (int i = 0; i < 16; ++i)
+          mx[i & 7] = fmax3(mx[i & 7], __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]));
+      const float m_raw = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmax3(fmax3(mx[3], mx[4], mx[5]), mx[6], mx[7]));
       const float m_blk = m_raw * a.scale_log2;   // scale > 0
+      FA_PROF_ADD(ps_max, t0);
+      t0 = FA_PROF_NOW();
       // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 above it.
       const float m_new = fmaxf(m_used, m_blk);
       const bool first = (j == 0);
@@ -545,7 +622,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       if (first) m_used = (m_new == -INFINITY) ? 0.f : m_new;
       if (__any_sync(0xffffffffu, grow)) {
         // O holds the sum of blocks 0..j-1; P.V of block j-1 must have finished before it is touched.
-        if (!mbar_wait(&o_full[w], (j - 1) & 1, timeout, abort_flag)) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&o_full[w], (j - 1) & 1, timeout, abort_flag))) {
           ok = false;
           break;
         }
@@ -566,27 +643,61 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
           m_used = m_new;
         }
       }
-      float l_part[4] = {0.f, 0.f, 0.f, 0.f};     // independent partial row sums
-      const float neg_m = -m_used;
+      FA_PROF_ADD(ps_resc, t0);
+      t0 = FA_PROF_NOW();
+      // Exponentials: of every four values, kPoly take the polynomial on the FMA pipe, the others
+      // the special-function unit, so that the two pipes work side by side.  Scalar arithmetic on
+      // purpose: the packed two-value instructions only run on one of the two FMA pipes.
+      float l_part[8];                            // independent partial row sums
+#pragma unroll
+      for (int k = 0; k < 8; ++k) l_part[k] = 0.f;
+      const float sc = a.scale_log2, neg_m = -m_used;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i]), a.scale_log2, neg_m));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][2 * i + 1]), a.scale_log2, neg_m));
-          l_part[i & 3] += p0 + p1;
+          const float x0 = fmaf(__uint_as_float(sv[c][2 * i]), sc, neg_m);
+          const float x1 = fmaf(__uint_as_float(sv[c][2 * i + 1]), sc, neg_m);
+          float p0, p1;
+#ifdef FM_FLASH_PROFILE
+          if constexpr (kPoly >= 5) {           // timing experiments of developer builds: no exponential
+            p0 = x0;
+            p1 = x1;
+          } else
+#endif
+          {
+            // value 2i of a pair uses the polynomial when (i & 1) * 2 < kPoly, value 2i + 1 when
+            // (i & 1) * 2 + 1 < kPoly: kPoly of every four consecutive values
+            p0 = ((i & 1) * 2 < kPoly) ? poly_exp2(x0) : fast_exp2(x0);
+            p1 = ((i & 1) * 2 + 1 < kPoly) ? poly_exp2(x1) : fast_exp2(x1);
+          }
+          l_part[i & 7] += p0;
+          l_part[(i + 4) & 7] += p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
         // P columns [16c, 16c+16) alias score columns; the scores are already in registers
         tmem_st_32x16(t_s + c * 16, pk);
       }
       tmem_st_wait();
-      l_run += (l_part[0] + l_part[1]) + (l_part[2] + l_part[3]);
+      l_run += ((l_part[0] + l_part[1]) + (l_part[2] + l_part[3])) + ((l_part[4] + l_part[5]) + (l_part[6] + l_part[7]));
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[w]);
+      FA_PROF_ADD(ps_exp, t0);
     }
+#ifdef FM_FLASH_PROFILE
+    if (a.prof != nullptr && sw == 0 && lane == 0) {
+      long long* pr = a.prof + (long long)blockIdx.x * 16;
+      pr[4] = clock64() - ps_total;
+      pr[5] = ps_wait;
+      pr[6] = 0;
+      pr[7] = ps_max;
+      pr[8] = ps_resc;
+      pr[9] = ps_exp;
+      pr[10] = nb;
+    }
+#endif
     if (ok && nb > 0 && mbar_wait(&o_full[w], (nb - 1) & 1, timeout, abort_flag)) {
       tc_fence_after_sync();
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -622,6 +733,416 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// =========================================================================================
+// Third-generation forward.  Measured on this kernel family: a tcgen05 product whose A and B
+// operands both stream from shared memory (Q.K^T above) needs about 1230 cycles per 128^3, one
+// whose A operand sits in TMEM (P.V) the nominal 512; the shared-memory operand port, not the
+// tensor core, sets the pace.  Q does not change over the key loop, so here it is written to
+// TMEM once and both products take A from TMEM.  One CTA owns ONE 128-row query tile:
+//   TMEM columns: O [0,128) | S_0 [128,256) | S_1 [256,384) | Q (bf16 pairs) [384,448)
+// The two score buffers alternate over key blocks: while softmax group g (four warps, one
+// thread per row) works on block j in S_g, the tensor core already computes block j+1 into the
+// other buffer and P.V of block j-1.  The two groups take even and odd blocks; the running
+// reference maximum of a row is handed from the group of block j to the group of block j+1
+// through shared memory and a named barrier right after the maximum pass, so the exponential
+// passes of consecutive blocks overlap.  Each group keeps its own partial row sum, rescaled
+// whenever it sees a new reference maximum; O is rescaled (rarely: only when the maximum grows
+// by more than 2^8) by the group that detects the growth, between P.V of block j-1 and P.V of
+// block j.  K/V blocks go through three-stage TMA rings.
+// =========================================================================================
+constexpr int kFa3Threads = 384;   // warps 0-3 / 4-7: the two softmax groups; 8: TMA, 9: MMA, 10-11 idle
+constexpr int kFa3Stages = 3;
+constexpr int kKernelIdFlashFwd3 = 23;
+constexpr int kFa3DefaultPoly = 0;
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+// Register re-allocation between warpgroups (four consecutive warps): the producer group gives
+// registers back to the pool, the softmax groups take them.
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void warpgroup_reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
+template <int kPoly>
+__global__ void __launch_bounds__(kFa3Threads, 1)
+flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;                                  // kFa3Stages tiles
+  uint8_t* sV = smem + kFa3Stages * kTileBytes;        // kFa3Stages tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kFa3Stages * kTileBytes);
+  uint64_t* k_full = bars;                       // [3]
+  uint64_t* v_full = bars + kFa3Stages;          // [3]
+  uint64_t* k_empty = bars + 2 * kFa3Stages;     // [3]
+  uint64_t* v_empty = bars + 3 * kFa3Stages;     // [3]
+  uint64_t* s_full = bars + 4 * kFa3Stages;      // [2] per score buffer
+  uint64_t* p_full = s_full + 2;                 // [2]
+  uint64_t* o_full = s_full + 4;                 // [2] by block parity
+  uint64_t* q_ready = s_full + 6;                // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 7);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* m_pub = reinterpret_cast<float*>(s_full + 8);   // [128] reference maximum handed to the next block
+  float* l_x = m_pub + 128;                              // [2][128] partial row sums of the two groups
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = (a.s + kFaBM - 1) / kFaBM;
+  // One-dimensional grid, longest tiles first (tile t costs t + 1 key blocks); neighbouring CTAs
+  // are the query heads of one KV group, which share K/V in L2.
+  const int hq_all = a.G * a.qpg;
+  const int per_tile = hq_all * a.b;
+  const int qt = nq - 1 - (int)blockIdx.x / per_tile;
+  const int rem_lin = (int)blockIdx.x % per_tile;
+  const int h = rem_lin % hq_all, bb = rem_lin / hq_all;
+  const int g_kv = h / a.qpg, hi = h % a.qpg;
+  const int heads_per_group = a.qpg + 2;
+  const int col_q = ((bb * a.G + g_kv) * heads_per_group + hi) * kFaD;
+  const int col_k = ((bb * a.G + g_kv) * heads_per_group + a.qpg) * kFaD;
+  const int col_v = col_k + kFaD;
+  const int nkv = (a.s + kFaBN - 1) / kFaBN;
+  const int nb = min(qt + 1, nkv);
+  const uint64_t timeout = a.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kFa3Stages; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&o_full[i], 1);
+    }
+    mbar_init(q_ready, 8);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap);
+  }
+  if (warp == 9) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr uint32_t kColO = 0, kColS = 128, kColQ = 384;
+
+  if (warp >= 8) {
+  warpgroup_reg_dec<40>();
+  if (warp == 8) {
+    if (lane == 0) {
+      for (int j = 0; j < nb; ++j) {
+        const int st = j % kFa3Stages;
+        const uint32_t ph = ((j / kFa3Stages) & 1) ^ 1;
+        if (!mbar_wait(&k_empty[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd3, 100 + st, 0, 0);
+          break;
+        }
+        mbar_expect_tx(&k_full[st], kTileBytes);
+        tma_load_2d(sK + st * kTileBytes, &tmap, &k_full[st], col_k, j * kFaBN);
+        tma_load_2d(sK + st * kTileBytes + kTileBytes / 2, &tmap, &k_full[st], col_k + 64, j * kFaBN);
+        if (!mbar_wait(&v_empty[st], ph, timeout, abort_flag)) {
+          report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd3, 110 + st, 0, 0);
+          break;
+        }
+        mbar_expect_tx(&v_full[st], kTileBytes);
+        tma_load_2d(sV + st * kTileBytes, &tmap, &v_full[st], col_v, j * kFaBN);
+        tma_load_2d(sV + st * kTileBytes + kTileBytes / 2, &tmap, &v_full[st], col_v + 64, j * kFaBN);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
+      bool ok = true;
+      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
+        if (mbar_wait(bar, parity, timeout, abort_flag)) return true;
+        report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd3, what, 0, 0);
+        return false;
+      };
+      auto issue_qk = [&](int j) {      // S_{j&1} = Q K_j^T, A = Q from TMEM
+        const uint32_t k_addr = smem_u32(sK + (j % kFa3Stages) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
+          umma_bf16_ts(tmem_base + kColS + (j & 1) * 128, tmem_base + kColQ + kk * 8,
+                       umma_smem_desc(k_addr + off, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[j & 1]);
+        umma_commit(&k_empty[j % kFa3Stages]);
+      };
+      auto issue_pv = [&](int j) {      // O += P_{j&1} V_j, A = P from TMEM
+        const uint32_t v_addr = smem_u32(sV + (j % kFa3Stages) * kTileBytes);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16_ts(tmem_base + kColO, tmem_base + kColS + (j & 1) * 128 + kk * 8,
+                       umma_smem_desc(v_addr + kk * 2048, kTileBytes / 2, 1024), idesc_pv,
+                       (j > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(&o_full[j & 1]);
+        umma_commit(&v_empty[j % kFa3Stages]);
+      };
+      [[maybe_unused]] long long pm_total = FA_PROF_NOW(), pm_wait_p = 0, pm_wait_kv = 0;
+      ok = wait_or_fail(q_ready, 0, 200);
+      if (ok) ok = wait_or_fail(&k_full[0], 0, 210);
+      if (ok) {
+        tc_fence_after_sync();
+        issue_qk(0);
+      }
+      for (int j = 0; ok && j < nb; ++j) {
+        if (j + 1 < nb) {
+          // the score buffer of block j+1 held P of block j-1, which P.V(j-1), issued before, consumes
+          [[maybe_unused]] long long t0 = FA_PROF_NOW();
+          ok = wait_or_fail(&k_full[(j + 1) % kFa3Stages], ((j + 1) / kFa3Stages) & 1, 240);
+          FA_PROF_ADD(pm_wait_kv, t0);
+          if (!ok) break;
+          tc_fence_after_sync();
+          issue_qk(j + 1);
+        }
+        [[maybe_unused]] long long t1 = FA_PROF_NOW();
+        ok = wait_or_fail(&v_full[j % kFa3Stages], (j / kFa3Stages) & 1, 230);
+        FA_PROF_ADD(pm_wait_kv, t1);
+        t1 = FA_PROF_NOW();
+        if (ok) ok = wait_or_fail(&p_full[j & 1], (j >> 1) & 1, 220 + (j & 1));
+        FA_PROF_ADD(pm_wait_p, t1);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_pv(j);
+      }
+#ifdef FM_FLASH_PROFILE
+      if (a.prof != nullptr) {
+        long long* pr = a.prof + (long long)blockIdx.x * 16;
+        pr[0] = clock64() - pm_total;
+        pr[1] = pm_wait_p;
+        pr[2] = pm_wait_kv;
+        pr[3] = nb;
+      }
+#endif
+    }
+  }
+  } else {
+    warpgroup_reg_inc<232>();
+    // ------------------------------- softmax warps -------------------------------
+    const int g = warp >> 2;             // softmax group: blocks j with (j & 1) == g
+    const int q = warp & 3;              // TMEM lane quarter
+    const int r = q * 32 + lane;
+    const int row = qt * kFaBM + r;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t t_s = tmem_base + kColS + g * 128 + lane_addr;   // S (fp32) / P (packed bf16)
+    const uint32_t t_o = tmem_base + kColO + lane_addr;
+    // named barriers: 1 + (block parity) * 4 + q hands the maximum from the group of block j to
+    // the group of block j + 1 (32 threads arrive, 32 wait); 9 + q joins both groups at the end
+    bool ok = true;
+    {
+      // this group's half of the Q row (64 bf16, already packed in pairs) straight into TMEM
+      uint32_t qv[32];
+      if (row < a.s) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.qkv + (long long)row * a.row_stride + col_q + g * 64);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const uint4 t = src[u];
+          qv[4 * u] = t.x; qv[4 * u + 1] = t.y; qv[4 * u + 2] = t.z; qv[4 * u + 3] = t.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) qv[i] = 0u;
+      }
+      tmem_st_32x32(tmem_base + kColQ + g * 32 + lane_addr, qv);
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(q_ready);
+    }
+    float m_seen = -INFINITY, l_own = 0.f;
+    const float sc = a.scale_log2;
+    [[maybe_unused]] long long ps_total = FA_PROF_NOW(), ps_wait = 0, ps_max = 0, ps_bar = 0, ps_exp = 0, ps_resc = 0;
+    for (int j = g; j < nb; j += 2) {
+      [[maybe_unused]] long long t0 = FA_PROF_NOW();
+      // After a failed wait the group keeps walking its blocks (without touching TMEM) so that
+      // the other group never waits alone at a named barrier.
+      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s_full[g], (j >> 1) & 1, timeout, abort_flag))) {
+        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd3, 300 + g, 0, 0);
+        ok = false;
+      }
+      if (!ok) {
+        if (j > 0) named_bar_sync(1 + ((j - 1) & 1) * 4 + q, 64);
+        named_bar_arrive(1 + (j & 1) * 4 + q, 64);
+        continue;
+      }
+      tc_fence_after_sync();
+      FA_PROF_ADD(ps_wait, t0);
+      t0 = FA_PROF_NOW();
+      const int kv0 = j * kFaBN;
+      const bool diag = (j == qt);
+      uint32_t sv[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
+      tmem_ld_wait();
+      if (diag || kv0 + kFaBN > a.s) {
+        // only the diagonal block and a ragged last block need masking
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = kv0 + c * 32 + i;
+            if ((diag && col > row) || col >= a.s) sv[c][i] = 0xff800000u;   // -inf
+          }
+      }
+      float mx[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) mx[k] = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          mx[i & 7] = fmax3(mx[i & 7], __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]));
+      const float m_blk =
+          fmaxf(fmax3(mx[0], mx[1], mx[2]), fmax3(fmax3(mx[3], mx[4], mx[5]), mx[6], mx[7])) * sc;   // scale > 0
+      FA_PROF_ADD(ps_max, t0);
+      t0 = FA_PROF_NOW();
+      // the reference maximum after block j-1, from the other group
+      if (j > 0) {
+        named_bar_sync(1 + ((j - 1) & 1) * 4 + q, 64);
+        const float m_prev = m_pub[r];
+        if (m_prev != m_seen) {
+          l_own *= exp2f(m_seen - m_prev);    // m_seen = -inf only while l_own = 0: 0 * 0
+          m_seen = m_prev;
+        }
+      }
+      FA_PROF_ADD(ps_bar, t0);
+      t0 = FA_PROF_NOW();
+      // Lazy rescale: keep the reference maximum unless the block's is more than 2^8 above it.
+      const float m_new = fmaxf(m_seen, m_blk);
+      const bool first = (j == 0);
+      const bool grow = !first && (m_new > m_seen + 8.0f);
+      const float m_old = m_seen;
+      if (first) m_seen = (m_new == -INFINITY) ? 0.f : m_new;
+      if (grow) m_seen = m_new;
+      m_pub[r] = m_seen;
+      named_bar_arrive(1 + (j & 1) * 4 + q, 64);      // the next block's group may go on
+      if (__any_sync(0xffffffffu, grow)) {
+        // O holds the sum of blocks 0..j-1; P.V of block j-1 must have finished before it is touched.
+        if (!__all_sync(0xffffffffu, mbar_wait(&o_full[(j - 1) & 1], ((j - 1) >> 1) & 1, timeout, abort_flag))) {
+          ok = false;
+          continue;
+        }
+        tc_fence_after_sync();
+        const float f = grow ? exp2f(m_old - m_new) : 1.0f;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_o + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tmem_st_32x32(t_o + c * 32, v);
+        }
+        tmem_st_wait();
+        if (grow) l_own *= f;
+      }
+      FA_PROF_ADD(ps_resc, t0);
+      t0 = FA_PROF_NOW();
+      float l_part[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) l_part[k] = 0.f;
+      const float neg_m = -m_seen;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float x0 = fmaf(__uint_as_float(sv[c][2 * i]), sc, neg_m);
+          const float x1 = fmaf(__uint_as_float(sv[c][2 * i + 1]), sc, neg_m);
+          const float p0 = ((i & 1) * 2 < kPoly) ? poly_exp2(x0) : fast_exp2(x0);
+          const float p1 = ((i & 1) * 2 + 1 < kPoly) ? poly_exp2(x1) : fast_exp2(x1);
+          l_part[i & 7] += p0;
+          l_part[(i + 4) & 7] += p1;
+          pk[i] = pack_bf16x2(p0, p1);
+        }
+        tmem_st_32x16(t_s + c * 16, pk);     // P over the scores, which are already in registers
+      }
+      tmem_st_wait();
+      l_own += ((l_part[0] + l_part[1]) + (l_part[2] + l_part[3])) + ((l_part[4] + l_part[5]) + (l_part[6] + l_part[7]));
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[g]);
+      FA_PROF_ADD(ps_exp, t0);
+    }
+#ifdef FM_FLASH_PROFILE
+    if (a.prof != nullptr && warp == 0 && lane == 0) {
+      long long* pr = a.prof + (long long)blockIdx.x * 16;
+      pr[4] = clock64() - ps_total;
+      pr[5] = ps_wait;
+      pr[6] = ps_bar;
+      pr[7] = ps_max;
+      pr[8] = ps_resc;
+      pr[9] = ps_exp;
+      pr[10] = (nb + 1) / 2;
+    }
+#endif
+    // the group that did not own the last block still has to see its reference maximum
+    if (((nb - 1) & 1) != g) {
+      named_bar_sync(1 + ((nb - 1) & 1) * 4 + q, 64);
+      const float m_last = m_pub[r];
+      if (m_last != m_seen) {
+        l_own *= exp2f(m_seen - m_last);
+        m_seen = m_last;
+      }
+    }
+    l_x[g * 128 + r] = l_own;
+    named_bar_sync(9 + q, 64);
+    const float l_run = l_x[r] + l_x[128 + r];
+    if (ok && mbar_wait(&o_full[(nb - 1) & 1], ((nb - 1) >> 1) & 1, timeout, abort_flag)) {
+      tc_fence_after_sync();
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      const int hq = a.G * a.qpg;
+      __nv_bfloat16* dst = a.out + (((long long)row * a.b + bb) * hq + h) * kFaD + g * 64;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {       // this group's half of the head dimension
+        uint32_t v[32];
+        tmem_ld_32x32(t_o + g * 64 + c * 32, v);
+        tmem_ld_wait();
+        if (row < a.s) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
+            reinterpret_cast<uint4*>(dst)[c * 4 + u] = o;
+          }
+        }
+      }
+      if (row < a.s && g == 0)
+        a.lse[((long long)bb * hq + h) * a.s + row] = (m_seen + log2f(l_run)) * 0.6931471805599453f;
+    }
+    tc_fence_before_sync();
+  }
+
+  if (*abort_flag) {
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
@@ -1474,20 +1995,110 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
   a.lse = lse;
   a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
   a.status = status;
-  if (version == 2) {
-    static bool configured2 = false;
-    if (!configured2) {
-      cudaError_t e2 = cudaFuncSetAttribute(fm::flash_fwd2_kernel,
-                                            cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  a.prof = nullptr;
+#ifdef FM_FLASH_PROFILE
+  constexpr int kMaxFwd2Version = 27;
+#else
+  constexpr int kMaxFwd2Version = 24;
+#endif
+  a.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
+  a.row_stride = cols;
+  if (version == 3 || (version >= 30 && version <= 34)) {
+    using Fwd3Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
+    static const Fwd3Fn kFwd3[5] = {fm::flash_fwd3_kernel<0>, fm::flash_fwd3_kernel<1>, fm::flash_fwd3_kernel<2>,
+                                    fm::flash_fwd3_kernel<3>, fm::flash_fwd3_kernel<4>};
+    const int variant = version == 3 ? fm::kFa3DefaultPoly : version - 30;
+    constexpr int smem3 = 2 * fm::kFa3Stages * fm::kTileBytes + 1024 + 2048;
+    static bool configured3[5] = {false, false, false, false, false};
+    if (!configured3[variant]) {
+      cudaError_t e3 = cudaFuncSetAttribute(kFwd3[variant], cudaFuncAttributeMaxDynamicSharedMemorySize, smem3);
+      if (e3 != cudaSuccess) {
+        fm_set_error(cudaGetErrorString(e3));
+        return (int)e3;
+      }
+      configured3[variant] = true;
+    }
+    const int nq3 = (s + fm::kFaBM - 1) / fm::kFaBM;
+    dim3 grid3((unsigned)(nq3 * G * qpg * b), 1, 1);
+#ifdef FM_FLASH_PROFILE
+    static long long* prof3_dev = nullptr;
+    const size_t prof3_n = (size_t)grid3.x * 16;
+    if (getenv("FLUIDMOE_FLASH_PROFILE") != nullptr) {
+      cudaFree(prof3_dev);
+      cudaMalloc(&prof3_dev, prof3_n * sizeof(long long));
+      cudaMemset(prof3_dev, 0, prof3_n * sizeof(long long));
+      a.prof = prof3_dev;
+    }
+#endif
+    kFwd3[variant]<<<grid3, fm::kFa3Threads, smem3, stream>>>(tmap, a);
+#ifdef FM_FLASH_PROFILE
+    if (a.prof != nullptr) {
+      cudaStreamSynchronize(stream);
+      std::vector<long long> hp(prof3_n);
+      cudaMemcpy(hp.data(), prof3_dev, prof3_n * sizeof(long long), cudaMemcpyDeviceToHost);
+      double sum[16] = {0};
+      for (size_t c = 0; c < grid3.x; ++c)
+        for (int k = 0; k < 16; ++k) sum[k] += (double)hp[c * 16 + k];
+      const double mb = sum[3] > 0 ? sum[3] : 1, sb = sum[10] > 0 ? sum[10] : 1;
+      fprintf(stderr,
+              "[flash_fwd3 profile v%d] cycles: mma thread per block %.0f (wait P %.0f, wait K/V %.0f) | softmax "
+              "thread per own block %.0f: wait S %.0f, max pass %.0f, wait other group %.0f, rescale %.0f, exp pass %.0f\n",
+              version, sum[0] / mb, sum[1] / mb, sum[2] / mb, sum[4] / sb, sum[5] / sb, sum[7] / sb, sum[6] / sb,
+              sum[8] / sb, sum[9] / sb);
+    }
+#endif
+  } else if (version == 2 || (version >= 20 && version <= kMaxFwd2Version)) {
+    // versions 20..24 pick the share of polynomial exponentials (0..4 of every 4 pairs)
+    using Fwd2Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
+#ifdef FM_FLASH_PROFILE
+    static const Fwd2Fn kFwd2[8] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<1>, fm::flash_fwd2_kernel<2>,
+                                    fm::flash_fwd2_kernel<3>, fm::flash_fwd2_kernel<4>, fm::flash_fwd2_kernel<5>,
+                                    fm::flash_fwd2_kernel<6>, fm::flash_fwd2_kernel<7>};
+#else
+    static const Fwd2Fn kFwd2[5] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<1>, fm::flash_fwd2_kernel<2>,
+                                    fm::flash_fwd2_kernel<3>, fm::flash_fwd2_kernel<4>};
+#endif
+    const int variant = version == 2 ? fm::kFa2DefaultPoly : version - 20;
+    constexpr int smem2 = smem;
+    static bool configured2[8] = {false, false, false, false, false, false, false, false};
+    if (!configured2[variant]) {
+      cudaError_t e2 = cudaFuncSetAttribute(kFwd2[variant], cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
       if (e2 != cudaSuccess) {
         fm_set_error(cudaGetErrorString(e2));
         return (int)e2;
       }
-      configured2 = true;
+      configured2[variant] = true;
     }
     const int nq = (s + fm::kFaBM - 1) / fm::kFaBM;
     dim3 grid2((unsigned)(((nq + 1) / 2) * G * qpg * b), 1, 1);
-    fm::flash_fwd2_kernel<<<grid2, fm::kFa2Threads, smem, stream>>>(tmap, a);
+#ifdef FM_FLASH_PROFILE
+    // developer build: synchronous launch, then the per-CTA counters averaged over the CTAs
+    static long long* prof_dev = nullptr;
+    const size_t prof_n = (size_t)grid2.x * 16;
+    if (getenv("FLUIDMOE_FLASH_PROFILE") != nullptr) {
+      cudaFree(prof_dev);
+      cudaMalloc(&prof_dev, prof_n * sizeof(long long));
+      cudaMemset(prof_dev, 0, prof_n * sizeof(long long));
+      a.prof = prof_dev;
+    }
+#endif
+    kFwd2[variant]<<<grid2, fm::kFa2Threads, smem2, stream>>>(tmap, a);
+#ifdef FM_FLASH_PROFILE
+    if (a.prof != nullptr) {
+      cudaStreamSynchronize(stream);
+      std::vector<long long> hp(prof_n);
+      cudaMemcpy(hp.data(), prof_dev, prof_n * sizeof(long long), cudaMemcpyDeviceToHost);
+      double sum[16] = {0};
+      for (size_t c = 0; c < grid2.x; ++c)
+        for (int k = 0; k < 16; ++k) sum[k] += (double)hp[c * 16 + k];
+      const double mb = sum[3] > 0 ? sum[3] : 1, sb = sum[10] > 0 ? sum[10] : 1;
+      fprintf(stderr,
+              "[flash_fwd2 profile v%d] per tile-block, cycles: mma thread total %.0f (wait P %.0f, wait K/V %.0f) | "
+              "softmax thread total %.0f: wait S %.0f, (unused %.0f), max pass %.0f, rescale %.0f, exp pass %.0f\n",
+              version, sum[0] / mb, sum[1] / mb, sum[2] / mb, sum[4] / sb, sum[5] / sb, sum[6] / sb, sum[7] / sb,
+              sum[8] / sb, sum[9] / sb);
+    }
+#endif
   } else {
     dim3 grid((s + fm::kFaBM - 1) / fm::kFaBM, G * qpg, b);
     fm::flash_fwd_kernel<<<grid, fm::kFaThreads, smem, stream>>>(tmap, a);

@@ -141,12 +141,12 @@ def case_flash(a):
     sc = 1.0 / math.sqrt(d)
     qkv = _r(s, 1, G, (qpg + 2) * d)
     fl = 4.0 * s * s * G * qpg * d / 2
-    for ver in (2, 1):
+    for ver in a.fwd_versions:
         report(f"flash fwd v{ver} causal s={s} heads={G * qpg}/{G}",
                timed(lambda: flash.flash_attn_fwd_packed(qkv, qpg, d, sc, version=ver)), fl)
     out, lse = flash.flash_attn_fwd_packed(qkv, qpg, d, sc)
     dout = torch.randn_like(out)
-    for ver in (2, 1):
+    for ver in a.bwd_versions:
         report(f"flash bwd v{ver} (delta + main + dq store)",
                timed(lambda: flash.flash_attn_bwd_packed(dout, qkv, out, lse, qpg, d, sc, version=ver)), 2.5 * fl)
     heads = qkv.view(s, 1, G, qpg + 2, d)
@@ -270,6 +270,9 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=2)
     ap.add_argument("--q-per-kv", type=int, default=4)
     ap.add_argument("--elems", type=int, default=1 << 28)
+    ap.add_argument("--fwd-versions", type=int, nargs="+", default=[2, 1],
+                    help="attention forward kernels to time (2: default; 20..24: share of polynomial exponentials; 1: first generation)")
+    ap.add_argument("--bwd-versions", type=int, nargs="+", default=[2, 1])
     a = ap.parse_args(argv)
     torch.manual_seed(0)
     for name in (list(CASES) if a.case == "all" else [a.case]):

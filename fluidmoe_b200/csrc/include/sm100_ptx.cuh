@@ -391,6 +391,83 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t* r)
         "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
 }
+// ---------------------------------------------------------------------------------------
+// Fast issue path.  One thread issues every MMA of a CTA, and that thread executes scalar code
+// at roughly one dependent instruction per 5 cycles: building two 64-bit descriptors and a
+// predicate per MMA (about 30 instructions) costs more than the 64 cycles a 128 x 128 x 16
+// product takes on the tensor core (measured: 150 cycles per MMA with descriptors built in the
+// loop, 65 with the low descriptor words precomputed and straight-line issue).  Within a tile
+// only the start address changes between k-steps, and it sits in the low word, so an issue loop
+// keeps the low words of the eight k-steps in registers, adds a stage offset and joins them
+// with the constant high word.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+// high word: SBO, descriptor version, SWIZZLE_128B
+__host__ __device__ constexpr uint32_t umma_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29);
+}
+__device__ __forceinline__ uint64_t umma_desc_join(uint32_t lo, uint32_t hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+// Low words of the eight k-steps (16 elements each) of a [128 x 128] bf16 operand stored as two
+// 128-byte-swizzled [128 rows x 64] slabs `slab_bytes` apart.
+//   K-major (rows = M or N index, 64 k per slab): step kk starts 32 bytes further along the row.
+//   MN-major (rows = k index, 64 M/N per slab): step kk starts 16 rows further; LBO = slab pitch.
+__device__ __forceinline__ void umma_lo_k_major(uint32_t base, uint32_t slab_bytes, uint32_t (&lo)[8]) {
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) lo[kk] = umma_desc_lo(base + (kk >> 2) * slab_bytes + (kk & 3) * 32, 0);
+}
+__device__ __forceinline__ void umma_lo_mn_major(uint32_t base, uint32_t slab_bytes, uint32_t (&lo)[8]) {
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) lo[kk] = umma_desc_lo(base + kk * 2048, slab_bytes);
+}
+// accumulating MMA with a constant predicate (no register, no setp on a register)
+__device__ __forceinline__ void umma_bf16_acc(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.u32 p, 1, 1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ts_acc(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.u32 p, 1, 1;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate);
+// D (+)= A B over the eight k-steps of a 128-deep product.  `a_add` / `b_add`: stage offset of
+// the operand in 16-byte units; `first_acc`: whether the first step accumulates onto D.
+__device__ __forceinline__ void umma8_ss(uint32_t tmem_d, const uint32_t (&a_lo)[8], uint32_t a_add,
+                                         const uint32_t (&b_lo)[8], uint32_t b_add, uint32_t idesc,
+                                         uint32_t first_acc) {
+  constexpr uint32_t hi = umma_desc_hi(1024);
+  umma_bf16(tmem_d, umma_desc_join(a_lo[0] + a_add, hi), umma_desc_join(b_lo[0] + b_add, hi), idesc, first_acc);
+#pragma unroll
+  for (int kk = 1; kk < 8; ++kk)
+    umma_bf16_acc(tmem_d, umma_desc_join(a_lo[kk] + a_add, hi), umma_desc_join(b_lo[kk] + b_add, hi), idesc);
+}
+// The same with A in TMEM: step kk reads eight 32-bit columns (16 bf16) starting at column
+// (kk / 4) * group_cols + (kk % 4) * 8 of `tmem_a` (group_cols = 32: 64 contiguous columns).
+__device__ __forceinline__ void umma8_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t group_cols,
+                                         const uint32_t (&b_lo)[8], uint32_t b_add, uint32_t idesc,
+                                         uint32_t first_acc) {
+  constexpr uint32_t hi = umma_desc_hi(1024);
+  umma_bf16_ts(tmem_d, tmem_a, umma_desc_join(b_lo[0] + b_add, hi), idesc, first_acc);
+#pragma unroll
+  for (int kk = 1; kk < 8; ++kk)
+    umma_bf16_ts_acc(tmem_d, tmem_a + (kk >> 2) * group_cols + (kk & 3) * 8,
+                     umma_desc_join(b_lo[kk] + b_add, hi), idesc);
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b,
                                              uint32_t idesc, uint32_t accumulate) {

@@ -17,6 +17,7 @@
 #include <cuda_runtime.h>
 #include <cstdio>
 #include <cstdlib>
+#include <type_traits>
 #include <vector>
 #include <math.h>
 #include <stdio.h>
@@ -51,9 +52,16 @@ struct FlashFwdArgs {
 #ifdef FM_FLASH_PROFILE
 #define FA_PROF_NOW() clock64()
 #define FA_PROF_ADD(acc, t0) acc += clock64() - (t0)
+// event trace of CTA 0, key blocks [8, 24): slot (j - 8) * 16 + k behind the per-CTA counters
+#define FA_TRACE(a, j, k)                                                             \
+  do {                                                                                \
+    if ((a).prof != nullptr && blockIdx.x == 0 && (j) >= 8 && (j) < 24)               \
+      (a).prof[(long long)gridDim.x * 16 + ((j) - 8) * 16 + (k)] = clock64();         \
+  } while (0)
 #else
 #define FA_PROF_NOW() 0ll
 #define FA_PROF_ADD(acc, t0) (void)(t0)
+#define FA_TRACE(a, j, k) (void)0
 #endif
 
 __global__ void __launch_bounds__(kFaThreads, 1)
@@ -367,7 +375,9 @@ constexpr int kKernelIdFlashFwd2 = 21;
 constexpr int kFa2DefaultPoly = 0;
 
 // kPoly: of every four value pairs, how many take their exponential from poly_exp2x2.
-template <int kPoly>
+// kUniform: the whole MMA warp walks the issue loop and one elected lane issues, so that the
+// compiler can keep descriptors and loop state in the warp's uniform registers.
+template <int kPoly, bool kUniform = false>
 __global__ void __launch_bounds__(kFa2Threads, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -465,41 +475,59 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (kUniform || lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
       bool ok = true;
-      auto issue_qk = [&](int w, int j) {
-        const uint32_t q_addr = smem_u32(sQ + w * kTileBytes);
-        const uint32_t k_addr = smem_u32(sK + (j & 1) * kTileBytes);
-#ifdef FM_FLASH_PROFILE
-        if constexpr (kPoly != 7)       // timing experiment: P.V only
-#endif
+      // Every operand descriptor of the loop, complete, in registers: the issuing thread shares
+      // its scheduler with two busy softmax warps and gets an issue slot only every 15 to 20
+      // cycles, so each extra instruction per MMA (an address add, a register-pair move) shows
+      // up in the tensor pipe's idle time.  The loop below is specialised on the tile and on
+      // the K/V stage so that every index into these arrays is a compile-time constant.
+      constexpr uint32_t kDescHi = umma_desc_hi(1024);
+      uint64_t qd[2][8], kd[2][8], vd[2][8];
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
-          umma_bf16(tmem_base + w * 128, umma_smem_desc(q_addr + off, 0, 1024),
-                    umma_smem_desc(k_addr + off, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
+      for (int t = 0; t < 2; ++t) {
+        uint32_t lo[8];
+        umma_lo_k_major(smem_u32(sQ + t * kTileBytes), kTileBytes / 2, lo);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) qd[t][kk] = umma_desc_join(lo[kk], kDescHi);
+        umma_lo_k_major(smem_u32(sK + t * kTileBytes), kTileBytes / 2, lo);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) kd[t][kk] = umma_desc_join(lo[kk], kDescHi);
+        umma_lo_mn_major(smem_u32(sV + t * kTileBytes), kTileBytes / 2, lo);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) vd[t][kk] = umma_desc_join(lo[kk], kDescHi);
+      }
+      auto issue_qk = [&](auto w_c, auto st_c) {          // S_w = Q_w K(stage)^T
+        constexpr int W = decltype(w_c)::value, ST = decltype(st_c)::value;
+        const uint32_t d = tmem_base + W * 128;
+        if (!kUniform || elect_one()) {
+          umma_bf16(d, qd[W][0], kd[ST][0], idesc_qk, 0u);
+#pragma unroll
+          for (int kk = 1; kk < 8; ++kk) umma_bf16_acc(d, qd[W][kk], kd[ST][kk], idesc_qk);
+          umma_commit(&s_full[W]);
         }
-        umma_commit(&s_full[w]);
+        if (kUniform) __syncwarp();
       };
-      auto issue_pv = [&](int w, int j) {
-        const uint32_t v_addr = smem_u32(sV + (j & 1) * kTileBytes);
-#ifdef FM_FLASH_PROFILE
-        if constexpr (kPoly != 6)       // timing experiment: Q.K^T only
-#endif
+      auto issue_pv = [&](auto w_c, auto st_c, uint32_t first_acc) {   // O_w (+)= P_w V(stage)
+        constexpr int W = decltype(w_c)::value, ST = decltype(st_c)::value;
+        const uint32_t d = tmem_base + 256 + W * 128, pa = tmem_base + W * 128;
+        if (!kUniform || elect_one()) {
+          umma_bf16_ts(d, pa, vd[ST][0], idesc_pv, first_acc);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ts(tmem_base + 256 + w * 128, tmem_base + w * 128 + kk * 8,
-                       umma_smem_desc(v_addr + kk * 2048, kTileBytes / 2, 1024), idesc_pv,
-                       (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&o_full[w]);
+          for (int kk = 1; kk < 8; ++kk) umma_bf16_ts_acc(d, pa + kk * 8, vd[ST][kk], idesc_pv);
+          umma_commit(&o_full[W]);
+        }
+        if (kUniform) __syncwarp();
       };
       auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
         if (mbar_wait(bar, parity, timeout, abort_flag)) return true;
         report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd2, what, 0, 0);
         return false;
       };
+      using I0 = std::integral_constant<int, 0>;
+      using I1 = std::integral_constant<int, 1>;
       [[maybe_unused]] long long pm_total = FA_PROF_NOW(), pm_wait_p = 0, pm_wait_kv = 0;
       // prologue: S_w(0) for both tiles
       for (int w = 0; ok && w < 2; ++w)
@@ -507,43 +535,54 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       if (ok && nmax > 0) ok = wait_or_fail(&k_full[0], 0, 210);
       if (ok) {
         tc_fence_after_sync();
-        for (int w = 0; w < 2; ++w)
-          if (nblk[w] > 0) issue_qk(w, 0);
-        umma_commit(&k_empty[0]);
+        if (nblk[0] > 0) issue_qk(I0{}, I0{});
+        if (nblk[1] > 0) issue_qk(I1{}, I0{});
+        if (!kUniform || elect_one()) umma_commit(&k_empty[0]);
       }
-      for (int j = 0; ok && j < nmax; ++j) {
-        const int st = j & 1;
+      // one key block of both tiles, K/V stage ST (compile time)
+      auto step = [&](auto st_c, int j) {
+        constexpr int ST = decltype(st_c)::value;
+        using SN = std::integral_constant<int, ST ^ 1>;
         const uint32_t ph = (j >> 1) & 1;
         [[maybe_unused]] long long t0 = FA_PROF_NOW();
-        ok = wait_or_fail(&v_full[st], ph, 230 + st);
+        if (!wait_or_fail(&v_full[ST], ph, 230 + ST)) return false;
         FA_PROF_ADD(pm_wait_kv, t0);
         bool k_next_ready = false;
-        for (int w = 0; ok && w < 2; ++w) {
-          if (j >= nblk[w]) continue;
+        auto tile = [&](auto w_c) {
+          constexpr int W = decltype(w_c)::value;
+          if (j >= nblk[W]) return true;
           t0 = FA_PROF_NOW();
-          ok = wait_or_fail(&p_full[w], j & 1, 220 + w);
+          FA_TRACE(a, j, W * 8 + 0);                    // MMA thread starts waiting for P_w(j)
+          if (!wait_or_fail(&p_full[W], j & 1, 220 + W)) return false;
           FA_PROF_ADD(pm_wait_p, t0);
-          if (!ok) break;
+          FA_TRACE(a, j, W * 8 + 1);                    // ... has it
           tc_fence_after_sync();
-          issue_pv(w, j);
-          if (j + 1 < nblk[w]) {
+          issue_pv(w_c, st_c, j > 0 ? 1u : 0u);
+          FA_TRACE(a, j, W * 8 + 2);                    // P.V issued
+          if (j + 1 < nblk[W]) {
             if (!k_next_ready) {
               t0 = FA_PROF_NOW();
-              ok = wait_or_fail(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 240);
+              if (!wait_or_fail(&k_full[ST ^ 1], ((j + 1) >> 1) & 1, 240)) return false;
               FA_PROF_ADD(pm_wait_kv, t0);
-              if (!ok) break;
               tc_fence_after_sync();
               k_next_ready = true;
             }
-            issue_qk(w, j + 1);
+            issue_qk(w_c, SN{});
+            FA_TRACE(a, j, W * 8 + 3);                  // Q.K^T of the next block issued
           }
+          return true;
+        };
+        if (!tile(I0{})) return false;
+        if (!tile(I1{})) return false;
+        if (!kUniform || elect_one()) {
+          umma_commit(&v_empty[ST]);
+          if (j + 1 < nmax) umma_commit(&k_empty[ST ^ 1]);
         }
-        if (!ok) break;
-        umma_commit(&v_empty[st]);
-        if (j + 1 < nmax) umma_commit(&k_empty[(j + 1) & 1]);
-      }
+        return true;
+      };
+      for (int j = 0; ok && j < nmax; ++j) ok = (j & 1) ? step(I1{}, j) : step(I0{}, j);
 #ifdef FM_FLASH_PROFILE
-      if (a.prof != nullptr) {
+      if (a.prof != nullptr && lane == 0) {
         long long* pr = a.prof + (long long)blockIdx.x * 16;
         pr[0] = clock64() - pm_total;
         pr[1] = pm_wait_p;
@@ -554,11 +593,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
     }
   } else {
     // ------------------------------- softmax warps -------------------------------
-    // One thread per query row.  The score row (128 fp32 values in TMEM) is streamed twice in
-    // chunks of 32 columns with the next chunk's load in flight behind the current chunk's
-    // arithmetic: once for the row maximum, once for the exponentials.  Holding only two chunks
-    // in registers (instead of the whole row) leaves the compiler room to interleave the
-    // special-function and the polynomial exponentials of many value pairs.
+    // One thread per query row; the row's 128 scores of a key block stay in registers.
     const int sw = warp - 2;
     const int w = sw >> 2;               // which query tile this warp owns
     const int q = warp & 3;              // TMEM lane quarter
@@ -581,6 +616,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       }
       tc_fence_after_sync();
       FA_PROF_ADD(ps_wait, t0);
+      if (lane == 0 && q == 2 % 4) FA_TRACE(a, j, w * 8 + 4);      // softmax has S_w(j)
       t0 = FA_PROF_NOW();
       const int kv0 = j * kFaBN;
       // only the diagonal block and a ragged last block need masking
@@ -614,6 +650,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       const float m_raw = fmaxf(fmax3(mx[0], mx[1], mx[2]), fmax3(fmax3(mx[3], mx[4], mx[5]), mx[6], mx[7]));
       const float m_blk = m_raw * a.scale_log2;   // scale > 0
       FA_PROF_ADD(ps_max, t0);
+      if (lane == 0 && q == 2 % 4) FA_TRACE(a, j, w * 8 + 5);      // maximum done
       t0 = FA_PROF_NOW();
       // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 above it.
       const float m_new = fmaxf(m_used, m_blk);
@@ -661,7 +698,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
           const float x1 = fmaf(__uint_as_float(sv[c][2 * i + 1]), sc, neg_m);
           float p0, p1;
 #ifdef FM_FLASH_PROFILE
-          if constexpr (kPoly >= 5) {           // timing experiments of developer builds: no exponential
+          if constexpr (kPoly == 5) {           // timing experiment of developer builds: no exponential
             p0 = x0;
             p1 = x1;
           } else
@@ -684,6 +721,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[w]);
+      if (lane == 0 && q == 2 % 4) FA_TRACE(a, j, w * 8 + 6);      // P_w(j) handed over
       FA_PROF_ADD(ps_exp, t0);
     }
 #ifdef FM_FLASH_PROFILE
@@ -845,7 +883,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
   constexpr uint32_t kColO = 0, kColS = 128, kColQ = 384;
 
   if (warp >= 8) {
-  warpgroup_reg_dec<40>();
+  warpgroup_reg_dec<72>();
   if (warp == 8) {
     if (lane == 0) {
       for (int j = 0; j < nb; ++j) {
@@ -877,24 +915,19 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd3, what, 0, 0);
         return false;
       };
+      uint32_t k_lo[8], v_lo[8];      // low descriptor words of the eight k-steps, stage 0
+      umma_lo_k_major(smem_u32(sK), kTileBytes / 2, k_lo);
+      umma_lo_mn_major(smem_u32(sV), kTileBytes / 2, v_lo);
+      constexpr uint32_t kTileAdd = kTileBytes >> 4;
       auto issue_qk = [&](int j) {      // S_{j&1} = Q K_j^T, A = Q from TMEM
-        const uint32_t k_addr = smem_u32(sK + (j % kFa3Stages) * kTileBytes);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (kk >> 2) * (kTileBytes / 2) + (kk & 3) * 32;
-          umma_bf16_ts(tmem_base + kColS + (j & 1) * 128, tmem_base + kColQ + kk * 8,
-                       umma_smem_desc(k_addr + off, 0, 1024), idesc_qk, kk > 0 ? 1u : 0u);
-        }
+        umma8_ts(tmem_base + kColS + (j & 1) * 128, tmem_base + kColQ, 32, k_lo, (j % kFa3Stages) * kTileAdd,
+                 idesc_qk, 0u);
         umma_commit(&s_full[j & 1]);
         umma_commit(&k_empty[j % kFa3Stages]);
       };
       auto issue_pv = [&](int j) {      // O += P_{j&1} V_j, A = P from TMEM
-        const uint32_t v_addr = smem_u32(sV + (j % kFa3Stages) * kTileBytes);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ts(tmem_base + kColO, tmem_base + kColS + (j & 1) * 128 + kk * 8,
-                       umma_smem_desc(v_addr + kk * 2048, kTileBytes / 2, 1024), idesc_pv,
-                       (j > 0 || kk > 0) ? 1u : 0u);
+        umma8_ts(tmem_base + kColO, tmem_base + kColS + (j & 1) * 128, 32, v_lo, (j % kFa3Stages) * kTileAdd,
+                 idesc_pv, j > 0 ? 1u : 0u);
         umma_commit(&o_full[j & 1]);
         umma_commit(&v_empty[j % kFa3Stages]);
       };
@@ -937,7 +970,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
     }
   }
   } else {
-    warpgroup_reg_inc<232>();
+    warpgroup_reg_inc<216>();
     // ------------------------------- softmax warps -------------------------------
     const int g = warp >> 2;             // softmax group: blocks j with (j & 1) == g
     const int q = warp & 3;              // TMEM lane quarter
@@ -1624,28 +1657,31 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, false, false);   // A K-major, B K-major
       constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, true, true);     // A MN-major, B MN-major
       constexpr uint32_t id_km = umma_idesc_bf16(128, 128, false, true);    // A K-major / TMEM, B MN-major
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aS = smem_u32(sdS), aO = smem_u32(sdO);
       constexpr uint32_t HALF = kTileBytes / 2;
-      auto kdesc = [&](uint32_t base, int kk) {   // K-major operand, k-step kk of 8
-        return umma_smem_desc(base + (kk >> 2) * HALF + (kk & 3) * 32, 0, 1024);
-      };
-      auto mdesc = [&](uint32_t base, int kk) {   // MN-major operand ([128 k rows][64] slabs)
-        return umma_smem_desc(base + kk * 2048, HALF, 1024);
-      };
+      constexpr uint32_t kTileAdd = kTileBytes >> 4;
+      // low descriptor words of the eight k-steps of every operand in both of its roles
+      // (K-major: the tile's rows are the M / N index; MN-major: the tile's rows are the k index)
+      uint32_t k_km[8], v_km[8], q_km[8], o_km[8], s_km[8], k_mn[8], q_mn[8], o_mn[8], s_mn[8];
+      umma_lo_k_major(smem_u32(sK), HALF, k_km);
+      umma_lo_k_major(smem_u32(sV), HALF, v_km);
+      umma_lo_k_major(smem_u32(sQ), HALF, q_km);      // stage 0; stage 1 is one tile further
+      umma_lo_k_major(smem_u32(sdO), HALF, o_km);
+      umma_lo_k_major(smem_u32(sdS), HALF, s_km);
+      umma_lo_mn_major(smem_u32(sK), HALF, k_mn);
+      umma_lo_mn_major(smem_u32(sQ), HALF, q_mn);
+      umma_lo_mn_major(smem_u32(sdO), HALF, o_mn);
+      umma_lo_mn_major(smem_u32(sdS), HALF, s_mn);
       auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
         if (mbar_wait(bar, parity, timeout, abort_flag)) return true;
         report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, what, 0, 0);
         return false;
       };
       auto issue_s = [&](int n) {     // S^T(n) = K Q(n)^T
-        const uint32_t aQ = smem_u32(sQ + (n & 1) * kTileBytes);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_s, kdesc(aK, kk), kdesc(aQ, kk), id_kk, kk > 0);
+        umma8_ss(t_s, k_km, 0, q_km, (n & 1) * kTileAdd, id_kk, 0u);
         umma_commit(s_full);
       };
       auto issue_dp = [&]() {         // dP^T(n) = V dO(n)^T
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dp, kdesc(aV, kk), kdesc(aO, kk), id_kk, kk > 0);
+        umma8_ss(t_dp, v_km, 0, o_km, 0, id_kk, 0u);
         umma_commit(dp_full);
       };
       bool ok = wait_or_fail(kv_full, 0, 200);
@@ -1658,14 +1694,11 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       }
       for (int n = 0; ok && n < nsteps; ++n) {
         const uint32_t par = n & 1;
-        const uint32_t aQ = smem_u32(sQ + (n & 1) * kTileBytes);
         if (!(ok = wait_or_fail(p_full, par, 210))) break;
         tc_fence_after_sync();
         // dV += P^T dO, A from TMEM: query positions 0-63 sit in columns [0, 32) of the S^T block,
         // positions 64-127 in columns [64, 96) (each softmax warp writes over its own scores)
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_bf16_ts(t_dv, t_s + (kk >> 2) * 64 + (kk & 3) * 8, mdesc(aO, kk), id_km, (n > 0 || kk > 0));
+        umma8_ts(t_dv, t_s, 64, o_mn, 0, id_km, n > 0 ? 1u : 0u);
         umma_commit(do_empty);
         if (n + 1 < nsteps) {
           if (!(ok = wait_or_fail(&q_full[(n + 1) & 1], ((n + 1) >> 1) & 1, 220))) break;
@@ -1676,11 +1709,9 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         tc_fence_after_sync();
         // dQ first: its drain (and then dP^T of the next step, which re-uses the columns) is on the
         // critical path, dK is not
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dp, mdesc(aS, kk), mdesc(aK, kk), id_mm, kk > 0);
+        umma8_ss(t_dp, s_mn, 0, k_mn, 0, id_mm, 0u);
         umma_commit(dq_full);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(t_dk, kdesc(aS, kk), mdesc(aQ, kk), id_km, (n > 0 || kk > 0));
+        umma8_ss(t_dk, s_km, 0, q_mn, (n & 1) * kTileAdd, id_km, n > 0 ? 1u : 0u);
         umma_commit(&q_empty[n & 1]);
         if (n + 1 < nsteps) {
           if (!(ok = wait_or_fail(do_full, par ^ 1, 235))) break;
@@ -1996,11 +2027,7 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
   a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
   a.status = status;
   a.prof = nullptr;
-#ifdef FM_FLASH_PROFILE
-  constexpr int kMaxFwd2Version = 27;
-#else
-  constexpr int kMaxFwd2Version = 24;
-#endif
+  constexpr int kMaxFwd2Version = 26;
   a.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
   a.row_stride = cols;
   if (version == 3 || (version >= 30 && version <= 34)) {
@@ -2050,14 +2077,16 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
   } else if (version == 2 || (version >= 20 && version <= kMaxFwd2Version)) {
     // versions 20..24 pick the share of polynomial exponentials (0..4 of every 4 pairs)
     using Fwd2Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
-#ifdef FM_FLASH_PROFILE
+    // 20..24: share of polynomial exponentials; 25: developer timing experiment; 26: the whole MMA warp
+    // walks the issue loop (uniform issue)
     static const Fwd2Fn kFwd2[8] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<1>, fm::flash_fwd2_kernel<2>,
-                                    fm::flash_fwd2_kernel<3>, fm::flash_fwd2_kernel<4>, fm::flash_fwd2_kernel<5>,
-                                    fm::flash_fwd2_kernel<6>, fm::flash_fwd2_kernel<7>};
+                                    fm::flash_fwd2_kernel<3>, fm::flash_fwd2_kernel<4>,
+#ifdef FM_FLASH_PROFILE
+                                    fm::flash_fwd2_kernel<5>,
 #else
-    static const Fwd2Fn kFwd2[5] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<1>, fm::flash_fwd2_kernel<2>,
-                                    fm::flash_fwd2_kernel<3>, fm::flash_fwd2_kernel<4>};
+                                    fm::flash_fwd2_kernel<0>,
 #endif
+                                    fm::flash_fwd2_kernel<0, true>, fm::flash_fwd2_kernel<0, true>};
     const int variant = version == 2 ? fm::kFa2DefaultPoly : version - 20;
     constexpr int smem2 = smem;
     static bool configured2[8] = {false, false, false, false, false, false, false, false};
@@ -2074,7 +2103,7 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
 #ifdef FM_FLASH_PROFILE
     // developer build: synchronous launch, then the per-CTA counters averaged over the CTAs
     static long long* prof_dev = nullptr;
-    const size_t prof_n = (size_t)grid2.x * 16;
+    const size_t prof_n = (size_t)grid2.x * 16 + 16 * 16;
     if (getenv("FLUIDMOE_FLASH_PROFILE") != nullptr) {
       cudaFree(prof_dev);
       cudaMalloc(&prof_dev, prof_n * sizeof(long long));
@@ -2092,6 +2121,17 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
       for (size_t c = 0; c < grid2.x; ++c)
         for (int k = 0; k < 16; ++k) sum[k] += (double)hp[c * 16 + k];
       const double mb = sum[3] > 0 ? sum[3] : 1, sb = sum[10] > 0 ? sum[10] : 1;
+      {
+        const long long* tr = hp.data() + (size_t)grid2.x * 16;
+        const long long base = tr[0];
+        const char* ev[8] = {"mma:waitP", "mma:gotP", "mma:PVissued", "mma:QKissued", "smx:gotS", "smx:max", "smx:Pdone", ""};
+        for (int jj = 0; jj < 6; ++jj)
+          for (int w = 0; w < 2; ++w) {
+            fprintf(stderr, "  trace block %d tile %d:", jj + 8, w);
+            for (int e = 0; e < 7; ++e) fprintf(stderr, " %s=%lld", ev[e], tr[jj * 16 + w * 8 + e] - base);
+            fprintf(stderr, "\n");
+          }
+      }
       fprintf(stderr,
               "[flash_fwd2 profile v%d] per tile-block, cycles: mma thread total %.0f (wait P %.0f, wait K/V %.0f) | "
               "softmax thread total %.0f: wait S %.0f, (unused %.0f), max pass %.0f, rescale %.0f, exp pass %.0f\n",

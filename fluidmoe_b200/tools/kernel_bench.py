@@ -252,7 +252,20 @@ def case_fused(a):
     report(f"FC2 + combine (scatter epilogue) + unpermute {rows}x{F}x{H}", timed(fc2), 2.0 * rows * F * H)
 
 
-CASES = dict(gemm=case_gemm, fc1=case_fc1, dact=case_dact, wgrad=case_wgrad, wgrad_adam=case_wgrad_adam, flash=case_flash, norm=case_norm,
+def case_mma_issue(a):
+    """Builds and runs the stand-alone MMA issue probe (``mma_issue_probe.cu`` next to this file)."""
+    import subprocess
+    import tempfile
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = os.path.join(tempfile.mkdtemp(), "mma_issue_probe")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    subprocess.run([f"{cuda}/bin/nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
+                    "-I", os.path.join(os.path.dirname(here), "csrc", "include"), "-o", exe,
+                    os.path.join(here, "mma_issue_probe.cu"), "-lcuda"], check=True)
+    print(subprocess.run([exe, "64"], check=True, capture_output=True, text=True).stdout, flush=True)
+
+
+CASES = dict(mma_issue=case_mma_issue, gemm=case_gemm, fc1=case_fc1, dact=case_dact, wgrad=case_wgrad, wgrad_adam=case_wgrad_adam, flash=case_flash, norm=case_norm,
              permute=case_permute, adam=case_adam, ce=case_ce, rope=case_rope, fused=case_fused)
 
 

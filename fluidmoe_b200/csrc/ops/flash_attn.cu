@@ -372,7 +372,7 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 
 constexpr int kFa2Threads = 320;   // TMA warp, MMA warp, 4 + 4 softmax warps
 constexpr int kKernelIdFlashFwd2 = 21;
-constexpr int kFa2DefaultPoly = 0;
+constexpr int kFa2DefaultPoly = 6;    // index into the launcher's table: uniform issue, no polynomial share
 
 // kPoly: of every four value pairs, how many take their exponential from poly_exp2x2.
 // kUniform: the whole MMA warp walks the issue loop and one elected lane issues, so that the
@@ -1653,7 +1653,8 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {   // the whole warp walks the issue loop (uniform control flow keeps descriptors and loop
+        // state in the warp's uniform registers); one elected lane issues the MMAs and commits
       constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, false, false);   // A K-major, B K-major
       constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, true, true);     // A MN-major, B MN-major
       constexpr uint32_t id_km = umma_idesc_bf16(128, 128, false, true);    // A K-major / TMEM, B MN-major
@@ -1672,17 +1673,23 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       umma_lo_mn_major(smem_u32(sdO), HALF, o_mn);
       umma_lo_mn_major(smem_u32(sdS), HALF, s_mn);
       auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
-        if (mbar_wait(bar, parity, timeout, abort_flag)) return true;
+        if (__all_sync(0xffffffffu, mbar_wait(bar, parity, timeout, abort_flag))) return true;
         report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, what, 0, 0);
         return false;
       };
       auto issue_s = [&](int n) {     // S^T(n) = K Q(n)^T
-        umma8_ss(t_s, k_km, 0, q_km, (n & 1) * kTileAdd, id_kk, 0u);
-        umma_commit(s_full);
+        if (elect_one()) {
+          umma8_ss(t_s, k_km, 0, q_km, (n & 1) * kTileAdd, id_kk, 0u);
+          umma_commit(s_full);
+        }
+        __syncwarp();
       };
       auto issue_dp = [&]() {         // dP^T(n) = V dO(n)^T
-        umma8_ss(t_dp, v_km, 0, o_km, 0, id_kk, 0u);
-        umma_commit(dp_full);
+        if (elect_one()) {
+          umma8_ss(t_dp, v_km, 0, o_km, 0, id_kk, 0u);
+          umma_commit(dp_full);
+        }
+        __syncwarp();
       };
       bool ok = wait_or_fail(kv_full, 0, 200);
       if (ok && nsteps > 0) ok = wait_or_fail(&q_full[0], 0, 201);
@@ -1698,8 +1705,11 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         tc_fence_after_sync();
         // dV += P^T dO, A from TMEM: query positions 0-63 sit in columns [0, 32) of the S^T block,
         // positions 64-127 in columns [64, 96) (each softmax warp writes over its own scores)
-        umma8_ts(t_dv, t_s, 64, o_mn, 0, id_km, n > 0 ? 1u : 0u);
-        umma_commit(do_empty);
+        if (elect_one()) {
+          umma8_ts(t_dv, t_s, 64, o_mn, 0, id_km, n > 0 ? 1u : 0u);
+          umma_commit(do_empty);
+        }
+        __syncwarp();
         if (n + 1 < nsteps) {
           if (!(ok = wait_or_fail(&q_full[(n + 1) & 1], ((n + 1) >> 1) & 1, 220))) break;
           tc_fence_after_sync();
@@ -1709,10 +1719,13 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         tc_fence_after_sync();
         // dQ first: its drain (and then dP^T of the next step, which re-uses the columns) is on the
         // critical path, dK is not
-        umma8_ss(t_dp, s_mn, 0, k_mn, 0, id_mm, 0u);
-        umma_commit(dq_full);
-        umma8_ss(t_dk, s_km, 0, q_mn, (n & 1) * kTileAdd, id_km, n > 0 ? 1u : 0u);
-        umma_commit(&q_empty[n & 1]);
+        if (elect_one()) {
+          umma8_ss(t_dp, s_mn, 0, k_mn, 0, id_mm, 0u);
+          umma_commit(dq_full);
+          umma8_ss(t_dk, s_km, 0, q_mn, (n & 1) * kTileAdd, id_km, n > 0 ? 1u : 0u);
+          umma_commit(&q_empty[n & 1]);
+        }
+        __syncwarp();
         if (n + 1 < nsteps) {
           if (!(ok = wait_or_fail(do_full, par ^ 1, 235))) break;
           if (!(ok = wait_or_fail(dq_read, par, 240))) break;
@@ -1720,7 +1733,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
           issue_dp();
         }
       }
-      if (ok) umma_commit(done_full);
+      if (ok && elect_one()) umma_commit(done_full);
     }
   } else if (warp < 10) {
     // ---- softmax warps: thread (r, hf) owns key/value position j*128 + r and query positions

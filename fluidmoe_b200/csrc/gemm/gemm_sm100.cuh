@@ -596,8 +596,28 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
     }
   } else if (warp == 1) {
     // ------------------------------- MMA issuer (leader CTA only) -------------------------------
-    if (lane == 0 && leader) {
+    // The whole warp walks the loop and one elected lane issues: with uniform control flow the
+    // compiler keeps loop state and descriptors in the warp's uniform registers, and the issuing
+    // warp, which shares its scheduler with busy epilogue warps, spends fewer issue slots per MMA.
+    // The low descriptor words of the k-steps of stage 0 are computed once; a stage adds its
+    // byte offset / 16 and the constant high word is joined on.
+    if (leader) {
       constexpr uint32_t idesc = umma_idesc_bf16(2 * kBM, BN, A_MN, B_MN);
+      constexpr int kSteps = kBK / 16;
+      constexpr uint32_t kDescHi = umma_desc_hi(1024);
+      constexpr uint32_t kStageAdd = STAGE_BYTES >> 4;
+      uint32_t a_lo[kSteps], b_lo[kSteps];
+      {
+        const uint32_t sa0 = smem_u32(smem), sb0 = sa0 + A_BYTES;
+#pragma unroll
+        for (int k = 0; k < kSteps; ++k) {
+          a_lo[k] = A_MN ? umma_desc_lo(sa0 + k * 2048, 64 * kBK * 2) : umma_desc_lo(sa0 + k * 32, 0);
+          b_lo[k] = B_MN ? umma_desc_lo(sb0 + k * 2048, 64 * kBK * 2) : umma_desc_lo(sb0 + k * 32, 0);
+        }
+      }
+      auto wait_all = [&](uint64_t* bar, uint32_t parity) {
+        return __all_sync(0xffffffffu, mbar_wait(bar, parity, timeout, abort_flag)) != 0;
+      };
       TileWalker<BN, 2 * kBM> walker(args);
       Tile t;
       int stage = 0;
@@ -606,42 +626,38 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int ti = pair_id; ok && walker.get(ti, t); ti += num_pairs) {
-        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, timeout, abort_flag)) {
-          report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 200 + acc, 0, 0);
+        if (!wait_all(&tempty[acc], acc_phase ^ 1)) {
+          if (lane == 0) report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 200 + acc, 0, 0);
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < t.nk; ++kb) {
-          if (!mbar_wait(&full[stage], phase, timeout, abort_flag)) {
-            report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 300 + stage, 0, 0);
+          if (!wait_all(&full[stage], phase)) {
+            if (lane == 0) report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 300 + stage, 0, 0);
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sb = sa + A_BYTES;
+          if (elect_one()) {
+            const uint32_t sadd = stage * kStageAdd;
+            umma2_bf16(d_tmem, umma_desc_join(a_lo[0] + sadd, kDescHi), umma_desc_join(b_lo[0] + sadd, kDescHi), idesc,
+                       kb > 0 ? 1u : 0u);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k) {
-            uint64_t da, db;
-            if constexpr (!A_MN)
-              da = umma_smem_desc(sa + k * 32, 0, 1024);
-            else
-              da = umma_smem_desc(sa + k * 2048, 64 * kBK * 2, 1024);
-            if constexpr (!B_MN)
-              db = umma_smem_desc(sb + k * 32, 0, 1024);
-            else
-              db = umma_smem_desc(sb + k * 2048, 64 * kBK * 2, 1024);
-            umma2_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            for (int k = 1; k < kSteps; ++k)
+              umma2_bf16_acc(d_tmem, umma_desc_join(a_lo[k] + sadd, kDescHi), umma_desc_join(b_lo[k] + sadd, kDescHi),
+                             idesc);
+            umma2_commit_mc(&empty[stage], 3);   // frees the stage in both CTAs
           }
-          umma2_commit_mc(&empty[stage], 3);   // frees the stage in both CTAs
+          __syncwarp();
           if (++stage == kStages2) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma2_commit_mc(&tfull[acc], 3);
+        if (elect_one()) umma2_commit_mc(&tfull[acc], 3);
+        __syncwarp();
         if (++acc == 2) {
           acc = 0;
           acc_phase ^= 1;

@@ -349,6 +349,15 @@ __device__ __forceinline__ void umma2_bf16(uint32_t tmem_d, uint64_t desc_a, uin
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// accumulating form with a constant predicate (see the fast issue path below)
+__device__ __forceinline__ void umma2_bf16_acc(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.u32 p, 1, 1;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc)
+      : "memory");
+}
 // Arrive on the barrier at this shared-memory offset in every CTA of `cta_mask` once the MMAs
 // issued so far have completed.
 __device__ __forceinline__ void umma2_commit_mc(uint64_t* bar, uint16_t cta_mask) {

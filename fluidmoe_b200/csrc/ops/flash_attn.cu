@@ -777,23 +777,23 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
 }
 
 // =========================================================================================
-// Third-generation forward.  Measured on this kernel family: a tcgen05 product whose A and B
-// operands both stream from shared memory (Q.K^T above) needs about 1230 cycles per 128^3, one
-// whose A operand sits in TMEM (P.V) the nominal 512; the shared-memory operand port, not the
-// tensor core, sets the pace.  Q does not change over the key loop, so here it is written to
-// TMEM once and both products take A from TMEM.  One CTA owns ONE 128-row query tile:
-//   TMEM columns: O [0,128) | S_0 [128,256) | S_1 [256,384) | Q (bf16 pairs) [384,448)
-// The two score buffers alternate over key blocks: while softmax group g (four warps, one
-// thread per row) works on block j in S_g, the tensor core already computes block j+1 into the
-// other buffer and P.V of block j-1.  The two groups take even and odd blocks; the running
+// Third-generation forward.  What the cycle counters and the event trace of the second
+// generation showed: the softmax of a tile (about 1900 cycles per key block) sits in series
+// with the tile's own two products, because P is written over S and the next Q.K^T can only
+// follow P.V.  Here one CTA owns ONE 128-row query tile and P has columns of its own:
+//   TMEM columns: O [0,128) | S_0 [128,256) | S_1 [256,384) | P_0 [384,448) | P_1 [448,512)
+// Two softmax groups (four warps each, one thread per row) take the even and the odd key
+// blocks.  A group reads its score block into registers and releases the buffer at once, so the
+// tensor core computes the scores of block j+2 while the group is still busy with the
+// exponentials of block j; when it has finished, its next scores are waiting.  The running
 // reference maximum of a row is handed from the group of block j to the group of block j+1
-// through shared memory and a named barrier right after the maximum pass, so the exponential
-// passes of consecutive blocks overlap.  Each group keeps its own partial row sum, rescaled
-// whenever it sees a new reference maximum; O is rescaled (rarely: only when the maximum grows
-// by more than 2^8) by the group that detects the growth, between P.V of block j-1 and P.V of
-// block j.  K/V blocks go through three-stage TMA rings.
+// through shared memory and a named barrier right after the maximum pass.  Each group keeps
+// its own partial row sum, rescaled whenever it sees a new reference maximum; O is rescaled
+// (rarely: only when the maximum grows by more than 2^8) by the group that detects the growth,
+// between P.V of block j-1 and P.V of block j.  K/V blocks go through three-stage TMA rings; the
+// MMA warp walks its loop as a whole and one elected lane issues.
 // =========================================================================================
-constexpr int kFa3Threads = 384;   // warps 0-3 / 4-7: the two softmax groups; 8: TMA, 9: MMA, 10-11 idle
+constexpr int kFa3Threads = 384;   // warps 0-3 / 4-7: the two softmax groups; 8: TMA, 9 / 10: MMA issue, 11 idle
 constexpr int kFa3Stages = 3;
 constexpr int kKernelIdFlashFwd3 = 23;
 constexpr int kFa3DefaultPoly = 0;
@@ -821,9 +821,10 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sK = smem;                                  // kFa3Stages tiles
-  uint8_t* sV = smem + kFa3Stages * kTileBytes;        // kFa3Stages tiles
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 2 * kFa3Stages * kTileBytes);
+  uint8_t* sQ = smem;                                        // one tile
+  uint8_t* sK = smem + kTileBytes;                           // kFa3Stages tiles
+  uint8_t* sV = smem + (1 + kFa3Stages) * kTileBytes;        // kFa3Stages tiles
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (1 + 2 * kFa3Stages) * kTileBytes);
   uint64_t* k_full = bars;                       // [3]
   uint64_t* v_full = bars + kFa3Stages;          // [3]
   uint64_t* k_empty = bars + 2 * kFa3Stages;     // [3]
@@ -831,10 +832,11 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
   uint64_t* s_full = bars + 4 * kFa3Stages;      // [2] per score buffer
   uint64_t* p_full = s_full + 2;                 // [2]
   uint64_t* o_full = s_full + 4;                 // [2] by block parity
-  uint64_t* q_ready = s_full + 6;                // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 7);
+  uint64_t* q_full = s_full + 6;                 // [1]
+  uint64_t* s_free = s_full + 7;                 // [2] the group has its score block in registers
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 9);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* m_pub = reinterpret_cast<float*>(s_full + 8);   // [128] reference maximum handed to the next block
+  float* m_pub = reinterpret_cast<float*>(s_full + 10);  // [128] reference maximum handed to the next block
   float* l_x = m_pub + 128;                              // [2][128] partial row sums of the two groups
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -866,8 +868,9 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);
       mbar_init(&o_full[i], 1);
+      mbar_init(&s_free[i], 4);
     }
-    mbar_init(q_ready, 8);
+    mbar_init(q_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap);
@@ -880,12 +883,15 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  constexpr uint32_t kColO = 0, kColS = 128, kColQ = 384;
+  constexpr uint32_t kColO = 0, kColS = 128, kColP = 384;
 
   if (warp >= 8) {
-  warpgroup_reg_dec<72>();
+  warpgroup_reg_dec<96>();
   if (warp == 8) {
     if (lane == 0) {
+      mbar_expect_tx(q_full, kTileBytes);
+      tma_load_2d(sQ, &tmap, q_full, col_q, qt * kFaBM);
+      tma_load_2d(sQ + kTileBytes / 2, &tmap, q_full, col_q + 64, qt * kFaBM);
       for (int j = 0; j < nb; ++j) {
         const int st = j % kFa3Stages;
         const uint32_t ph = ((j / kFa3Stages) & 1) ^ 1;
@@ -905,49 +911,59 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         tma_load_2d(sV + st * kTileBytes + kTileBytes / 2, &tmap, &v_full[st], col_v + 64, j * kFaBN);
       }
     }
-  } else if (warp == 9) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
-      bool ok = true;
-      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
-        if (mbar_wait(bar, parity, timeout, abort_flag)) return true;
-        report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd3, what, 0, 0);
-        return false;
-      };
-      uint32_t k_lo[8], v_lo[8];      // low descriptor words of the eight k-steps, stage 0
+  } else if (warp == 9 || warp == 10) {
+    // Two issuing warps on two schedulers: warp 9 issues the score products, warp 10 the P.V
+    // products.  The two streams touch different accumulators and are ordered only through the
+    // barriers below, and an issuing warp that shares its scheduler with two busy softmax warps
+    // needs about 85 cycles per MMA: one warp could not issue the sixteen MMAs of a key block in
+    // the 1024 cycles the tensor core needs for them.
+    constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
+    constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
+    constexpr uint32_t kTileAdd = kTileBytes >> 4;
+    bool ok = true;
+    auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
+      if (__all_sync(0xffffffffu, mbar_wait(bar, parity, timeout, abort_flag))) return true;
+      if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd3, what, 0, 0);
+      return false;
+    };
+    [[maybe_unused]] long long pm_total = FA_PROF_NOW(), pm_wait_p = 0, pm_wait_kv = 0;
+    if (warp == 9) {
+      uint32_t q_lo[8], k_lo[8];      // low descriptor words of the eight k-steps, stage 0
+      umma_lo_k_major(smem_u32(sQ), kTileBytes / 2, q_lo);
       umma_lo_k_major(smem_u32(sK), kTileBytes / 2, k_lo);
-      umma_lo_mn_major(smem_u32(sV), kTileBytes / 2, v_lo);
-      constexpr uint32_t kTileAdd = kTileBytes >> 4;
-      auto issue_qk = [&](int j) {      // S_{j&1} = Q K_j^T, A = Q from TMEM
-        umma8_ts(tmem_base + kColS + (j & 1) * 128, tmem_base + kColQ, 32, k_lo, (j % kFa3Stages) * kTileAdd,
-                 idesc_qk, 0u);
-        umma_commit(&s_full[j & 1]);
-        umma_commit(&k_empty[j % kFa3Stages]);
-      };
-      auto issue_pv = [&](int j) {      // O += P_{j&1} V_j, A = P from TMEM
-        umma8_ts(tmem_base + kColO, tmem_base + kColS + (j & 1) * 128, 32, v_lo, (j % kFa3Stages) * kTileAdd,
-                 idesc_pv, j > 0 ? 1u : 0u);
-        umma_commit(&o_full[j & 1]);
-        umma_commit(&v_empty[j % kFa3Stages]);
-      };
-      [[maybe_unused]] long long pm_total = FA_PROF_NOW(), pm_wait_p = 0, pm_wait_kv = 0;
-      ok = wait_or_fail(q_ready, 0, 200);
-      if (ok) ok = wait_or_fail(&k_full[0], 0, 210);
-      if (ok) {
-        tc_fence_after_sync();
-        issue_qk(0);
-      }
-      for (int j = 0; ok && j < nb; ++j) {
-        if (j + 1 < nb) {
-          // the score buffer of block j+1 held P of block j-1, which P.V(j-1), issued before, consumes
-          [[maybe_unused]] long long t0 = FA_PROF_NOW();
-          ok = wait_or_fail(&k_full[(j + 1) % kFa3Stages], ((j + 1) / kFa3Stages) & 1, 240);
-          FA_PROF_ADD(pm_wait_kv, t0);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_qk(j + 1);
+      auto issue_qk = [&](int j) {      // S_{j&1} = Q K_j^T
+        if (elect_one()) {
+          umma8_ss(tmem_base + kColS + (j & 1) * 128, q_lo, 0, k_lo, (j % kFa3Stages) * kTileAdd, idesc_qk, 0u);
+          umma_commit(&s_full[j & 1]);
+          umma_commit(&k_empty[j % kFa3Stages]);
         }
+        __syncwarp();
+      };
+      ok = wait_or_fail(q_full, 0, 200);
+      for (int j = 0; ok && j < nb; ++j) {
+        // blocks 0 and 1 find their buffers free; block j >= 2 follows the group of block j - 2,
+        // which releases the buffer as soon as it has the scores in registers
+        [[maybe_unused]] long long t0 = FA_PROF_NOW();
+        if (j >= 2) ok = wait_or_fail(&s_free[j & 1], ((j - 2) >> 1) & 1, 250 + (j & 1));
+        if (ok) ok = wait_or_fail(&k_full[j % kFa3Stages], (j / kFa3Stages) & 1, 240);
+        FA_PROF_ADD(pm_wait_kv, t0);
+        if (!ok) break;
+        tc_fence_after_sync();
+        issue_qk(j);
+      }
+    } else {
+      uint32_t v_lo[8];
+      umma_lo_mn_major(smem_u32(sV), kTileBytes / 2, v_lo);
+      auto issue_pv = [&](int j) {      // O += P_{j&1} V_j, A = P from TMEM
+        if (elect_one()) {
+          umma8_ts(tmem_base + kColO, tmem_base + kColP + (j & 1) * 64, 32, v_lo, (j % kFa3Stages) * kTileAdd,
+                   idesc_pv, j > 0 ? 1u : 0u);
+          umma_commit(&o_full[j & 1]);
+          umma_commit(&v_empty[j % kFa3Stages]);
+        }
+        __syncwarp();
+      };
+      for (int j = 0; ok && j < nb; ++j) {
         [[maybe_unused]] long long t1 = FA_PROF_NOW();
         ok = wait_or_fail(&v_full[j % kFa3Stages], (j / kFa3Stages) & 1, 230);
         FA_PROF_ADD(pm_wait_kv, t1);
@@ -959,7 +975,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         issue_pv(j);
       }
 #ifdef FM_FLASH_PROFILE
-      if (a.prof != nullptr) {
+      if (a.prof != nullptr && lane == 0) {
         long long* pr = a.prof + (long long)blockIdx.x * 16;
         pr[0] = clock64() - pm_total;
         pr[1] = pm_wait_p;
@@ -970,38 +986,19 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
     }
   }
   } else {
-    warpgroup_reg_inc<216>();
+    warpgroup_reg_inc<200>();
     // ------------------------------- softmax warps -------------------------------
     const int g = warp >> 2;             // softmax group: blocks j with (j & 1) == g
     const int q = warp & 3;              // TMEM lane quarter
     const int r = q * 32 + lane;
     const int row = qt * kFaBM + r;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t t_s = tmem_base + kColS + g * 128 + lane_addr;   // S (fp32) / P (packed bf16)
+    const uint32_t t_s = tmem_base + kColS + g * 128 + lane_addr;   // this group's score buffer (fp32)
+    const uint32_t t_p = tmem_base + kColP + g * 64 + lane_addr;    // this group's P buffer (bf16 pairs)
     const uint32_t t_o = tmem_base + kColO + lane_addr;
     // named barriers: 1 + (block parity) * 4 + q hands the maximum from the group of block j to
     // the group of block j + 1 (32 threads arrive, 32 wait); 9 + q joins both groups at the end
     bool ok = true;
-    {
-      // this group's half of the Q row (64 bf16, already packed in pairs) straight into TMEM
-      uint32_t qv[32];
-      if (row < a.s) {
-        const uint4* src = reinterpret_cast<const uint4*>(a.qkv + (long long)row * a.row_stride + col_q + g * 64);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const uint4 t = src[u];
-          qv[4 * u] = t.x; qv[4 * u + 1] = t.y; qv[4 * u + 2] = t.z; qv[4 * u + 3] = t.w;
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) qv[i] = 0u;
-      }
-      tmem_st_32x32(tmem_base + kColQ + g * 32 + lane_addr, qv);
-      tmem_st_wait();
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(q_ready);
-    }
     float m_seen = -INFINITY, l_own = 0.f;
     const float sc = a.scale_log2;
     [[maybe_unused]] long long ps_total = FA_PROF_NOW(), ps_wait = 0, ps_max = 0, ps_bar = 0, ps_exp = 0, ps_resc = 0;
@@ -1027,6 +1024,9 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
 #pragma unroll
       for (int c = 0; c < 4; ++c) tmem_ld_32x32(t_s + c * 32, sv[c]);
       tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[g]);      // the buffer may take the scores of block j + 2
       if (diag || kv0 + kFaBN > a.s) {
         // only the diagonal block and a ragged last block need masking
 #pragma unroll
@@ -1091,6 +1091,11 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       }
       FA_PROF_ADD(ps_resc, t0);
       t0 = FA_PROF_NOW();
+      // P.V of block j - 2 read this group's P buffer; it has to be done before P is overwritten
+      if (j >= 2 && !__all_sync(0xffffffffu, mbar_wait(&o_full[g], ((j >> 1) - 1) & 1, timeout, abort_flag))) {
+        ok = false;
+        continue;
+      }
       float l_part[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k) l_part[k] = 0.f;
@@ -1108,7 +1113,7 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
           l_part[(i + 4) & 7] += p1;
           pk[i] = pack_bf16x2(p0, p1);
         }
-        tmem_st_32x16(t_s + c * 16, pk);     // P over the scores, which are already in registers
+        tmem_st_32x16(t_p + c * 16, pk);
       }
       tmem_st_wait();
       l_own += ((l_part[0] + l_part[1]) + (l_part[2] + l_part[3])) + ((l_part[4] + l_part[5]) + (l_part[6] + l_part[7]));
@@ -1534,7 +1539,7 @@ flash_bwd_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
 // TMEM: S^T/P^T, dP^T/dQ, dV, dK = 512 columns.  The softmax scale is applied once at the end
 // (to dK here, to dQ in the store kernel).
 // =========================================================================================
-constexpr int kFaB2Threads = 448;   // TMA warp, MMA warp, 8 softmax warps, 4 dQ-drain warps
+constexpr int kFaB2Threads = 480;   // TMA warp, MMA warp A, 8 softmax warps, 4 dQ-drain warps, MMA warp B
 constexpr int kKernelIdFlashBwd2 = 23;
 constexpr int kFaB2StageBytes = 4 * 2 * 4096;   // per drain warp: two [32 rows][32 fp32] boxes
 constexpr int kFaB2Smem = 6 * kTileBytes + kFaB2StageBytes + 2 * 2 * 128 * 4 + 256;
@@ -1599,14 +1604,14 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       mbar_init(&stats_full[i], 128);
     }
     mbar_init(do_full, 1);
-    mbar_init(do_empty, 1);
+    mbar_init(do_empty, 2);       // dV (issuing warp A) and dP^T (issuing warp B) have read dO
     mbar_init(s_full, 1);
     mbar_init(p_full, 8);
     mbar_init(dp_full, 1);
     mbar_init(ds_full, 8);
     mbar_init(dq_full, 1);
     mbar_init(dq_read, 4);
-    mbar_init(done_full, 1);
+    mbar_init(done_full, 2);      // both issuing warps
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_qkv);
@@ -1652,31 +1657,32 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         tma_load_2d(sdO + kTileBytes / 2, &tmap_do, do_full, col_do + 64, i * kFaBM);
       }
     }
-  } else if (warp == 1) {
-    {   // the whole warp walks the issue loop (uniform control flow keeps descriptors and loop
-        // state in the warp's uniform registers); one elected lane issues the MMAs and commits
-      constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, false, false);   // A K-major, B K-major
-      constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, true, true);     // A MN-major, B MN-major
-      constexpr uint32_t id_km = umma_idesc_bf16(128, 128, false, true);    // A K-major / TMEM, B MN-major
-      constexpr uint32_t HALF = kTileBytes / 2;
-      constexpr uint32_t kTileAdd = kTileBytes >> 4;
-      // low descriptor words of the eight k-steps of every operand in both of its roles
-      // (K-major: the tile's rows are the M / N index; MN-major: the tile's rows are the k index)
-      uint32_t k_km[8], v_km[8], q_km[8], o_km[8], s_km[8], k_mn[8], q_mn[8], o_mn[8], s_mn[8];
+  } else if (warp == 1 || warp == 14) {
+    // Two issuing warps on two schedulers, each walking its loop as a whole with one elected lane
+    // issuing (uniform control flow keeps descriptors and loop state in uniform registers):
+    //   warp 1:  S^T(n) = K Q^T and dV += P^T dO       (P^T sits over S^T, so the two stay in order)
+    //   warp 14: dP^T(n) = V dO^T, dQ = dS K, dK += dS^T Q   (dQ sits over dP^T, likewise)
+    // An issuing warp shares its scheduler with busy softmax warps and needs about 85 cycles per
+    // MMA; one warp could not issue the forty MMAs of a step in the 2560 cycles the tensor core
+    // needs for them.  The two streams are ordered against each other only through barriers.
+    constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, false, false);   // A K-major, B K-major
+    constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, true, true);     // A MN-major, B MN-major
+    constexpr uint32_t id_km = umma_idesc_bf16(128, 128, false, true);    // A K-major / TMEM, B MN-major
+    constexpr uint32_t HALF = kTileBytes / 2;
+    constexpr uint32_t kTileAdd = kTileBytes >> 4;
+    auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
+      if (__all_sync(0xffffffffu, mbar_wait(bar, parity, timeout, abort_flag))) return true;
+      if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, what, 0, 0);
+      return false;
+    };
+    bool ok = wait_or_fail(kv_full, 0, 200);
+    if (warp == 1) {
+      // low descriptor words of the eight k-steps (K-major: the tile's rows are the M / N index;
+      // MN-major: the tile's rows are the k index)
+      uint32_t k_km[8], q_km[8], o_mn[8];
       umma_lo_k_major(smem_u32(sK), HALF, k_km);
-      umma_lo_k_major(smem_u32(sV), HALF, v_km);
       umma_lo_k_major(smem_u32(sQ), HALF, q_km);      // stage 0; stage 1 is one tile further
-      umma_lo_k_major(smem_u32(sdO), HALF, o_km);
-      umma_lo_k_major(smem_u32(sdS), HALF, s_km);
-      umma_lo_mn_major(smem_u32(sK), HALF, k_mn);
-      umma_lo_mn_major(smem_u32(sQ), HALF, q_mn);
       umma_lo_mn_major(smem_u32(sdO), HALF, o_mn);
-      umma_lo_mn_major(smem_u32(sdS), HALF, s_mn);
-      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
-        if (__all_sync(0xffffffffu, mbar_wait(bar, parity, timeout, abort_flag))) return true;
-        report_status(a.status, kStatusMbarTimeout, kKernelIdFlashBwd2, what, 0, 0);
-        return false;
-      };
       auto issue_s = [&](int n) {     // S^T(n) = K Q(n)^T
         if (elect_one()) {
           umma8_ss(t_s, k_km, 0, q_km, (n & 1) * kTileAdd, id_kk, 0u);
@@ -1684,24 +1690,13 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
         }
         __syncwarp();
       };
-      auto issue_dp = [&]() {         // dP^T(n) = V dO(n)^T
-        if (elect_one()) {
-          umma8_ss(t_dp, v_km, 0, o_km, 0, id_kk, 0u);
-          umma_commit(dp_full);
-        }
-        __syncwarp();
-      };
-      bool ok = wait_or_fail(kv_full, 0, 200);
       if (ok && nsteps > 0) ok = wait_or_fail(&q_full[0], 0, 201);
-      if (ok && nsteps > 0) ok = wait_or_fail(do_full, 0, 202);
       if (ok && nsteps > 0) {
         tc_fence_after_sync();
         issue_s(0);
-        issue_dp();
       }
       for (int n = 0; ok && n < nsteps; ++n) {
-        const uint32_t par = n & 1;
-        if (!(ok = wait_or_fail(p_full, par, 210))) break;
+        if (!(ok = wait_or_fail(p_full, n & 1, 210))) break;
         tc_fence_after_sync();
         // dV += P^T dO, A from TMEM: query positions 0-63 sit in columns [0, 32) of the S^T block,
         // positions 64-127 in columns [64, 96) (each softmax warp writes over its own scores)
@@ -1715,6 +1710,30 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
           tc_fence_after_sync();
           issue_s(n + 1);
         }
+      }
+    } else {
+      uint32_t v_km[8], o_km[8], s_km[8], k_mn[8], q_mn[8], s_mn[8];
+      umma_lo_k_major(smem_u32(sV), HALF, v_km);
+      umma_lo_k_major(smem_u32(sdO), HALF, o_km);
+      umma_lo_k_major(smem_u32(sdS), HALF, s_km);
+      umma_lo_mn_major(smem_u32(sK), HALF, k_mn);
+      umma_lo_mn_major(smem_u32(sQ), HALF, q_mn);     // stage 0; stage 1 is one tile further
+      umma_lo_mn_major(smem_u32(sdS), HALF, s_mn);
+      auto issue_dp = [&]() {         // dP^T(n) = V dO(n)^T
+        if (elect_one()) {
+          umma8_ss(t_dp, v_km, 0, o_km, 0, id_kk, 0u);
+          umma_commit(dp_full);
+          umma_commit(do_empty);
+        }
+        __syncwarp();
+      };
+      if (ok && nsteps > 0) ok = wait_or_fail(do_full, 0, 202);
+      if (ok && nsteps > 0) {
+        tc_fence_after_sync();
+        issue_dp();
+      }
+      for (int n = 0; ok && n < nsteps; ++n) {
+        const uint32_t par = n & 1;
         if (!(ok = wait_or_fail(ds_full, par, 230))) break;
         tc_fence_after_sync();
         // dQ first: its drain (and then dP^T of the next step, which re-uses the columns) is on the
@@ -1733,8 +1752,9 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
           issue_dp();
         }
       }
-      if (ok && elect_one()) umma_commit(done_full);
     }
+    if (ok && elect_one()) umma_commit(done_full);
+    __syncwarp();
   } else if (warp < 10) {
     // ---- softmax warps: thread (r, hf) owns key/value position j*128 + r and query positions
     //      [hf*64, hf*64 + 64) of the step's tile ----
@@ -1868,7 +1888,7 @@ flash_bwd2_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_con
       }
     }
     tc_fence_before_sync();
-  } else {
+  } else if (warp < 14) {
     // ---- dQ drain warps: warp `q` owns query rows [32q, 32q + 32) of the step's tile and moves them
     //      in two halves of 64 columns: TMEM -> registers -> two swizzled [32 rows][32 fp32] boxes in
     //      shared memory -> TMA reduce-add into the fp32 dQ buffer. ----
@@ -2048,7 +2068,7 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
     static const Fwd3Fn kFwd3[5] = {fm::flash_fwd3_kernel<0>, fm::flash_fwd3_kernel<1>, fm::flash_fwd3_kernel<2>,
                                     fm::flash_fwd3_kernel<3>, fm::flash_fwd3_kernel<4>};
     const int variant = version == 3 ? fm::kFa3DefaultPoly : version - 30;
-    constexpr int smem3 = 2 * fm::kFa3Stages * fm::kTileBytes + 1024 + 2048;
+    constexpr int smem3 = (1 + 2 * fm::kFa3Stages) * fm::kTileBytes + 1024 + 2048;
     static bool configured3[5] = {false, false, false, false, false};
     if (!configured3[variant]) {
       cudaError_t e3 = cudaFuncSetAttribute(kFwd3[variant], cudaFuncAttributeMaxDynamicSharedMemorySize, smem3);

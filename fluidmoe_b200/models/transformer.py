@@ -146,7 +146,7 @@ class TransformerLayerFunction(torch.autograd.Function):
                         from ..parallel.fused_dropless import build_device_plan
                         rplan = build_device_plan(top_idx, top_probs, L.num_experts)
                         combined, st = fused.dropless.forward(fused._buf(ep), ep, rplan, ln2_out, w1, w2, act,
-                                                              save_pre)
+                                                              save_pre, needs_grad)
                     else:
                         rplan = moe_dropless.build_plan(top_idx, top_probs, L.num_experts, L.ep_group)
                         combined, st = moe_dropless.forward(rplan, ln2_out, w1, w2, act, L.ep_group, save_pre)

@@ -155,7 +155,8 @@ class DroplessExchange:
         lib.gemm_launch(desc, _native.stream_ptr())
 
     # ------------------------------------------------------------------ forward
-    def forward(self, b: _DroplessBuffers, ep, plan: DeviceDroplessPlan, x, w1, w2, activation, save_pre):
+    def forward(self, b: _DroplessBuffers, ep, plan: DeviceDroplessPlan, x, w1, w2, activation, save_pre,
+                needs_grad=None):
         """Returns ``(combined [T*k, H] in permuted order (complete only after ``wait_combined``),
         state for backward)``."""
         from ..models.moe import MoEForwardState
@@ -180,7 +181,9 @@ class DroplessExchange:
                               group_rows=b.group_rows, group_offs=b.group_offs, save_pre=save_pre,
                               gate=self._gate(b, b.flags_fwd), act_out=act, pre_out=pre)
         b.flags_fwd.local.zero_()
-        if save_pre:
+        if save_pre if needs_grad is None else needs_grad:
+            # the weight-gradient GEMM reads whole 128-row groups: rows behind a group's last token
+            # must be zero (they meet zero gradient rows, but uninitialised memory may hold NaN)
             self._zero_padding(b, act)
         self._scatter(b, ep, act, w2, "kn", b.combined, b.cnt_combine_tbl)
         return b.combined.local, MoEForwardState(b.tokens_em.local, b.probs_em.local, pre, act)

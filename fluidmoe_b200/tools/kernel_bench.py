@@ -265,7 +265,19 @@ def case_mma_issue(a):
     print(subprocess.run([exe, "64"], check=True, capture_output=True, text=True).stdout, flush=True)
 
 
-CASES = dict(mma_issue=case_mma_issue, gemm=case_gemm, fc1=case_fc1, dact=case_dact, wgrad=case_wgrad, wgrad_adam=case_wgrad_adam, flash=case_flash, norm=case_norm,
+def case_softmax_pass(a):
+    """Builds and runs the stand-alone probe of the softmax exponential pass (``softmax_pass_probe.cu``)."""
+    import subprocess
+    import tempfile
+    here = os.path.dirname(os.path.abspath(__file__))
+    exe = os.path.join(tempfile.mkdtemp(), "softmax_pass_probe")
+    cuda = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    subprocess.run([f"{cuda}/bin/nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-o", exe,
+                    os.path.join(here, "softmax_pass_probe.cu")], check=True)
+    print(subprocess.run([exe], check=True, capture_output=True, text=True).stdout, flush=True)
+
+
+CASES = dict(mma_issue=case_mma_issue, softmax_pass=case_softmax_pass, gemm=case_gemm, fc1=case_fc1, dact=case_dact, wgrad=case_wgrad, wgrad_adam=case_wgrad_adam, flash=case_flash, norm=case_norm,
              permute=case_permute, adam=case_adam, ce=case_ce, rope=case_rope, fused=case_fused)
 
 

@@ -916,7 +916,8 @@ template <class Epi>
 static int dispatch_gate(const FmGemmDesc* d, const CUtensorMap& ta, const CUtensorMap& tb,
                          const GemmArgs& args, const Epi& epi, int grid, cudaStream_t s) {
   if (d->gate_flags != nullptr && d->gate_k_blocks_per_src > 0) {
-    GateKSource g{d->gate_flags, d->gate_k_blocks_per_src, d->gate_blocks_per_group};
+    GateKSource g{d->gate_flags, d->gate_k_blocks_per_src, d->gate_blocks_per_group,
+                  d->gate_expected > 0 ? d->gate_expected : 1};
     return dispatch_shape(d, ta, tb, args, epi, g, grid, s);
   }
   if (d->gate_flags != nullptr) {

@@ -177,6 +177,7 @@ struct GateKSource {
   const int* flags;
   int kblocks_per_src;
   int row_blocks;      // 128-row blocks per source
+  int units_per_row;   // arrivals counted per row (1: whole rows; h: a row arrives head by head)
   __device__ __forceinline__ bool wait(const Tile&, const GemmArgs&, volatile int*) const {
     return true;
   }
@@ -187,10 +188,11 @@ struct GateKSource {
     const int idx = src * row_blocks + (t.row_base + t.m0) / kBM;
     int observed = 0;
     const uint64_t t0 = a.wait_ns ? global_timer_ns() : 0;
-    const bool ok = flag_wait_ge(flags + idx, t.rows_valid, a.timeout_ns, abort_flag, &observed);
+    const int want = t.rows_valid * units_per_row;
+    const bool ok = flag_wait_ge(flags + idx, want, a.timeout_ns, abort_flag, &observed);
     if (a.wait_ns) atomicAdd(a.wait_ns, (unsigned long long)(global_timer_ns() - t0));
     if (ok) return true;
-    report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, 10000 + idx, t.rows_valid, observed);
+    report_status(a.status, kStatusFlagTimeout, kKernelIdGemm, 10000 + idx, want, observed);
     return false;
   }
 };

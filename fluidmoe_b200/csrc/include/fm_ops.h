@@ -63,6 +63,14 @@ int fm_moe_plan(const long long* top_idx, const float* top_probs, int T, int k, 
 int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg, int d,
                       float scale, unsigned long long timeout_ns, int* status, int version,
                       cudaStream_t stream);
+// The same with the HP -> SP exchange in the epilogue: every output row is also stored into
+// push_dst[owner] ([rows per rank, push_P * heads * d], this rank's head columns) and
+// push_flags[owner][push_me * push_row_blocks + block] is raised by the rows written (batch 1,
+// 128 | push_sl, default kernel only).  push_dst == null: no exchange.
+int fm_flash_attn_fwd_push(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg, int d,
+                           float scale, unsigned long long timeout_ns, int* status, int version,
+                           void* const* push_dst, int* const* push_flags, int push_me, int push_P,
+                           int push_sl, int push_row_blocks, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

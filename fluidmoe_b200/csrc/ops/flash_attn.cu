@@ -46,6 +46,13 @@ struct FlashFwdArgs {
   long long* prof;       // developer builds (FM_FLASH_PROFILE): per-CTA cycle counters, else null
   const __nv_bfloat16* qkv;   // packed projection buffer (third-generation kernel reads Q rows itself)
   long long row_stride;       // elements between consecutive sequence positions
+  // Optional HP -> SP exchange in the epilogue (batch 1, 128 | rows per rank): every output row is
+  // also stored into the `attn_in` buffer of the rank that owns its sequence position, at this
+  // rank's head columns, and the owner's arrival counter of the row's 128-row block and of this
+  // source is raised by the number of rows written (once per warp and head).
+  __nv_bfloat16* const* push_dst;   // [P] peers' attn_in [rows per rank, P * heads * d], or null
+  int* const* push_flags;           // [P] peers' counters [P * row_blocks]
+  int push_me, push_P, push_sl, push_row_blocks;
 };
 
 // Cycle counters of one softmax thread and of the MMA thread, per CTA (developer builds only).
@@ -741,6 +748,13 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       const int hq = a.G * a.qpg;
       __nv_bfloat16* dst = a.out + (((long long)row * a.b + bb) * hq + h) * kFaD;
+      // HP -> SP in the epilogue: the row also goes to the rank that owns its sequence position
+      const int push_p = a.push_dst != nullptr ? row / a.push_sl : 0;
+      const int push_i = row - push_p * a.push_sl;
+      uint4* push_to = nullptr;
+      if (a.push_dst != nullptr && row < a.s)
+        push_to = reinterpret_cast<uint4*>(a.push_dst[push_p] + (long long)push_i * a.push_P * hq * kFaD +
+                                           ((long long)a.push_me * hq + h) * kFaD);
 #pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
@@ -755,11 +769,21 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
             o.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
             o.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
             reinterpret_cast<uint4*>(dst)[c * 4 + u] = o;
+            if (push_to != nullptr) push_to[c * 4 + u] = o;
           }
         }
       }
       if (row < a.s)
         a.lse[((long long)bb * hq + h) * a.s + row] = (m_used + log2f(l_run)) * 0.6931471805599453f;
+      if (a.push_dst != nullptr) {
+        // one release per warp: its 32 rows share the owner and the 128-row block
+        const int row0 = row - lane;
+        __syncwarp();
+        if (lane == 0 && row0 < a.s) {
+          __threadfence_system();
+          flag_release_add(a.push_flags[push_p] + a.push_me * a.push_row_blocks + push_i / 128, min(32, a.s - row0));
+        }
+      }
     }
     tc_fence_before_sync();
   }
@@ -2353,9 +2377,21 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg,
-                                 int d, float scale, unsigned long long timeout_ns, int* status,
-                                 int version, cudaStream_t stream) {
+extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg, int d,
+                                 float scale, unsigned long long timeout_ns, int* status, int version,
+                                 cudaStream_t stream) {
+  return fm_flash_attn_fwd_push(qkv, out, lse, s, b, G, qpg, d, scale, timeout_ns, status, version, nullptr, nullptr,
+                                0, 1, 0, 0, stream);
+}
+
+extern "C" int fm_flash_attn_fwd_push(const void* qkv, void* out, float* lse, int s, int b, int G, int qpg, int d,
+                                      float scale, unsigned long long timeout_ns, int* status, int version,
+                                      void* const* push_dst, int* const* push_flags, int push_me, int push_P,
+                                      int push_sl, int push_row_blocks, cudaStream_t stream) {
+  if (push_dst != nullptr && (version != 2 || b != 1 || push_sl <= 0 || push_sl % 128 != 0 || push_P * push_sl != s)) {
+    fm_set_error("flash_attn_fwd: the epilogue exchange needs the default kernel, batch 1 and 128 | rows per rank");
+    return -1;
+  }
   if (d != fm::kFaD) {
     fm_set_error("flash_attn_fwd: head_dim must be 128");
     return -1;
@@ -2410,6 +2446,9 @@ extern "C" int fm_flash_attn_fwd(const void* qkv, void* out, float* lse, int s, 
   constexpr int kMaxFwd2Version = 26;
   a.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
   a.row_stride = cols;
+  a.push_dst = reinterpret_cast<__nv_bfloat16* const*>(push_dst);
+  a.push_flags = push_flags;
+  a.push_me = push_me; a.push_P = push_P; a.push_sl = push_sl; a.push_row_blocks = push_row_blocks;
   if (version == 4 || (version >= 40 && version <= 44)) {
     using Fwd4Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
     static const Fwd4Fn kFwd4[5] = {fm::flash_fwd4_kernel<0>, fm::flash_fwd4_kernel<1>, fm::flash_fwd4_kernel<2>,

@@ -57,6 +57,13 @@ void bind_ops(py::module_& m) {
     chk(fm_flash_attn_fwd(p<const void*>(qkv), p<void*>(out), p<float*>(lse), s_, b, G, qpg, d, scale,
                           timeout_ns, p<int*>(status), version, st(s)), "flash_attn_fwd");
   });
+  m.def("flash_attn_fwd_push", [](u qkv, u out, u lse, int s_, int b, int G, int qpg, int d, float scale,
+                                  unsigned long long timeout_ns, u status, int version, u push_dst, u push_flags,
+                                  int me, int P, int sl, int row_blocks, u s) {
+    chk(fm_flash_attn_fwd_push(p<const void*>(qkv), p<void*>(out), p<float*>(lse), s_, b, G, qpg, d, scale,
+                               timeout_ns, p<int*>(status), version, p<void* const*>(push_dst),
+                               p<int* const*>(push_flags), me, P, sl, row_blocks, st(s)), "flash_attn_fwd_push");
+  });
   m.def("cross_entropy", [](u logits, u labels, u loss, int T, int V, float scale, u s) {
     chk(fm_cross_entropy(p<void*>(logits), p<const long long*>(labels), p<float*>(loss), T, V, scale, st(s)),
         "cross_entropy");

@@ -129,8 +129,8 @@ def qkv_projection_forward(x: torch.Tensor, qkv_weight: torch.Tensor, plan: CPPl
 
 
 def output_projection_forward(attn_out: torch.Tensor, proj_weight: torch.Tensor, plan: CPPlan,
-                              mode: str = "a2a", fused_ctx=None, residual: Optional[torch.Tensor] = None
-                              ) -> Tuple[torch.Tensor, torch.Tensor]:
+                              mode: str = "a2a", fused_ctx=None, residual: Optional[torch.Tensor] = None,
+                              pushed: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """attn_out ``[s, b, h_local, d]`` -> ``(out [s_local*b, H], attn_input_full [s_local*b, n_h*d])``.
 
     ``residual`` (same shape as out) is added in the GEMM epilogue when given.
@@ -154,7 +154,7 @@ def output_projection_forward(attn_out: torch.Tensor, proj_weight: torch.Tensor,
         a_full = attn_out.reshape(T, dpr)
         return with_residual(a_full, proj_weight), a_full
     if mode == "fused":
-        return fused_ctx.hp2sp_outproj(attn_out, proj_weight, plan, residual)
+        return fused_ctx.hp2sp_outproj(attn_out, proj_weight, plan, residual, pushed)
     if mode == "a2a":
         a_full = comm.hp2sp(attn_out, plan.group).view(T, P * dpr)
         return with_residual(a_full, proj_weight), a_full

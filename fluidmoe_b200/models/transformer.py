@@ -15,6 +15,7 @@ explicit attention backward (no saved autograd sub-graph) and a CPU/gloo executi
 from __future__ import annotations
 
 import math
+import os
 from typing import Callable, Optional, Union
 
 import torch
@@ -116,11 +117,15 @@ class TransformerLayerFunction(torch.autograd.Function):
             if rotary is not None:
                 rope.rope_packed_(qkv_full, rotary, cp.q_per_group, cp.head_dim)
             G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
+            # with the device-initiated transport the attention kernel's epilogue stores every output
+            # row at its sequence owner as well (when the shape allows), so no push kernel follows
+            push = (fused.attention_push_args(cp, qkv_full)
+                    if mode_attn == "fused" and cp.cp_size > 1 and L.attention_epilogue_push else None)
             with nvtx_range("attention"):
-                attn_out, lse = attn_ops.attention_fwd_packed(qkv_full, qpg, d, 1.0 / math.sqrt(d))
+                attn_out, lse = attn_ops.attention_fwd_packed(qkv_full, qpg, d, 1.0 / math.sqrt(d), push=push)
             with nvtx_range("hp2sp_outproj"):
                 h1, attn_in_full = attn_mod.output_projection_forward(attn_out, proj_w, cp, mode_attn, fused,
-                                                                      residual=x2)
+                                                                      residual=x2, pushed=push is not None)
         else:
             h1 = x2
 
@@ -435,6 +440,8 @@ class TransformerLayer(nn.Module):
         # Drop the FC1 pre-activation after the forward pass and rebuild it in the backward pass
         # (one more FC1 GEMM per layer for [rows, F or 2F] less saved memory).
         self.recompute_fc1 = bool(recompute_fc1)
+        # HP -> SP exchange inside the attention kernel's epilogue (device-initiated transport only)
+        self.attention_epilogue_push = os.environ.get("FLUIDMOE_ATTN_EPILOGUE_PUSH", "1") == "1"
         self.router_logit_bias = None   # optional fp32 [E] prior added to the router logits (set_router_bias)
         if parallel_ctx is not None:
             cp_group = cp_group if cp_group is not None else parallel_ctx.cp_group

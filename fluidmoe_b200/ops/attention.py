@@ -72,15 +72,23 @@ def attention_bwd(dout: torch.Tensor, q: torch.Tensor, k: torch.Tensor, v: torch
     return to(dq, q), to(dk, k), to(dv, v)
 
 
-def attention_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float = None):
-    """Causal GQA attention on the packed projection buffer ``[s, b, G, (qpg + 2) * d]``.
-    Returns ``(out [s, b, G*qpg, d], lse or None)``."""
+def native_forward(qkv: torch.Tensor, head_dim: int) -> bool:
+    """Whether ``attention_fwd_packed`` will run this library's kernel on this input."""
     import os
+    from . import flash
+    return flash.supported(qkv, head_dim) and os.environ.get("FLUIDMOE_ATTN", "native") == "native"
+
+
+def attention_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float = None, push=None):
+    """Causal GQA attention on the packed projection buffer ``[s, b, G, (qpg + 2) * d]``.
+    Returns ``(out [s, b, G*qpg, d], lse or None)``.  ``push``: see ``flash.flash_attn_fwd_packed``
+    (only with the native kernel; the caller checks ``native_forward`` and ``flash.can_push``)."""
     from . import flash
     s, b, G, gs = qkv.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
-    if flash.supported(qkv, head_dim) and os.environ.get("FLUIDMOE_ATTN", "native") == "native":
-        return flash.flash_attn_fwd_packed(qkv, q_per_group, head_dim, scale)
+    if native_forward(qkv, head_dim):
+        return flash.flash_attn_fwd_packed(qkv, q_per_group, head_dim, scale, push=push)
+    assert push is None, "the epilogue exchange needs the native attention kernel"
     heads = qkv.view(s, b, G, q_per_group + 2, head_dim)
     q = heads[:, :, :, :q_per_group].reshape(s, b, G * q_per_group, head_dim)
     return attention_fwd(q, heads[:, :, :, q_per_group], heads[:, :, :, q_per_group + 1], scale, True)

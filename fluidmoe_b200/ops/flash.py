@@ -18,17 +18,34 @@ def supported(qkv: torch.Tensor, head_dim: int) -> bool:
             and _native.available() and hasattr(_native.lib(), "flash_attn_fwd"))
 
 
-def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float, version: int = 0):
-    """qkv: [s, b, G, (qpg + 2) * d] -> (out [s, b, G*qpg, d], lse [b, G*qpg, s])."""
+def can_push(qkv: torch.Tensor, rows_per_rank: int, version: int = 0) -> bool:
+    """Whether the forward kernel can do the HP -> SP exchange in its epilogue for this input."""
+    return (version or VERSION) == 2 and qkv.shape[1] == 1 and rows_per_rank > 0 and rows_per_rank % 128 == 0
+
+
+def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, scale: float, version: int = 0,
+                          push=None):
+    """qkv: [s, b, G, (qpg + 2) * d] -> (out [s, b, G*qpg, d], lse [b, G*qpg, s]).
+
+    ``push`` (``dict(dst_table, flags_table, me, P, rows_per_rank, row_blocks)``): every output row is
+    also stored into the sequence owner's buffer and the owner's arrival counter is raised, which
+    replaces the separate HP -> SP push (fluid/attention/forward.py:435-476)."""
     global LAUNCHES
     s, b, G, gs = qkv.shape
     hq = G * q_per_group
     out = torch.empty(s, b, hq, head_dim, dtype=qkv.dtype, device=qkv.device)
     lse = torch.empty(b, hq, s, dtype=torch.float32, device=qkv.device)
     LAUNCHES += 1
-    _native.lib().flash_attn_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), s, b, G, q_per_group,
-                                 head_dim, float(scale), 0, status_buffer(qkv.device).data_ptr(),
-                                 version or VERSION, _native.stream_ptr())
+    if push is None:
+        _native.lib().flash_attn_fwd(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), s, b, G, q_per_group,
+                                     head_dim, float(scale), 0, status_buffer(qkv.device).data_ptr(),
+                                     version or VERSION, _native.stream_ptr())
+    else:
+        _native.lib().flash_attn_fwd_push(qkv.data_ptr(), out.data_ptr(), lse.data_ptr(), s, b, G, q_per_group,
+                                          head_dim, float(scale), 0, status_buffer(qkv.device).data_ptr(),
+                                          version or VERSION, push["dst_table"], push["flags_table"],
+                                          push["me"], push["P"], push["rows_per_rank"], push["row_blocks"],
+                                          _native.stream_ptr())
     return out, lse
 
 

@@ -405,10 +405,21 @@ class FusedCommContext:
             _native.lib().rows_push(src2d.data_ptr(), dst.ptr_table, flags.ptr_table, rows_blk, src2d.shape[1],
                                     P, self.rank, row_blocks, 0, _native.stream_ptr())
 
-    def _ksource_gate(self, flags: SymmTensor, cols_per_src: int, row_blocks: int) -> dict:
+    def _ksource_gate(self, flags: SymmTensor, cols_per_src: int, row_blocks: int, units_per_row: int = 1) -> dict:
         return dict(gate_flags=flags.local.data_ptr(), gate_k_blocks_per_src=cols_per_src // 64,
                     gate_blocks_per_group=row_blocks, k_rotate=self.rank * (cols_per_src // 64),
-                    timeout_ns=self.timeout_ns, wait_ns=self._wait_ptr(0))
+                    gate_expected=units_per_row, timeout_ns=self.timeout_ns, wait_ns=self._wait_ptr(0))
+
+    def attention_push_args(self, plan, qkv_full):
+        """Arguments that let the attention kernel do the HP -> SP exchange in its epilogue, or
+        ``None`` when it cannot (batch > 1, rows per rank not a multiple of 128, other kernel)."""
+        from ..ops import attention as attn_ops, flash
+        T = plan.seq_local * plan.batch
+        if not attn_ops.native_forward(qkv_full, plan.head_dim) or not flash.can_push(qkv_full, T):
+            return None
+        b = self._attn[plan._fused_layer]
+        return dict(dst_table=b.attn_in.ptr_table, flags_table=b.flags_proj.ptr_table, me=self.rank,
+                    P=plan.cp_size, rows_per_rank=T, row_blocks=b.row_blocks)
 
     def qkv_sp2hp(self, x, qkv_weight, plan):
         """QKV projection whose epilogue performs the SP->HP exchange (fluid/attention/forward.py:130-277)."""
@@ -420,17 +431,21 @@ class FusedCommContext:
         b.cnt_qkv.local.zero_()
         return b.qkv_full.local.view(P * sl, bt, plan.groups_per_rank, plan.group_size)
 
-    def hp2sp_outproj(self, attn_out, proj_weight, plan, residual):
+    def hp2sp_outproj(self, attn_out, proj_weight, plan, residual, pushed: bool = False):
         """HP->SP push followed by the output projection whose K loop consumes each source's
-        column block as it arrives, local block first (fluid/attention/forward.py:332-484)."""
+        column block as it arrives, local block first (fluid/attention/forward.py:332-484).
+        ``pushed``: the attention kernel's epilogue has already stored the rows at their owners
+        (one arrival per row and head), so there is nothing left to push."""
         b = self._attn[plan._fused_layer]
         P, sl, bt, dpr = plan.cp_size, plan.seq_local, plan.batch, plan.attn_per_rank
         T = sl * bt
-        self._rows_push(attn_out.reshape(P * T, dpr), P, b.attn_in, b.flags_proj, b.row_blocks)
+        if not pushed:
+            self._rows_push(attn_out.reshape(P * T, dpr), P, b.attn_in, b.flags_proj, b.row_blocks)
         out = residual.clone() if residual is not None else None
         out = gemm.grouped_gemm(b.attn_in.local, proj_weight, b_layout="nk", out=out,
                                 accumulate=residual is not None,
-                                gate=self._ksource_gate(b.flags_proj, dpr, b.row_blocks))
+                                gate=self._ksource_gate(b.flags_proj, dpr, b.row_blocks,
+                                                        plan.heads_per_rank if pushed else 1))
         b.flags_proj.local.zero_()
         return out, b.attn_in.local
 

@@ -203,10 +203,20 @@ def run_ours(args):
         sched.disable()
     else:
         sched.enable(device)
+    # knobs the tuner measured on this kind of box (tools/tune.py writes tools/tuned_defaults.json);
+    # a flag given on the command line wins
+    from fluidmoe_b200.tools.experiment_configs import get_block_benchmark_defaults
+    tuned_fused = get_block_benchmark_defaults(os.environ.get("FLUIDMOE_TUNED_NODE", "b200_2gpu_fused"))
+    tuned_p2p = get_block_benchmark_defaults(os.environ.get("FLUIDMOE_TUNED_NODE_P2P", "b200_2gpu_p2p"))
+    ar_bw = float(tuned_p2p.get("shared_ar_bw") or 3.0e8)
+    grad_reduce = args.grad_reduce or (tuned_fused.get("fused_grad_reduce") if heap else None) or None
     ddp = FluidDDP(None, model, sched, dp_cp_group=pc.dp_cp_group, expert_dp_group=pc.expert_dp_group,
                    ar_enabled=args.mode == "full",
                    gap_budgets={"moe_combine": 0.5, "moe_dispatch": 0.5, "attn_proj": 0.3, "attn_qkv": 0.3},
-                   shared_ar_bw=3.0e8, expert_ar_bw=3.0e8, grad_reduce=args.grad_reduce or None)
+                   shared_ar_bw=ar_bw, expert_ar_bw=ar_bw, grad_reduce=grad_reduce)
+    sched.eager_ar_min_bytes = int(tuned_fused.get("fused_eager_ar_min_bytes", sched.eager_ar_min_bytes))
+    if args.dw_side_ctas == 0:
+        args.dw_side_ctas = int(tuned_fused.get("fused_dw_side_ctas", 0))
     opt = FluidOptimizerWrapper(
         FusedAdam(model.parameters(), lr=1e-4, weight_decay=0.0,
                   state_dtype=torch.bfloat16 if args.opt_state == "bf16" else torch.float32), sched)

@@ -84,7 +84,7 @@ def tune_allreduce(cfg, bench, pc, device, comm, td) -> dict:
     return dict(shared_ar_bw=bytes_per_ms, expert_ar_bw=bytes_per_ms, gap_budgets=budgets)
 
 
-def _time_fused(cfg, bench, pc, device, td, eager_min_bytes, grad_reduce, side_ctas):
+def _time_fused(cfg, bench, pc, device, td, eager_ar_min_bytes, grad_reduce, dw_side_ctas):
     from ..parallel.ddp import FluidDDP
     from ..parallel.scheduler import BackwardScheduler
     BackwardScheduler.reset()
@@ -94,8 +94,8 @@ def _time_fused(cfg, bench, pc, device, td, eager_min_bytes, grad_reduce, side_c
     x = common.make_input(cfg, pc, device)
     ddp = FluidDDP(None, model, sched, dp_cp_group=pc.dp_cp_group, expert_dp_group=pc.expert_dp_group,
                    grad_reduce=grad_reduce)
-    sched.eager_ar_min_bytes = int(eager_min_bytes)
-    sched.dw_on_side_stream, sched.dw_max_ctas = side_ctas > 0, side_ctas
+    sched.eager_ar_min_bytes = int(eager_ar_min_bytes)
+    sched.dw_on_side_stream, sched.dw_max_ctas = dw_side_ctas > 0, dw_side_ctas
     common.run_iters(ddp.module, x, td["warmup"], pc)
     ms = common.time_iters(ddp.module, x, td["iters"], pc)
     del ddp, model
@@ -123,7 +123,8 @@ def main(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--model", default="mixtral_8x7b")
     ap.add_argument("--comm", default="p2p")
-    ap.add_argument("--node", default=None)
+    ap.add_argument("--node-name", dest="node", default=None,
+                    help="key under which the tuned values are stored (not --node: the launcher would take it for --node-rank)")
     ap.add_argument("--skip-chunks", action="store_true")
     args = ap.parse_args(argv)
     td = dict(TUNE_DEFAULTS)

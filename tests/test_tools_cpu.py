@@ -309,7 +309,7 @@ def test_tuner_searches_chunks_and_persists(tmp_path, monkeypatch, capsys):
     monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "ar_sizes_mb", (1,))
     monkeypatch.setattr(tune, "TUNE_DEFAULTS", experiment_configs.TUNE_DEFAULTS)
     BackwardScheduler.reset()
-    tune.main(["--model", "tiny_test", "--comm", "p2p", "--node", "testbox"])
+    tune.main(["--model", "tiny_test", "--comm", "p2p", "--node-name", "testbox"])
     out = capsys.readouterr().out
     assert "[tune] all regions 1 chunk" in out and "[tune] wrote" in out
     saved = json.loads((tmp_path / "tuned.json").read_text())["testbox"]
@@ -318,3 +318,22 @@ def test_tuner_searches_chunks_and_persists(tmp_path, monkeypatch, capsys):
     merged = experiment_configs.get_block_benchmark_defaults("testbox")
     assert merged["moe_combine_chunks"] == saved["moe_combine_chunks"]
     BackwardScheduler.reset()
+
+
+def test_tuner_fused_knob_search_with_a_stub_timer(monkeypatch, capsys):
+    """The knob search of the device-initiated transport: every trial reaches the timer with the
+    knob names the search uses, and a knob is kept only when it saves at least ``min_saving_ms``."""
+    import inspect
+    from fluidmoe_b200.tools import tune
+    # the real timer takes the knobs under the names the search passes
+    assert list(inspect.signature(tune._time_fused).parameters)[5:] == ["eager_ar_min_bytes", "grad_reduce", "dw_side_ctas"]
+    seen = []
+
+    def fake_time(cfg, bench, pc, device, td, eager_ar_min_bytes, grad_reduce, dw_side_ctas):
+        seen.append((eager_ar_min_bytes, grad_reduce, dw_side_ctas))
+        return 10.0 - (1.0 if grad_reduce == "symm" else 0.0) - (0.01 if dw_side_ctas else 0.0)
+
+    monkeypatch.setattr(tune, "_time_fused", fake_time)
+    best = tune.tune_fused({}, {}, None, None, dict(min_saving_ms=0.05, side_ctas=(48,)))
+    assert best == {"fused_eager_ar_min_bytes": 32 << 20, "fused_grad_reduce": "symm", "fused_dw_side_ctas": 0}
+    assert len(seen) == 5 and seen[0] == (32 << 20, "nccl", 0)

@@ -28,6 +28,11 @@ int fm_gather_rows(const void* x, const long long* idx, void* out, long long row
                    cudaStream_t s);
 int fm_unpermute_reduce(const void* rows, const int* slot, const void* residual, void* out, int T,
                         int k, int H, cudaStream_t s);
+// The same, preceded by a bounded wait on `wait_n` per-source arrival counters (>= wait_expected).
+int fm_unpermute_reduce_gated(const void* rows, const int* slot, const void* residual, void* out, int T, int k,
+                              int H, const int* wait_flags, int wait_n, int wait_expected,
+                              unsigned long long* wait_ns, unsigned long long timeout_ns, int* status,
+                              cudaStream_t s);
 // Moments are fp32, or bf16 when state_bf16 != 0.
 // Adam for bf16 parameter / bf16 moments / fp32 gradient with small CTAs (128 threads, <= 80 registers)
 // that fit on an SM beside a resident tensor-core kernel; meant for a side stream.

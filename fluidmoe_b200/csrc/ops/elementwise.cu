@@ -309,10 +309,33 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
 // Un-permute: out[t] = residual[t] + sum_j rows[slot[t, j]], fp32 accumulation, slots < 0
 // skipped.  Deterministic (a gather, not a scatter-add).
 // --------------------------------------------------------------------------------------------
+constexpr int kKernelIdUnpermuteWait = 15;
+// Optionally the kernel first waits, bounded, until the arrival counters of the `wait_n` sources
+// have reached `wait_expected` (rows pushed by peers into `rows`): the consumer polls its own
+// counters instead of a stand-alone wait kernel in front of it.  The time the slowest thread of CTA 0
+// waited is added to `wait_ns` (communication the step could not hide).
 __global__ void unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ rows,
                                         const int* __restrict__ slot,
                                         const __nv_bfloat16* __restrict__ residual,
-                                        __nv_bfloat16* __restrict__ out, int T, int k, int H) {
+                                        __nv_bfloat16* __restrict__ out, int T, int k, int H,
+                                        const int* wait_flags, int wait_n, int wait_expected,
+                                        unsigned long long* wait_ns, unsigned long long timeout_ns,
+                                        int* status) {
+  if (wait_flags != nullptr) {
+    __shared__ unsigned long long slowest;
+    if (threadIdx.x == 0) slowest = 0;
+    __syncthreads();
+    if ((int)threadIdx.x < wait_n) {
+      int observed = 0;
+      const uint64_t t0 = global_timer_ns();
+      if (!flag_wait_ge(wait_flags + threadIdx.x, wait_expected, timeout_ns, nullptr, &observed) &&
+          blockIdx.x == 0)
+        report_status(status, kStatusFlagTimeout, kKernelIdUnpermuteWait, (int)threadIdx.x, wait_expected, observed);
+      if (wait_ns != nullptr && blockIdx.x == 0) atomicMax(&slowest, (unsigned long long)(global_timer_ns() - t0));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && blockIdx.x == 0 && wait_ns != nullptr) atomicAdd(wait_ns, slowest);
+  }
   const int nvec = H / 8;
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -838,8 +861,22 @@ extern "C" int fm_unpermute_reduce(const void* rows, const int* slot, const void
   }
   fm::unpermute_reduce_kernel<<<grid_for(T, 8), 256, 0, s>>>(
       (const __nv_bfloat16*)rows, slot, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, T, k,
-      H);
+      H, nullptr, 0, 0, nullptr, 0, nullptr);
   return check_launch("unpermute_reduce");
+}
+
+extern "C" int fm_unpermute_reduce_gated(const void* rows, const int* slot, const void* residual,
+                                         void* out, int T, int k, int H, const int* wait_flags, int wait_n,
+                                         int wait_expected, unsigned long long* wait_ns,
+                                         unsigned long long timeout_ns, int* status, cudaStream_t s) {
+  if (H % 8 != 0 || k > 16 || wait_n > 256) {
+    fm_set_error("unpermute_reduce_gated: H must be a multiple of 8, k at most 16, at most 256 sources");
+    return -1;
+  }
+  fm::unpermute_reduce_kernel<<<grid_for(T, 8), 256, 0, s>>>(
+      (const __nv_bfloat16*)rows, slot, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, T, k,
+      H, wait_flags, wait_n, wait_expected, wait_ns, timeout_ns ? timeout_ns : 4000000000ull, status);
+  return check_launch("unpermute_reduce_gated");
 }
 
 extern "C" int fm_adam(void* p, float* master, float* g, void* m, void* v, long long n, float lr,

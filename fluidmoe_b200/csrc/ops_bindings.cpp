@@ -44,6 +44,12 @@ void bind_ops(py::module_& m) {
     chk(fm_gather_rows(p<const void*>(x), p<const long long*>(idx), p<void*>(out), rows, H, st(s)),
         "gather_rows");
   });
+  m.def("unpermute_reduce_gated", [](u rows, u slot, u res, u out, int T, int k, int H, u flags, int n, int expected,
+                                     u wait_ns, unsigned long long timeout_ns, u status, u s) {
+    chk(fm_unpermute_reduce_gated(p<const void*>(rows), p<const int*>(slot), p<const void*>(res), p<void*>(out), T, k,
+                                  H, p<const int*>(flags), n, expected, p<unsigned long long*>(wait_ns), timeout_ns,
+                                  p<int*>(status), st(s)), "unpermute_reduce_gated");
+  });
   m.def("unpermute_reduce", [](u rows, u slot, u res, u out, int T, int k, int H, u s) {
     chk(fm_unpermute_reduce(p<const void*>(rows), p<const int*>(slot), p<const void*>(res),
                             p<void*>(out), T, k, H, st(s)), "unpermute_reduce");

@@ -88,7 +88,10 @@ def gather_rows(x, idx, out=None):
     return out
 
 
-def unpermute_reduce(rows, slot_of_token, residual=None):
+def unpermute_reduce(rows, slot_of_token, residual=None, wait=None):
+    """``wait`` (``dict(flags, n, expected, wait_ns, timeout_ns, status)``, addresses as ints): the
+    kernel first waits, bounded, until the ``n`` per-source arrival counters at ``flags`` have
+    reached ``expected`` (rows that peers push into ``rows``)."""
     if rows.dtype != torch.bfloat16 or rows.shape[1] % 8 or not rows.is_contiguous() or slot_of_token.shape[1] > 16:
         return None
     T, k = slot_of_token.shape
@@ -98,7 +101,12 @@ def unpermute_reduce(rows, slot_of_token, residual=None):
         residual = residual.contiguous()
         assert residual.dtype == torch.bfloat16
     out = torch.empty(T, H, dtype=rows.dtype, device=rows.device)
-    _native.lib().unpermute_reduce(rows.data_ptr(), slot.data_ptr(), _ptr(residual), out.data_ptr(), T, k, H, _s())
+    if wait is None:
+        _native.lib().unpermute_reduce(rows.data_ptr(), slot.data_ptr(), _ptr(residual), out.data_ptr(), T, k, H, _s())
+    else:
+        _native.lib().unpermute_reduce_gated(rows.data_ptr(), slot.data_ptr(), _ptr(residual), out.data_ptr(), T, k,
+                                             H, wait["flags"], wait["n"], wait["expected"], wait["wait_ns"],
+                                             wait["timeout_ns"], wait["status"], _s())
     return out
 
 

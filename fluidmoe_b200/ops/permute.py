@@ -29,13 +29,17 @@ def permute_rows(x: torch.Tensor, sorted_indices: torch.Tensor, out: Optional[to
 
 
 def unpermute_reduce(rows: torch.Tensor, slot_of_token: torch.Tensor,
-                     residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``out[t] = residual[t] + sum_j rows[slot_of_token[t, j]]`` (slots < 0 are skipped)."""
+                     residual: Optional[torch.Tensor] = None, wait=None) -> torch.Tensor:
+    """``out[t] = residual[t] + sum_j rows[slot_of_token[t, j]]`` (slots < 0 are skipped).
+    ``wait``: see ``elementwise.unpermute_reduce`` (native kernel only; returns ``None`` when the
+    native kernel cannot take this input, so that the caller can wait by other means)."""
     if _native.use_native(rows) and hasattr(_native.lib(), "unpermute_reduce"):
         from . import elementwise
-        res = elementwise.unpermute_reduce(rows, slot_of_token, residual)
+        res = elementwise.unpermute_reduce(rows, slot_of_token, residual, wait)
         if res is not None:
             return res
+    if wait is not None:
+        return None
     T, k = slot_of_token.shape
     idx = slot_of_token.long()
     gathered = rows[idx.clamp(min=0)].float()                      # [T, k, H]

@@ -328,9 +328,18 @@ class FusedCommContext:
         waited for (and reset) the counters with ``wait_dispatch_grad``."""
         b = self._buf(plan)
         cnt = b.cnt_combine if rows.data_ptr() == b.combined.local.data_ptr() else b.cnt_dperm
+        out = None
         if not waited:
-            self._wait_counters(cnt, plan.S * self._n_tiles(plan.hidden_size) * EPI_SPLIT)
-        out = permute.unpermute_reduce(rows, slot_of_token, residual)
+            # the gather kernel polls the arrival counters itself; a stand-alone wait kernel only when
+            # the native gather cannot take this input
+            expected = plan.S * self._n_tiles(plan.hidden_size) * EPI_SPLIT
+            out = permute.unpermute_reduce(rows, slot_of_token, residual, wait=dict(
+                flags=cnt.local.data_ptr(), n=self.world, expected=expected, wait_ns=self._wait_ptr(1),
+                timeout_ns=self.timeout_ns, status=status_buffer(self.device).data_ptr()))
+            if out is None:
+                self._wait_counters(cnt, expected)
+        if out is None:
+            out = permute.unpermute_reduce(rows, slot_of_token, residual)
         if not waited:
             cnt.local.zero_()
         return out

@@ -379,12 +379,15 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
 
 constexpr int kFa2Threads = 320;   // TMA warp, MMA warp, 4 + 4 softmax warps
 constexpr int kKernelIdFlashFwd2 = 21;
-constexpr int kFa2DefaultPoly = 6;    // index into the launcher's table: uniform issue, no polynomial share
+constexpr int kFa2DefaultPoly = 7;    // index into the launcher's table: uniform issue, P handed over in two parts
 
 // kPoly: of every four value pairs, how many take their exponential from poly_exp2x2.
 // kUniform: the whole MMA warp walks the issue loop and one elected lane issues, so that the
 // compiler can keep descriptors and loop state in the warp's uniform registers.
-template <int kPoly, bool kUniform = false>
+// kPParts (1, 2 or 4): the softmax hands P over in that many parts of 128 / kPParts keys and the
+// k-steps of P.V that read a part are issued as soon as it is there, so that they overlap the
+// exponentials of the later parts (the tile's softmax and its two products sit in series).
+template <int kPoly, bool kUniform = false, int kPParts = 1>
 __global__ void __launch_bounds__(kFa2Threads, 1)
 flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -402,6 +405,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
   uint64_t* s_full = bars + 10;      // [2] per tile
   uint64_t* p_full = bars + 12;      // [2]
   uint64_t* o_full = bars + 14;      // [2]
+  uint64_t* p_part = bars + 18;      // [2][3] parts 0 .. kPParts-2 of P (the last part is p_full)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -438,6 +442,7 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 4);
+      for (int c = 0; c < 3; ++c) mbar_init(&p_part[i * 3 + c], 4);
       mbar_init(&o_full[i], 1);
     }
     *abort_flag = 0;
@@ -517,14 +522,18 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         }
         if (kUniform) __syncwarp();
       };
-      auto issue_pv = [&](auto w_c, auto st_c, uint32_t first_acc) {   // O_w (+)= P_w V(stage)
+      // k-steps [k0, k1) of O_w (+)= P_w V(stage); the last call (k1 == 8) commits
+      auto issue_pv = [&](auto w_c, auto st_c, uint32_t first_acc, int k0, int k1) {
         constexpr int W = decltype(w_c)::value, ST = decltype(st_c)::value;
         const uint32_t d = tmem_base + 256 + W * 128, pa = tmem_base + W * 128;
         if (!kUniform || elect_one()) {
-          umma_bf16_ts(d, pa, vd[ST][0], idesc_pv, first_acc);
 #pragma unroll
-          for (int kk = 1; kk < 8; ++kk) umma_bf16_ts_acc(d, pa + kk * 8, vd[ST][kk], idesc_pv);
-          umma_commit(&o_full[W]);
+          for (int kk = 0; kk < 8; ++kk) {
+            if (kk < k0 || kk >= k1) continue;
+            if (kk == 0) umma_bf16_ts(d, pa, vd[ST][0], idesc_pv, first_acc);
+            else umma_bf16_ts_acc(d, pa + kk * 8, vd[ST][kk], idesc_pv);
+          }
+          if (k1 == 8) umma_commit(&o_full[W]);
         }
         if (kUniform) __syncwarp();
       };
@@ -560,11 +569,18 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
           if (j >= nblk[W]) return true;
           t0 = FA_PROF_NOW();
           FA_TRACE(a, j, W * 8 + 0);                    // MMA thread starts waiting for P_w(j)
+          constexpr int kStepsPerPart = 8 / kPParts;
+#pragma unroll
+          for (int part = 0; part + 1 < kPParts; ++part) {
+            if (!wait_or_fail(&p_part[W * 3 + part], j & 1, 225 + W)) return false;
+            tc_fence_after_sync();
+            issue_pv(w_c, st_c, j > 0 ? 1u : 0u, part * kStepsPerPart, (part + 1) * kStepsPerPart);
+          }
           if (!wait_or_fail(&p_full[W], j & 1, 220 + W)) return false;
           FA_PROF_ADD(pm_wait_p, t0);
           FA_TRACE(a, j, W * 8 + 1);                    // ... has it
           tc_fence_after_sync();
-          issue_pv(w_c, st_c, j > 0 ? 1u : 0u);
+          issue_pv(w_c, st_c, j > 0 ? 1u : 0u, 8 - kStepsPerPart, 8);
           FA_TRACE(a, j, W * 8 + 2);                    // P.V issued
           if (j + 1 < nblk[W]) {
             if (!k_next_ready) {
@@ -722,6 +738,15 @@ flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
         }
         // P columns [16c, 16c+16) alias score columns; the scores are already in registers
         tmem_st_32x16(t_s + c * 16, pk);
+        if constexpr (kPParts > 1) {
+          // chunk c holds 32 keys: part boundaries after chunk 1 (two parts) or after every chunk (four)
+          if (c < 3 && (kPParts == 4 || c == 1)) {
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_part[w * 3 + (kPParts == 4 ? c : 0)]);
+          }
+        }
       }
       tmem_st_wait();
       l_run += ((l_part[0] + l_part[1]) + (l_part[2] + l_part[3])) + ((l_part[4] + l_part[5]) + (l_part[6] + l_part[7]));
@@ -2443,7 +2468,7 @@ extern "C" int fm_flash_attn_fwd_push(const void* qkv, void* out, float* lse, in
   a.timeout_ns = timeout_ns ? timeout_ns : 4000000000ull;
   a.status = status;
   a.prof = nullptr;
-  constexpr int kMaxFwd2Version = 26;
+  constexpr int kMaxFwd2Version = 28;
   a.qkv = reinterpret_cast<const __nv_bfloat16*>(qkv);
   a.row_stride = cols;
   a.push_dst = reinterpret_cast<__nv_bfloat16* const*>(push_dst);
@@ -2515,18 +2540,19 @@ extern "C" int fm_flash_attn_fwd_push(const void* qkv, void* out, float* lse, in
     // versions 20..24 pick the share of polynomial exponentials (0..4 of every 4 pairs)
     using Fwd2Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
     // 20..24: share of polynomial exponentials; 25: developer timing experiment; 26: the whole MMA warp
-    // walks the issue loop (uniform issue)
-    static const Fwd2Fn kFwd2[8] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<1>, fm::flash_fwd2_kernel<2>,
+    // walks the issue loop (uniform issue); 27 / 28: 26 with P handed over in two / four parts
+    static const Fwd2Fn kFwd2[9] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<1>, fm::flash_fwd2_kernel<2>,
                                     fm::flash_fwd2_kernel<3>, fm::flash_fwd2_kernel<4>,
 #ifdef FM_FLASH_PROFILE
                                     fm::flash_fwd2_kernel<5>,
 #else
                                     fm::flash_fwd2_kernel<0>,
 #endif
-                                    fm::flash_fwd2_kernel<0, true>, fm::flash_fwd2_kernel<0, true>};
+                                    fm::flash_fwd2_kernel<0, true>, fm::flash_fwd2_kernel<0, true, 2>,
+                                    fm::flash_fwd2_kernel<0, true, 4>};
     const int variant = version == 2 ? fm::kFa2DefaultPoly : version - 20;
     constexpr int smem2 = smem;
-    static bool configured2[8] = {false, false, false, false, false, false, false, false};
+    static bool configured2[9] = {false, false, false, false, false, false, false, false, false};
     if (!configured2[variant]) {
       cudaError_t e2 = cudaFuncSetAttribute(kFwd2[variant], cudaFuncAttributeMaxDynamicSharedMemorySize, smem2);
       if (e2 != cudaSuccess) {

@@ -1236,353 +1236,6 @@ flash_fwd3_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a
 }
 
 // =========================================================================================
-// Fourth-generation forward: the second generation's pipeline (two query tiles per CTA
-// ping-pong, P written over S, O in TMEM with lazy rescale) with every query row split over two
-// threads.  The probe of the exponential pass (tools/softmax_pass_probe.cu) shows a scheduler
-// needs four resident softmax warps before the special-function unit, not dependent-instruction
-// latency, sets the pace; with one thread per row a tile's softmax has one warp per scheduler.
-// Here warps (t, hf, q) with tile t, column half hf and TMEM lane quarter q own 64 of a row's
-// 128 scores each: two warps per scheduler work on a tile's block at the same time.  The two
-// halves of a row exchange their partial maximum through shared memory and a named barrier per
-// block (the slot alternates with the block parity), keep partial row sums and add them at the
-// end, and rescale / write their own 64 columns of O.
-// Warp layout (640 threads): warps 0-7 tile 0 (0-3 half 0, 4-7 half 1), warps 8-15 tile 1,
-// warps 16-19 the producer warpgroup (16: TMA, 17: MMA issue).  The producer group hands
-// registers to the softmax groups (setmaxnreg), which then have 104 each.
-// =========================================================================================
-constexpr int kFa4Threads = 640;
-constexpr int kKernelIdFlashFwd4 = 24;
-
-template <int kPoly>
-__global__ void __launch_bounds__(kFa4Threads, 1)
-flash_fwd4_kernel(const __grid_constant__ CUtensorMap tmap, const FlashFwdArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>(
-      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;                      // 2 tiles
-  uint8_t* sK = smem + 2 * kTileBytes;     // 2 stages
-  uint8_t* sV = smem + 4 * kTileBytes;     // 2 stages
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * kTileBytes);
-  uint64_t* q_full = bars;           // [2]
-  uint64_t* k_full = bars + 2;       // [2]
-  uint64_t* v_full = bars + 4;       // [2]
-  uint64_t* k_empty = bars + 6;      // [2]
-  uint64_t* v_empty = bars + 8;      // [2]
-  uint64_t* s_full = bars + 10;      // [2] per tile
-  uint64_t* p_full = bars + 12;      // [2]
-  uint64_t* o_full = bars + 14;      // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* xch = reinterpret_cast<float*>(bars + 18);   // [3][tile][half][row]: block parity 0 / 1, row sums
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nq = (a.s + kFaBM - 1) / kFaBM;
-  const int npairs = (nq + 1) / 2;
-  // One-dimensional grid ordered by work (longest tile pair first); neighbouring CTAs are the
-  // query heads of one KV group, which share K/V in L2.
-  const int hq_all = a.G * a.qpg;
-  const int per_pair = hq_all * a.b;
-  const int pair = npairs - 1 - (int)blockIdx.x / per_pair;
-  const int rem_lin = (int)blockIdx.x % per_pair;
-  const int h = rem_lin % hq_all, bb = rem_lin / hq_all;
-  const int g = h / a.qpg, hi = h % a.qpg;
-  const int heads_per_group = a.qpg + 2;
-  const int col_q = ((bb * a.G + g) * heads_per_group + hi) * kFaD;
-  const int col_k = ((bb * a.G + g) * heads_per_group + a.qpg) * kFaD;
-  const int col_v = col_k + kFaD;
-  const int nkv = (a.s + kFaBN - 1) / kFaBN;
-  int nblk[2];
-  nblk[0] = min(2 * pair + 1, nkv);
-  nblk[1] = (2 * pair + 1 < nq) ? min(2 * pair + 2, nkv) : 0;
-  const int nmax = max(nblk[0], nblk[1]);
-  const uint64_t timeout = a.timeout_ns;
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&q_full[i], 1);
-      mbar_init(&k_full[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 8);
-      mbar_init(&o_full[i], 1);
-    }
-    *abort_flag = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&tmap);
-  }
-  if (warp == 17) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp >= 16) {
-    warpgroup_reg_dec<56>();
-    if (warp == 16) {
-      if (lane == 0) {
-        for (int w = 0; w < 2; ++w) {
-          if (nblk[w] == 0) continue;
-          const int q0 = (2 * pair + w) * kFaBM;
-          mbar_expect_tx(&q_full[w], kTileBytes);
-          tma_load_2d(sQ + w * kTileBytes, &tmap, &q_full[w], col_q, q0);
-          tma_load_2d(sQ + w * kTileBytes + kTileBytes / 2, &tmap, &q_full[w], col_q + 64, q0);
-        }
-        for (int j = 0; j < nmax; ++j) {
-          const int st = j & 1;
-          const uint32_t ph = ((j >> 1) & 1) ^ 1;
-          if (!mbar_wait(&k_empty[st], ph, timeout, abort_flag)) {
-            report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd4, 100 + st, 0, 0);
-            break;
-          }
-          mbar_expect_tx(&k_full[st], kTileBytes);
-          tma_load_2d(sK + st * kTileBytes, &tmap, &k_full[st], col_k, j * kFaBN);
-          tma_load_2d(sK + st * kTileBytes + kTileBytes / 2, &tmap, &k_full[st], col_k + 64, j * kFaBN);
-          if (!mbar_wait(&v_empty[st], ph, timeout, abort_flag)) {
-            report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd4, 110 + st, 0, 0);
-            break;
-          }
-          mbar_expect_tx(&v_full[st], kTileBytes);
-          tma_load_2d(sV + st * kTileBytes, &tmap, &v_full[st], col_v, j * kFaBN);
-          tma_load_2d(sV + st * kTileBytes + kTileBytes / 2, &tmap, &v_full[st], col_v + 64, j * kFaBN);
-        }
-      }
-    } else if (warp == 17) {
-      // the whole warp walks the issue loop, one elected lane issues (uniform control flow)
-      constexpr uint32_t idesc_qk = umma_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, false, true);
-      constexpr uint32_t kTileAdd = kTileBytes >> 4;
-      bool ok = true;
-      uint32_t q_lo[8], k_lo[8], v_lo[8];      // low descriptor words of the eight k-steps, tile / stage 0
-      umma_lo_k_major(smem_u32(sQ), kTileBytes / 2, q_lo);
-      umma_lo_k_major(smem_u32(sK), kTileBytes / 2, k_lo);
-      umma_lo_mn_major(smem_u32(sV), kTileBytes / 2, v_lo);
-      auto wait_or_fail = [&](uint64_t* bar, uint32_t parity, int what) {
-        if (__all_sync(0xffffffffu, mbar_wait(bar, parity, timeout, abort_flag))) return true;
-        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd4, what, 0, 0);
-        return false;
-      };
-      auto issue_qk = [&](int w, int j) {       // S_w = Q_w K_j^T
-        if (elect_one()) {
-          umma8_ss(tmem_base + w * 128, q_lo, w * kTileAdd, k_lo, (j & 1) * kTileAdd, idesc_qk, 0u);
-          umma_commit(&s_full[w]);
-        }
-        __syncwarp();
-      };
-      auto issue_pv = [&](int w, int j) {       // O_w (+)= P_w V_j, A = P from TMEM
-        if (elect_one()) {
-          umma8_ts(tmem_base + 256 + w * 128, tmem_base + w * 128, 32, v_lo, (j & 1) * kTileAdd, idesc_pv,
-                   j > 0 ? 1u : 0u);
-          umma_commit(&o_full[w]);
-        }
-        __syncwarp();
-      };
-      for (int w = 0; ok && w < 2; ++w)
-        if (nblk[w] > 0) ok = wait_or_fail(&q_full[w], 0, 200 + w);
-      if (ok && nmax > 0) ok = wait_or_fail(&k_full[0], 0, 210);
-      if (ok) {
-        tc_fence_after_sync();
-        for (int w = 0; w < 2; ++w)
-          if (nblk[w] > 0) issue_qk(w, 0);
-        if (elect_one()) umma_commit(&k_empty[0]);
-        __syncwarp();
-      }
-      for (int j = 0; ok && j < nmax; ++j) {
-        const int st = j & 1;
-        ok = wait_or_fail(&v_full[st], (j >> 1) & 1, 230 + st);
-        bool k_next_ready = false;
-        for (int w = 0; ok && w < 2; ++w) {
-          if (j >= nblk[w]) continue;
-          ok = wait_or_fail(&p_full[w], j & 1, 220 + w);
-          if (!ok) break;
-          tc_fence_after_sync();
-          issue_pv(w, j);
-          if (j + 1 < nblk[w]) {
-            if (!k_next_ready) {
-              ok = wait_or_fail(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, 240);
-              if (!ok) break;
-              tc_fence_after_sync();
-              k_next_ready = true;
-            }
-            issue_qk(w, j + 1);
-          }
-        }
-        if (!ok) break;
-        if (elect_one()) {
-          umma_commit(&v_empty[st]);
-          if (j + 1 < nmax) umma_commit(&k_empty[(j + 1) & 1]);
-        }
-        __syncwarp();
-      }
-    }
-  } else {
-    warpgroup_reg_inc<104>();
-    // ------------------------------- softmax warps -------------------------------
-    const int w = warp >> 3;             // which query tile
-    const int hf = (warp >> 2) & 1;      // which 64 of the row's 128 scores / of O's 128 columns
-    const int q = warp & 3;              // TMEM lane quarter
-    const int r = q * 32 + lane;
-    const int qt = 2 * pair + w;
-    const int row = qt * kFaBM + r;
-    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const uint32_t t_s = tmem_base + w * 128 + hf * 64 + lane_addr;         // my scores (fp32)
-    const uint32_t t_p = tmem_base + w * 128 + hf * 32 + lane_addr;         // my part of P (bf16 pairs over S)
-    const uint32_t t_o = tmem_base + 256 + w * 128 + hf * 64 + lane_addr;   // my columns of O
-    const int bar_id = 1 + w * 4 + q;    // named barrier of the two warps that share these rows
-    const int nb = nblk[w];
-    const float sc = a.scale_log2;
-    float m_used = -INFINITY, l_run = 0.f;
-    bool ok = true;
-    for (int j = 0; j < nb; ++j) {
-      // After a failed wait the warp keeps walking the loop (without touching TMEM) so that its
-      // partner never waits alone at the named barrier.
-      if (ok && !__all_sync(0xffffffffu, mbar_wait(&s_full[w], j & 1, timeout, abort_flag))) {
-        if (lane == 0) report_status(a.status, kStatusMbarTimeout, kKernelIdFlashFwd4, 300 + w, 0, 0);
-        ok = false;
-      }
-      if (!ok) {
-        named_bar_sync(bar_id, 64);
-        continue;
-      }
-      tc_fence_after_sync();
-      const int kv0 = j * kFaBN + hf * 64;
-      const bool diag = (j == qt);
-      uint32_t sv[2][32];
-      tmem_ld_32x32(t_s, sv[0]);
-      tmem_ld_32x32(t_s + 32, sv[1]);
-      tmem_ld_wait();
-      if (diag || j * kFaBN + kFaBN > a.s) {
-        // only the diagonal block and a ragged last block need masking
-#pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = kv0 + c * 32 + i;
-            if ((diag && col > row) || col >= a.s) sv[c][i] = 0xff800000u;   // -inf
-          }
-      }
-      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-      for (int c = 0; c < 2; ++c)
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-          mx[i & 3] = fmax3(mx[i & 3], __uint_as_float(sv[c][2 * i]), __uint_as_float(sv[c][2 * i + 1]));
-      float m_raw = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      {
-        // Both halves of a row use the same reference maximum.  The slot alternates with the block
-        // parity: a value is overwritten two blocks later, after the partner has passed the barrier
-        // of the block in between, which it reaches only after reading.
-        float* slot = xch + ((j & 1) * 2 + w) * 256;
-        slot[hf * 128 + r] = m_raw;
-        named_bar_sync(bar_id, 64);
-        m_raw = fmaxf(m_raw, slot[(hf ^ 1) * 128 + r]);
-      }
-      const float m_blk = m_raw * sc;   // scale > 0
-      // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8 above it.
-      const float m_new = fmaxf(m_used, m_blk);
-      const bool first = (j == 0);
-      const bool grow = !first && (m_new > m_used + 8.0f);
-      if (first) m_used = (m_new == -INFINITY) ? 0.f : m_new;
-      if (__any_sync(0xffffffffu, grow)) {
-        // O holds the sum of blocks 0..j-1; P.V of block j-1 must have finished before it is touched.
-        if (!__all_sync(0xffffffffu, mbar_wait(&o_full[w], (j - 1) & 1, timeout, abort_flag))) {
-          ok = false;
-          continue;       // this block's named barrier is already behind us
-        }
-        tc_fence_after_sync();
-        const float f = grow ? exp2f(m_used - m_new) : 1.0f;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(t_o + c * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-          tmem_st_32x32(t_o + c * 32, v);
-        }
-        tmem_st_wait();
-        if (grow) {
-          l_run *= f;
-          m_used = m_new;
-        }
-      }
-      float l_part[4] = {0.f, 0.f, 0.f, 0.f};
-      const float neg_m = -m_used;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float x0 = fmaf(__uint_as_float(sv[c][2 * i]), sc, neg_m);
-          const float x1 = fmaf(__uint_as_float(sv[c][2 * i + 1]), sc, neg_m);
-          const float p0 = ((i & 1) * 2 < kPoly) ? poly_exp2(x0) : fast_exp2(x0);
-          const float p1 = ((i & 1) * 2 + 1 < kPoly) ? poly_exp2(x1) : fast_exp2(x1);
-          l_part[i & 3] += p0;
-          l_part[(i + 2) & 3] += p1;
-          pk[i] = pack_bf16x2(p0, p1);
-        }
-        // P (bf16 pairs) lies over the first half of the tile's score columns; every score of the
-        // tile is in registers by now (the partner passed the named barrier after its loads)
-        tmem_st_32x16(t_p + c * 16, pk);
-      }
-      tmem_st_wait();
-      l_run += (l_part[0] + l_part[1]) + (l_part[2] + l_part[3]);
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[w]);
-    }
-    {
-      // the row sum is the sum of the two halves' sums (same reference maximum)
-      float* slot = xch + (4 + w) * 256;
-      slot[hf * 128 + r] = l_run;
-      named_bar_sync(bar_id, 64);
-      l_run += slot[(hf ^ 1) * 128 + r];
-    }
-    if (ok && nb > 0 && mbar_wait(&o_full[w], (nb - 1) & 1, timeout, abort_flag)) {
-      tc_fence_after_sync();
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      const int hq = a.G * a.qpg;
-      __nv_bfloat16* dst = a.out + (((long long)row * a.b + bb) * hq + h) * kFaD + hf * 64;
-#pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_o + c * 32, v);
-        tmem_ld_wait();
-        if (row < a.s) {
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(v[8 * u + 0]) * inv, __uint_as_float(v[8 * u + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(v[8 * u + 2]) * inv, __uint_as_float(v[8 * u + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(v[8 * u + 4]) * inv, __uint_as_float(v[8 * u + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(v[8 * u + 6]) * inv, __uint_as_float(v[8 * u + 7]) * inv);
-            reinterpret_cast<uint4*>(dst)[c * 4 + u] = o;
-          }
-        }
-      }
-      if (row < a.s && hf == 0)
-        a.lse[((long long)bb * hq + h) * a.s + row] = (m_used + log2f(l_run)) * 0.6931471805599453f;
-    }
-    tc_fence_before_sync();
-  }
-
-  if (*abort_flag) {
-    const uint64_t t0 = global_timer_ns();
-    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 17) {
-    tc_fence_after_sync();
-    tmem_dealloc(tmem_base, 512);
-  }
-}
-
-// =========================================================================================
 // Backward.  One CTA owns a 128-position key/value block of one KV head and walks every query
 // tile (and every query head of the group) that attends to it.  Per step, on tcgen05:
 //   S  = Q K^T,  dP = dO V^T                      (accumulators in TMEM)
@@ -2474,28 +2127,11 @@ extern "C" int fm_flash_attn_fwd_push(const void* qkv, void* out, float* lse, in
   a.push_dst = reinterpret_cast<__nv_bfloat16* const*>(push_dst);
   a.push_flags = push_flags;
   a.push_me = push_me; a.push_P = push_P; a.push_sl = push_sl; a.push_row_blocks = push_row_blocks;
-  if (version == 4 || (version >= 40 && version <= 44)) {
-    using Fwd4Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
-    static const Fwd4Fn kFwd4[5] = {fm::flash_fwd4_kernel<0>, fm::flash_fwd4_kernel<1>, fm::flash_fwd4_kernel<2>,
-                                    fm::flash_fwd4_kernel<3>, fm::flash_fwd4_kernel<4>};
-    const int variant = version == 4 ? 0 : version - 40;
-    constexpr int smem4 = smem + 6 * 256 * 4;     // + the exchange of row maxima / row sums between the halves
-    static bool configured4[5] = {false, false, false, false, false};
-    if (!configured4[variant]) {
-      cudaError_t e4 = cudaFuncSetAttribute(kFwd4[variant], cudaFuncAttributeMaxDynamicSharedMemorySize, smem4);
-      if (e4 != cudaSuccess) {
-        fm_set_error(cudaGetErrorString(e4));
-        return (int)e4;
-      }
-      configured4[variant] = true;
-    }
-    const int nq4 = (s + fm::kFaBM - 1) / fm::kFaBM;
-    dim3 grid4((unsigned)(((nq4 + 1) / 2) * G * qpg * b), 1, 1);
-    kFwd4[variant]<<<grid4, fm::kFa4Threads, smem4, stream>>>(tmap, a);
-  } else if (version == 3 || (version >= 30 && version <= 34)) {
+  if (version == 3 || (version >= 30 && version <= 34)) {
     using Fwd3Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
-    static const Fwd3Fn kFwd3[5] = {fm::flash_fwd3_kernel<0>, fm::flash_fwd3_kernel<1>, fm::flash_fwd3_kernel<2>,
-                                    fm::flash_fwd3_kernel<3>, fm::flash_fwd3_kernel<4>};
+    // 30: special-function exponentials only; 32: two of every four values on the FMA pipe
+    static const Fwd3Fn kFwd3[5] = {fm::flash_fwd3_kernel<0>, fm::flash_fwd3_kernel<0>, fm::flash_fwd3_kernel<2>,
+                                    fm::flash_fwd3_kernel<2>, fm::flash_fwd3_kernel<2>};
     const int variant = version == 3 ? fm::kFa3DefaultPoly : version - 30;
     constexpr int smem3 = (1 + 2 * fm::kFa3Stages) * fm::kTileBytes + 1024 + 2048;
     static bool configured3[5] = {false, false, false, false, false};
@@ -2539,10 +2175,11 @@ extern "C" int fm_flash_attn_fwd_push(const void* qkv, void* out, float* lse, in
   } else if (version == 2 || (version >= 20 && version <= kMaxFwd2Version)) {
     // versions 20..24 pick the share of polynomial exponentials (0..4 of every 4 pairs)
     using Fwd2Fn = void (*)(const CUtensorMap, const fm::FlashFwdArgs);
-    // 20..24: share of polynomial exponentials; 25: developer timing experiment; 26: the whole MMA warp
+    // 20: one issuing lane, special-function exponentials; 22: two of every four exponentials on the FMA
+    // pipe; 25: developer timing experiment; 26: the whole MMA warp
     // walks the issue loop (uniform issue); 27 / 28: 26 with P handed over in two / four parts
-    static const Fwd2Fn kFwd2[9] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<1>, fm::flash_fwd2_kernel<2>,
-                                    fm::flash_fwd2_kernel<3>, fm::flash_fwd2_kernel<4>,
+    static const Fwd2Fn kFwd2[9] = {fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<0>, fm::flash_fwd2_kernel<2>,
+                                    fm::flash_fwd2_kernel<2>, fm::flash_fwd2_kernel<2>,
 #ifdef FM_FLASH_PROFILE
                                     fm::flash_fwd2_kernel<5>,
 #else

@@ -17,6 +17,12 @@ int fm_norm_bwd(const void* dy, const void* x, const void* w, const float* mean,
                 int kind, cudaStream_t s);
 int fm_rope_packed(void* t, const float* freqs, long long rows, int heads_per_row, int rope_heads,
                    int d, int rot, int rows_per_pos, int backward, cudaStream_t s);
+// The same, preceded by a bounded wait on `wait_n` per-source arrival counters (>= wait_expected):
+// RoPE is the first consumer of the projection buffer that peers fill.
+int fm_rope_packed_gated(void* t, const float* freqs, long long rows, int heads_per_row, int rope_heads, int d,
+                         int rot, int rows_per_pos, int backward, const int* wait_flags, int wait_n,
+                         int wait_expected, unsigned long long* wait_ns, unsigned long long timeout_ns,
+                         int* status, cudaStream_t s);
 // dlogits [T, E] fp32 from the slot-probability gradients (softmax-over-top-k backward, optional
 // load-balancing term aux_coef * tpe[e] and z-loss term z_coef * lse * softmax); tpe / logits may be null.
 int fm_router_bwd(const float* dprobs_slots, const int* slot_of_token, const long long* top_idx,
@@ -50,6 +56,13 @@ int fm_flash_attn_bwd(const void* qkv, const void* out, const void* dout, const 
                       float* dq_accum, void* dqkv, int s, int b, int G, int qpg, int d, float scale,
                       unsigned long long timeout_ns, int* status, int version, float* dkv_accum, int hsplit,
                       cudaStream_t stream);
+// The same, with the first kernel of the backward (the delta pass, the first reader of `dout`)
+// preceded by a bounded wait on `wait_n` per-source arrival counters (>= wait_expected).
+int fm_flash_attn_bwd_gated(const void* qkv, const void* out, const void* dout, const float* lse, float* delta,
+                            float* dq_accum, void* dqkv, int s, int b, int G, int qpg, int d, float scale,
+                            unsigned long long timeout_ns, int* status, int version, float* dkv_accum, int hsplit,
+                            const int* wait_flags, int wait_n, int wait_expected, unsigned long long* wait_ns,
+                            cudaStream_t stream);
 
 // Cross-entropy forward + backward in place: loss_out[row] = lse - logit[label]; logits are
 // overwritten with (softmax - onehot) * grad_scale (rows with a negative label get zeros).

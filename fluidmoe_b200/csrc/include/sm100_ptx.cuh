@@ -276,6 +276,29 @@ __device__ __forceinline__ bool flag_wait_ge(const int* flag, int expected, uint
   return false;
 }
 
+// Prologue of a kernel that consumes rows pushed by peers: the first `n` threads of every CTA wait,
+// bounded, until the `n` per-source arrival counters have reached `expected`; the others wait at
+// the CTA barrier.  CTA 0 reports a timeout and adds the time its slowest thread waited to
+// `wait_ns` (communication the step could not hide).  Replaces a stand-alone wait kernel in front
+// of the consumer.  Needs n <= blockDim.x.
+__device__ __forceinline__ void wait_counters_cta(const int* flags, int n, int expected,
+                                                  unsigned long long* wait_ns, uint64_t timeout_ns,
+                                                  int* status, int kernel_id) {
+  __shared__ unsigned long long slowest_wait;
+  if (threadIdx.x == 0) slowest_wait = 0;
+  __syncthreads();
+  if ((int)threadIdx.x < n) {
+    int observed = 0;
+    const uint64_t t0 = global_timer_ns();
+    if (!flag_wait_ge(flags + threadIdx.x, expected, timeout_ns, nullptr, &observed) && blockIdx.x == 0)
+      report_status(status, kStatusFlagTimeout, kernel_id, (int)threadIdx.x, expected, observed);
+    if (wait_ns != nullptr && blockIdx.x == 0)
+      atomicMax(&slowest_wait, (unsigned long long)(global_timer_ns() - t0));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && blockIdx.x == 0 && wait_ns != nullptr) atomicAdd(wait_ns, slowest_wait);
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -215,9 +215,15 @@ __global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float*
 // the rest (the value head) is left alone.  Position of a row = row / rows_per_pos.
 // sign = +1 forward, -1 backward (transposed rotation).
 // --------------------------------------------------------------------------------------------
+constexpr int kKernelIdRopeWait = 16;
 __global__ void rope_packed_kernel(__nv_bfloat16* __restrict__ t, const float* __restrict__ freqs,
                                    long long rows, int heads_per_row, int rope_heads, int d,
-                                   int rot, int rows_per_pos, int backward) {
+                                   int rot, int rows_per_pos, int backward, const int* wait_flags,
+                                   int wait_n, int wait_expected, unsigned long long* wait_ns,
+                                   unsigned long long timeout_ns, int* status) {
+  // first consumer of the projection buffer that peers fill: wait for their rows here
+  if (wait_flags != nullptr)
+    wait_counters_cta(wait_flags, wait_n, wait_expected, wait_ns, timeout_ns, status, kKernelIdRopeWait);
   const int half = rot / 2;
   const int vec_per_head = half / 8;
   const long long total = rows * rope_heads * vec_per_head;
@@ -321,21 +327,8 @@ __global__ void unpermute_reduce_kernel(const __nv_bfloat16* __restrict__ rows,
                                         const int* wait_flags, int wait_n, int wait_expected,
                                         unsigned long long* wait_ns, unsigned long long timeout_ns,
                                         int* status) {
-  if (wait_flags != nullptr) {
-    __shared__ unsigned long long slowest;
-    if (threadIdx.x == 0) slowest = 0;
-    __syncthreads();
-    if ((int)threadIdx.x < wait_n) {
-      int observed = 0;
-      const uint64_t t0 = global_timer_ns();
-      if (!flag_wait_ge(wait_flags + threadIdx.x, wait_expected, timeout_ns, nullptr, &observed) &&
-          blockIdx.x == 0)
-        report_status(status, kStatusFlagTimeout, kKernelIdUnpermuteWait, (int)threadIdx.x, wait_expected, observed);
-      if (wait_ns != nullptr && blockIdx.x == 0) atomicMax(&slowest, (unsigned long long)(global_timer_ns() - t0));
-    }
-    __syncthreads();
-    if (threadIdx.x == 0 && blockIdx.x == 0 && wait_ns != nullptr) atomicAdd(wait_ns, slowest);
-  }
+  if (wait_flags != nullptr)
+    wait_counters_cta(wait_flags, wait_n, wait_expected, wait_ns, timeout_ns, status, kKernelIdUnpermuteWait);
   const int nvec = H / 8;
   const int warps_per_block = blockDim.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -826,9 +819,23 @@ extern "C" int fm_rope_packed(void* t, const float* freqs, long long rows, int h
     fm_set_error("rope: rot_dim must be a multiple of 16 and at most head_dim");
     return -1;
   }
+  return fm_rope_packed_gated(t, freqs, rows, heads_per_row, rope_heads, d, rot, rows_per_pos, backward, nullptr,
+                              0, 0, nullptr, 0, nullptr, s);
+}
+
+extern "C" int fm_rope_packed_gated(void* t, const float* freqs, long long rows, int heads_per_row,
+                                    int rope_heads, int d, int rot, int rows_per_pos, int backward,
+                                    const int* wait_flags, int wait_n, int wait_expected,
+                                    unsigned long long* wait_ns, unsigned long long timeout_ns, int* status,
+                                    cudaStream_t s) {
+  if (rot % 16 != 0 || d % 8 != 0 || rot > d || wait_n > 256) {
+    fm_set_error("rope: rot_dim must be a multiple of 16 and at most head_dim (and at most 256 sources)");
+    return -1;
+  }
   const long long total = rows * rope_heads * (rot / 16);
   fm::rope_packed_kernel<<<grid_for(total, 256), 256, 0, s>>>(
-      (__nv_bfloat16*)t, freqs, rows, heads_per_row, rope_heads, d, rot, rows_per_pos, backward);
+      (__nv_bfloat16*)t, freqs, rows, heads_per_row, rope_heads, d, rot, rows_per_pos, backward, wait_flags,
+      wait_n, wait_expected, wait_ns, timeout_ns ? timeout_ns : 4000000000ull, status);
   return check_launch("rope_packed");
 }
 

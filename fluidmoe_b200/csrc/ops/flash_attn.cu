@@ -1262,8 +1262,14 @@ struct FlashBwdArgs {
   float* dkv_accum;      // [s, b, G, 2, d] fp32, zero-initialised; used when hsplit > 1
 };
 
+constexpr int kKernelIdDeltaWait = 17;
 __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ dout,
-                                  float* __restrict__ delta, int s, int b, int hq) {
+                                  float* __restrict__ delta, int s, int b, int hq, const int* wait_flags,
+                                  int wait_n, int wait_expected, unsigned long long* wait_ns,
+                                  unsigned long long timeout_ns, int* status) {
+  // first consumer of the output gradient that peers fill (SP -> HP exchange of the backward pass)
+  if (wait_flags != nullptr)
+    wait_counters_cta(wait_flags, wait_n, wait_expected, wait_ns, timeout_ns, status, kKernelIdDeltaWait);
   // one warp per (row, batch, head): delta[b, h, row] = sum_d dO * O   (d == 128)
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long total = (long long)s * b * hq;
@@ -2283,6 +2289,20 @@ extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* d
                                  float* delta, float* dq_accum, void* dqkv, int s, int b, int G, int qpg,
                                  int d, float scale, unsigned long long timeout_ns, int* status,
                                  int version, float* dkv_accum, int hsplit, cudaStream_t stream) {
+  return fm_flash_attn_bwd_gated(qkv, out, dout, lse, delta, dq_accum, dqkv, s, b, G, qpg, d, scale, timeout_ns,
+                                 status, version, dkv_accum, hsplit, nullptr, 0, 0, nullptr, stream);
+}
+
+extern "C" int fm_flash_attn_bwd_gated(const void* qkv, const void* out, const void* dout, const float* lse,
+                                       float* delta, float* dq_accum, void* dqkv, int s, int b, int G, int qpg,
+                                       int d, float scale, unsigned long long timeout_ns, int* status,
+                                       int version, float* dkv_accum, int hsplit, const int* wait_flags,
+                                       int wait_n, int wait_expected, unsigned long long* wait_ns,
+                                       cudaStream_t stream) {
+  if (wait_n > 256) {
+    fm_set_error("flash_attn_bwd: at most 256 sources");
+    return -1;
+  }
   if (d != fm::kFaD) {
     fm_set_error("flash_attn_bwd: head_dim must be 128");
     return -1;
@@ -2301,7 +2321,8 @@ extern "C" int fm_flash_attn_bwd(const void* qkv, const void* out, const void* d
   }
   const long long nrows = (long long)s * b * hq;
   fm::attn_delta_kernel<<<(unsigned)((nrows + 7) / 8), 256, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, s, b, hq);
+      reinterpret_cast<const __nv_bfloat16*>(out), reinterpret_cast<const __nv_bfloat16*>(dout), delta, s, b, hq,
+      wait_flags, wait_n, wait_expected, wait_ns, timeout_ns ? timeout_ns : 4000000000ull, status);
   constexpr int smem = 6 * fm::kTileBytes + 1024 + 256;
   static bool configured = false;
   if (!configured) {

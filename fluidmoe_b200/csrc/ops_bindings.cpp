@@ -31,6 +31,13 @@ void bind_ops(py::module_& m) {
                     p<const float*>(rstd), p<const void*>(res), p<void*>(dx), p<float*>(partial),
                     p<float*>(dw), p<float*>(db), T, H, kind, st(s)), "norm_bwd");
   });
+  m.def("rope_packed_gated", [](u t, u freqs, long long rows, int hpr, int rope_heads, int d, int rot,
+                                int rows_per_pos, int backward, u flags, int n, int expected, u wait_ns,
+                                unsigned long long timeout_ns, u status, u s) {
+    chk(fm_rope_packed_gated(p<void*>(t), p<const float*>(freqs), rows, hpr, rope_heads, d, rot, rows_per_pos,
+                             backward, p<const int*>(flags), n, expected, p<unsigned long long*>(wait_ns),
+                             timeout_ns, p<int*>(status), st(s)), "rope_packed_gated");
+  });
   m.def("rope_packed", [](u t, u freqs, long long rows, int hpr, int rope_heads, int d, int rot,
                           int rows_per_pos, int backward, u s) {
     chk(fm_rope_packed(p<void*>(t), p<const float*>(freqs), rows, hpr, rope_heads, d, rot,
@@ -73,6 +80,14 @@ void bind_ops(py::module_& m) {
   m.def("cross_entropy", [](u logits, u labels, u loss, int T, int V, float scale, u s) {
     chk(fm_cross_entropy(p<void*>(logits), p<const long long*>(labels), p<float*>(loss), T, V, scale, st(s)),
         "cross_entropy");
+  });
+  m.def("flash_attn_bwd_gated", [](u qkv, u out, u dout, u lse, u delta, u dq, u dqkv, int s_, int b, int G, int qpg,
+                                   int d, float scale, unsigned long long timeout_ns, u status, int version, u dkv,
+                                   int hsplit, u flags, int n, int expected, u wait_ns, u s) {
+    chk(fm_flash_attn_bwd_gated(p<const void*>(qkv), p<const void*>(out), p<const void*>(dout), p<const float*>(lse),
+                                p<float*>(delta), p<float*>(dq), p<void*>(dqkv), s_, b, G, qpg, d, scale, timeout_ns,
+                                p<int*>(status), version, p<float*>(dkv), hsplit, p<const int*>(flags), n, expected,
+                                p<unsigned long long*>(wait_ns), st(s)), "flash_attn_bwd_gated");
   });
   m.def("flash_attn_bwd", [](u qkv, u out, u dout, u lse, u delta, u dq, u dqkv, int s_, int b, int G, int qpg,
                              int d, float scale, unsigned long long timeout_ns, u status, int version, u dkv, int hsplit, u s) {

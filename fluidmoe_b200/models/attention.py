@@ -75,7 +75,7 @@ def split_qkv(qkv_full: torch.Tensor, plan: CPPlan):
 # forward
 # ============================================================================================
 def qkv_projection_forward(x: torch.Tensor, qkv_weight: torch.Tensor, plan: CPPlan,
-                           mode: str = "a2a", fused_ctx=None) -> torch.Tensor:
+                           mode: str = "a2a", fused_ctx=None, defer_wait: bool = False) -> torch.Tensor:
     """x ``[s_local*b, H]`` -> ``qkv_full [s, b, G, gs]`` (this rank's heads, full sequence).
 
     Counterpart of ``qkv_projection_p2p_forward`` (fluid/attention/forward.py:130-277).
@@ -86,7 +86,7 @@ def qkv_projection_forward(x: torch.Tensor, qkv_weight: torch.Tensor, plan: CPPl
     if P == 1:
         return gemm.gemm_nt(x, qkv_weight).view(sl, b, G, gs)
     if mode == "fused":
-        return fused_ctx.qkv_sp2hp(x, qkv_weight, plan)
+        return fused_ctx.qkv_sp2hp(x, qkv_weight, plan, defer_wait)
     if mode == "a2a":
         full = gemm.gemm_nt(x, qkv_weight)                        # [T, P*ppr]
         send = full.view(sl, b, P, ppr).permute(2, 0, 1, 3).contiguous()
@@ -219,7 +219,8 @@ def _valid_chunks(n: int, requested: int, what: str) -> int:
 
 
 def outproj_sp2hp_backward(d_out: torch.Tensor, proj_weight: torch.Tensor, plan: CPPlan,
-                           num_chunks: int = 1, mode: str = "a2a", fused_ctx=None) -> torch.Tensor:
+                           num_chunks: int = 1, mode: str = "a2a", fused_ctx=None,
+                           defer_wait: bool = False) -> torch.Tensor:
     """Region ``attn_proj``: ``dAttn = dOut @ Wproj`` per sequence chunk, each chunk sent through
     its SP->HP all-to-all while the next chunk is computed.  Returns ``[s, b, h_local, d]``.
     (fluid/attention/backward.py:46-184)"""
@@ -235,7 +236,7 @@ def outproj_sp2hp_backward(d_out: torch.Tensor, proj_weight: torch.Tensor, plan:
                 sched.execute_dw_tasks(max_defer_tasks=2)
             return out
         if mode == "fused":
-            return fused_ctx.outproj_dx_sp2hp(d_out, proj_weight, plan)
+            return fused_ctx.outproj_dx_sp2hp(d_out, proj_weight, plan, defer_wait)
         C = _valid_chunks(sl, num_chunks, "attn_proj") if sched.is_enabled() else 1
         dev, dt = d_out.device, d_out.dtype
         if C == 1:

@@ -112,10 +112,16 @@ class TransformerLayerFunction(torch.autograd.Function):
         if L.has_attention:
             with nvtx_range("ln1"):
                 ln1_out, mean1, rstd1 = norm.norm_fwd(x2, ln1_w, ln1_b, L.norm_eps, L.norm_type)
+            # device-initiated transport: the first kernel that reads a buffer peers are filling waits
+            # for their arrival counters itself (here RoPE), no stand-alone wait kernel in between
+            defer = mode_attn == "fused" and cp.cp_size > 1 and rotary is not None
             with nvtx_range("qkv_sp2hp"):
-                qkv_full = attn_mod.qkv_projection_forward(ln1_out, qkv_w, cp, mode_attn, fused)
+                qkv_full = attn_mod.qkv_projection_forward(ln1_out, qkv_w, cp, mode_attn, fused, defer_wait=defer)
             if rotary is not None:
-                rope.rope_packed_(qkv_full, rotary, cp.q_per_group, cp.head_dim)
+                rope.rope_packed_(qkv_full, rotary, cp.q_per_group, cp.head_dim,
+                                  wait=fused.take_pending_wait() if defer else None)
+                if defer:
+                    fused.finish_pending_wait()
             G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
             # with the device-initiated transport the attention kernel's epilogue stores every output
             # row at its sequence owner as well (when the shape allows), so no push kernel follows
@@ -373,15 +379,20 @@ class TransformerLayerFunction(torch.autograd.Function):
 
         # ---- R3: out-proj dX -> SP->HP ----
         attn_mod.output_projection_register_dw(lid, attn_in_full, dh1, proj_w)
+        defer = mode_attn == "fused" and cp.cp_size > 1     # the attention backward waits for the exchange itself
         with nvtx_range("bwd_attn_proj"):
-            d_attn = attn_mod.outproj_sp2hp_backward(dh1, proj_w, cp, L.attn_proj_chunks, mode_attn, fused)
+            d_attn = attn_mod.outproj_sp2hp_backward(dh1, proj_w, cp, L.attn_proj_chunks, mode_attn, fused,
+                                                     defer_wait=defer)
 
         # ---- attention backward (+ RoPE backward), packed per KV group ----
         with nvtx_range("bwd_attention"):
             G, qpg, d = cp.groups_per_rank, cp.q_per_group, cp.head_dim
             dqkv_hp = attn_ops.attention_bwd_packed(d_attn, qkv_full, attn_out,
                                                     lse if ctx.has_lse else None, qpg, d,
-                                                    1.0 / math.sqrt(d))
+                                                    1.0 / math.sqrt(d),
+                                                    wait=fused.take_pending_wait() if defer else None)
+            if defer:
+                fused.finish_pending_wait()
             if ctx.has_rotary:
                 rope.rope_packed_(dqkv_hp, rotary, qpg, d, backward=True)
 

@@ -95,7 +95,7 @@ def attention_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sca
 
 
 def attention_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse, q_per_group: int,
-                         head_dim: int, scale: float = None) -> torch.Tensor:
+                         head_dim: int, scale: float = None, wait=None) -> torch.Tensor:
     """Gradient of the packed projection buffer from the saved output (and log-sum-exp).
     ``FLUIDMOE_ATTN_BWD=native`` (default) selects this library's tcgen05 kernel, ``library`` the
     vendor attention backward."""
@@ -105,7 +105,9 @@ def attention_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tenso
     scale = scale if scale is not None else 1.0 / math.sqrt(head_dim)
     have_lse = lse is not None and lse.dim() == 3 and lse.dtype == torch.float32
     if have_lse and flash.supported(qkv, head_dim) and os.environ.get("FLUIDMOE_ATTN_BWD", "native") == "native":
-        return flash.flash_attn_bwd_packed(dout, qkv, out, lse, q_per_group, head_dim, scale)
+        return flash.flash_attn_bwd_packed(dout, qkv, out, lse, q_per_group, head_dim, scale, wait=wait)
+    if wait is not None:
+        wait["standalone"]()      # other back-ends cannot wait themselves
     qpg, d = q_per_group, head_dim
     heads = qkv.view(s, b, G, qpg + 2, d)
     q = heads[:, :, :, :qpg].reshape(s, b, G * qpg, d)

@@ -57,15 +57,20 @@ def norm_bwd(dy, x, weight, mean, rstd, kind, has_bias, residual_grad):
     return dx, dw, db
 
 
-def rope_packed_(qkv, freqs, q_per_group, head_dim, backward):
+def rope_packed_(qkv, freqs, q_per_group, head_dim, backward, wait=None):
     s, b, G, gs = qkv.shape
     rot = freqs.shape[-1]
     if qkv.dtype != torch.bfloat16 or rot % 16 or not qkv.is_contiguous():
         return None
     f = freqs.reshape(-1, rot).to(torch.float32).contiguous()
     assert f.shape[0] >= s
-    _native.lib().rope_packed(qkv.data_ptr(), f.data_ptr(), s * b * G, q_per_group + 2, q_per_group + 1,
-                              head_dim, rot, b * G, int(backward), _s())
+    if wait is None:
+        _native.lib().rope_packed(qkv.data_ptr(), f.data_ptr(), s * b * G, q_per_group + 2, q_per_group + 1,
+                                  head_dim, rot, b * G, int(backward), _s())
+    else:
+        _native.lib().rope_packed_gated(qkv.data_ptr(), f.data_ptr(), s * b * G, q_per_group + 2, q_per_group + 1,
+                                        head_dim, rot, b * G, int(backward), wait["flags"], wait["n"],
+                                        wait["expected"], wait["wait_ns"], wait["timeout_ns"], wait["status"], _s())
     return qkv
 
 

@@ -51,9 +51,10 @@ def flash_attn_fwd_packed(qkv: torch.Tensor, q_per_group: int, head_dim: int, sc
 
 def flash_attn_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tensor, lse: torch.Tensor,
                           q_per_group: int, head_dim: int, scale: float, version: int = 0,
-                          head_split=None) -> torch.Tensor:
+                          head_split=None, wait=None) -> torch.Tensor:
     """Gradient of the packed projection buffer, ``[s, b, G, (qpg + 2) * d]`` (dq heads, dk, dv per
-    KV group), from the saved output and log-sum-exp."""
+    KV group), from the saved output and log-sum-exp.  ``wait`` (``dict(flags, n, expected, wait_ns)``,
+    addresses as ints): per-source arrival counters of ``dout`` that the first kernel waits for."""
     global LAUNCHES
     s, b, G, gs = qkv.shape
     hq = G * q_per_group
@@ -73,8 +74,13 @@ def flash_attn_bwd_packed(dout: torch.Tensor, qkv: torch.Tensor, out: torch.Tens
                 hsplit *= 2
     dkv = torch.zeros(s, b, G, 2, head_dim, dtype=torch.float32, device=qkv.device) if hsplit > 1 else None
     LAUNCHES += 3 + (1 if hsplit > 1 else 0)
-    _native.lib().flash_attn_bwd(qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
-                                 dq_accum.data_ptr(), dqkv.data_ptr(), s, b, G, q_per_group, head_dim, float(scale),
-                                 0, status_buffer(qkv.device).data_ptr(), ver,
-                                 dkv.data_ptr() if dkv is not None else 0, hsplit, _native.stream_ptr())
+    args = (qkv.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(), delta.data_ptr(),
+            dq_accum.data_ptr(), dqkv.data_ptr(), s, b, G, q_per_group, head_dim, float(scale),
+            0, status_buffer(qkv.device).data_ptr(), ver, dkv.data_ptr() if dkv is not None else 0, hsplit)
+    if wait is None:
+        _native.lib().flash_attn_bwd(*args, _native.stream_ptr())
+    else:
+        # `dout` is still being filled by peers: the first kernel waits for their arrival counters
+        _native.lib().flash_attn_bwd_gated(*args, wait["flags"], wait["n"], wait["expected"], wait["wait_ns"],
+                                           _native.stream_ptr())
     return dqkv

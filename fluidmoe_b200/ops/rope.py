@@ -49,14 +49,19 @@ def apply_rope_bwd(dt: torch.Tensor, freqs: torch.Tensor) -> torch.Tensor:
 
 
 def rope_packed_(qkv: torch.Tensor, freqs: torch.Tensor, q_per_group: int, head_dim: int,
-                 backward: bool = False) -> torch.Tensor:
-    """In place on ``qkv [s, b, G, (q_per_group + 2) * d]``: rotate q heads and the k head."""
+                 backward: bool = False, wait=None) -> torch.Tensor:
+    """In place on ``qkv [s, b, G, (q_per_group + 2) * d]``: rotate q heads and the k head.
+    ``wait`` (``dict(flags, n, expected, wait_ns, timeout_ns, status, standalone)``): ``qkv`` is still
+    being filled by peers; the native kernel waits for their arrival counters itself, any other path
+    calls ``wait["standalone"]()`` first."""
     s, b, G, gs = qkv.shape
     if _native.use_native(qkv) and hasattr(_native.lib(), "rope_packed"):
         from . import elementwise
-        res = elementwise.rope_packed_(qkv, freqs, q_per_group, head_dim, backward)
+        res = elementwise.rope_packed_(qkv, freqs, q_per_group, head_dim, backward, wait)
         if res is not None:
             return res
+    if wait is not None:
+        wait["standalone"]()
     heads = qkv.view(s, b, G, q_per_group + 2, head_dim)
     part = heads[..., : q_per_group + 1, :].reshape(s, b, G * (q_per_group + 1), head_dim)
     fn = apply_rope_bwd if backward else apply_rope

@@ -113,6 +113,7 @@ class FusedCommContext:
         self.heap = SymmetricHeap(group, heap_bytes, self.device)
         self.rank, self.world = self.heap.rank, self.heap.world
         self.timeout_ns = int(timeout_ms * 1e6)
+        self._pending_wait = None
         self._layers: Dict[int, _LayerBuffers] = {}
         self._attn: Dict[int, _AttnBuffers] = {}
         self._sig: Dict[int, tuple] = {}
@@ -430,14 +431,37 @@ class FusedCommContext:
         return dict(dst_table=b.attn_in.ptr_table, flags_table=b.flags_proj.ptr_table, me=self.rank,
                     P=plan.cp_size, rows_per_rank=T, row_blocks=b.row_blocks)
 
-    def qkv_sp2hp(self, x, qkv_weight, plan):
-        """QKV projection whose epilogue performs the SP->HP exchange (fluid/attention/forward.py:130-277)."""
+    # ---- waits handed to the first consumer kernel instead of a stand-alone wait kernel ----
+    def _wait_or_defer(self, cnt: SymmTensor, expected: int, defer: bool) -> None:
+        if defer:
+            assert self._pending_wait is None, "the previous deferred wait was never consumed"
+            self._pending_wait = (cnt, expected)
+        else:
+            self._wait_counters(cnt, expected)
+            cnt.local.zero_()
+
+    def take_pending_wait(self):
+        """Arguments for the kernel that reads the buffer peers are still filling (it waits for the
+        arrival counters in its prologue); ``standalone`` runs the stand-alone wait kernel for
+        back-ends that cannot.  The caller ends with ``finish_pending_wait()``."""
+        cnt, expected = self._pending_wait
+        return dict(flags=cnt.local.data_ptr(), n=self.world, expected=expected, wait_ns=self._wait_ptr(1),
+                    timeout_ns=self.timeout_ns, status=status_buffer(self.device).data_ptr(),
+                    standalone=lambda: self._wait_counters(cnt, expected))
+
+    def finish_pending_wait(self) -> None:
+        cnt, _ = self._pending_wait
+        self._pending_wait = None
+        cnt.local.zero_()
+
+    def qkv_sp2hp(self, x, qkv_weight, plan, defer_wait: bool = False):
+        """QKV projection whose epilogue performs the SP->HP exchange (fluid/attention/forward.py:130-277).
+        ``defer_wait``: the caller's next kernel (RoPE) waits for the peers' column blocks itself."""
         b = self._attn[plan._fused_layer]
         P, sl, bt, ppr = plan.cp_size, plan.seq_local, plan.batch, plan.proj_per_rank
         T = sl * bt
         self._colscatter_gemm(x, qkv_weight, "nk", P, ppr, b.qkv_full, b.cnt_qkv_tbl, self.rank * T)
-        self._wait_counters(b.cnt_qkv, T * (ppr // 32))
-        b.cnt_qkv.local.zero_()
+        self._wait_or_defer(b.cnt_qkv, T * (ppr // 32), defer_wait)
         return b.qkv_full.local.view(P * sl, bt, plan.groups_per_rank, plan.group_size)
 
     def hp2sp_outproj(self, attn_out, proj_weight, plan, residual, pushed: bool = False):
@@ -458,8 +482,9 @@ class FusedCommContext:
         b.flags_proj.local.zero_()
         return out, b.attn_in.local
 
-    def outproj_dx_sp2hp(self, d_out, proj_weight, plan):
-        """Region attn_proj: ``dAttn = dOut @ Wproj`` with the SP->HP exchange in the epilogue."""
+    def outproj_dx_sp2hp(self, d_out, proj_weight, plan, defer_wait: bool = False):
+        """Region attn_proj: ``dAttn = dOut @ Wproj`` with the SP->HP exchange in the epilogue.
+        ``defer_wait``: the attention backward's first kernel waits for the peers' blocks itself."""
         from .scheduler import get_backward_scheduler
         b = self._attn[plan._fused_layer]
         P, sl, bt, dpr = plan.cp_size, plan.seq_local, plan.batch, plan.attn_per_rank
@@ -468,8 +493,7 @@ class FusedCommContext:
         sched = get_backward_scheduler()
         if sched.is_enabled():
             sched.execute_dw_tasks(max_defer_tasks=2)
-        self._wait_counters(b.cnt_dattn, T * (dpr // 32))
-        b.cnt_dattn.local.zero_()
+        self._wait_or_defer(b.cnt_dattn, T * (dpr // 32), defer_wait)
         return b.d_attn.local.view(P * sl, bt, plan.heads_per_rank, plan.head_dim)
 
     def hp2sp_qkv_dx(self, dqkv_hp, qkv_weight, plan):

@@ -151,6 +151,34 @@ def timed_region(torch, dist, world, fn_step, steps):
     return t[0].item(), t[1].item()
 
 
+class LossReader:
+    """Device-to-host read of every step's loss without stalling the launch queue: the 4-byte value is
+    copied into a pinned buffer right behind the step and read on the host one step later (the last
+    one at the end of the timed loop), the way a training loop logs its loss."""
+
+    def __init__(self, torch, steps):
+        self.torch, self.steps = torch, steps
+        self.buf = [torch.zeros((), dtype=torch.float32).pin_memory() for _ in range(2)]
+        self.ev = [torch.cuda.Event() for _ in range(2)]
+        self.pending = None
+        self.values = []
+
+    def _consume(self):
+        if self.pending is not None:
+            self.ev[self.pending].synchronize()
+            self.values.append(float(self.buf[self.pending]))
+            self.pending = None
+
+    def submit(self, i, loss):
+        slot = i & 1
+        self._consume()                       # the previous step's value: its copy finished long ago
+        self.buf[slot].copy_(loss.detach().float(), non_blocking=True)
+        self.ev[slot].record()
+        self.pending = slot
+        if i == self.steps - 1:
+            self._consume()                   # the last step is read before the timed loop ends
+
+
 def make_batches(torch, n, seq, batch, vocab, seed):
     """Pinned host batches of token ids, one extra position for the shifted labels."""
     g = torch.Generator().manual_seed(seed)
@@ -247,10 +275,11 @@ def run_ours(args):
     def step_device(i):
         last["loss"] = train_step(dev_batches[i % n_batches])
 
+    reader = LossReader(torch, args.steps)
+
     def step_e2e(i):
         ids = host[i % n_batches].to(device, non_blocking=True)
-        last["loss_val"] = train_step(ids).item()
-        trace.append(last["loss_val"])
+        reader.submit(i, train_step(ids))
 
     for i in range(args.warmup):
         step_device(i)
@@ -269,6 +298,9 @@ def run_ours(args):
     ms, _ = timed_region(torch, dist, world, step_device, args.steps)
     launches = gemm.LAUNCHES + elementwise.LAUNCHES + _extra_launches() - l0
     _, wall_e2e = timed_region(torch, dist, world, step_e2e, args.steps)
+    assert len(reader.values) == args.steps, "every step's loss is read on the host inside the timed region"
+    last["loss_val"] = reader.values[-1]
+    trace.extend(reader.values)
     clocks = sampler.stop() if rank == 0 else {}
     gemm.check_status()
     tokens = world * seq * batch * args.steps
@@ -296,7 +328,8 @@ def run_ours(args):
                    "loss": float(last["loss_val"]), **({"loss_trace": trace} if args.loss_trace else {})},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": wall_e2e / args.steps,
-                "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4,
+                "loss_readback": "copied to pinned memory behind every step, read on the host one step later (last step at the end of the loop)"},
         "gpu_launches": int(launches),
     })
     if world > 1:
@@ -456,10 +489,11 @@ def run_reference(args):
     def step_device(i):
         last["loss"] = train_step(dev_batches[i % n_batches])
 
+    reader = LossReader(torch, args.steps)
+
     def step_e2e(i):
         ids = host[i % n_batches].to(device, non_blocking=True)
-        last["loss_val"] = train_step(ids).item()
-        trace.append(last["loss_val"])
+        reader.submit(i, train_step(ids))
 
     try:
         for i in range(args.warmup):
@@ -475,6 +509,9 @@ def run_reference(args):
         sampler.start()
     ms, _ = timed_region(torch, dist, world, step_device, args.steps)
     _, wall_e2e = timed_region(torch, dist, world, step_e2e, args.steps)
+    assert len(reader.values) == args.steps, "every step's loss is read on the host inside the timed region"
+    last["loss_val"] = reader.values[-1]
+    trace.extend(reader.values)
     clocks = sampler.stop() if rank == 0 else {}
     tokens = world * seq * batch * args.steps
     value = tokens / (ms / 1e3)
@@ -494,7 +531,8 @@ def run_reference(args):
                    "loss": float(last["loss_val"]), **({"loss_trace": trace} if args.loss_trace else {})},
         "clocks": clocks,
         "e2e": {"value": tokens / (wall_e2e / 1e3), "unit": "tokens/s", "ms_per_step": wall_e2e / args.steps,
-                "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": (seq + 1) * batch * 8, "d2h_bytes_per_step": 4,
+                "loss_readback": "copied to pinned memory behind every step, read on the host one step later (last step at the end of the loop)"},
         "gpu_launches": 0,
     })
     dist.barrier()

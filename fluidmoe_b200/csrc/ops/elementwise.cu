@@ -125,7 +125,11 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 // --------------------------------------------------------------------------------------------
 constexpr int kNormBwdChunks = 4;  // columns per thread = 8 * chunks  ->  H <= 8192
 
-__global__ void __launch_bounds__(kNormThreads)
+// kChunks (1, 2 or 4) is chosen from H: the per-thread arrays below are sized by it, and with
+// four chunks the kernel needs 195 registers, which leaves one CTA of eight warps per SM and makes
+// it latency-bound (0.31 of the copy bandwidth at H = 4096); two chunks fit two CTAs per SM.
+template <int kChunks>
+__global__ void __launch_bounds__(kNormThreads, kChunks <= 2 ? 2 : 1)
 norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                 const __nv_bfloat16* __restrict__ w, const float* __restrict__ mean,
                 const float* __restrict__ rstd, const __nv_bfloat16* __restrict__ res_grad,
@@ -133,9 +137,9 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
                 int kind) {
   __shared__ float red[kNormThreads / 32];
   const int nvec = H / 8;
-  float dg[kNormBwdChunks][8], db[kNormBwdChunks][8], g[kNormBwdChunks][8];
+  float dg[kChunks][8], db[kChunks][8], g[kChunks][8];
 #pragma unroll
-  for (int c = 0; c < kNormBwdChunks; ++c) {
+  for (int c = 0; c < kChunks; ++c) {
     const int i = threadIdx.x + c * kNormThreads;
     if (i < nvec) unpack8(reinterpret_cast<const uint4*>(w)[i], g[c]);
 #pragma unroll
@@ -144,10 +148,10 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   for (long long r = blockIdx.x; r < T; r += gridDim.x) {
     const float mu = kind == 0 ? mean[r] : 0.f;
     const float rs = rstd[r];
-    float xh[kNormBwdChunks][8], gy[kNormBwdChunks][8];
+    float xh[kChunks][8], gy[kChunks][8];
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
-    for (int c = 0; c < kNormBwdChunks; ++c) {
+    for (int c = 0; c < kChunks; ++c) {
       const int i = threadIdx.x + c * kNormThreads;
       if (i < nvec) {
         float xv[8], dv[8];
@@ -167,7 +171,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
     const float c1 = block_sum<kNormThreads>(s1, red) / H;
     const float c2 = kind == 0 ? block_sum<kNormThreads>(s2, red) / H : 0.f;
 #pragma unroll
-    for (int c = 0; c < kNormBwdChunks; ++c) {
+    for (int c = 0; c < kChunks; ++c) {
       const int i = threadIdx.x + c * kNormThreads;
       if (i < nvec) {
         float o[8];
@@ -185,7 +189,7 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
   float* pg = partial + (long long)blockIdx.x * 2 * H;
 #pragma unroll
-  for (int c = 0; c < kNormBwdChunks; ++c) {
+  for (int c = 0; c < kChunks; ++c) {
     const int i = threadIdx.x + c * kNormThreads;
     if (i < nvec) {
 #pragma unroll
@@ -197,16 +201,27 @@ norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __res
   }
 }
 
-__global__ void norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
-                                       float* __restrict__ db, int nblocks, int H) {
-  const int col = blockIdx.x * blockDim.x + threadIdx.x;
-  if (col >= 2 * H) return;
+// Column sums of the partial buffer: a CTA owns 32 columns, its eight warps take every eighth
+// partial row each and the eight sums meet in shared memory.
+__global__ void __launch_bounds__(256)
+norm_bwd_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw,
+                       float* __restrict__ db, int nblocks, int H) {
+  __shared__ float part[8][33];
+  const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+  const int col = blockIdx.x * 32 + lane;
   float s = 0.f;
-  for (int b = 0; b < nblocks; ++b) s += partial[(long long)b * 2 * H + col];
-  if (col < H)
-    dw[col] = s;
-  else if (db != nullptr)
-    db[col - H] = s;
+  if (col < 2 * H)
+    for (int b = grp; b < nblocks; b += 8) s += partial[(long long)b * 2 * H + col];
+  part[grp][lane] = s;
+  __syncthreads();
+  if (grp == 0 && col < 2 * H) {
+#pragma unroll
+    for (int g2 = 1; g2 < 8; ++g2) s += part[g2][lane];
+    if (col < H)
+      dw[col] = s;
+    else if (db != nullptr)
+      db[col - H] = s;
+  }
 }
 
 // --------------------------------------------------------------------------------------------
@@ -803,12 +818,17 @@ extern "C" int fm_norm_bwd(const void* dy, const void* x, const void* w, const f
   }
   using bf = __nv_bfloat16;
   const int nb = fm_norm_bwd_blocks(T);
-  fm::norm_bwd_kernel<<<nb, fm::kNormThreads, 0, s>>>((const bf*)dy, (const bf*)x, (const bf*)w,
-                                                     mean, rstd, (const bf*)res_grad, (bf*)dx,
-                                                     partial, T, H, kind);
+  const int nvec = H / 8;
+  auto launch = [&](auto kernel) {
+    kernel<<<nb, fm::kNormThreads, 0, s>>>((const bf*)dy, (const bf*)x, (const bf*)w, mean, rstd,
+                                           (const bf*)res_grad, (bf*)dx, partial, T, H, kind);
+  };
+  if (nvec <= fm::kNormThreads) launch(fm::norm_bwd_kernel<1>);
+  else if (nvec <= 2 * fm::kNormThreads) launch(fm::norm_bwd_kernel<2>);
+  else launch(fm::norm_bwd_kernel<4>);
   int rc = check_launch("norm_bwd");
   if (rc) return rc;
-  fm::norm_bwd_reduce_kernel<<<(2 * H + 255) / 256, 256, 0, s>>>(partial, dw, db, nb, H);
+  fm::norm_bwd_reduce_kernel<<<(2 * H + 31) / 32, 256, 0, s>>>(partial, dw, db, nb, H);
   return check_launch("norm_bwd_reduce");
 }
 

@@ -15,6 +15,7 @@ int fm_norm_bwd_blocks(int T);
 int fm_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                 const void* res_grad, void* dx, float* partial, float* dw, float* db, int T, int H,
                 int kind, cudaStream_t s);
+// `freqs`: (cos, sin) pairs of the rotation angles, fp32 [positions][rot][2].
 int fm_rope_packed(void* t, const float* freqs, long long rows, int heads_per_row, int rope_heads,
                    int d, int rot, int rows_per_pos, int backward, cudaStream_t s);
 // The same, preceded by a bounded wait on `wait_n` per-source arrival counters (>= wait_expected):

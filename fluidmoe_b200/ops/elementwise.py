@@ -57,12 +57,29 @@ def norm_bwd(dy, x, weight, mean, rstd, kind, has_bias, residual_grad):
     return dx, dw, db
 
 
+_ROPE_TABLES = {}
+
+
+def _cos_sin_table(freqs, rot):
+    """``[positions, rot, 2]`` fp32 (cos, sin) of the angle tensor, computed once per angle tensor
+    (keyed by storage address, shape and in-place version; a few entries are kept)."""
+    key = (freqs.data_ptr(), tuple(freqs.shape), freqs._version, str(freqs.device))
+    tab = _ROPE_TABLES.get(key)
+    if tab is None:
+        f = freqs.reshape(-1, rot).to(torch.float32)
+        tab = torch.stack((torch.cos(f), torch.sin(f)), dim=-1).contiguous()
+        if len(_ROPE_TABLES) >= 8:
+            _ROPE_TABLES.pop(next(iter(_ROPE_TABLES)))
+        _ROPE_TABLES[key] = tab
+    return tab
+
+
 def rope_packed_(qkv, freqs, q_per_group, head_dim, backward, wait=None):
     s, b, G, gs = qkv.shape
     rot = freqs.shape[-1]
     if qkv.dtype != torch.bfloat16 or rot % 16 or not qkv.is_contiguous():
         return None
-    f = freqs.reshape(-1, rot).to(torch.float32).contiguous()
+    f = _cos_sin_table(freqs, rot)
     assert f.shape[0] >= s
     if wait is None:
         _native.lib().rope_packed(qkv.data_ptr(), f.data_ptr(), s * b * G, q_per_group + 2, q_per_group + 1,

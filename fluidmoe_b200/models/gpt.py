@@ -45,6 +45,33 @@ class _FinalNorm(torch.autograd.Function):
         return dx, None, None, None, None
 
 
+class _Embedding(torch.autograd.Function):
+    """Token embedding whose backward adds the touched rows straight into the parameter's fp32
+    gradient buffer (``weight.main_grad``, set by ``FluidDDP``): a step touches ``tokens`` of the
+    ``vocab`` rows, so this moves ``tokens x H`` values instead of building a dense ``[vocab, H]``
+    gradient, converting it and adding it over the whole table.  Without a gradient buffer it
+    returns the dense gradient like ``F.embedding``.  Rows that occur several times are summed with
+    floating-point atomics on the GPU, i.e. in no fixed order."""
+
+    @staticmethod
+    def forward(ctx, ids, weight):
+        ctx.save_for_backward(ids)
+        ctx.weight = weight
+        return F.embedding(ids, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        w = ctx.weight
+        flat_ids, flat_dy = ids.reshape(-1), dy.reshape(-1, dy.shape[-1])
+        main = getattr(w, "main_grad", None)
+        if main is not None and main.dtype == torch.float32:
+            main.index_add_(0, flat_ids, flat_dy.float())
+            return None, None
+        grad = torch.zeros_like(w, dtype=torch.float32).index_add_(0, flat_ids, flat_dy.float())
+        return None, grad.to(w.dtype)
+
+
 class _HeadLoss(torch.autograd.Function):
     """LM head GEMM + mean cross-entropy; the backward produces dh and queues the head dW."""
 
@@ -127,7 +154,7 @@ class MoEGPT(nn.Module):
         final hidden states when ``labels`` is None."""
         s_loc, b = ids.shape
         P = comm.group_size(self.cp_group)
-        x = self.embedding(ids)                                   # [s_loc, b, H]
+        x = _Embedding.apply(ids, self.embedding.weight)          # [s_loc, b, H]
         x = self.decoder(x, self.rotary(s_loc * P, ids.device))
         h = _FinalNorm.apply(x.reshape(s_loc * b, -1), self.final_norm_weight, self.final_norm_bias,
                              self.norm_eps, self.norm_type)

@@ -198,3 +198,31 @@ def test_reference_import_paths_resolve():
     assert TL2 is TransformerLayer and DDP2 is FluidDDP
     assert compute_round_robin_schedule(8)[0] == [(0, 7), (1, 6), (2, 5), (3, 4)]
     assert fluid.__version__ == "1.0.0"
+
+
+def test_embedding_backward_adds_touched_rows_into_the_gradient_buffer():
+    """``models.gpt._Embedding``: with an fp32 ``main_grad`` on the weight the touched rows are added
+    there and no dense gradient is produced; without one the dense gradient equals ``F.embedding``'s."""
+    import torch
+    import torch.nn.functional as F
+    from fluidmoe_b200.models.gpt import _Embedding
+
+    torch.manual_seed(0)
+    V, H = 50, 16
+    ids = torch.randint(0, V, (12, 3))
+    ids[0, 0] = ids[1, 1] = 7                      # a repeated row
+    gy = torch.randn(12, 3, H)
+    w_ref = torch.randn(V, H, requires_grad=True)
+    F.embedding(ids, w_ref).backward(gy)
+
+    w = w_ref.detach().clone().requires_grad_(True)
+    y = _Embedding.apply(ids, w)
+    assert torch.equal(y, F.embedding(ids, w_ref))
+    y.backward(gy)
+    assert torch.allclose(w.grad, w_ref.grad, atol=1e-6)
+
+    w2 = w_ref.detach().clone().requires_grad_(True)
+    w2.main_grad = torch.ones(V, H)                # accumulates on top of what is there
+    _Embedding.apply(ids, w2).backward(gy)
+    assert w2.grad is None
+    assert torch.allclose(w2.main_grad, 1.0 + w_ref.grad, atol=1e-6)

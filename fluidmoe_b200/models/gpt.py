@@ -104,9 +104,11 @@ class _HeadLoss(torch.autograd.Function):
         w = ctx.w
         if ctx.fused:
             h, dlogits, n = ctx.saved_tensors
-            dlogits.mul_((dloss / n).to(dlogits.dtype))
-            dh = gemm.gemm_nn(dlogits, w)
-            _register_dense_dw("lm_head", -1, h, dlogits, w)
+            # d(loss)/d(logits) as the kernel left it is for a sum; the factor dloss / n goes onto the
+            # two [T, H] tensors around it instead of one pass over the [T, V] logits
+            scale = (dloss / n).float()
+            dh = gemm.gemm_nn(dlogits, w).mul_(scale)
+            _register_dense_dw("lm_head", -1, h * scale, dlogits, w)
             return dh, None, None
         h, logits, lse, labels, n = ctx.saved_tensors
         p = torch.exp(logits.float() - lse.unsqueeze(1))

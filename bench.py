@@ -350,6 +350,25 @@ def _profile_one_step(torch, step_fn, path, rank=0):
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
     with open(path, "w") as f:
         f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=90))
+        # where the device sat idle: the largest gaps between consecutive kernels on the timeline
+        evs = []
+        for ev in prof.events():
+            tr = getattr(ev, "time_range", None)
+            if ev.device_time_total > 0 and tr is not None and str(getattr(ev, "device_type", "")).endswith("CUDA"):
+                evs.append((tr.start, tr.end, ev.name))
+        evs.sort()
+        gaps, busy_end, idle = [], None, 0.0
+        for st, en, name in evs:
+            if busy_end is not None and st > busy_end:
+                gaps.append((st - busy_end, prev_name, name))
+                idle += st - busy_end
+            if busy_end is None or en > busy_end:
+                busy_end, prev_name = en, name
+        if evs:
+            f.write("\n\ndevice timeline: %.3f ms from first kernel start to last kernel end, %.3f ms idle in %d gaps; "
+                    "largest gaps (us, after -> before):\n" % ((busy_end - evs[0][0]) / 1e3, idle / 1e3, len(gaps)))
+            for g, a, b in sorted(gaps, reverse=True)[:25]:
+                f.write(f"{g:10.1f}  {a[:70]}  ->  {b[:70]}\n")
         f.write("\n\nper-launch device time of the GEMM kernels (us), in launch order:\n")
         for ev in prof.events():
             if "gemm" in ev.name and "sm100_kernel" in ev.name and ev.device_time_total > 0:

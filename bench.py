@@ -369,10 +369,15 @@ def _profile_one_step(torch, step_fn, path, rank=0):
                     "largest gaps (us, after -> before):\n" % ((busy_end - evs[0][0]) / 1e3, idle / 1e3, len(gaps)))
             for g, a, b in sorted(gaps, reverse=True)[:25]:
                 f.write(f"{g:10.1f}  {a[:70]}  ->  {b[:70]}\n")
-        f.write("\n\nper-launch device time of the GEMM kernels (us), in launch order:\n")
+        # a collective that runs beside a persistent GEMM takes SMs from it: show the overlap per launch
+        coll = [(st, en) for st, en, name in evs if "nccl" in name.lower() or "allreduce" in name.lower()]
+        f.write("\n\nper-launch device time of the GEMM kernels (us) and the part of it during which a "
+                "collective kernel ran on another stream, in launch order:\n")
         for ev in prof.events():
             if "gemm" in ev.name and "sm100_kernel" in ev.name and ev.device_time_total > 0:
-                f.write(f"{ev.device_time_total:10.1f}  {ev.name[:110]}\n")
+                tr = getattr(ev, "time_range", None)
+                ov = sum(max(0.0, min(tr.end, en) - max(tr.start, st)) for st, en in coll) if tr is not None else 0.0
+                f.write(f"{ev.device_time_total:10.1f} {ov:9.1f}  {ev.name[:110]}\n")
 
 
 def _extra_launches() -> int:

@@ -1,7 +1,12 @@
 // Epilogues and host launcher of the tcgen05 GEMM (see gemm_sm100.cuh for the main loop).
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
+
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "../include/fm_api.h"
 #include "gemm_sm100.cuh"
@@ -841,8 +846,81 @@ static int launch_one(const CUtensorMap& ta, const CUtensorMap& tb, const GemmAr
   return 0;
 }
 
+// Workspace of the dynamic tile order, one per (device, stream): launches on one stream run one
+// after another, so they can share claim counters (used in rotation; a launch zeroes the counter
+// that comes up half a rotation later) and the log (entries carry the launch's epoch).  A stream
+// that is being captured into a graph keeps the static order, because a replay would repeat the
+// epoch of the capture.
+struct SchedWorkspace {
+  int* ctrs = nullptr;
+  unsigned long long* log = nullptr;
+  size_t log_entries = 0;
+  unsigned int epoch = 0;
+};
+constexpr int kSchedCounters = 64;
+
+static bool sched_dynamic_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("FLUIDMOE_GEMM_DYNAMIC_TILES");
+    on = (e == nullptr || e[0] != '0') ? 1 : 0;
+  }
+  return on == 1;
+}
+
+// Fills the scheduler fields of `args` for a launch of `pairs` CTA pairs over at most `tiles`
+// tiles; leaves them empty (static order) when the dynamic order is off or cannot be used.
+static void sched_prepare(GemmArgs& args, int pairs, long long tiles, cudaStream_t stream) {
+  args.sched_ctr = nullptr;
+  args.sched_ctr_reset = nullptr;
+  args.sched_log = nullptr;
+  args.sched_cap = 0;
+  args.sched_epoch = 0;
+  if (!sched_dynamic_enabled() || tiles <= pairs || tiles > (1ll << 24)) return;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    (void)cudaGetLastError();
+    return;
+  }
+  static std::mutex mu;
+  static std::map<std::pair<int, cudaStream_t>, SchedWorkspace> table;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  std::lock_guard<std::mutex> lock(mu);
+  SchedWorkspace& ws = table[std::make_pair(dev, stream)];
+  if (ws.ctrs == nullptr) {
+    if (cudaMalloc(&ws.ctrs, kSchedCounters * sizeof(int)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      ws.ctrs = nullptr;
+      return;
+    }
+    cudaMemsetAsync(ws.ctrs, 0, kSchedCounters * sizeof(int), stream);
+  }
+  // A pair can claim every tile but the other pairs' first ones, and one claim past the end.
+  const size_t cap_per_pair = (size_t)(tiles + 2);
+  const size_t need = cap_per_pair * (size_t)pairs;
+  if (need > ws.log_entries) {
+    // The old log may still be read by a launch in flight on this stream: it is not freed (logs
+    // only grow a few times, while the largest problem of a model is met for the first time).
+    unsigned long long* fresh = nullptr;
+    if (cudaMalloc(&fresh, need * sizeof(unsigned long long)) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return;
+    }
+    cudaMemsetAsync(fresh, 0, need * sizeof(unsigned long long), stream);
+    ws.log = fresh;
+    ws.log_entries = need;
+  }
+  if (++ws.epoch == 0) ws.epoch = 1;
+  args.sched_ctr = ws.ctrs + ws.epoch % kSchedCounters;
+  args.sched_ctr_reset = ws.ctrs + (ws.epoch + kSchedCounters / 2) % kSchedCounters;
+  args.sched_log = ws.log;
+  args.sched_cap = (int)cap_per_pair;
+  args.sched_epoch = ws.epoch;
+}
+
 template <bool A_MN, bool B_MN, class Epi, class Gate>
-static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args,
+static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args_in,
                        const Epi& epi, const Gate& gate, int grid, cudaStream_t stream) {
   auto kern = gemm2_sm100_kernel<A_MN, B_MN, Epi, Gate>;
   constexpr int smem = gemm2_smem_bytes();
@@ -880,6 +958,8 @@ static int launch_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmA
   grid &= ~1;   // whole CTA pairs
   if (grid > 2 * max_pairs) grid = 2 * max_pairs;
   if (grid < 2) grid = 2;
+  GemmArgs args = args_in;
+  sched_prepare(args, grid / 2, args_in.sched_cap, stream);   // sched_cap arrives as the tile bound
   kern<<<grid, kGemmThreads, smem, stream>>>(ta, tb, args, epi, gate);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -1011,13 +1091,25 @@ extern "C" int fm_gemm_launch(const FmGemmDesc* d, cudaStream_t stream) {
   int grid = sm_count();
   if (d->max_ctas > 0 && d->max_ctas < grid) grid = d->max_ctas;
   // Do not launch more CTAs than tiles when the tile count is known on the host.
-  if (d->group_rows == nullptr) {
+  {
     const int npt = d->gated ? d->bn / 2 : d->bn;
     const long long nt = (d->N + npt - 1) / npt;
     const int tm = d->cta_pair ? 2 * kBM : kBM;
-    const long long mt = d->mode == 0 ? (d->uniform_rows + tm - 1) / tm : (d->M + tm - 1) / tm;
-    const long long tiles = nt * mt * d->num_groups * (d->cta_pair ? 2 : 1);
-    if (tiles < grid) grid = (int)(tiles > 0 ? tiles : 1);
+    if (d->group_rows == nullptr) {
+      const long long mt = d->mode == 0 ? (d->uniform_rows + tm - 1) / tm : (d->M + tm - 1) / tm;
+      const long long tiles = nt * mt * d->num_groups * (d->cta_pair ? 2 : 1);
+      if (tiles < grid) grid = (int)(tiles > 0 ? tiles : 1);
+    }
+    // Upper bound of the tile count for the dynamic tile order of the CTA-pair kernel (the launcher
+    // replaces it by the log's row length).  With row counts in device memory the rows of A bound it.
+    long long bound;
+    if (d->mode == 1)
+      bound = nt * ((d->M + tm - 1) / tm) * d->num_groups;
+    else if (d->group_rows == nullptr)
+      bound = nt * ((d->uniform_rows + tm - 1) / tm) * d->num_groups;
+    else
+      bound = nt * (d->a_outer / tm + d->num_groups);
+    args.sched_cap = (int)(bound < (1ll << 30) ? bound : 0);
   }
 
   switch (d->epi) {

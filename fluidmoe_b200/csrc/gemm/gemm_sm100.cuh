@@ -1,7 +1,9 @@
 // Persistent, warp-specialised tcgen05 GEMM for sm_100a.
 //
 // One CTA (or a CTA pair sharing a 256 x BN tile through tcgen05.mma.cta_group::2) per SM walks a
-// static list of output tiles.  Warp 0 feeds a shared-memory ring (5 stages for the CTA pair, 4 or 3
+// list of output tiles: a static one for the single CTA, one claimed tile by tile from a counter for
+// the CTA pair (`TileOrder`), so that pairs which start late, because a collective kernel holds
+// their SMs, do fewer tiles instead of making the whole GEMM late.  Warp 0 feeds a shared-memory ring (5 stages for the CTA pair, 4 or 3
 // for a single CTA) with TMA tiled loads
 // (128-byte swizzle), warp 1 issues tcgen05.mma with the accumulator in TMEM (two accumulators, so
 // the epilogue of tile i overlaps the main loop of tile i+1), warps 2-9 (two per TMEM lane quarter,
@@ -31,6 +33,7 @@ constexpr int kEpiStageFloats = 32 * 36;   // per epilogue warp: 32 rows x 32 co
 constexpr int kEpiWarps = 8;    // two warps per TMEM lane quarter, each takes half the columns
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kKernelIdGemm = 1;
+constexpr int kKernelIdGemm2 = 2;
 
 struct GemmArgs {
   int mode;          // 0 grouped-M, 1 grouped-K
@@ -56,6 +59,15 @@ struct GemmArgs {
   // waiting in a gate for rows that had not arrived yet.  Divided by the number of CTAs it
   // bounds the communication time this kernel could not hide.
   unsigned long long* wait_ns;
+  // Dynamic tile order of the CTA-pair kernel (nullptr = every pair walks tiles pair, pair + pairs,
+  // ...).  `sched_ctr` is this launch's claim counter (zero at launch), `sched_ctr_reset` a counter
+  // that no launch in flight uses and that this launch zeroes for a later one, `sched_log` holds
+  // `sched_cap` entries per pair: entry j = (sched_epoch << 32 | tile) is the j-th tile of the pair.
+  int* sched_ctr;
+  int* sched_ctr_reset;
+  unsigned long long* sched_log;
+  int sched_cap;
+  unsigned int sched_epoch;
 };
 
 struct Tile {
@@ -120,6 +132,63 @@ struct TileWalker {
       ++g;
     }
     return false;
+  }
+};
+
+// Which tile a CTA pair computes j-th.  Static order: pair, pair + pairs, ...  Dynamic order: the
+// first tile is the static one, every further tile is claimed from a counter in global memory by
+// the leader CTA's producer lane, which writes it into the pair's row of a log in global memory; the
+// other roles of both CTAs (peer producer, MMA warp, epilogue warps) read the log.  An entry is one
+// 64-bit word (launch epoch << 32 | tile), so a reader needs no ordering beyond the load itself, and
+// entries of earlier launches never match.  A persistent kernel with a static order finishes as
+// late as its slowest pair: when a collective kernel on another stream holds a few SMs, the pairs
+// that could not start until it left still had their full share of tiles to do, and the GEMM took
+// its own time plus the collective's.  With claimed tiles the late pairs simply do fewer.
+struct TileOrder {
+  unsigned long long* row;
+  int* ctr;
+  unsigned int epoch;
+  int cap, pair_id, num_pairs;
+  __device__ TileOrder(const GemmArgs& a, int pair, int pairs)
+      : row(a.sched_log ? a.sched_log + (size_t)pair * a.sched_cap : nullptr), ctr(a.sched_ctr),
+        epoch(a.sched_epoch), cap(a.sched_cap), pair_id(pair), num_pairs(pairs) {}
+  __device__ __forceinline__ bool dynamic() const { return row != nullptr; }
+  __device__ __forceinline__ int claim() const { return num_pairs + atomicAdd(ctr, 1); }
+  __device__ __forceinline__ bool publish(int j, int tile, int* status, volatile int* abort_flag) const {
+    if (j >= cap) {   // the host sized the log for every tile of the problem: cannot happen
+      report_status(status, kStatusBadArgs, kKernelIdGemm2, 900, cap, j);
+      *abort_flag = 1;
+      return false;
+    }
+    const unsigned long long v = ((unsigned long long)epoch << 32) | (unsigned int)tile;
+    asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(row + j), "l"(v) : "memory");
+    return true;
+  }
+  // Raw entry j (issue early, decode late: the load's latency hides behind other work).
+  __device__ __forceinline__ unsigned long long peek(int j) const {
+    unsigned long long v = 0;
+    if (j < cap) asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(row + j) : "memory");
+    return v;
+  }
+  __device__ __forceinline__ bool valid(unsigned long long v) const { return (unsigned int)(v >> 32) == epoch; }
+  // Tile j of this pair; -1 when the wait was given up (bounded like every other wait).
+  __device__ __forceinline__ int get(int j, unsigned long long seen, unsigned long long timeout_ns, int* status,
+                                     volatile int* abort_flag) const {
+    if (!dynamic()) return pair_id + j * num_pairs;
+    if (valid(seen)) return (int)(unsigned int)seen;
+    if (j >= cap) return -1;
+    const uint64_t t0 = global_timer_ns();
+    while (true) {
+      const unsigned long long v = peek(j);
+      if (valid(v)) return (int)(unsigned int)v;
+      if (*abort_flag) return -1;
+      if (global_timer_ns() - t0 > timeout_ns) {
+        report_status(status, kStatusFlagTimeout, kKernelIdGemm2, 901, j, (int)(v >> 32));
+        *abort_flag = 1;
+        return -1;
+      }
+      __nanosleep(100);
+    }
   }
 };
 
@@ -478,7 +547,6 @@ gemm_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
 // *arrival*, not of a load).  Each CTA drains its own 128 accumulator rows from its own TMEM.
 // =========================================================================================
 constexpr int kStages2 = 5;
-constexpr int kKernelIdGemm2 = 2;
 
 constexpr int gemm2_smem_bytes() {
   return kStages2 * (kBM * kBK * 2 + 128 * kBK * 2) + kEpiWarps * kEpiStageFloats * 4 + 1024 + 256;
@@ -544,15 +612,29 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
     // ------------------------------- TMA producer (both CTAs) -------------------------------
     if (lane == 0) {
       TileWalker<BN, 2 * kBM> walker(args);
+      const TileOrder order(args, pair_id, num_pairs);
+      const bool claimer = order.dynamic() && leader;
+      if (claimer && pair_id == 0 && args.sched_ctr_reset != nullptr) *args.sched_ctr_reset = 0;
       Tile t;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int ti = pair_id; ok && walker.get(ti, t); ti += num_pairs) {
+      int ti = pair_id;
+      for (int j = 0; ok && ti >= 0 && walker.get(ti, t); ++j) {
+        // The claim of the next tile is issued here and written to the log after the first block's
+        // loads, so the counter's round trip hides behind them; every reader finds the entry a
+        // whole tile before it needs it.
+        int claimed = 0;
+        bool published = !claimer;
+        if (claimer) claimed = order.claim();
         Tile mine = t;                       // this CTA's 128 rows of the pair tile
         mine.m0 = t.m0 + (int)cta_rank * kBM;
         mine.rows_valid = max(0, min(kBM, t.rows_valid - (int)cta_rank * kBM));
         if (mine.rows_valid > 0 && !gate.wait(mine, args, abort_flag)) break;
+        if (t.nk == 0 && !published) {
+          ok = order.publish(j + 1, claimed, args.status, abort_flag);
+          published = true;
+        }
         for (int kb = 0; kb < t.nk; ++kb) {
           const int kbe = args.k_rotate ? (kb + args.k_rotate) % t.nk : kb;
           if (mine.rows_valid > 0 && !gate.wait_k(mine, kbe, kb == 0, args, abort_flag)) {
@@ -593,7 +675,13 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
             stage = 0;
             phase ^= 1;
           }
+          if (!published) {
+            ok = order.publish(j + 1, claimed, args.status, abort_flag);
+            published = true;
+          }
         }
+        if (!ok) break;
+        ti = claimer ? claimed : order.get(j + 1, 0ull, timeout, args.status, abort_flag);
       }
     }
   } else if (warp == 1) {
@@ -621,13 +709,16 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
         return __all_sync(0xffffffffu, mbar_wait(bar, parity, timeout, abort_flag)) != 0;
       };
       TileWalker<BN, 2 * kBM> walker(args);
+      const TileOrder order(args, pair_id, num_pairs);
       Tile t;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int ti = pair_id; ok && walker.get(ti, t); ti += num_pairs) {
+      int ti = pair_id;
+      for (int j = 0; ok && ti >= 0 && walker.get(ti, t); ++j) {
+        unsigned long long seen = 0;   // log entry of the next tile, fetched during the last k block
         if (!wait_all(&tempty[acc], acc_phase ^ 1)) {
           if (lane == 0) report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 200 + acc, 0, 0);
           break;
@@ -635,6 +726,7 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < t.nk; ++kb) {
+          if (order.dynamic() && kb == t.nk - 1) seen = order.peek(j + 1);
           if (!wait_all(&full[stage], phase)) {
             if (lane == 0) report_status(args.status, kStatusMbarTimeout, kKernelIdGemm2, 300 + stage, 0, 0);
             ok = false;
@@ -664,6 +756,9 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
           acc = 0;
           acc_phase ^= 1;
         }
+        // every lane reads the same entry, so the tile index stays uniform across the warp
+        ti = order.get(j + 1, seen, timeout, args.status, abort_flag);
+        ti = __shfl_sync(0xffffffffu, ti, 0);
       }
     }
   } else {
@@ -672,17 +767,27 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
     const int chalf = (warp - 2) >> 2;
     TileWalker<BN, 2 * kBM> walker(args);
     TileWalker<BN, 2 * kBM> peek(args);
+    const TileOrder order(args, pair_id, num_pairs);
     Tile t;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int ti = pair_id; walker.get(ti, t); ti += num_pairs) {
+    int ti = pair_id;
+    for (int j = 0; ti >= 0 && walker.get(ti, t); ++j) {
       Tile mine = t;
       mine.m0 = t.m0 + (int)cta_rank * kBM;
       mine.rows_valid = max(0, min(kBM, t.rows_valid - (int)cta_rank * kBM));
+      // The producer wrote the next tile's log entry while it loaded this tile, which the epilogue
+      // reaches at least one main loop later.
+      unsigned long long seen = 0;
+      if (order.dynamic()) {
+        if (lane == 0) seen = order.peek(j + 1);
+        seen = __shfl_sync(0xffffffffu, seen, 0);
+      }
       if constexpr (EpiHasPrefetch<Epi>::value) {
         Tile nx;
-        if (ti == pair_id) epi.template prefetch<BN>(mine, args, q * 32 + lane, chalf);
-        if (peek.get(ti + num_pairs, nx)) {
+        if (j == 0) epi.template prefetch<BN>(mine, args, q * 32 + lane, chalf);
+        const int tn = order.dynamic() ? (order.valid(seen) ? (int)(unsigned int)seen : -1) : ti + num_pairs;
+        if (tn >= 0 && peek.get(tn, nx)) {
           nx.rows_valid = max(0, min(kBM, nx.rows_valid - (int)cta_rank * kBM));
           nx.m0 += (int)cta_rank * kBM;
           epi.template prefetch<BN>(nx, args, q * 32 + lane, chalf);
@@ -710,6 +815,8 @@ gemm2_sm100_kernel(const __grid_constant__ CUtensorMap tma_a,
         acc = 0;
         acc_phase ^= 1;
       }
+      if (lane == 0) ti = order.get(j + 1, seen, timeout, args.status, abort_flag);
+      ti = __shfl_sync(0xffffffffu, ti, 0);
     }
   }
 

@@ -214,3 +214,45 @@ def test_wgrad_adam_epilogue_matches_fp32_reference(G, rows_per, M, N, cta_pair,
     for name, got, ref in (("m", m, m_ref), ("v", v, v_ref), ("p", p, w_ref)):
         err = ((got.float() - ref).norm() / ref.norm()).item()
         assert err < 6e-3, (name, err)
+
+
+def test_cta_pair_claimed_tile_order_few_pairs_many_launches(cta_pair):
+    """Two CTA pairs claim the 64 tiles of the problem one by one (the order is dynamic whenever
+    there are more tiles than pairs); 80 launches walk the claim counters round more than once,
+    and a second stream, with a workspace of its own, runs beside the first."""
+    torch.manual_seed(3)
+    a = _rand(2048, 256)
+    w = _rand(2048, 256)
+    ref = a.float() @ w.float().t()
+    side = torch.cuda.Stream()
+    outs = []
+    for i in range(80):
+        outs.append(gemm.grouped_gemm(a, w, b_layout="nk", max_ctas=4))
+        if i % 8 == 0:
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                outs.append(gemm.grouped_gemm(a, w, b_layout="nk", max_ctas=6))
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for o in (outs[0], outs[1], outs[40], outs[-1]):
+        _close(o, ref)
+    assert all(torch.equal(o, outs[0]) for o in outs[1:])
+
+
+def test_cta_pair_claimed_tile_order_with_row_counts_on_the_device(cta_pair):
+    """Row counts in device memory: the host only knows a bound of the tile count, pairs stop at
+    the first claim past the last tile, and empty groups contribute no tile."""
+    torch.manual_seed(4)
+    G, K, N = 6, 128, 1024
+    rows = torch.tensor([700, 0, 256, 1, 1030, 0], dtype=torch.int32)
+    offs = torch.tensor([0, 768, 768, 1024, 1280, 2560], dtype=torch.int32)
+    a = _rand(2560, K)
+    w = _rand(G, N, K)
+    out = gemm.grouped_gemm(a, w, b_layout="nk", group_rows=rows.cuda(), group_offs=offs.cuda(), max_ctas=4)
+    torch.cuda.synchronize()
+    gemm.check_status()
+    for g in range(G):
+        o, r = offs[g].item(), rows[g].item()
+        if r:
+            _close(out[o:o + r], a[o:o + r].float() @ w[g].float().t())

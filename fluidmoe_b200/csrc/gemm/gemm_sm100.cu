@@ -899,6 +899,7 @@ static void sched_prepare(GemmArgs& args, int pairs, long long tiles, cudaStream
   // A pair can claim every tile but the other pairs' first ones, and one claim past the end.
   const size_t cap_per_pair = (size_t)(tiles + 2);
   const size_t need = cap_per_pair * (size_t)pairs;
+  if (need * sizeof(unsigned long long) > ((size_t)64 << 20)) return;   // very many tiles: static order
   if (need > ws.log_entries) {
     // The old log may still be read by a launch in flight on this stream: it is not freed (logs
     // only grow a few times, while the largest problem of a model is met for the first time).

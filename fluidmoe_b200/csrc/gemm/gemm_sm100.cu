@@ -559,6 +559,22 @@ struct EpiDAct {
   int gated;   // activation is SwiGLU: pre_in / dpre hold [gate | up] halves `n_half` apart
   int n_half;
 
+  static constexpr bool kPrefetch = true;
+  // Called one tile ahead: pull this thread's row of the pre-activations (gate and up half of the
+  // tile's columns) into L2 while the tensor core still works on the tile.
+  template <int BN>
+  __device__ __forceinline__ void prefetch(const Tile& t, const GemmArgs& a, int r, int chalf) const {
+    if (r >= t.rows_valid) return;
+    const int col0 = t.n_tile * BN + chalf * (BN / 2);
+    const __nv_bfloat16* src = pre_in + ((long long)t.row_base + t.m0 + r) * ld_pre_in + col0;
+#pragma unroll
+    for (int l = 0; l < BN / 2; l += 64) {     // 64 bf16 = one 128-byte line
+      if (col0 + l >= a.N) break;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(src + l));
+      if (gated) asm volatile("prefetch.global.L2 [%0];" ::"l"(src + n_half + l));
+    }
+  }
+
   template <int BN>
   __device__ __forceinline__ void run(const Tile& t, const GemmArgs& a, uint32_t taddr, int r,
                                       bool zero, int chalf, float* stg) const {
@@ -569,8 +585,85 @@ struct EpiDAct {
     const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
     const float p = (row_ok && probs) ? probs[row] : 1.0f;
     float dp = 0.f;
+    const int c_first = chalf * (BN / 64), c_last = (chalf + 1) * (BN / 64);
+    const __nv_bfloat16* pre0 = pre_in + row0 * ld_pre_in;
+    __nv_bfloat16* dpre0 = dpre + row0 * ld_dpre;
+    if (gated && rows_ok == 32 && t.n_tile * BN + c_last * 32 <= a.N && ((ld_pre_in | ld_dpre | n_half) & 7) == 0 &&
+        aligned16(pre0) && aligned16(dpre0)) {
+      // Whole SwiGLU tile inside the matrix (the common case).  Only the accumulator goes through
+      // the shared-memory stage; gate and up pre-activations are read, and their gradients written,
+      // in the coalesced layout (4 lanes x 16 bytes per row, 8 rows per pass), and all eight loads
+      // of a block are issued before the accumulator is fetched, so their latency overlaps.  The
+      // probability gradient is summed per (row, lane quad) and folded to one value per row at the end.
+      const int sub = lane >> 2, c8 = (lane & 3) * 8;
+      float pr[4], dq[4];
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        pr[pass] = probs ? probs[row0 + pass * 8 + sub] : 1.0f;
+        dq[pass] = 0.f;
+      }
 #pragma unroll 1
-    for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+      for (int c = c_first; c < c_last; ++c) {
+        const int col = t.n_tile * BN + c * 32;
+        uint4 rg[4], ru[4];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const long long o = (long long)(pass * 8 + sub) * ld_pre_in + col + c8;
+          rg[pass] = *reinterpret_cast<const uint4*>(pre0 + o);
+          ru[pass] = *reinterpret_cast<const uint4*>(pre0 + o + n_half);
+        }
+        {
+          float v[32];
+          load_acc(taddr + c * 32, v, zero);
+          stage_put(stg, lane, v);
+        }
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const int rr = pass * 8 + sub;
+          const float4 va = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+          const float4 vb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+          const float vv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+          const uint32_t* wg = reinterpret_cast<const uint32_t*>(&rg[pass]);
+          const uint32_t* wu = reinterpret_cast<const uint32_t*>(&ru[pass]);
+          float og[8], ou[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            // bf16 -> fp32 is a 16-bit shift of the bit pattern
+            const uint32_t gw = wg[i >> 1], uw = wu[i >> 1];
+            const float gi = __uint_as_float((i & 1) ? (gw & 0xffff0000u) : (gw << 16));
+            const float ui = __uint_as_float((i & 1) ? (uw & 0xffff0000u) : (uw << 16));
+            const float sg = sigmoid_f(gi);
+            const float sl = gi * sg;
+            dq[pass] += vv[i] * sl * ui;
+            const float da = vv[i] * pr[pass];
+            og[i] = da * ui * (sg * (1.0f + gi * (1.0f - sg)));
+            ou[i] = da * sl;
+          }
+          uint4 pg, pu;
+          pg.x = pack_bf16x2(og[0], og[1]); pg.y = pack_bf16x2(og[2], og[3]);
+          pg.z = pack_bf16x2(og[4], og[5]); pg.w = pack_bf16x2(og[6], og[7]);
+          pu.x = pack_bf16x2(ou[0], ou[1]); pu.y = pack_bf16x2(ou[2], ou[3]);
+          pu.z = pack_bf16x2(ou[4], ou[5]); pu.w = pack_bf16x2(ou[6], ou[7]);
+          const long long o = (long long)rr * ld_dpre + col + c8;
+          *reinterpret_cast<uint4*>(dpre0 + o) = pg;
+          *reinterpret_cast<uint4*>(dpre0 + o + n_half) = pu;
+        }
+      }
+      __syncwarp();
+      // row pass * 8 + sub: sum over its four lanes, then hand every lane the sum of its own row
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        float x = dq[pass];
+        x += __shfl_xor_sync(0xffffffffu, x, 1);
+        x += __shfl_xor_sync(0xffffffffu, x, 2);
+        x = __shfl_sync(0xffffffffu, x, (lane & 7) * 4);
+        if ((lane >> 3) == pass) dp = x;
+      }
+      if (dprobs_partial) dprobs_partial[(row * n_tiles + t.n_tile) * 2 + chalf] = dp;
+      return;
+    }
+#pragma unroll 1
+    for (int c = c_first; c < c_last; ++c) {
       const int col = t.n_tile * BN + c * 32;
       if (col >= a.N) break;
       float v[32];

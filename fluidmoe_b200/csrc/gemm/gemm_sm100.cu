@@ -503,8 +503,74 @@ struct EpiAct {
     const int rows_ok = max(0, min(32, t.rows_valid - (r - lane)));
     const float p = (row_ok && probs) ? probs[row] : 1.0f;
     if (a.gated) {
+      const int c_first = chalf * (BN / 128), c_last = (chalf + 1) * (BN / 128);
+      __nv_bfloat16* act0 = act_out + row0 * ld_act;
+      __nv_bfloat16* pre0 = pre_out ? pre_out + row0 * ld_pre : nullptr;
+      if (rows_ok == 32 && t.n_tile * (BN / 2) + c_last * 32 <= a.N && ((ld_act | ld_pre | a.n_half) & 7) == 0 &&
+          aligned16(act0) && aligned16(pre0)) {
+        // Whole SwiGLU tile inside the matrix (the common case): the up half goes through the
+        // shared-memory stage first and is kept in the coalesced layout (4 lanes x 8 columns per
+        // row, 8 rows per pass), the gate half follows, and activation and both pre-activation
+        // halves are computed and stored in that layout: two trips through the stage per block
+        // instead of one per stored array.
+        const int sub = lane >> 2, c8 = (lane & 3) * 8;
+        float pr[4];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) pr[pass] = probs ? probs[row0 + pass * 8 + sub] : 1.0f;
 #pragma unroll 1
-      for (int c = chalf * (BN / 128); c < (chalf + 1) * (BN / 128); ++c) {
+        for (int c = c_first; c < c_last; ++c) {
+          const int col = t.n_tile * (BN / 2) + c * 32;
+          float ur[4][8];
+          {
+            float u[32];
+            load_acc(taddr + BN / 2 + c * 32, u, zero);
+            stage_put(stg, lane, u);
+          }
+#pragma unroll
+          for (int pass = 0; pass < 4; ++pass) {
+            const int rr = pass * 8 + sub;
+            const float4 xa = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+            const float4 xb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+            ur[pass][0] = xa.x; ur[pass][1] = xa.y; ur[pass][2] = xa.z; ur[pass][3] = xa.w;
+            ur[pass][4] = xb.x; ur[pass][5] = xb.y; ur[pass][6] = xb.z; ur[pass][7] = xb.w;
+            if (pre0) {
+              uint4 q;
+              q.x = pack_bf16x2(xa.x, xa.y); q.y = pack_bf16x2(xa.z, xa.w);
+              q.z = pack_bf16x2(xb.x, xb.y); q.w = pack_bf16x2(xb.z, xb.w);
+              *reinterpret_cast<uint4*>(pre0 + (long long)rr * ld_pre + a.n_half + col + c8) = q;
+            }
+          }
+          {
+            float g[32];
+            load_acc(taddr + c * 32, g, zero);
+            stage_put(stg, lane, g);
+          }
+#pragma unroll
+          for (int pass = 0; pass < 4; ++pass) {
+            const int rr = pass * 8 + sub;
+            const float4 xa = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+            const float4 xb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+            const float gv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+            if (pre0) {
+              uint4 q;
+              q.x = pack_bf16x2(xa.x, xa.y); q.y = pack_bf16x2(xa.z, xa.w);
+              q.z = pack_bf16x2(xb.x, xb.y); q.w = pack_bf16x2(xb.z, xb.w);
+              *reinterpret_cast<uint4*>(pre0 + (long long)rr * ld_pre + col + c8) = q;
+            }
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = silu_f(gv[i]) * ur[pass][i] * pr[pass];
+            uint4 q;
+            q.x = pack_bf16x2(o[0], o[1]); q.y = pack_bf16x2(o[2], o[3]);
+            q.z = pack_bf16x2(o[4], o[5]); q.w = pack_bf16x2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(act0 + (long long)rr * ld_act + col + c8) = q;
+          }
+        }
+        __syncwarp();
+        return;
+      }
+#pragma unroll 1
+      for (int c = c_first; c < c_last; ++c) {
         const int col = t.n_tile * (BN / 2) + c * 32;
         if (col >= a.N) break;
         float g[32], u[32];

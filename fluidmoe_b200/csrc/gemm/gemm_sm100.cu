@@ -587,8 +587,51 @@ struct EpiAct {
         put_block_bf16(stg, lane, g, rows_ok, row_ok, act_out + row0 * ld_act + col, ld_act, ncols);
       }
     } else {
+      const int c_first = chalf * (BN / 64), c_last = (chalf + 1) * (BN / 64);
+      __nv_bfloat16* act0 = act_out + row0 * ld_act;
+      __nv_bfloat16* pre0 = pre_out ? pre_out + row0 * ld_pre : nullptr;
+      if (rows_ok == 32 && t.n_tile * BN + c_last * 32 <= a.N && ((ld_act | ld_pre) & 7) == 0 && aligned16(act0) &&
+          aligned16(pre0)) {
+        // Whole tile inside the matrix: one trip through the stage per block, pre-activation and
+        // activation are packed and stored from the coalesced layout.
+        const int sub = lane >> 2, c8 = (lane & 3) * 8;
+        float pr[4];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) pr[pass] = probs ? probs[row0 + pass * 8 + sub] : 1.0f;
 #pragma unroll 1
-      for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); ++c) {
+        for (int c = c_first; c < c_last; ++c) {
+          const int col = t.n_tile * BN + c * 32;
+          {
+            float v[32];
+            load_acc(taddr + c * 32, v, zero);
+            stage_put(stg, lane, v);
+          }
+#pragma unroll
+          for (int pass = 0; pass < 4; ++pass) {
+            const int rr = pass * 8 + sub;
+            const float4 xa = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+            const float4 xb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+            const float xv[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+            if (pre0) {
+              uint4 q;
+              q.x = pack_bf16x2(xa.x, xa.y); q.y = pack_bf16x2(xa.z, xa.w);
+              q.z = pack_bf16x2(xb.x, xb.y); q.w = pack_bf16x2(xb.z, xb.w);
+              *reinterpret_cast<uint4*>(pre0 + (long long)rr * ld_pre + col + c8) = q;
+            }
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = act_f(act_kind, xv[i]) * pr[pass];
+            uint4 q;
+            q.x = pack_bf16x2(o[0], o[1]); q.y = pack_bf16x2(o[2], o[3]);
+            q.z = pack_bf16x2(o[4], o[5]); q.w = pack_bf16x2(o[6], o[7]);
+            *reinterpret_cast<uint4*>(act0 + (long long)rr * ld_act + col + c8) = q;
+          }
+        }
+        __syncwarp();
+        return;
+      }
+#pragma unroll 1
+      for (int c = c_first; c < c_last; ++c) {
         const int col = t.n_tile * BN + c * 32;
         if (col >= a.N) break;
         float v[32];
@@ -717,6 +760,61 @@ struct EpiDAct {
       }
       __syncwarp();
       // row pass * 8 + sub: sum over its four lanes, then hand every lane the sum of its own row
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        float x = dq[pass];
+        x += __shfl_xor_sync(0xffffffffu, x, 1);
+        x += __shfl_xor_sync(0xffffffffu, x, 2);
+        x = __shfl_sync(0xffffffffu, x, (lane & 7) * 4);
+        if ((lane >> 3) == pass) dp = x;
+      }
+      if (dprobs_partial) dprobs_partial[(row * n_tiles + t.n_tile) * 2 + chalf] = dp;
+      return;
+    }
+    if (!gated && rows_ok == 32 && t.n_tile * BN + c_last * 32 <= a.N && ((ld_pre_in | ld_dpre) & 7) == 0 &&
+        aligned16(pre0) && aligned16(dpre0)) {
+      // The same for a plain activation (GELU, SiLU): one array in, one out.
+      const int sub = lane >> 2, c8 = (lane & 3) * 8;
+      float pr[4], dq[4];
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        pr[pass] = probs ? probs[row0 + pass * 8 + sub] : 1.0f;
+        dq[pass] = 0.f;
+      }
+#pragma unroll 1
+      for (int c = c_first; c < c_last; ++c) {
+        const int col = t.n_tile * BN + c * 32;
+        uint4 rx[4];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass)
+          rx[pass] = *reinterpret_cast<const uint4*>(pre0 + (long long)(pass * 8 + sub) * ld_pre_in + col + c8);
+        {
+          float v[32];
+          load_acc(taddr + c * 32, v, zero);
+          stage_put(stg, lane, v);
+        }
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const int rr = pass * 8 + sub;
+          const float4 va = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8);
+          const float4 vb = *reinterpret_cast<const float4*>(stg + rr * kStgLd + c8 + 4);
+          const float vv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+          const uint32_t* wx = reinterpret_cast<const uint32_t*>(&rx[pass]);
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const uint32_t xw = wx[i >> 1];
+            const float xi = __uint_as_float((i & 1) ? (xw & 0xffff0000u) : (xw << 16));
+            dq[pass] += vv[i] * act_f(act_kind, xi);
+            o[i] = vv[i] * pr[pass] * dact_f(act_kind, xi);
+          }
+          uint4 q;
+          q.x = pack_bf16x2(o[0], o[1]); q.y = pack_bf16x2(o[2], o[3]);
+          q.z = pack_bf16x2(o[4], o[5]); q.w = pack_bf16x2(o[6], o[7]);
+          *reinterpret_cast<uint4*>(dpre0 + (long long)rr * ld_dpre + col + c8) = q;
+        }
+      }
+      __syncwarp();
 #pragma unroll
       for (int pass = 0; pass < 4; ++pass) {
         float x = dq[pass];

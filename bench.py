@@ -351,32 +351,27 @@ def _profile_one_step(torch, step_fn, path, rank=0):
     with open(path, "w") as f:
         f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=90))
         # where the device sat idle: the largest gaps between consecutive kernels on the timeline
+        from fluidmoe_b200.utils.timeline import idle_gaps, merge_intervals, overlap
         evs = []
         for ev in prof.events():
             tr = getattr(ev, "time_range", None)
             if ev.device_time_total > 0 and tr is not None and str(getattr(ev, "device_type", "")).endswith("CUDA"):
                 evs.append((tr.start, tr.end, ev.name))
-        evs.sort()
-        gaps, busy_end, idle = [], None, 0.0
-        for st, en, name in evs:
-            if busy_end is not None and st > busy_end:
-                gaps.append((st - busy_end, prev_name, name))
-                idle += st - busy_end
-            if busy_end is None or en > busy_end:
-                busy_end, prev_name = en, name
+        span, idle, gaps = idle_gaps(evs)
         if evs:
             f.write("\n\ndevice timeline: %.3f ms from first kernel start to last kernel end, %.3f ms idle in %d gaps; "
-                    "largest gaps (us, after -> before):\n" % ((busy_end - evs[0][0]) / 1e3, idle / 1e3, len(gaps)))
+                    "largest gaps (us, after -> before):\n" % (span / 1e3, idle / 1e3, len(gaps)))
             for g, a, b in sorted(gaps, reverse=True)[:25]:
                 f.write(f"{g:10.1f}  {a[:70]}  ->  {b[:70]}\n")
         # a collective that runs beside a persistent GEMM takes SMs from it: show the overlap per launch
-        coll = [(st, en) for st, en, name in evs if "nccl" in name.lower() or "allreduce" in name.lower()]
+        # (the profiler lists a collective twice, as a kernel and as an annotation: the union counts once)
+        coll = merge_intervals((st, en) for st, en, name in evs if "nccl" in name.lower() or "allreduce" in name.lower())
         f.write("\n\nper-launch device time of the GEMM kernels (us) and the part of it during which a "
                 "collective kernel ran on another stream, in launch order:\n")
         for ev in prof.events():
             if "gemm" in ev.name and "sm100_kernel" in ev.name and ev.device_time_total > 0:
                 tr = getattr(ev, "time_range", None)
-                ov = sum(max(0.0, min(tr.end, en) - max(tr.start, st)) for st, en in coll) if tr is not None else 0.0
+                ov = overlap(tr.start, tr.end, coll) if tr is not None else 0.0
                 f.write(f"{ev.device_time_total:10.1f} {ov:9.1f}  {ev.name[:110]}\n")
 
 

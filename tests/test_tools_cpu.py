@@ -337,3 +337,17 @@ def test_tuner_fused_knob_search_with_a_stub_timer(monkeypatch, capsys):
     best = tune.tune_fused({}, {}, None, None, dict(min_saving_ms=0.05, side_ctas=(48,)))
     assert best == {"fused_eager_ar_min_bytes": 32 << 20, "fused_grad_reduce": "symm", "fused_dw_side_ctas": 0}
     assert len(seen) == 5 and seen[0] == (32 << 20, "nccl", 0)
+
+
+def test_timeline_idle_gaps_and_collective_overlap():
+    """The step profile's arithmetic: gaps that no stream fills, and how long a collective ran beside
+    a kernel, counting a collective once although the profiler lists it as kernel and annotation."""
+    from fluidmoe_b200.utils.timeline import idle_gaps, merge_intervals, overlap
+    recs = [(0.0, 10.0, "a"), (12.0, 20.0, "b"), (15.0, 30.0, "side"), (30.0, 31.0, "c"), (40.0, 41.0, "d")]
+    span, idle, gaps = idle_gaps(recs)
+    assert span == 41.0 and idle == 2.0 + 9.0
+    assert gaps == [(2.0, "a", "b"), (9.0, "c", "d")]          # b -> side -> c leaves no gap
+    assert idle_gaps([]) == (0.0, 0.0, [])
+    coll = merge_intervals([(5.0, 9.0), (5.0, 9.0), (8.0, 14.0), (20.0, 20.0), (25.0, 26.0)])
+    assert coll == [(5.0, 14.0), (25.0, 26.0)]
+    assert overlap(0.0, 10.0, coll) == 5.0 and overlap(12.0, 30.0, coll) == 3.0 and overlap(30.0, 40.0, coll) == 0.0

@@ -52,3 +52,8 @@ layer.fluid_spec = _module("fluid.layer.fluid_spec", _spec)
 setup = _module("fluid.setup", _ddp)
 csrc = _module("fluid.csrc", _symm)
 _sys.modules["fluid.distributed"] = distributed
+
+# Export list: every public name of the implementation package plus the three underscore-prefixed
+# all-to-all primitives that the reference exports by name (fluid/__init__.py:90-131).
+__all__ = sorted({_k for _k in vars(_f) if not _k.startswith("_") and not isinstance(getattr(_f, _k), _types.ModuleType)}
+                 | {"_all_to_all", "_all_to_all_sp2hp_forward", "_all_to_all_hp2sp_forward"})

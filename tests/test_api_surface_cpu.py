@@ -169,8 +169,21 @@ def test_megatron_layer_spec_without_megatron_raises():
 def test_reference_import_paths_resolve():
     import importlib
     fluid = importlib.import_module("fluid")
-    for name in fluid.__all__ if hasattr(fluid, "__all__") else []:
+    for name in fluid.__all__:
         assert hasattr(fluid, name), name
+    # the names the reference exports (fluid/__init__.py:90-131)
+    exported = """_all_to_all _all_to_all_sp2hp_forward _all_to_all_hp2sp_forward MultiCardOverlapContext
+        BackwardScheduler get_p2p_backend get_backward_scheduler router_forward dispatch_fc1_p2p_forward
+        fc2_combine_p2p_forward combine_fc2_backward fc1_dispatch_backward register_moe_dw_tasks router_backward
+        register_router_dw_task qkv_projection_p2p_forward scaled_dot_product_attention_forward
+        output_projection_p2p_forward outproj_sp2hp_backward hp2sp_qkv_backward output_projection_register_dw
+        TransformerLayerFunction TransformerLayer TransformerModel FluidDDP FluidOptimizerWrapper
+        setup_model_and_optimizer""".split()
+    missing = [n for n in exported if n not in fluid.__all__ or not callable(getattr(fluid, n, None))]
+    assert not missing, missing
+    ns = {}
+    exec("from fluid import *", ns)          # star import honours the export list
+    assert "_all_to_all" in ns and "TransformerLayer" in ns
     from fluid import (FluidDDP, FluidOptimizerWrapper, MoEBaseline, MultiCardOverlapContext,  # noqa: F401
                        TransformerLayer, TransformerLayerFunction, TransformerModel, get_backward_scheduler,
                        get_fluid_custom_layers, get_p2p_backend, moe_multicard_p2p_overlap_forward,

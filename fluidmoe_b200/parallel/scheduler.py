@@ -145,6 +145,11 @@ class FlatGradBuffer:
     def has_pending(self) -> bool:
         return self.read < self.committed
 
+    def has_remainder(self) -> bool:
+        """True while anything written, committed or not, is still unreduced
+        (fluid/core/scheduler.py:112-115)."""
+        return self.read < self.write
+
     def pending_bytes(self) -> int:
         if self.primary is None:
             return 0

@@ -239,3 +239,22 @@ def test_embedding_backward_adds_touched_rows_into_the_gradient_buffer():
     _Embedding.apply(ids, w2).backward(gy)
     assert w2.grad is None
     assert torch.allclose(w2.main_grad, 1.0 + w_ref.grad, atol=1e-6)
+
+
+def test_flat_gradient_buffer_cursors():
+    """write / committed / read cursors of the flat gradient buffer: `has_remainder` counts what is
+    written but not committed too, `has_pending` only what the all-reduce may take."""
+    from fluidmoe_b200.parallel.scheduler import FlatGradBuffer
+    a, b = torch.nn.Parameter(torch.zeros(4)), torch.nn.Parameter(torch.zeros(6))
+    buf = FlatGradBuffer()
+    buf.setup([a, b])
+    assert not buf.has_remainder() and not buf.has_pending()
+    buf.write_grad(b, torch.ones(6))                 # out of layout order: the prefix is not complete yet
+    assert not buf.has_remainder()
+    buf.write_grad(a, torch.ones(4))
+    assert buf.has_remainder() and not buf.has_pending() and buf.pending_bytes() == 0
+    buf.commit()
+    assert buf.has_pending() and buf.pending_bytes() == 10 * 4
+    seen = []
+    buf.submit_block(lambda t, scale: seen.append(t.numel()))
+    assert seen == [10] and not buf.has_pending() and not buf.has_remainder()

@@ -54,6 +54,29 @@ def check_split_matrix(input_splits: Optional[List[int]], output_splits: Optiona
                     f"which expects {recv_list[src]}")
 
 
+def _debug_check_alltoallv_splits(input_rows: int, output_rows: int, input_split_sizes: Optional[List[int]],
+                                  output_split_sizes: Optional[List[int]], group, tag: str = "") -> None:
+    """Checks of an all-to-all-v call under the reference's name and argument order
+    (fluid/core/comm.py:98-105).  Does nothing unless ``FLUID_DEBUG_A2A_SPLITS=1`` and both lists
+    are given; then the lists must have one entry per rank, add up to the rows of the buffers they
+    describe, and agree across ranks (``check_split_matrix``)."""
+    if os.environ.get("FLUID_DEBUG_A2A_SPLITS", "0") != "1":
+        return
+    if input_split_sizes is None or output_split_sizes is None:
+        return
+    world, me = group_size(group), group_rank(group)
+    ins, outs = [int(v) for v in input_split_sizes], [int(v) for v in output_split_sizes]
+    where = f"all-to-all-v '{tag}' on rank {me}"
+    if len(ins) != world or len(outs) != world:
+        raise SplitMismatchError(f"{where}: {len(ins)} input and {len(outs)} output splits for {world} ranks")
+    if sum(ins) != int(input_rows):
+        raise SplitMismatchError(f"{where}: input splits add up to {sum(ins)}, the buffer has {input_rows} rows")
+    if sum(outs) != int(output_rows):
+        raise SplitMismatchError(f"{where}: output splits add up to {sum(outs)}, the buffer has {output_rows} rows")
+    if world > 1:
+        check_split_matrix(ins, outs, group, int(input_rows))
+
+
 def all_to_all(x: torch.Tensor, group=None, input_splits: Optional[List[int]] = None,
                output_splits: Optional[List[int]] = None,
                output: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -154,7 +154,10 @@ class FluidDDP(nn.Module):
         ``finish_grad_sync`` once, after the last micro-batch."""
         return self.scheduler.no_sync()
 
-    def finish_grad_sync(self) -> None:
+    def finish_grad_sync(self, force_all_reduce: bool = False) -> None:
+        """Run what is left of the weight-gradient queue and finish every gradient reduction.
+        ``force_all_reduce`` is accepted for callers written against Megatron's DDP interface
+        (fluid/setup.py:332); the reduction here is always a full all-reduce."""
         self.scheduler.finish_batch()
         fused = getattr(self, "fused_ctx", None)
         if fused is not None:
@@ -183,8 +186,8 @@ class FluidDDP(nn.Module):
     def state_dict(self, *args, **kwargs):
         return self.module.state_dict(*args, **kwargs)
 
-    def load_state_dict(self, state_dict, strict: bool = True):
-        return self.module.load_state_dict(state_dict, strict=strict)
+    def load_state_dict(self, state_dict, *args, **kwargs):
+        return self.module.load_state_dict(state_dict, *args, **kwargs)
 
     def sharded_state_dict(self, *args, **kwargs):
         fn = getattr(self.module, "sharded_state_dict", None)
@@ -196,19 +199,38 @@ class FluidOptimizerWrapper:
     (fluid/setup.py:388-418)."""
 
     def __init__(self, optimizer, scheduler: Optional[BackwardScheduler] = None):
-        self.optimizer = optimizer
-        self.scheduler = scheduler or get_backward_scheduler()
+        self._optimizer = optimizer
+        self._scheduler = scheduler or get_backward_scheduler()
+
+    @property
+    def optimizer(self):
+        return self._optimizer
+
+    @property
+    def scheduler(self) -> BackwardScheduler:
+        return self._scheduler
 
     def step(self, *args, **kwargs):
-        out = self.optimizer.step(*args, **kwargs)
-        self.scheduler.clear_iteration()
+        out = self._optimizer.step(*args, **kwargs)
+        self._scheduler.clear_iteration()
         return out
 
     def zero_grad(self, *args, **kwargs):
-        return self.optimizer.zero_grad(*args, **kwargs)
+        return self._optimizer.zero_grad(*args, **kwargs)
 
+    # Everything else is the wrapped optimizer's: reads fall through, and so do writes of public
+    # attributes (a training loop that sets ``opt.param_groups`` or a flag reaches the optimizer
+    # itself, fluid/setup.py:403-410); only names with a leading underscore live on the wrapper.
     def __getattr__(self, name):
-        return getattr(self.optimizer, name)
+        if name in ("_optimizer", "_scheduler"):     # not set yet (unpickling, failed __init__)
+            raise AttributeError(name)
+        return getattr(self._optimizer, name)
+
+    def __setattr__(self, name, value):
+        if name.startswith("_"):
+            object.__setattr__(self, name, value)
+        else:
+            setattr(self._optimizer, name, value)
 
 
 def setup_model_and_optimizer(model_provider_func: Callable, model_type=None, checkpointing_context=None,

@@ -216,6 +216,15 @@ _BACKEND: Optional[P2PBackend] = None
 _LOCK = threading.Lock()
 
 
+def _has_nvlink() -> bool:
+    """True when some pair of this machine's GPUs can address each other's memory (what the
+    device-initiated transports need; fluid/core/p2p_backend.py:396-407)."""
+    if not torch.cuda.is_available():
+        return False
+    n = torch.cuda.device_count()
+    return any(torch.cuda.can_device_access_peer(i, j) for i in range(n) for j in range(i + 1, n))
+
+
 def get_p2p_backend() -> P2PBackend:
     """Process-wide back-end chosen from ``FLUIDMOE_P2P_BACKEND`` (default ``auto``)."""
     global _BACKEND

@@ -94,6 +94,7 @@ class StreamManager:
         self._events: Dict[Hashable, object] = {}
         self._lock = threading.Lock()
         self.data_ready_event = None
+        self._one_sided_ready = False
 
     def initialize(self, device) -> None:
         device = torch.device(device)
@@ -143,8 +144,28 @@ class StreamManager:
             self._events[key] = ev
         return ev
 
+    def init_nvshmem(self) -> None:
+        """Bring up the one-sided transport of the pairwise back-end.  The reference initialises
+        NVSHMEM here (fluid/core/stream.py:109-176); its place is taken by the symmetric heap
+        over peer memory, which the symmetric back-end maps for the world group.  With the
+        collective back-end selected there is nothing to bring up and the flag stays False."""
+        if self._one_sided_ready:
+            return
+        if self._device is None or self._device.type != "cuda":
+            raise RuntimeError("the one-sided transport needs a CUDA device: call initialize(device) first")
+        from .p2p_backend import SymmetricP2PBackend, get_p2p_backend
+        backend = get_p2p_backend()
+        if isinstance(backend, SymmetricP2PBackend):
+            backend._state(None, self._device)
+            self._one_sided_ready = True
+
+    @property
+    def nvshmem_initialized(self) -> bool:
+        return self._one_sided_ready
+
     def reset(self) -> None:
         with self._lock:
+            self._one_sided_ready = False
             self._device = None
             self._comm = self._dw = self._ar = None
             self._events.clear()

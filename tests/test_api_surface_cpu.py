@@ -258,3 +258,57 @@ def test_flat_gradient_buffer_cursors():
     seen = []
     buf.submit_block(lambda t, scale: seen.append(t.numel()))
     assert seen == [10] and not buf.has_pending() and not buf.has_remainder()
+
+
+def test_optimizer_wrapper_passes_public_attributes_through():
+    """Reads and writes of public attributes reach the wrapped optimizer (fluid/setup.py:403-410);
+    `step` resets the scheduler's iteration state; the DDP wrapper accepts Megatron's
+    `finish_grad_sync(force_all_reduce=...)` spelling."""
+    import inspect
+    import fluidmoe_b200 as fm
+
+    class _Sched:
+        cleared = 0
+
+        def clear_iteration(self):
+            self.cleared += 1
+
+    lin = torch.nn.Linear(3, 2)
+    inner = torch.optim.SGD(lin.parameters(), lr=0.1)
+    sched = _Sched()
+    opt = fm.FluidOptimizerWrapper(inner, sched)
+    assert opt.optimizer is inner and opt.scheduler is sched
+    assert opt.param_groups is inner.param_groups
+    opt.my_flag = 7
+    assert inner.my_flag == 7 and "my_flag" not in vars(opt)
+    lin(torch.ones(1, 3)).sum().backward()
+    opt.step()
+    assert sched.cleared == 1
+    opt.zero_grad()
+    assert all(p.grad is None or float(p.grad.abs().sum()) == 0.0 for p in lin.parameters())
+    assert opt.state_dict().keys() == inner.state_dict().keys()
+    assert "force_all_reduce" in inspect.signature(fm.FluidDDP.finish_grad_sync).parameters
+
+
+def test_compat_helpers_of_comm_backend_and_stream_modules(monkeypatch):
+    """Small names of the reference's core modules: the all-to-all-v split checker, the NVLink probe
+    and the stream manager's one-sided transport hooks."""
+    import fluid.core.comm as c
+    import fluid.core.p2p_backend as p
+    import fluid.core.stream as st
+    from fluidmoe_b200.parallel.comm import SplitMismatchError
+    c._debug_check_alltoallv_splits(4, 4, [1, 2], [3, 3], None, "off")        # disabled: nothing is checked
+    monkeypatch.setenv("FLUID_DEBUG_A2A_SPLITS", "1")
+    c._debug_check_alltoallv_splits(4, 4, [4], [4], None, "ok")               # one rank, consistent
+    c._debug_check_alltoallv_splits(4, 4, None, [4], None, "no lists")
+    with pytest.raises(SplitMismatchError, match="2 input"):
+        c._debug_check_alltoallv_splits(4, 4, [2, 2], [4], None, "len")
+    with pytest.raises(SplitMismatchError, match="add up to 3"):
+        c._debug_check_alltoallv_splits(4, 4, [3], [4], None, "sum")
+    with pytest.raises(SplitMismatchError, match="output splits add up to 5"):
+        c._debug_check_alltoallv_splits(4, 4, [4], [5], None, "sum")
+    assert p._has_nvlink() in (True, False)
+    mgr = st.StreamManager()
+    assert mgr.nvshmem_initialized is False
+    with pytest.raises(RuntimeError, match="CUDA device"):
+        mgr.init_nvshmem()

@@ -43,12 +43,23 @@ moe.forward = _module("fluid.moe.forward", _moe)
 moe.backward = _module("fluid.moe.backward", _moe)
 for _n in ("grouped_fc1_act", "grouped_fc2", "grouped_fc2_dx", "grouped_fc1_dx"):
     setattr(moe, _n, getattr(_f, _n))
+    setattr(moe.forward if _n in ("grouped_fc1_act", "grouped_fc2") else moe.backward, _n, getattr(_f, _n))
 attention = _module("fluid.attention", _attention)
 attention.forward = _module("fluid.attention.forward", _attention)
 attention.backward = _module("fluid.attention.backward", _attention)
 layer = _module("fluid.layer", _layer, _spec)
 layer.transformer = _module("fluid.layer.transformer", _layer)
 layer.fluid_spec = _module("fluid.layer.fluid_spec", _spec)
+
+
+def _lazy_layer_class(name):
+    # the Megatron module class exists only where megatron-core is installed
+    if name == "FluidTransformerLayer":
+        return _spec.build_fluid_transformer_layer_class()
+    raise AttributeError(name)
+
+
+layer.fluid_spec.__getattr__ = _lazy_layer_class
 setup = _module("fluid.setup", _ddp)
 csrc = _module("fluid.csrc", _symm)
 _sys.modules["fluid.distributed"] = distributed

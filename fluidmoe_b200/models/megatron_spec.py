@@ -74,8 +74,10 @@ def build_fluid_transformer_layer_class():
     class FluidTransformerLayer(MegatronModule):
         def __init__(self, config, submodules=None, layer_number: int = 1, pg_collection=None, vp_stage=None, **_):
             super().__init__(config=config)
-            cp_group = mpu.get_context_parallel_group()
-            ep_group = mpu.get_expert_model_parallel_group()
+            # groups from the collection Megatron hands over (fluid/layer/fluid_spec.py:43-46),
+            # from the global parallel state when it passes none
+            cp_group = getattr(pg_collection, "cp", None) or mpu.get_context_parallel_group()
+            ep_group = getattr(pg_collection, "ep", None) or mpu.get_expert_model_parallel_group()
             self.layer_number = layer_number
             self.layer = TransformerLayer(cp_group=cp_group, ep_group=ep_group,
                                           device=torch.device("cuda", torch.cuda.current_device()),

@@ -548,6 +548,32 @@ def fc1_dispatch_backward(plan: EPPlan, dpre_em: torch.Tensor, w1: torch.Tensor,
 # ============================================================================================
 # weight-gradient tasks
 # ============================================================================================
+def recompute_fc1_gemm(all_expert_tokens: torch.Tensor, all_tokens_per_expert, weight1: torch.Tensor) -> torch.Tensor:
+    """FC1 pre-activations again from the dispatched tokens: ``tokens_e @ weight1[e]`` for every
+    local expert e, rows of expert e being the next ``all_tokens_per_expert[e]`` rows
+    (fluid/moe/backward.py:616-646).  The layer itself recomputes through
+    ``MoEForwardState.pre_em``; this is the stand-alone form of the same GEMM."""
+    counts = [int(n) for n in all_tokens_per_expert]
+    if all_expert_tokens.shape[0] == 0:
+        return all_expert_tokens.new_empty(0, weight1.shape[-1])
+    dev = all_expert_tokens.device
+    rows = torch.tensor(counts, dtype=torch.int32, device=dev)
+    offs = torch.tensor([sum(counts[:i]) for i in range(len(counts))], dtype=torch.int32, device=dev)
+    return gemm.grouped_gemm(all_expert_tokens, weight1.detach(), b_layout="kn", group_rows=rows, group_offs=offs)
+
+
+def skip_all_dw() -> bool:
+    """Ablation ``FLUID_SKIP_ALL_DW=1``: deferrable weight-gradient tasks run only at the end of the
+    backward pass, in no communication window (fluid/moe/backward.py:361-363)."""
+    return bool(get_backward_scheduler().skip_all_dw)
+
+
+def skip_dispatch_dw() -> bool:
+    """Ablation ``FLUID_SKIP_DISPATCH_DW=1``: none of them in the window of the dispatch-gradient
+    exchange (fluid/moe/backward.py:366-368)."""
+    return bool(get_backward_scheduler().skip_dispatch_dw)
+
+
 def fused_optimizer_of(param, sched):
     """The optimizer that wants to run in this parameter's weight-gradient epilogue, or None.
     Only taken on the first (and only) gradient write of a step, when the parameter has no

@@ -228,6 +228,10 @@ class BackwardScheduler:
         self.ar_enabled = False
         # ablation switches
         self.stage2_enabled = True        # run dW tasks inside communication windows
+        # Ablations under the reference's environment names (fluid/moe/backward.py:40-41,280-287):
+        # keep deferrable dW tasks out of every window / out of the dispatch-gradient window only.
+        self.skip_all_dw = os.environ.get("FLUID_SKIP_ALL_DW", "0") == "1"
+        self.skip_dispatch_dw = os.environ.get("FLUID_SKIP_DISPATCH_DW", "0") == "1"
         self.cross_region_flow = True     # leftovers flow into later windows
         self.use_profiled_gaps = True
         self.fixed_ar_budget = 0          # bytes per gap when > 0 (overrides the model)
@@ -419,7 +423,8 @@ class BackwardScheduler:
         if not self._dw_queue:
             return 0
         self._ensure_device()
-        if not self.stage2_enabled and not self._in_finish:
+        if not self._in_finish and (not self.stage2_enabled or self.skip_all_dw or
+                                    (self.skip_dispatch_dw and self._current_region == "moe_dispatch")):
             # Ablation: nothing runs inside windows except tasks that must not be deferred.
             max_defer_tasks = 0
         tok = get_overhead_profiler().enter("overhead.bwd_execute_dw")

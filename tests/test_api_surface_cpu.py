@@ -312,3 +312,30 @@ def test_compat_helpers_of_comm_backend_and_stream_modules(monkeypatch):
     assert mgr.nvshmem_initialized is False
     with pytest.raises(RuntimeError, match="CUDA device"):
         mgr.init_nvshmem()
+
+
+def test_moe_backward_helpers_under_reference_names(monkeypatch):
+    """`recompute_fc1_gemm` (fluid/moe/backward.py:616-646) against a per-expert matmul, the dW
+    ablation probes, and the grouped-GEMM aliases of the forward / backward submodules."""
+    import fluid.moe.backward as mb
+    import fluid.moe.forward as mf
+    import fluid.layer.fluid_spec as spec
+    from fluidmoe_b200.parallel.scheduler import BackwardScheduler
+    torch.manual_seed(0)
+    counts = [3, 0, 5]
+    tokens = torch.randn(8, 16)
+    w1 = torch.randn(3, 16, 24)
+    pre = mb.recompute_fc1_gemm(tokens, counts, w1)
+    ref = torch.cat([tokens[0:3] @ w1[0], tokens[3:8] @ w1[2]])
+    assert torch.allclose(pre, ref, atol=1e-5)
+    assert mb.recompute_fc1_gemm(tokens[:0], [0, 0, 0], w1).shape == (0, 24)
+    assert mb.skip_all_dw() is False and mb.skip_dispatch_dw() is False
+    s = BackwardScheduler()                      # the process-wide scheduler; the flags start from the environment
+    monkeypatch.setattr(s, "skip_all_dw", True)
+    monkeypatch.setattr(s, "skip_dispatch_dw", True)
+    assert mb.skip_all_dw() is True and mb.skip_dispatch_dw() is True
+    assert callable(mf.grouped_fc1_act) and callable(mf.grouped_fc2)
+    assert callable(mb.grouped_fc1_dx) and callable(mb.grouped_fc2_dx)
+    if "megatron" not in sys.modules:
+        with pytest.raises(ImportError, match="megatron-core"):
+            spec.FluidTransformerLayer

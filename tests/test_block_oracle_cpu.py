@@ -270,6 +270,8 @@ def test_fc1_recompute_gives_the_same_gradients(act, cf, world, mode):
     dict(fixed_ar_budget=4096),                          # a fixed number of bytes per gap
     dict(pending_ar_enabled=False),                      # no trickled reductions after the exchanges
     dict(stage2_enabled=False, pending_ar_enabled=False, cross_region_flow=False),
+    dict(skip_all_dw=True),                              # FLUID_SKIP_ALL_DW: no deferrable dW in any window
+    dict(skip_dispatch_dw=True),                         # FLUID_SKIP_DISPATCH_DW: none in the dispatch-gradient window
 ])
 def test_scheduler_ablation_switches_keep_the_gradients(toggles):
     """The switches the reference's ablation runs flip (tests/run_block_benchmark.py:286-323: stage-2

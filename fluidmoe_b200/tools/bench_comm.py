@@ -35,7 +35,12 @@ def _check(out, rank, world, n, device, name):
             raise AssertionError(f"{name}: data from rank {p} is corrupt on rank {rank}")
 
 
-def _time(fn, iters=20, warmup=5):
+_ITERS, _WARMUP = 20, 5     # replaced by --iters / --warmup
+
+
+def _time(fn, iters=None, warmup=None):
+    iters = _ITERS if iters is None else iters
+    warmup = _WARMUP if warmup is None else warmup
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
@@ -92,7 +97,11 @@ def main(argv=None):
     ap.add_argument("--sizes-mib", type=float, nargs="+", default=[0.5, 2, 8, 32, 128])
     ap.add_argument("--allreduce", action="store_true")
     ap.add_argument("--ctas", type=int, nargs="+", default=[24], help="CTA counts of the two-shot kernel to try")
+    ap.add_argument("--iters", type=int, default=_ITERS, help="timed repetitions per size and method")
+    ap.add_argument("--warmup", type=int, default=_WARMUP, help="untimed repetitions before them")
     args = ap.parse_args(argv)
+    global _ITERS, _WARMUP
+    _ITERS, _WARMUP = max(1, args.iters), max(0, args.warmup)
     device = init_distributed()
     rank, world = dist.get_rank(), dist.get_world_size()
     if args.allreduce:

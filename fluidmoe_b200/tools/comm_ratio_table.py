@@ -118,9 +118,16 @@ def main(argv=None):
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--seq-len", type=int, default=None, help="override the preset's sequence length")
+    common.add_parallel_args(ap)
     args = ap.parse_args(argv)
+    if common.handle_list_models(args):
+        return
     bench = get_block_benchmark_defaults()
-    device, cfg, pc = common.setup(args.model, {"num_layers": args.layers} if args.layers else {}, "a2a")
+    over = {"num_layers": args.layers} if args.layers else {}
+    if args.seq_len:
+        over["seq_len"] = args.seq_len
+    device, cfg, pc = common.setup(args.model, over, "a2a", args=args)
     model = common.build_model(cfg, bench, pc, device, "a2a")
     x = common.make_input(cfg, pc, device)
     get_backward_scheduler().disable()

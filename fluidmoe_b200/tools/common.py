@@ -15,13 +15,74 @@ def p0(*a):
         print(*a, flush=True)
 
 
-def setup(model: str, overrides: dict = None, comm_mode: str = "auto", heap_bytes: int = 4 << 30):
+CHUNK_KEYS = ("moe_combine_chunks", "moe_dispatch_chunks", "attn_proj_chunks", "attn_qkv_chunks")
+
+
+def add_parallel_args(ap, chunks: bool = False) -> None:
+    """The flags the reference's drivers share (tests/run_block_benchmark.py:188-196): listing the
+    presets, the data / sequence / expert parallel sizes, and (``chunks``) the four chunk counts.
+    A size left out follows from the world size; a chunk count left out keeps the tuned default."""
+    ap.add_argument("--list-models", action="store_true", help="print the model presets and exit")
+    ap.add_argument("--dp-size", type=int, default=None, help="data-parallel replicas (default: world / cp)")
+    ap.add_argument("--cp-size", type=int, default=None, help="sequence-parallel ranks (default: ep, else world / dp)")
+    ap.add_argument("--ep-size", type=int, default=None, help="expert-parallel ranks (must equal --cp-size)")
+    if chunks:
+        for key in CHUNK_KEYS:
+            ap.add_argument("--" + key.replace("_", "-"), type=int, default=None)
+
+
+def handle_list_models(args) -> bool:
+    """Print the presets when ``--list-models`` was given; the caller then returns."""
+    if not getattr(args, "list_models", False):
+        return False
+    from .model_configs import MODEL_CONFIGS
+    for name, cfg in MODEL_CONFIGS.items():
+        print(f"{name:28s} hidden {cfg['hidden_size']:5d}  heads {cfg['num_heads']}/{cfg['num_kv_heads']}  "
+              f"ffn {cfg['ffn_hidden']:6d}  experts {cfg['num_experts']:3d} top-{cfg['top_k']}  "
+              f"layers {cfg.get('num_layers', 2)}  seq {cfg.get('seq_len', cfg.get('seq_per_rank', 0))}")
+    return True
+
+
+def resolve_parallel_sizes(world: int, dp_size=None, cp_size=None, ep_size=None):
+    """``(dp, cp)`` for a world of ``world`` ranks from whichever of the three sizes were given.
+    Sequence and expert parallelism share their group, so they must agree, and dp x cp must be
+    the world size."""
+    if cp_size is not None and ep_size is not None and cp_size != ep_size:
+        raise ValueError(f"--cp-size {cp_size} and --ep-size {ep_size} differ: the two share one group here")
+    cp = cp_size or ep_size
+    if cp is None:
+        if dp_size is not None and world % dp_size != 0:
+            raise ValueError(f"--dp-size {dp_size} does not divide the world size {world}")
+        cp = world // (dp_size or 1)
+    if cp <= 0 or world % cp != 0:
+        raise ValueError(f"sequence / expert parallel size {cp} does not divide the world size {world}")
+    dp = world // cp
+    if dp_size is not None and dp_size != dp:
+        raise ValueError(f"--dp-size {dp_size} x cp {cp} is not the world size {world}")
+    return dp, cp
+
+
+def apply_chunk_args(args, bench: dict) -> dict:
+    """Chunk counts given on the command line replace the tuned defaults in ``bench``."""
+    for key in CHUNK_KEYS:
+        val = getattr(args, key, None)
+        if val is not None:
+            bench[key] = int(val)
+    return bench
+
+
+def setup(model: str, overrides: dict = None, comm_mode: str = "auto", heap_bytes: int = 4 << 30, args=None):
+    """Process group, preset and parallel context.  ``args`` may carry ``dp_size / cp_size /
+    ep_size`` from ``add_parallel_args``; without them every rank joins one sequence- and
+    expert-parallel group."""
     device = init_distributed()
     cfg = get_model_config(model)
     cfg.update(overrides or {})
     world = dist.get_world_size() if dist.is_initialized() else 1
-    fused = comm_mode in ("auto", "fused") and device.type == "cuda" and world > 1
-    pc = init_parallel(ep_size=world, device=device, symmetric_heap_bytes=heap_bytes if fused else 0)
+    _, cp = resolve_parallel_sizes(world, getattr(args, "dp_size", None), getattr(args, "cp_size", None),
+                                   getattr(args, "ep_size", None))
+    fused = comm_mode in ("auto", "fused") and device.type == "cuda" and cp > 1
+    pc = init_parallel(ep_size=cp, device=device, symmetric_heap_bytes=heap_bytes if fused else 0)
     return device, cfg, pc
 
 

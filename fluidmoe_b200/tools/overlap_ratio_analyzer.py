@@ -25,9 +25,18 @@ def main(argv=None):
     ap.add_argument("--model", default="mixtral_8x7b")
     ap.add_argument("--comm", default="p2p")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--mode", choices=["sync", "interleaved"], default="interleaved",
+                    help="interleaved: gradient reductions are trickled into the backward pass; "
+                         "sync: they all run at its end")
+    ap.add_argument("--num-layers", type=int, default=None, help="override the preset's layer count")
+    common.add_parallel_args(ap)
     args = ap.parse_args(argv)
+    if common.handle_list_models(args):
+        return
     bench = get_block_benchmark_defaults()
-    device, cfg, pc = common.setup(args.model, None, args.comm)
+    device, cfg, pc = common.setup(args.model, {"num_layers": args.num_layers} if args.num_layers else None,
+                                   args.comm, args=args)
     model = common.build_model(cfg, bench, pc, device, args.comm)
     x = common.make_input(cfg, pc, device)
     sched = get_backward_scheduler()
@@ -35,8 +44,10 @@ def main(argv=None):
     sched.configure_allreduce(True, pc.dp_cp_group, pc.expert_dp_group, bench.get("gap_budgets"),
                               bench.get("shared_ar_bw"), bench.get("expert_ar_bw"))
     model.setup_ar_buffer()
+    if args.mode == "sync":
+        sched.ar_enabled = False      # nothing is reduced inside the backward pass (tests/overlap_ratio_analyzer.py:137)
     rotary = common.make_rotary(cfg, pc, device)
-    common.run_iters(model, x, 3, pc, rotary=rotary)
+    common.run_iters(model, x, args.warmup, pc, rotary=rotary)
     if pc.fused_ctx is not None and args.comm in ("auto", "fused"):
         sched.eager_ar = True
         iter_ms = common.time_iters(model, x, args.iters, pc, rotary=rotary)

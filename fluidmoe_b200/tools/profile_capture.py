@@ -49,11 +49,14 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=2)
     ap.add_argument("--trace", default="", help="write a Chrome trace of the captured iterations here")
     ap.add_argument("--table", default="", help="write a per-kernel table of the captured iterations here")
+    common.add_parallel_args(ap)
     args = ap.parse_args(argv)
+    if common.handle_list_models(args):
+        return
     os.environ.setdefault("FLUID_NVTX", "1")
     bench = get_block_benchmark_defaults()
     comm_mode = "a2a" if args.impl == "fluidmoe-f" else "auto"
-    device, cfg, pc = common.setup(args.model, {"num_layers": args.layers} if args.layers else {}, comm_mode)
+    device, cfg, pc = common.setup(args.model, {"num_layers": args.layers} if args.layers else {}, comm_mode, args=args)
     model = common.build_model(cfg, bench, pc, device, comm_mode)
     x = common.make_input(cfg, pc, device)
     sched = get_backward_scheduler()

@@ -193,13 +193,16 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--heap-gb", type=float, default=4.0)
+    common.add_parallel_args(ap, chunks=True)
     args = ap.parse_args(argv)
-    bench = get_block_benchmark_defaults()
+    if common.handle_list_models(args):
+        return
+    bench = common.apply_chunk_args(args, get_block_benchmark_defaults())
     args.warmup = args.warmup if args.warmup is not None else bench["warmup"]
     args.iters = args.iters if args.iters is not None else bench["iters"]
     names = [n for n in args.model.split(",") if n]
     comm_mode = "a2a" if args.impl in ("fluidmoe-f", "reference") and args.comm == "auto" else args.comm
-    device, _, pc = common.setup(names[0], None, comm_mode, heap_bytes=int(args.heap_gb * (1 << 30)))
+    device, _, pc = common.setup(names[0], None, comm_mode, heap_bytes=int(args.heap_gb * (1 << 30)), args=args)
     for name in names:
         cfg = get_model_config(name)
         if args.layers:

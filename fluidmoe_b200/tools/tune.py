@@ -126,10 +126,13 @@ def main(argv=None):
     ap.add_argument("--node-name", dest="node", default=None,
                     help="key under which the tuned values are stored (not --node: the launcher would take it for --node-rank)")
     ap.add_argument("--skip-chunks", action="store_true")
+    common.add_parallel_args(ap)
     args = ap.parse_args(argv)
+    if common.handle_list_models(args):
+        return
     td = dict(TUNE_DEFAULTS)
     bench = get_block_benchmark_defaults(args.node)
-    device, cfg, pc = common.setup(args.model, None, args.comm)
+    device, cfg, pc = common.setup(args.model, None, args.comm, args=args)
     result = {}
     if not args.skip_chunks:
         result.update(tune_chunks(cfg, bench, pc, device, args.comm, td))

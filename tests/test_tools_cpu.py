@@ -351,3 +351,35 @@ def test_timeline_idle_gaps_and_collective_overlap():
     coll = merge_intervals([(5.0, 9.0), (5.0, 9.0), (8.0, 14.0), (20.0, 20.0), (25.0, 26.0)])
     assert coll == [(5.0, 14.0), (25.0, 26.0)]
     assert overlap(0.0, 10.0, coll) == 5.0 and overlap(12.0, 30.0, coll) == 3.0 and overlap(30.0, 40.0, coll) == 0.0
+
+
+def test_driver_flags_shared_with_the_reference(capsys):
+    """`--list-models`, the three parallel sizes and the chunk counts on the drivers
+    (tests/run_block_benchmark.py:188-196 and the tools beside it)."""
+    import argparse
+    from fluidmoe_b200.parallel.scheduler import BackwardScheduler
+    from fluidmoe_b200.tools import common, overlap_ratio_analyzer, run_block_benchmark, tune
+    for tool in (run_block_benchmark, overlap_ratio_analyzer, tune):
+        tool.main(["--list-models"])
+        out = capsys.readouterr().out
+        assert "mixtral_8x7b" in out and "tiny_test" in out and "RESULT" not in out
+    # sizes: any subset fixes the rest; contradictions are refused
+    assert common.resolve_parallel_sizes(8) == (1, 8)
+    assert common.resolve_parallel_sizes(8, dp_size=2) == (2, 4)
+    assert common.resolve_parallel_sizes(8, cp_size=4, ep_size=4) == (2, 4)
+    assert common.resolve_parallel_sizes(1, dp_size=1, cp_size=1, ep_size=1) == (1, 1)
+    for bad in (dict(cp_size=4, ep_size=2), dict(dp_size=3), dict(dp_size=4, cp_size=4), dict(cp_size=3)):
+        with pytest.raises(ValueError):
+            common.resolve_parallel_sizes(8, **bad)
+    # chunk counts from the command line replace the tuned defaults, the others stay
+    ap = argparse.ArgumentParser()
+    common.add_parallel_args(ap, chunks=True)
+    args = ap.parse_args(["--moe-combine-chunks", "4", "--attn-qkv-chunks", "1"])
+    bench = common.apply_chunk_args(args, dict(moe_combine_chunks=2, moe_dispatch_chunks=2, attn_proj_chunks=8, attn_qkv_chunks=4))
+    assert bench == dict(moe_combine_chunks=4, moe_dispatch_chunks=2, attn_proj_chunks=8, attn_qkv_chunks=1)
+    # and the block benchmark takes them (one process: every size is 1)
+    BackwardScheduler.reset()
+    run_block_benchmark.main(["--model", "tiny_test", "--impl", "fluidmoe-full", "--warmup", "1", "--iters", "1",
+                              "--dp-size", "1", "--cp-size", "1", "--ep-size", "1", "--moe-dispatch-chunks", "1"])
+    assert "RESULT impl=fluidmoe-full" in capsys.readouterr().out
+    BackwardScheduler.reset()

@@ -19,6 +19,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 import _baseline_loop as loop  # noqa: E402
 from fluidmoe_b200.tools import external_baselines as eb  # noqa: E402
+from fluidmoe_b200.tools.experiment_configs import get_deepspeed_ulysses_defaults  # noqa: E402
 
 
 def build_blocks(cfg, pc, device):
@@ -31,7 +32,7 @@ def deepspeed_config(args) -> dict:
     return {
         "train_micro_batch_size_per_gpu": args.batch,
         "gradient_accumulation_steps": 1,
-        "zero_optimization": {"stage": 0},
+        "zero_optimization": {"stage": int(get_deepspeed_ulysses_defaults()["zero_stage"])},
         "bf16": {"enabled": True},
         "communication_data_type": "fp32",
         "optimizer": {"type": "AdamW", "params": {"lr": args.lr, "weight_decay": 0.0, "betas": [0.9, 0.999]}},

@@ -22,6 +22,17 @@ BLOCK_BENCHMARK_DEFAULTS = dict(
 )
 TUNE_DEFAULTS = dict(max_chunks=8, min_saving_ms=0.05, warmup=3, iters=10, ar_sizes_mb=(1, 4, 16, 64, 256, 512),
                      gap_percentile=10, gap_safety=0.8)
+# settings of the DeepSpeed-Ulysses comparison arm (examples/pretrain_deepspeed.py, tools/external_baselines.py)
+DEEPSPEED_ULYSSES_DEFAULTS = dict(zero_stage=0, learning_rate=1e-4, warmup=3, iters=10)
+
+
+def get_tune_defaults() -> dict:
+    """A copy of the tuner's settings (tools/experiment_configs.py:56-57 of the reference)."""
+    return json.loads(json.dumps(TUNE_DEFAULTS))
+
+
+def get_deepspeed_ulysses_defaults() -> dict:
+    return dict(DEEPSPEED_ULYSSES_DEFAULTS)
 
 
 def _path() -> str:

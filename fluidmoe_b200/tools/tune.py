@@ -20,7 +20,7 @@ import torch.distributed as dist
 
 from ..parallel.scheduler import BACKWARD_REGIONS, get_backward_scheduler
 from . import common
-from .experiment_configs import TUNE_DEFAULTS, get_block_benchmark_defaults, persist_block_benchmark_defaults
+from .experiment_configs import get_block_benchmark_defaults, get_tune_defaults, persist_block_benchmark_defaults
 
 _CHUNK_KEYS = {"moe_combine": "moe_combine_chunks", "moe_dispatch": "moe_dispatch_chunks",
                "attn_proj": "attn_proj_chunks", "attn_qkv": "attn_qkv_chunks"}
@@ -130,7 +130,7 @@ def main(argv=None):
     args = ap.parse_args(argv)
     if common.handle_list_models(args):
         return
-    td = dict(TUNE_DEFAULTS)
+    td = get_tune_defaults()
     bench = get_block_benchmark_defaults(args.node)
     device, cfg, pc = common.setup(args.model, None, args.comm, args=args)
     result = {}

@@ -383,3 +383,12 @@ def test_driver_flags_shared_with_the_reference(capsys):
                               "--dp-size", "1", "--cp-size", "1", "--ep-size", "1", "--moe-dispatch-chunks", "1"])
     assert "RESULT impl=fluidmoe-full" in capsys.readouterr().out
     BackwardScheduler.reset()
+
+
+def test_experiment_config_getters_return_copies():
+    from fluidmoe_b200.tools import experiment_configs as ec
+    td = ec.get_tune_defaults()
+    td["max_chunks"] = -1
+    assert ec.get_tune_defaults()["max_chunks"] == ec.TUNE_DEFAULTS["max_chunks"] != -1
+    ds = ec.get_deepspeed_ulysses_defaults()
+    assert ds["zero_stage"] == 0 and ds is not ec.DEEPSPEED_ULYSSES_DEFAULTS

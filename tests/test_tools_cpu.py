@@ -307,7 +307,6 @@ def test_tuner_searches_chunks_and_persists(tmp_path, monkeypatch, capsys):
     monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "iters", 1)
     monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "warmup", 1)
     monkeypatch.setitem(experiment_configs.TUNE_DEFAULTS, "ar_sizes_mb", (1,))
-    monkeypatch.setattr(tune, "TUNE_DEFAULTS", experiment_configs.TUNE_DEFAULTS)
     BackwardScheduler.reset()
     tune.main(["--model", "tiny_test", "--comm", "p2p", "--node-name", "testbox"])
     out = capsys.readouterr().out

@@ -10,7 +10,7 @@ from fluidmoe_b200 import (_all_to_all, _all_to_all_hp2sp_forward, _all_to_all_s
                            distributed)
 from fluidmoe_b200.models import attention as _attention, moe as _moe, transformer as _layer, megatron_spec as _spec
 from fluidmoe_b200.parallel import comm as _comm, ddp as _ddp, p2p_backend as _p2p, schedule as _schedule
-from fluidmoe_b200.parallel import scheduler as _scheduler, streams as _streams, symm as _symm
+from fluidmoe_b200.parallel import scheduler as _scheduler, shmem_compat as _shmem, streams as _streams, symm as _symm
 from fluidmoe_b200.ops import compat as _te_ops
 from fluidmoe_b200.utils import nvtx as _nvtx, overhead_profiler as _ohp, python_profile as _pyprof
 
@@ -61,7 +61,7 @@ def _lazy_layer_class(name):
 
 layer.fluid_spec.__getattr__ = _lazy_layer_class
 setup = _module("fluid.setup", _ddp)
-csrc = _module("fluid.csrc", _symm)
+csrc = _module("fluid.csrc", _symm, _shmem)
 _sys.modules["fluid.distributed"] = distributed
 
 # Export list: every public name of the implementation package plus the three underscore-prefixed

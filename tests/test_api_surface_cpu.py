@@ -339,3 +339,29 @@ def test_moe_backward_helpers_under_reference_names(monkeypatch):
     if "megatron" not in sys.modules:
         with pytest.raises(ImportError, match="megatron-core"):
             spec.FluidTransformerLayer
+
+
+def test_one_sided_extension_names_resolve_and_guard_their_state():
+    """`fluid.csrc` offers the entry points of the reference's extension
+    (fluid/csrc/nvshmem_ops.cpp:268-289); before initialisation every call that needs the heap says so."""
+    import fluid.csrc as c
+    for name in """nvshmem_init nvshmem_init_with_uniqueid nvshmem_get_uniqueid nvshmem_uniqueid_size nvshmem_finalize
+                   nvshmem_my_pe nvshmem_n_pes nvshmem_malloc_tensor nvshmem_free_tensor nvshmem_ptr
+                   putmem_signal_on_stream signal_wait_until_on_stream quiet_on_stream SIGNAL_SET CMP_GE""".split():
+        assert callable(getattr(c, name)), name
+    assert len(c.nvshmem_get_uniqueid()) == c.nvshmem_uniqueid_size()
+    assert c.nvshmem_is_initialized() is False
+    for call in (c.nvshmem_my_pe, c.nvshmem_n_pes, lambda: c.nvshmem_malloc_tensor(8, torch.float32),
+                 lambda: c.nvshmem_ptr(torch.zeros(4), 0), lambda: c.quiet_on_stream(0),
+                 lambda: c.putmem_signal_on_stream(16, torch.zeros(4), 16, 16, 1, c.SIGNAL_SET(), 0, 0),
+                 lambda: c.signal_wait_until_on_stream(16, c.CMP_GE(), 1, 0)):
+        with pytest.raises(RuntimeError, match="not initialised"):
+            call()
+    with pytest.raises(ValueError, match="does not match"):
+        c.nvshmem_init_with_uniqueid(3, 8, c.nvshmem_get_uniqueid())      # this process is rank 0 of 1
+    with pytest.raises(ValueError, match="unique id"):
+        c.nvshmem_init_with_uniqueid(0, 1, b"short")
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError, match="CUDA device"):
+            c.nvshmem_init()
+    c.nvshmem_finalize()                                                   # harmless when nothing is mapped

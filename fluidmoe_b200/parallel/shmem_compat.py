@@ -133,7 +133,7 @@ def putmem_signal_on_stream(dest_ptr: int, src: torch.Tensor, nbytes: int, sig_a
                             sig_op: int, pe: int, stream_ptr: int) -> None:
     """Copy ``nbytes`` of ``src`` to ``dest_ptr`` and then store ``sig_val`` at ``sig_addr`` (both
     addresses in PE ``pe``'s memory, from ``nvshmem_ptr``), ordered on the stream."""
-    heap = _heap()
+    _heap()      # the peer is addressed through the two pointers; ``pe`` is kept for the signature
     if not dest_ptr or not sig_addr:
         raise ValueError("destination and signal addresses must not be null")
     if int(sig_op) != _SIGNAL_SET:
@@ -145,7 +145,6 @@ def putmem_signal_on_stream(dest_ptr: int, src: torch.Tensor, nbytes: int, sig_a
     from .. import _native
     _native.lib().put_signal(src.data_ptr(), int(nbytes), int(dest_ptr), int(sig_addr), int(sig_val), 16,
                              _COUNTER.data_ptr(), int(stream_ptr))
-    del heap, pe   # the peer is addressed through the two pointers
 
 
 def signal_wait_until_on_stream(sig_addr: int, cmp_op: int, cmp_val: int, stream_ptr: int,

@@ -132,7 +132,9 @@ def nvshmem_ptr(t: torch.Tensor, pe: int) -> int:
 def putmem_signal_on_stream(dest_ptr: int, src: torch.Tensor, nbytes: int, sig_addr: int, sig_val: int,
                             sig_op: int, pe: int, stream_ptr: int) -> None:
     """Copy ``nbytes`` of ``src`` to ``dest_ptr`` and then store ``sig_val`` at ``sig_addr`` (both
-    addresses in PE ``pe``'s memory, from ``nvshmem_ptr``), ordered on the stream."""
+    addresses in PE ``pe``'s memory, from ``nvshmem_ptr``), ordered on the stream.  The copy
+    kernel's CTAs meet at one device counter of this module, so puts must not overlap in time:
+    issue them on one stream, as the pairwise back-end does."""
     _heap()      # the peer is addressed through the two pointers; ``pe`` is kept for the signature
     if not dest_ptr or not sig_addr:
         raise ValueError("destination and signal addresses must not be null")
